@@ -1,0 +1,42 @@
+"""Loader of libmacseek_b200.so (the C ABI in include/macseek_b200.h).  There is no fallback: if the library has not
+been built (python -m macseek_b200.build) importing this module fails."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmacseek_b200.so")
+
+
+class MsbError(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("libmacseek_b200.so is not built: run `python -m macseek_b200.build` (needs nvcc)")
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+lib.msb_last_error.restype = C.c_char_p
+lib.msb_version.restype = C.c_char_p
+lib.msb_block_bytes.restype = C.c_size_t
+lib.msb_row_bytes.restype = C.c_size_t
+lib.msb_row_bytes.argtypes = [C.c_int, C.c_int64]
+_vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+lib.msb_dequant.argtypes = [_i, _vp, _i64, _vp, _vp]
+lib.msb_matvec.argtypes = [_i, _vp, _i, _i, _vp, _vp, _i, _i, _vp]
+lib.msb_matvec_n.argtypes = [_i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]
+
+
+def check(rc):
+    if rc != 0:
+        raise MsbError("msb error %d: %s" % (rc, lib.msb_last_error().decode()))
+
+
+def device_status():
+    """Synchronise and return (then clear) the device failure word; raises on CUDA errors."""
+    rc = lib.msb_device_status()
+    if rc < 0:
+        check(rc)
+    return rc

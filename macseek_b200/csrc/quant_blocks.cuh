@@ -1,0 +1,399 @@
+// GGUF block decoders for sm_100a.  Two families per type:
+//   dequant8<T>  : exact dequantisation of 8 consecutive elements (bit-identical with the reference's CPU
+//                  ref::dequant_row, tests/ref/dequant.cpp:34-120: same float association, no FMA contraction).
+//   unit_dot<T>  : dot product of one 32-element unit of a weight row (staged in shared memory, 2-byte aligned) with
+//                  the activation.  Quantised types multiply integer codes with a 16-bit fixed-point copy of the
+//                  activation (two int8 limbs, dp4a), exact in int32 inside the unit, scaled and accumulated in fp32.
+//                  Dense types (F32/F16/BF16) use fp32 FMAs.
+// Block layouts as in the reference's src/kernels/quant_blocks.h:56,73,110,145 (IQ1_S {f16 d; u8 qs[32]; u16 qh[8]},
+// IQ2_XXS {f16 d; u16 qs[32]}, Q6_K {ql[128]; qh[64]; i8 sc[16]; f16 d}, Q5_K {f16 d,dmin; sc[12]; qh[32]; qs[128]},
+// Q8_0 {f16 d; i8 qs[32]}, IQ4_NL {f16 d; u8 qs[16]}).
+#pragma once
+#include "msb_common.cuh"
+
+namespace msb {
+
+// Shared-memory lookup tables are replicated so that lanes of a warp hit disjoint banks: copy c of entry i lives at
+// i * (entry_bytes * copies) + c * entry_bytes.
+constexpr int kIq1sCopies = 8;    // 2048 x 4 B x 8  = 64 KB
+constexpr int kIq2Copies = 16;    // 256 x 8 B x 16 = 32 KB (grid) + 128 x 8 B x 16 = 16 KB (signs)
+constexpr int kIq4Copies = 8;     // 256 x 4 B x 8  = 8 KB
+constexpr size_t kIq1sLutBytes = 2048 * 4 * kIq1sCopies;
+constexpr size_t kIq2GridLutBytes = 256 * 8 * kIq2Copies;
+constexpr size_t kIq2SignLutBytes = 128 * 8 * kIq2Copies;
+constexpr size_t kIq4LutBytes = 256 * 4 * kIq4Copies;
+
+__host__ __device__ constexpr size_t lut_bytes_for(int t) {
+  return t == IQ1_S ? kIq1sLutBytes : t == IQ2_XXS ? kIq2GridLutBytes + kIq2SignLutBytes : t == IQ4_NL ? kIq4LutBytes : 0;
+}
+__host__ __device__ constexpr bool is_dense(int t) { return t == F32 || t == F16 || t == BF16; }
+// bytes of `units` 32-element units of one row (units a multiple of 8 for the 256-element super-block types)
+__host__ __device__ constexpr int units_bytes(int t, int units) {
+  return block_elems(t) == 256 ? (units / 8) * block_bytes(t) : block_elems(t) == 32 ? units * block_bytes(t)
+                                                                                     : units * 32 * block_bytes(t);
+}
+
+#ifdef __CUDACC__
+struct LaneLuts {      // per-lane base pointers (already offset to the lane's copy)
+  const uint8_t* iq1s;
+  const uint8_t* iq2g;
+  const uint8_t* iq2s;
+  const uint8_t* iq4;
+};
+
+// Quantised activation in shared memory: U units of 32 elements.  x ~= scale[u] * (256 * hi + lo), hi signed bytes,
+// lo unsigned bytes.  plane[0][u] / plane[1][u] = hi bytes of elements 0..15 / 16..31, plane[2..3] = lo bytes.
+// sumA / sumB = integer sums of the fixed-point values over elements 0..15 / 16..31.
+struct XqSmem {
+  uint4* plane;   // [4][U]
+  float* scale;   // [U]
+  int* sumA;      // [U]
+  int* sumB;      // [U]
+  const float* xf;  // dense types: fp32 copy of x [32 U]
+  int U;
+};
+__host__ __device__ inline size_t xq_bytes(int U, bool dense) {
+  return dense ? (size_t)U * 128 : (size_t)U * (64 + 12);
+}
+struct XRegs { uint32_t h[8], l[8]; float s; int sa, sb; };
+
+__device__ __forceinline__ void load_xq(const XqSmem& x, int u, XRegs& r) {
+  const uint4 a = x.plane[u], b = x.plane[x.U + u], c = x.plane[2 * x.U + u], d = x.plane[3 * x.U + u];
+  r.h[0] = a.x; r.h[1] = a.y; r.h[2] = a.z; r.h[3] = a.w; r.h[4] = b.x; r.h[5] = b.y; r.h[6] = b.z; r.h[7] = b.w;
+  r.l[0] = c.x; r.l[1] = c.y; r.l[2] = c.z; r.l[3] = c.w; r.l[4] = d.x; r.l[5] = d.y; r.l[6] = d.z; r.l[7] = d.w;
+  r.s = x.scale[u]; r.sa = x.sumA[u]; r.sb = x.sumB[u];
+}
+
+// Quantise x[0 .. 32U) (global or shared fp32) into `q`.  Called by all `nthreads` threads of the block; 4 threads
+// cooperate on one unit (8 elements each).  Caller synchronises afterwards.
+__device__ __forceinline__ void quantize_x(const float* __restrict__ x, const XqSmem& q, int tid, int nthreads) {
+  const int lane4 = tid & 3;
+  for (int base = 0; base < q.U * 4; base += nthreads) {
+    const int item = base + tid;           // one item = 8 elements
+    const bool live = item < q.U * 4;      // nthreads is a multiple of 32: whole quads are live or not
+    const int u = item >> 2;
+    float v[8];
+    if (live) {
+      const float4 a = *reinterpret_cast<const float4*>(x + 8 * item);
+      const float4 b = *reinterpret_cast<const float4*>(x + 8 * item + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float inv = amax > 0.f ? 32767.f / amax : 0.f;
+    int sum = 0;
+    uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      int qv = __float2int_rn(v[i] * inv);
+      qv = max(-32767, min(32767, qv));
+      sum += qv;
+      hw[i >> 2] |= (uint32_t)((qv >> 8) & 0xFF) << (8 * (i & 3));
+      lw[i >> 2] |= (uint32_t)(qv & 0xFF) << (8 * (i & 3));
+    }
+    const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);   // lanes (0,1) -> sumA, (2,3) -> sumB
+    if (live) {
+      uint2* ph = reinterpret_cast<uint2*>(&q.plane[(lane4 >> 1) * q.U + u]) + (lane4 & 1);
+      uint2* pl = reinterpret_cast<uint2*>(&q.plane[(2 + (lane4 >> 1)) * q.U + u]) + (lane4 & 1);
+      *ph = make_uint2(hw[0], hw[1]);
+      *pl = make_uint2(lw[0], lw[1]);
+      if (lane4 == 0) { q.scale[u] = amax * (1.0f / 32767.f); q.sumA[u] = pair; }
+      if (lane4 == 2) q.sumB[u] = pair;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t lds_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+__device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t* p) { return lds_u16(p) | (lds_u16(p + 2) << 16); }
+__device__ __forceinline__ float lds_half(const uint8_t* p) {
+  return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(p)));
+}
+// N consecutive little-endian 32-bit words starting at a 2-byte aligned shared address (reads one word past the end
+// when the address is not 4-byte aligned; stage buffers are padded for that).
+template <int N>
+__device__ __forceinline__ void load_words(const uint8_t* p, uint32_t (&w)[N]) {
+  const uint32_t* a = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
+  const uint32_t sh = ((uint32_t)reinterpret_cast<uintptr_t>(p) & 2u) * 8u;
+  uint32_t t[N + 1];
+#pragma unroll
+  for (int i = 0; i <= N; i++) t[i] = a[i];
+#pragma unroll
+  for (int i = 0; i < N; i++) w[i] = __funnelshift_r(t[i], t[i + 1], sh);
+}
+
+// ---------------------------------------------------------------- decode_unit / dot_unit: one 32-element unit of a row
+// decode_unit turns the unit into 8 words of byte codes (element 4i+k in byte k of w[i]) plus the scalars needed to
+// finish; dot_unit multiplies them with one quantised activation column.  Splitting the two lets several activation
+// columns share one decode.
+template <int T> struct Dec { uint32_t w[8]; float a, b; };
+template <> struct Dec<Q6_K> { uint32_t w[8]; float a, s0, s1; };
+
+template <int T>
+__device__ __forceinline__ void decode_unit(const uint8_t* rowp, int u, const LaneLuts& L, Dec<T>& d);
+template <int T>
+__device__ __forceinline__ float dot_unit(const Dec<T>& d, const XRegs& x);
+
+// ---- IQ1_S: codes + 1 (0,1,2) unsigned; sum (code + delta) x = sum (code + 1) x + (delta - 1) sum x
+template <>
+__device__ __forceinline__ void decode_unit<IQ1_S>(const uint8_t* rowp, int u, const LaneLuts& L, Dec<IQ1_S>& d) {
+  const uint8_t* blk = rowp + (u >> 3) * 50;
+  const int ib = u & 7;
+  const uint32_t qs = lds_u32_a2(blk + 2 + 4 * ib);
+  const uint32_t qh = lds_u16(blk + 34 + 2 * ib);
+#pragma unroll
+  for (int l = 0; l < 4; l++) {
+    const uint32_t idx = ((qs >> (8 * l)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(L.iq1s + idx * (4 * kIq1sCopies));
+    d.w[2 * l] = v & 0x0F0F0F0Fu;
+    d.w[2 * l + 1] = (v >> 4) & 0x0F0F0F0Fu;
+  }
+  d.a = lds_half(blk) * (float)(2 * ((qh >> 12) & 7u) + 1);
+  d.b = (qh & 0x8000u) ? -1.125f : -0.875f;
+}
+template <>
+__device__ __forceinline__ float dot_unit<IQ1_S>(const Dec<IQ1_S>& d, const XRegs& x) {
+  int sh = 0, sl = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) { sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl); }
+  return d.a * x.s * ((float)(sh * 256 + sl) + d.b * (float)(x.sa + x.sb));
+}
+
+// ---- IQ2_XXS: signed bytes (+-8, +-25, +-43): negative elements are negated bytewise, (g ^ m) + (m & 1)
+template <>
+__device__ __forceinline__ void decode_unit<IQ2_XXS>(const uint8_t* rowp, int u, const LaneLuts& L, Dec<IQ2_XXS>& d) {
+  const uint8_t* blk = rowp + (u >> 3) * 66;
+  const uint8_t* a8 = blk + 2 + 8 * (u & 7);
+  const uint32_t q = lds_u32_a2(a8), a1 = lds_u32_a2(a8 + 4);
+#pragma unroll
+  for (int l = 0; l < 4; l++) {
+    const uint2 g = *reinterpret_cast<const uint2*>(L.iq2g + ((q >> (8 * l)) & 0xFFu) * (8 * kIq2Copies));
+    const uint2 m = *reinterpret_cast<const uint2*>(L.iq2s + ((a1 >> (7 * l)) & 127u) * (8 * kIq2Copies));
+    d.w[2 * l] = (g.x ^ m.x) + (m.x & 0x01010101u);
+    d.w[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
+  }
+  d.a = lds_half(blk) * (0.5f + (float)(a1 >> 28)) * 0.25f;
+  d.b = 0.f;
+}
+template <int T>
+__device__ __forceinline__ float dot_signed(const Dec<T>& d, const XRegs& x) {
+  int sh = 0, sl = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) { sh = dp4a_ss(d.w[i], x.h[i], sh); sl = dp4a_su(d.w[i], x.l[i], sl); }
+  return d.a * x.s * (float)(sh * 256 + sl);
+}
+template <>
+__device__ __forceinline__ float dot_unit<IQ2_XXS>(const Dec<IQ2_XXS>& d, const XRegs& x) { return dot_signed(d, x); }
+
+// ---- Q8_0: the int8 codes as they are
+template <>
+__device__ __forceinline__ void decode_unit<Q8_0>(const uint8_t* rowp, int u, const LaneLuts&, Dec<Q8_0>& d) {
+  const uint8_t* blk = rowp + u * 34;
+  load_words<8>(blk + 2, d.w);
+  d.a = lds_half(blk);
+  d.b = 0.f;
+}
+template <>
+__device__ __forceinline__ float dot_unit<Q8_0>(const Dec<Q8_0>& d, const XRegs& x) { return dot_signed(d, x); }
+
+// ---- IQ4_NL: nibble -> signed level through the byte-pair table
+template <>
+__device__ __forceinline__ void decode_unit<IQ4_NL>(const uint8_t* rowp, int u, const LaneLuts& L, Dec<IQ4_NL>& d) {
+  const uint8_t* blk = rowp + u * 18;
+  uint32_t q[4];
+  load_words<4>(blk + 2, q);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    uint32_t r[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+      r[k] = *reinterpret_cast<const uint32_t*>(L.iq4 + ((q[i] >> (8 * k)) & 0xFFu) * (4 * kIq4Copies));
+    const uint32_t t01 = __byte_perm(r[0], r[1], 0x5140), t23 = __byte_perm(r[2], r[3], 0x5140);
+    d.w[i] = __byte_perm(t01, t23, 0x5410);       // low nibbles  -> elements 4i .. 4i+3
+    d.w[4 + i] = __byte_perm(t01, t23, 0x7632);   // high nibbles -> elements 16+4i ..
+  }
+  d.a = lds_half(blk);
+  d.b = 0.f;
+}
+template <>
+__device__ __forceinline__ float dot_unit<IQ4_NL>(const Dec<IQ4_NL>& d, const XRegs& x) { return dot_signed(d, x); }
+
+// ---- Q6_K: codes 0..63 unsigned, two int8 scales per unit; sum (q - 32) x = sum q x - 32 sum x
+template <>
+__device__ __forceinline__ void decode_unit<Q6_K>(const uint8_t* rowp, int u, const LaneLuts&, Dec<Q6_K>& d) {
+  const uint8_t* blk = rowp + (u >> 3) * 210;
+  const int j = u & 7, half = j >> 2, q = j & 3;
+  uint32_t a[8], b[8];
+  load_words<8>(blk + 64 * half + 32 * (q & 1), a);
+  load_words<8>(blk + 128 + 32 * half, b);
+  const int nsh = 4 * (q >> 1), hsh = 2 * q;
+#pragma unroll
+  for (int i = 0; i < 8; i++) d.w[i] = ((a[i] >> nsh) & 0x0F0F0F0Fu) | (((b[i] >> hsh) & 0x03030303u) << 4);
+  const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192 + 8 * half + 2 * q);
+  d.a = lds_half(blk + 208);
+  d.s0 = (float)sc[0];
+  d.s1 = (float)sc[1];
+}
+template <>
+__device__ __forceinline__ float dot_unit<Q6_K>(const Dec<Q6_K>& d, const XRegs& x) {
+  int h0 = 0, l0 = 0, h1 = 0, l1 = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    h0 = dp4a_us(d.w[i], x.h[i], h0); l0 = dp4a_uu(d.w[i], x.l[i], l0);
+    h1 = dp4a_us(d.w[4 + i], x.h[4 + i], h1); l1 = dp4a_uu(d.w[4 + i], x.l[4 + i], l1);
+  }
+  return d.a * x.s * (d.s0 * (float)(h0 * 256 + l0 - 32 * x.sa) + d.s1 * (float)(h1 * 256 + l1 - 32 * x.sb));
+}
+
+// ---- Q5_K: codes 0..31 unsigned, y = (d * scale) q - dmin * min
+template <>
+__device__ __forceinline__ void decode_unit<Q5_K>(const uint8_t* rowp, int u, const LaneLuts&, Dec<Q5_K>& d) {
+  const uint8_t* blk = rowp + (u >> 3) * 176;
+  const int j = u & 7;
+  const uint8_t* sc = blk + 4;
+  uint32_t scale, mn;
+  if (j < 4) { scale = sc[j] & 63u; mn = sc[j + 4] & 63u; }
+  else { scale = (sc[j + 4] & 0xFu) | ((uint32_t)(sc[j - 4] >> 6) << 4); mn = (sc[j + 4] >> 4) | ((uint32_t)(sc[j] >> 6) << 4); }
+  uint32_t a[8], b[8];
+  load_words<8>(blk + 48 + 32 * (j >> 1), a);
+  load_words<8>(blk + 16, b);
+  const int nsh = 4 * (j & 1);
+#pragma unroll
+  for (int i = 0; i < 8; i++) d.w[i] = ((a[i] >> nsh) & 0x0F0F0F0Fu) | (((b[i] >> j) & 0x01010101u) << 4);
+  d.a = lds_half(blk) * (float)scale;
+  d.b = lds_half(blk + 2) * (float)mn;
+}
+template <>
+__device__ __forceinline__ float dot_unit<Q5_K>(const Dec<Q5_K>& d, const XRegs& x) {
+  int sh = 0, sl = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) { sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl); }
+  return x.s * (d.a * (float)(sh * 256 + sl) - d.b * (float)(x.sa + x.sb));
+}
+
+// dense types: fp32 activation from shared memory
+template <int T>
+__device__ __forceinline__ float unit_dot_dense(const uint8_t* rowp, int u, const float* xf) {
+  const float4* xv = reinterpret_cast<const float4*>(xf + 32 * u);
+  float acc = 0.f;
+  if (T == F32) {
+    uint32_t w[32];
+    load_words<32>(rowp + u * 128, w);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float4 v = xv[i];
+      acc = fmaf(__uint_as_float(w[4 * i]), v.x, acc); acc = fmaf(__uint_as_float(w[4 * i + 1]), v.y, acc);
+      acc = fmaf(__uint_as_float(w[4 * i + 2]), v.z, acc); acc = fmaf(__uint_as_float(w[4 * i + 3]), v.w, acc);
+    }
+  } else {
+    uint32_t w[16];
+    load_words<16>(rowp + u * 64, w);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float4 v = xv[i];
+      float a0, a1, a2, a3;
+      if (T == BF16) {
+        a0 = __uint_as_float(w[2 * i] << 16); a1 = __uint_as_float(w[2 * i] & 0xFFFF0000u);
+        a2 = __uint_as_float(w[2 * i + 1] << 16); a3 = __uint_as_float(w[2 * i + 1] & 0xFFFF0000u);
+      } else {
+        const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * i]));
+        const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * i + 1]));
+        a0 = p.x; a1 = p.y; a2 = r.x; a3 = r.y;
+      }
+      acc = fmaf(a0, v.x, acc); acc = fmaf(a1, v.y, acc); acc = fmaf(a2, v.z, acc); acc = fmaf(a3, v.w, acc);
+    }
+  }
+  return acc;
+}
+
+// ---------------------------------------------------------------- exact dequantisation of 8 consecutive elements
+// `blk` points at the block in GLOBAL memory (2-byte aligned), e8 = index of the 8-element group inside the block.
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
+__device__ __forceinline__ float ldg_half(const uint8_t* p) { return __half2float(__ushort_as_half((unsigned short)ldg_u16(p))); }
+
+template <int T>
+__device__ __forceinline__ void dequant8(const uint8_t* blk, int e8, const Tables& tb, float (&y)[8]);
+
+template <>
+__device__ __forceinline__ void dequant8<Q8_0>(const uint8_t* blk, int e8, const Tables&, float (&y)[8]) {
+  const float d = ldg_half(blk);
+#pragma unroll
+  for (int j = 0; j < 8; j++) y[j] = __fmul_rn((float)(int8_t)__ldg(blk + 2 + 8 * e8 + j), d);
+}
+template <>
+__device__ __forceinline__ void dequant8<IQ4_NL>(const uint8_t* blk, int e8, const Tables& tb, float (&y)[8]) {
+  const float d = ldg_half(blk);
+  const int hi = e8 >> 1, off = 8 * (e8 & 1);      // elements 0..15 = low nibbles of qs[0..15], 16..31 = high nibbles
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const uint32_t pr = __ldg(tb.iq4nl_pair + __ldg(blk + 2 + off + j));
+    y[j] = __fmul_rn(d, (float)(int8_t)(hi ? (pr >> 8) : (pr & 0xFF)));
+  }
+}
+template <>
+__device__ __forceinline__ void dequant8<IQ1_S>(const uint8_t* blk, int e8, const Tables& tb, float (&y)[8]) {
+  const int ib = e8 >> 2, l = e8 & 3;
+  const uint32_t qh = ldg_u16(blk + 34 + 2 * ib);
+  const float dl = __fmul_rn(ldg_half(blk), (float)(2 * ((qh >> 12) & 7u) + 1));
+  const float delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+  const uint32_t idx = __ldg(blk + 2 + 4 * ib + l) | (((qh >> (3 * l)) & 7u) << 8);
+  const int8_t* g = tb.iq1s_i8 + idx * 8;
+#pragma unroll
+  for (int j = 0; j < 8; j++) y[j] = __fmul_rn(dl, __fadd_rn((float)__ldg(g + j), delta));
+}
+template <>
+__device__ __forceinline__ void dequant8<IQ2_XXS>(const uint8_t* blk, int e8, const Tables& tb, float (&y)[8]) {
+  const int ib = e8 >> 2, l = e8 & 3;
+  const uint8_t* a8 = blk + 2 + 8 * ib;
+  const uint32_t a1 = ldg_u16(a8 + 4) | (ldg_u16(a8 + 6) << 16);
+  const float db = __fmul_rn(__fmul_rn(ldg_half(blk), __fadd_rn(0.5f, (float)(a1 >> 28))), 0.25f);
+  const uint2 g = __ldg(tb.iq2xxs_grid + __ldg(a8 + l));
+  const uint2 m = __ldg(tb.iq2_signmask + ((a1 >> (7 * l)) & 127u));
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const uint32_t gv = ((j < 4 ? g.x : g.y) >> (8 * (j & 3))) & 0xFFu;
+    const bool neg = ((j < 4 ? m.x : m.y) >> (8 * (j & 3))) & 1u;
+    y[j] = __fmul_rn(__fmul_rn(db, (float)gv), neg ? -1.f : 1.f);
+  }
+}
+template <>
+__device__ __forceinline__ void dequant8<Q6_K>(const uint8_t* blk, int e8, const Tables&, float (&y)[8]) {
+  // element e = 128*half + 32*q + l  (q = 0..3, l = 0..31): ql byte 64*half + 32*(q&1) + l, nibble q>>1;
+  // qh byte 128 + 32*half + l, bits 2q..2q+1; scale sc[8*half + 2*q + l/16]
+  const int e = 8 * e8, half = e >> 7, q = (e >> 5) & 3, l0 = e & 31;
+  const float d = ldg_half(blk + 208);
+  const float sc = (float)(int8_t)__ldg(blk + 192 + 8 * half + 2 * q + (l0 >> 4));
+  const float ds = __fmul_rn(d, sc);
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const uint32_t ql = __ldg(blk + 64 * half + 32 * (q & 1) + l0 + j), qh = __ldg(blk + 128 + 32 * half + l0 + j);
+    const int v = (int)(((ql >> (4 * (q >> 1))) & 0xFu) | (((qh >> (2 * q)) & 3u) << 4)) - 32;
+    y[j] = __fmul_rn(ds, (float)v);
+  }
+}
+template <>
+__device__ __forceinline__ void dequant8<Q5_K>(const uint8_t* blk, int e8, const Tables&, float (&y)[8]) {
+  const int e = 8 * e8, j = e >> 5, l0 = e & 31;          // sub-block j = 0..7
+  const uint8_t* sc = blk + 4;
+  uint32_t scale, mn;
+  if (j < 4) { scale = __ldg(sc + j) & 63u; mn = __ldg(sc + j + 4) & 63u; }
+  else {
+    scale = (__ldg(sc + j + 4) & 0xFu) | ((__ldg(sc + j - 4) >> 6) << 4);
+    mn = (__ldg(sc + j + 4) >> 4) | ((__ldg(sc + j) >> 6) << 4);
+  }
+  const float d1 = __fmul_rn(ldg_half(blk), (float)scale), m1 = __fmul_rn(ldg_half(blk + 2), (float)mn);
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const uint32_t ql = __ldg(blk + 48 + 32 * (j >> 1) + l0 + i), qh = __ldg(blk + 16 + l0 + i);
+    const int v = (int)((ql >> (4 * (j & 1))) & 0xFu) + (int)((qh >> j) & 1u) * 16;
+    y[i] = __fsub_rn(__fmul_rn(d1, (float)v), m1);
+  }
+}
+#endif  // __CUDACC__
+
+}  // namespace msb

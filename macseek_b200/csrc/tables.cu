@@ -1,0 +1,104 @@
+// Host-side status text and the per-device codebook tables of libmacseek_b200.
+#include <cstdarg>
+#include <cstring>
+#include <mutex>
+#include <vector>
+#include "msb_common.cuh"
+#include "iq_grids_packed.h"
+
+namespace msb {
+
+static thread_local char t_err[512] = "";
+const char* last_error_text() { return t_err; }
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err, sizeof t_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(kErrCuda, "CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
+}
+const char* type_name(int t) {
+  switch (t) {
+    case F32: return "F32"; case F16: return "F16"; case BF16: return "BF16"; case Q8_0: return "Q8_0";
+    case Q5_K: return "Q5_K"; case Q6_K: return "Q6_K"; case IQ2_XXS: return "IQ2_XXS"; case IQ1_S: return "IQ1_S";
+    case IQ4_NL: return "IQ4_NL";
+  }
+  return "?";
+}
+
+// GGUF IQ4_NL value table (16 signed levels)
+static const int8_t kIq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+namespace {
+constexpr int kMaxDev = 64;
+struct DevTables { bool ready = false; Tables t{}; };
+DevTables g_tables[kMaxDev];
+std::mutex g_mu;
+
+struct HostImage {
+  std::vector<uint32_t> iq1s_nib;
+  std::vector<uint32_t> iq2_grid;   // 2 words per entry
+  std::vector<uint32_t> iq2_sign;   // 2 words per entry
+  std::vector<uint16_t> iq4_pair;
+  std::vector<int8_t> iq1s_i8;
+  HostImage() : iq1s_nib(2048), iq2_grid(512), iq2_sign(256), iq4_pair(256), iq1s_i8(2048 * 8) {
+    for (int i = 0; i < 2048; i++) {
+      uint32_t v = 0;
+      for (int j = 0; j < 8; j++) {
+        const uint32_t f = (kMsbIq1sPacked[i] >> (2 * j)) & 3;   // value + 1
+        iq1s_i8[i * 8 + j] = (int8_t)((int)f - 1);
+        const int nib = j < 4 ? 2 * j : 2 * (j - 4) + 1;
+        v |= f << (4 * nib);
+      }
+      iq1s_nib[i] = v;
+    }
+    static const uint32_t lv[4] = {8, 25, 43, 0};
+    for (int i = 0; i < 256; i++)
+      for (int j = 0; j < 8; j++) iq2_grid[2 * i + j / 4] |= lv[(kMsbIq2xxsPacked[i] >> (2 * j)) & 3] << (8 * (j % 4));
+    for (int i = 0; i < 128; i++) {
+      const int bits = i | ((__builtin_popcount((unsigned)i) & 1) << 7);
+      for (int j = 0; j < 8; j++)
+        if ((bits >> j) & 1) iq2_sign[2 * i + j / 4] |= 0xFFu << (8 * (j % 4));
+    }
+    for (int b = 0; b < 256; b++)
+      iq4_pair[b] = (uint16_t)((uint8_t)kIq4nl[b & 15] | ((uint16_t)(uint8_t)kIq4nl[b >> 4] << 8));
+  }
+};
+
+template <typename T>
+cudaError_t upload(const std::vector<T>& v, const void** out) {
+  void* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, v.size() * sizeof(T));
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
+  *out = d;
+  return e;
+}
+}  // namespace
+
+int get_tables(Tables* out) {
+  int dev = 0;
+  MSB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDev) return fail(kErrArg, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DevTables& d = g_tables[dev];
+  if (!d.ready) {
+    static const HostImage img;
+    MSB_CUDA(upload(img.iq1s_nib, (const void**)&d.t.iq1s_nib));
+    MSB_CUDA(upload(img.iq2_grid, (const void**)&d.t.iq2xxs_grid));
+    MSB_CUDA(upload(img.iq2_sign, (const void**)&d.t.iq2_signmask));
+    MSB_CUDA(upload(img.iq4_pair, (const void**)&d.t.iq4nl_pair));
+    MSB_CUDA(upload(img.iq1s_i8, (const void**)&d.t.iq1s_i8));
+    MSB_CUDA(cudaMalloc((void**)&d.t.status, 256));
+    MSB_CUDA(cudaMemset(d.t.status, 0, 256));
+    d.ready = true;
+  }
+  *out = d.t;
+  return kOk;
+}
+
+}  // namespace msb
