@@ -51,6 +51,60 @@ int msb_matvec(int qtype, const void* W, int rows, int cols, const float* x, flo
 int msb_matvec_n(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate,
                  int groups, void* stream);
 
+/* ---------------------------------------------------------------- MoE decode (one token)
+ * ms::q::MoeDecodeArgs / ExpertSlot / moe_decode_scratch_bytes / encode_moe_decode[_table[_part]] / MoePart
+ * (src/kernels/quant.hpp:49-85, quant.mm:264-369).  dim and inter are run-time here (the reference fixes 5120 / 2304).
+ *   h[e][r] = silu(min(gate_e[r].x, L)) * clamp(up_e[r].x, -L, L) * w_e     (shared expert: w = 1, stored last)
+ *   y[r]   += sum_e down_e[r] . h[e]                                        (y is ACCUMULATED, quant.hpp:65)
+ * gate/up: [inter x dim] rows, down: [dim x inter] rows, raw GGUF blocks at 2-byte aligned addresses.
+ * Types: gate/up and down IQ1_S or IQ2_XXS; shared expert Q6_K or Q8_0 (quant.mm:255-261).
+ * scratch: at least msb_moe_decode_scratch_bytes(inter, n_routed), 16-byte aligned; holds h as f32 [n_routed+1][inter]
+ * afterwards.  Not thread-safe per device: the two kernels share library-owned scheduling counters (one MoE call in
+ * flight per device at a time, as the reference's module-owned scratch, docs/modules/quant.md:265-268). */
+#define MSB_MAX_ROUTED 16
+typedef struct { const void* gate; const void* up; const void* down; } msb_expert_slot;
+typedef struct {
+  int dim, inter;
+  int t_gate_up, t_down, t_shared;
+  int n_routed;                       /* 0 .. MSB_MAX_ROUTED */
+  int has_shared;
+  msb_expert_slot slot[MSB_MAX_ROUTED];
+  msb_expert_slot shared;
+  const float* weights;               /* device F32[n_routed] routing weights (may be GPU-written) */
+  const float* x;                     /* F32[dim] */
+  float* y;                           /* F32[dim], accumulated */
+  void* scratch;
+  size_t scratch_bytes;
+  float swiglu_limit;                 /* clamp L; 0 selects the reference's 10 */
+} msb_moe_decode_args;
+enum { MSB_MOE_ALL = 0, MSB_MOE_SHARED_GU = 1, MSB_MOE_AFTER_SHARED_GU = 2, MSB_MOE_SHARED = 3, MSB_MOE_ROUTED = 4,
+       MSB_MOE_SHARED_DOWN = 5 };
+size_t msb_moe_decode_scratch_bytes(int inter, int max_routed);
+int msb_moe_decode(const msb_moe_decode_args* a, void* stream);
+/* Routed matrices come from `table`: n_routed entries of 3 device addresses {gate, up, down} (uint64), a.slot[] is
+ * ignored -- encode_moe_decode_table_part (quant.hpp:75-85). */
+int msb_moe_decode_table_part(const msb_moe_decode_args* a, const uint64_t* table, int part, void* stream);
+/* HBM-resident experts resolved on the GPU (what replaces the reference's CPU<->GPU handshake per layer,
+ * src/model/ds41.mm:596-611): expert_table = [n_experts][3] device addresses, ids = device int32[n_routed] as written
+ * by msb_router_*; only experts with expert_lo <= id < expert_hi (the ones resident on this GPU under expert
+ * parallelism) are computed, the others contribute nothing to y. */
+int msb_moe_decode_ids(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
+                       int expert_hi, int part, void* stream);
+
+/* ---------------------------------------------------------------- router
+ * ms::arch::encode_router_fused / encode_router_topk / RouteLists / encode_route_lists (src/kernels/arch.hpp:79-97,
+ * arch.mm:173-239).  E experts (<= 512), top-k (<= 16); score_fn 0 = sqrt(softplus(logit)) (arch_router.metal:16-24),
+ * 1 = sigmoid (reference/inference/model.py:816-817); key = score + bias (bias may be NULL); ties -> lowest id;
+ * w = score / (sum + 1e-20) * route_scale; ids / w in descending key order. */
+size_t msb_router_scratch_bytes(int n_experts);
+int msb_router_fused(const float* x, const float* W, const float* bias, int* ids, float* w, void* scratch,
+                     size_t scratch_bytes, int n_experts, int dim, int k, int score_fn, float route_scale, void* stream);
+int msb_router_topk(const float* logits, const float* bias, int* ids, float* w, int n_tokens, int n_experts, int k,
+                    int score_fn, float route_scale, void* stream);
+/* counts u32[E], offsets u32[E+1], entry/tok/slot_of u32[n*k], lw f32[n*k]; entries t*k+j ordered by (expert, entry). */
+int msb_route_lists(const int* ids, const float* w, int n_tokens, int k, int n_experts, uint32_t* counts,
+                    uint32_t* offsets, uint32_t* entry, uint32_t* tok, float* lw, uint32_t* slot_of, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,3 +40,26 @@ def device_status():
     if rc < 0:
         check(rc)
     return rc
+
+
+class ExpertSlotC(C.Structure):
+    _fields_ = [("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p)]
+
+
+class MoeDecodeArgsC(C.Structure):
+    _fields_ = [("dim", C.c_int), ("inter", C.c_int), ("t_gate_up", C.c_int), ("t_down", C.c_int),
+                ("t_shared", C.c_int), ("n_routed", C.c_int), ("has_shared", C.c_int),
+                ("slot", ExpertSlotC * 16), ("shared", ExpertSlotC), ("weights", C.c_void_p), ("x", C.c_void_p),
+                ("y", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("swiglu_limit", C.c_float)]
+
+
+lib.msb_moe_decode_scratch_bytes.restype = C.c_size_t
+lib.msb_moe_decode_scratch_bytes.argtypes = [_i, _i]
+lib.msb_moe_decode.argtypes = [C.POINTER(MoeDecodeArgsC), _vp]
+lib.msb_moe_decode_table_part.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _i, _vp]
+lib.msb_moe_decode_ids.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _vp, _i, _i, _i, _vp]
+lib.msb_router_scratch_bytes.restype = C.c_size_t
+lib.msb_router_scratch_bytes.argtypes = [_i]
+lib.msb_router_fused.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _i, _f, _vp]
+lib.msb_router_topk.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]
+lib.msb_route_lists.argtypes = [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]

@@ -1,0 +1,63 @@
+"""Host mirror of the router part of the reference's arch module (namespace ms::arch, src/kernels/arch.hpp:79-97)."""
+import torch
+
+from . import _lib
+from .core import Enc, ptr
+
+kExperts, kTopK, kRouteScale = 384, 6, 1.5      # the reference's compile-time shape (arch.hpp:13,16)
+SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
+
+
+class Scratch:
+    """Device scratch of the fused router (logits + K-slice partials); the reference's arch::Scratch::router_logits."""
+
+    def __init__(self, n_experts=kExperts, device="cuda"):
+        self.n_experts = n_experts
+        self.buf = torch.zeros(_lib.lib.msb_router_scratch_bytes(n_experts) // 4, dtype=torch.float32, device=device)
+
+    @property
+    def router_logits(self):
+        return self.buf[:self.n_experts]
+
+    @staticmethod
+    def create(n_experts=kExperts, device="cuda"):
+        return Scratch(n_experts, device)
+
+
+def encode_router_fused(e: Enc, x, W, bias, ids, w, s: Scratch, k=kTopK, score_fn=SCORE_SQRT_SOFTPLUS,
+                        route_scale=kRouteScale):
+    """Fused F32 matvec (W [E][dim]) + score + bias top-k + normalise * route_scale, one launch (arch.hpp:83)."""
+    E, dim = W.shape
+    _lib.check(_lib.lib.msb_router_fused(ptr(x), ptr(W), ptr(bias), ptr(ids), ptr(w), ptr(s.buf), s.buf.numel() * 4,
+                                         E, dim, k, score_fn, route_scale, e.handle))
+
+
+def encode_router_topk(e: Enc, logits, bias, ids, w, n, k=kTopK, score_fn=SCORE_SQRT_SOFTPLUS, route_scale=kRouteScale):
+    """From precomputed logits [n][E] (arch.hpp:85)."""
+    E = logits.shape[-1]
+    _lib.check(_lib.lib.msb_router_topk(ptr(logits), ptr(bias), ptr(ids), ptr(w), n, E, k, score_fn, route_scale, e.handle))
+
+
+class RouteLists:
+    """arch.hpp:87-95: counts u32[E], offsets u32[E+1], entry/tok/slot_of u32[k n], w f32[k n]."""
+
+    def __init__(self, max_tokens, k=kTopK, n_experts=kExperts, device="cuda"):
+        self.max_tokens, self.k, self.n_experts = max_tokens, k, n_experts
+        i32 = dict(dtype=torch.int32, device=device)
+        self.counts = torch.zeros(n_experts, **i32)
+        self.offsets = torch.zeros(n_experts + 1, **i32)
+        self.entry = torch.zeros(max_tokens * k, **i32)
+        self.tok = torch.zeros(max_tokens * k, **i32)
+        self.w = torch.zeros(max_tokens * k, dtype=torch.float32, device=device)
+        self.slot_of = torch.zeros(max_tokens * k, **i32)
+
+    @staticmethod
+    def create(max_tokens, k=kTopK, n_experts=kExperts, device="cuda"):
+        return RouteLists(max_tokens, k, n_experts, device)
+
+
+def encode_route_lists(e: Enc, ids, w, n, L: RouteLists):
+    if n > L.max_tokens:
+        raise _lib.MsbError("route_lists: %d tokens > capacity %d" % (n, L.max_tokens))
+    _lib.check(_lib.lib.msb_route_lists(ptr(ids), ptr(w), n, L.k, L.n_experts, ptr(L.counts), ptr(L.offsets),
+                                        ptr(L.entry), ptr(L.tok), ptr(L.w), ptr(L.slot_of), e.handle))

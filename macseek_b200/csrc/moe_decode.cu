@@ -9,35 +9,9 @@
 // a host round trip.  A row's partial sums are always formed in the same order, whichever block computes it.
 #include <algorithm>
 #include "stream_pipe.cuh"
+#include "moe_decode_params.cuh"
 
 namespace msb {
-
-constexpr int kMaxRouted = 16;
-constexpr int kMoeNW = 8;
-
-struct MoeShape { int chunk; uint32_t pitch; };   // staged piece shape for one (type, K) pair
-
-struct MoeParams {
-  int dim, inter, n_routed, has_shared;
-  int gu_r, gu_s, d_r, d_s;               // which pieces this launch covers
-  const uint8_t* gate[kMaxRouted];
-  const uint8_t* up[kMaxRouted];
-  const uint8_t* down[kMaxRouted];
-  const uint8_t *sgate, *sup, *sdown;
-  const uint64_t* table;                  // optional [n_experts][3] device addresses {gate, up, down}
-  const int* ids;                         // device [n_routed] expert ids (with table)
-  int expert_lo, expert_hi;               // experts resident on this GPU (with table)
-  const float* weights;                   // device [n_routed]
-  const float* x;
-  float* y;
-  float* h;                               // [n_routed + 1][inter]
-  unsigned* sched;                        // [2] tile counter, finished-block counter (zero between launches)
-  float limit;
-  MoeShape gu_routed, gu_shared, d_routed, d_shared;
-  uint32_t stage_bytes;
-  int stages;
-  Tables tb;
-};
 
 struct MoeSmemHead {
   uint64_t full[kMaxStages], empty[kMaxStages];
@@ -61,8 +35,8 @@ __device__ __forceinline__ void resolve_local(const MoeParams& p, MoeSmemHead* h
   if (want_routed) {
     for (int k = 0; k < p.n_routed; k++) {
       if (p.table) {
-        const int id = p.ids[k];
-        if (id < p.expert_lo || id >= p.expert_hi) continue;
+        const int id = p.ids ? p.ids[k] : k;          // no ids: the table holds one entry per routed slot
+        if (p.ids && (id < p.expert_lo || id >= p.expert_hi)) continue;
         const uint64_t* row = p.table + (size_t)id * 3;
         hd->p0[nl] = reinterpret_cast<const uint8_t*>(down ? row[2] : row[0]);
         hd->p1[nl] = reinterpret_cast<const uint8_t*>(row[1]);

@@ -1,0 +1,38 @@
+// Launch parameters of the fused MoE decode kernels (moe_decode.cu), shared with the C entry points.
+#pragma once
+#include "msb_common.cuh"
+
+namespace msb {
+
+constexpr int kMaxRouted = 16;
+constexpr int kMoeNW = 8;
+
+struct MoeShape { int chunk; uint32_t pitch; };   // staged piece shape for one (type, K) pair
+
+struct MoeParams {
+  int dim, inter, n_routed, has_shared;
+  int gu_r, gu_s, d_r, d_s;               // which pieces this launch covers
+  const uint8_t* gate[kMaxRouted];
+  const uint8_t* up[kMaxRouted];
+  const uint8_t* down[kMaxRouted];
+  const uint8_t *sgate, *sup, *sdown;
+  const uint64_t* table;                  // optional [n_experts][3] device addresses {gate, up, down}
+  const int* ids;                         // device [n_routed] expert ids (with table)
+  int expert_lo, expert_hi;               // experts resident on this GPU (with table)
+  const float* weights;                   // device [n_routed]
+  const float* x;
+  float* y;
+  float* h;                               // [n_routed + 1][inter]
+  unsigned* sched;                        // [2] tile counter, finished-block counter (zero between launches)
+  float limit;
+  MoeShape gu_routed, gu_shared, d_routed, d_shared;
+  uint32_t stage_bytes;
+  int stages;
+  Tables tb;
+};
+
+size_t moe_decode_scratch_bytes(int inter, int max_routed);
+// part: 0 All, 1 SharedGu, 2 AfterSharedGu, 3 Shared, 4 Routed, 5 SharedDown
+int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, size_t scratch_bytes, cudaStream_t st);
+
+}  // namespace msb

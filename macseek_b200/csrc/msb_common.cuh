@@ -36,7 +36,7 @@ __host__ __device__ constexpr int block_bytes(int t) {
        : t == IQ2_XXS ? 66 : t == IQ1_S ? 50 : t == IQ4_NL ? 18 : 0;
 }
 inline bool type_known(int t) { return block_bytes(t) != 0; }
-inline size_t row_bytes(int t, int64_t cols) { return (size_t)(cols / block_elems(t)) * block_bytes(t); }
+__host__ __device__ inline size_t row_bytes(int t, int64_t cols) { return (size_t)(cols / block_elems(t)) * block_bytes(t); }
 const char* type_name(int t);
 
 // device-side failure word (one int per device, Tables::status): set by a kernel whose bounded wait ran out; read by

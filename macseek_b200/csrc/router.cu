@@ -1,0 +1,226 @@
+// MoE router: logits = W[E x dim] . x (fp32), score = sqrt(softplus) or sigmoid, top-k of score + bias (ties -> lowest
+// expert id), weights = score / (sum + 1e-20) * route_scale; plus the per-expert routing lists for the prefill grouped
+// GEMM.  Replaces the reference's arch_router_fused / arch_router_topk / arch_route_count / arch_route_scatter Metal
+// kernels (src/kernels/arch_router.metal:16-160) behind ms::arch::encode_router_fused / encode_router_topk /
+// encode_route_lists (src/kernels/arch.hpp:79-97, arch.mm:173-239).
+#include <algorithm>
+#include "msb_common.cuh"
+
+namespace msb {
+
+constexpr int kRouterMaxE = 512;   // experts per token handled by the one-warp selection (16 per lane)
+constexpr int kRouterMaxK = 16;
+constexpr int kRouterKSplit = 4;   // K slices per expert row in the fused kernel
+
+struct RouterParams {
+  const float* x;
+  const float* W;
+  const float* bias;     // may be null
+  float* logits;         // [E] (written by the fused kernel; diagnostic, as the reference's Scratch::router_logits)
+  float* partial;        // [E][kRouterKSplit]
+  int* ids;
+  float* wts;
+  unsigned* ticket;      // zero between launches
+  int E, dim, k, score_fn;
+  float route_scale;
+};
+
+__device__ __forceinline__ float router_score(float x, int score_fn) {
+  if (score_fn == 1) return 1.f / (1.f + expf(-x));
+  const float sp = x > 20.f ? x : log1pf(expf(x));   // softplus, threshold 20 (arch_router.metal:20-24)
+  return sqrtf(sp);
+}
+
+// One warp selects the top-k experts of one token (descending key; ties -> lowest id) and writes ids / weights.
+__device__ __forceinline__ void router_topk_warp(const float* logits, const float* bias, int E, int k, int score_fn,
+                                                 float route_scale, int lane, int* ids, float* wts) {
+  constexpr int EPL = kRouterMaxE / 32;
+  float sc[EPL], key[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; i++) {
+    const int e = lane + 32 * i;
+    if (e < E) {
+      sc[i] = router_score(logits[e], score_fn);
+      key[i] = sc[i] + (bias ? bias[e] : 0.f);
+    } else {
+      sc[i] = 0.f;
+      key[i] = -INFINITY;
+    }
+  }
+  float sum = 0.f, my_w = 0.f;
+  int my_e = 0;
+  unsigned taken = 0;
+  for (int j = 0; j < k; j++) {
+    // this lane's best remaining candidate: ascending expert id with a strict compare keeps the lowest id on ties
+    float bk = -INFINITY, bs = 0.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < EPL; i++) {
+      const int e = lane + 32 * i;
+      if (e < E && !((taken >> i) & 1u) && (be == 0x7fffffff || key[i] > bk)) { bk = key[i]; bs = sc[i]; be = e; }
+    }
+    float m = bk;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    int win = (bk == m) ? be : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) win = min(win, __shfl_xor_sync(0xffffffffu, win, o));
+    const float wscore = __shfl_sync(0xffffffffu, bs, win & 31);   // the owner's best candidate is the winner
+    if (lane == (win & 31)) taken |= 1u << (win >> 5);
+    sum += wscore;
+    if (lane == j) { my_e = win; my_w = wscore; }
+  }
+  const float inv = route_scale / (sum + 1e-20f);
+  if (lane < k) { ids[lane] = my_e; wts[lane] = my_w * inv; }
+}
+
+// Fused decode router: every warp computes one (expert, K-slice) partial dot; the block that finishes last sums the
+// slices in a fixed order, writes the logits and selects.
+__global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = blockIdx.x * 8 + warp;
+  const int slice = p.dim / kRouterKSplit;   // floats per slice, a multiple of 4
+  if (unit < p.E * kRouterKSplit) {
+    const int e = unit / kRouterKSplit, ks = unit % kRouterKSplit;
+    const float4* w = reinterpret_cast<const float4*>(p.W + (size_t)e * p.dim + (size_t)ks * slice);
+    const float4* xv = reinterpret_cast<const float4*>(p.x + (size_t)ks * slice);
+    float acc = 0.f;
+    for (int c = lane; c < slice / 4; c += 32) {
+      const float4 a = __ldg(w + c), b = xv[c];
+      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) p.partial[unit] = acc;
+  }
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(p.ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+    const volatile float* q = p.partial + (size_t)e * kRouterKSplit;
+    float s = q[0];
+#pragma unroll
+    for (int i = 1; i < kRouterKSplit; i++) s += q[i];
+    p.logits[e] = s;
+  }
+  __syncthreads();
+  if (warp == 0) router_topk_warp(p.logits, p.bias, p.E, p.k, p.score_fn, p.route_scale, lane, p.ids, p.wts);
+  if (threadIdx.x == 0) *p.ticket = 0;
+}
+
+// logits [n][E] -> ids [n][k], weights [n][k]; one warp per token.
+__global__ void __launch_bounds__(128) router_topk_kernel(const float* logits, const float* bias, int* ids, float* wts,
+                                                          int n, int E, int k, int score_fn, float route_scale) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= n) return;
+  router_topk_warp(logits + (size_t)t * E, bias, E, k, score_fn, route_scale, threadIdx.x & 31, ids + (size_t)t * k,
+                   wts + (size_t)t * k);
+}
+
+// ---- routing lists: entries i = t*k + j sorted by (expert, i).  No atomics: a warp owns an expert and scans all
+// entries in order with ballots, so the lists are identical from run to run.
+__global__ void __launch_bounds__(256) route_count_kernel(const int* ids, unsigned* counts, int N, int E) {
+  const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= E) return;
+  unsigned c = 0;
+  for (int i0 = 0; i0 < N; i0 += 32) {
+    const int i = i0 + lane;
+    c += __popc(__ballot_sync(0xffffffffu, i < N && ids[i] == e));
+  }
+  if (lane == 0) counts[e] = c;
+}
+__global__ void __launch_bounds__(1024) route_scan_kernel(const unsigned* counts, unsigned* offsets, int E) {
+  __shared__ unsigned buf[1024];
+  const int tid = threadIdx.x;
+  // E <= 1024 per pass; serial carry over passes
+  unsigned carry = 0;
+  for (int base = 0; base < E; base += 1024) {
+    const unsigned v = base + tid < E ? counts[base + tid] : 0;
+    buf[tid] = v;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      const unsigned a = tid >= o ? buf[tid - o] : 0;
+      __syncthreads();
+      buf[tid] += a;
+      __syncthreads();
+    }
+    if (base + tid < E) offsets[base + tid] = carry + buf[tid] - v;
+    carry += buf[1023];
+    __syncthreads();
+  }
+  if (tid == 0) offsets[E] = carry;
+}
+__global__ void __launch_bounds__(256) route_scatter_kernel(const int* ids, const float* w, const unsigned* offsets,
+                                                            unsigned* entry, unsigned* tok, float* lw, unsigned* slot_of,
+                                                            int N, int E, int k) {
+  const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= E) return;
+  unsigned pos = offsets[e];
+  for (int i0 = 0; i0 < N; i0 += 32) {
+    const int i = i0 + lane;
+    const bool hit = i < N && ids[i] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (hit) {
+      const unsigned q = pos + __popc(m & ((1u << lane) - 1u));
+      entry[q] = (unsigned)i; tok[q] = (unsigned)(i / k); lw[q] = w[i]; slot_of[i] = q;
+    }
+    pos += __popc(m);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+size_t router_scratch_bytes(int E) { return sizeof(float) * (size_t)E * (1 + kRouterKSplit); }
+
+int router_fused(const float* x, const float* W, const float* bias, int* ids, float* wts, void* scratch,
+                 size_t scratch_bytes, int E, int dim, int k, int score_fn, float route_scale, cudaStream_t st) {
+  if (E <= 0 || E > kRouterMaxE || k <= 0 || k > kRouterMaxK || k > E || dim <= 0 || dim % (4 * kRouterKSplit))
+    return fail(kErrArg, "router: bad shape (E %d dim %d k %d)", E, dim, k);
+  if (!x || !W || !ids || !wts || !scratch) return fail(kErrArg, "router: null pointer");
+  if (scratch_bytes < router_scratch_bytes(E)) return fail(kErrScratch, "router: scratch too small");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return fail(kErrArg, "router: x and W must be 16-byte aligned");
+  Tables tb;
+  int rc = get_tables(&tb);
+  if (rc) return rc;
+  RouterParams p;
+  p.x = x; p.W = W; p.bias = bias; p.ids = ids; p.wts = wts;
+  p.logits = reinterpret_cast<float*>(scratch);
+  p.partial = p.logits + E;
+  p.ticket = reinterpret_cast<unsigned*>(tb.status) + 16;
+  p.E = E; p.dim = dim; p.k = k; p.score_fn = score_fn; p.route_scale = route_scale;
+  const int units = E * kRouterKSplit;
+  router_fused_kernel<<<(units + 7) / 8, 256, 0, st>>>(p);
+  MSB_LAUNCH_CHECK("router_fused_kernel");
+  return kOk;
+}
+
+int router_topk(const float* logits, const float* bias, int* ids, float* wts, int n, int E, int k, int score_fn,
+                float route_scale, cudaStream_t st) {
+  if (E <= 0 || E > kRouterMaxE || k <= 0 || k > kRouterMaxK || k > E || n < 0)
+    return fail(kErrArg, "router_topk: bad shape (n %d E %d k %d)", n, E, k);
+  if (n == 0) return kOk;
+  if (!logits || !ids || !wts) return fail(kErrArg, "router_topk: null pointer");
+  router_topk_kernel<<<(n + 3) / 4, 128, 0, st>>>(logits, bias, ids, wts, n, E, k, score_fn, route_scale);
+  MSB_LAUNCH_CHECK("router_topk_kernel");
+  return kOk;
+}
+
+int route_lists(const int* ids, const float* w, int n, int k, int E, unsigned* counts, unsigned* offsets,
+                unsigned* entry, unsigned* tok, float* lw, unsigned* slot_of, cudaStream_t st) {
+  if (n < 0 || k <= 0 || E <= 0) return fail(kErrArg, "route_lists: bad shape");
+  if (!ids || !w || !counts || !offsets || !entry || !tok || !lw || !slot_of) return fail(kErrArg, "route_lists: null pointer");
+  const int N = n * k;
+  route_count_kernel<<<(E + 7) / 8, 256, 0, st>>>(ids, counts, N, E);
+  route_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, E);
+  route_scatter_kernel<<<(E + 7) / 8, 256, 0, st>>>(ids, w, offsets, entry, tok, lw, slot_of, N, E, k);
+  MSB_LAUNCH_CHECK("route_lists");
+  return kOk;
+}
+
+}  // namespace msb

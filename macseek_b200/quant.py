@@ -51,3 +51,85 @@ def encode_matvec(e: Enc, t, W, rows, cols, x, y, accumulate=False, groups=1):
 def encode_matvec_n(e: Enc, t, W, rows, cols, X, Y, n, accumulate=False, groups=1):
     """Y[n x rows] (+)= X[n x cols*groups] . W^T for n in 1..16 (quant.hpp:32-35)."""
     _lib.check(_lib.lib.msb_matvec_n(int(t), ptr(W), rows, cols, ptr(X), ptr(Y), n, int(accumulate), groups, e.handle))
+
+
+# ---------------------------------------------------------------- MoE decode (quant.hpp:49-85)
+kMaxRouted = 16
+
+
+class ExpertSlot:
+    """Three raw-block matrices of one expert: gate [inter x dim], up [inter x dim], down [dim x inter]."""
+
+    def __init__(self, gate=None, up=None, down=None):
+        self.gate, self.up, self.down = gate, up, down
+
+
+class MoePart(enum.IntEnum):
+    """quant.hpp:83"""
+    All = 0
+    SharedGu = 1
+    AfterSharedGu = 2
+    Shared = 3
+    Routed = 4
+    SharedDown = 5
+
+
+class MoeDecodeArgs:
+    """ms::q::MoeDecodeArgs with run-time dim / inter (the reference fixes kExpertDim = 5120, kExpertInter = 2304)."""
+
+    def __init__(self, dim=5120, inter=2304):
+        self.dim, self.inter = dim, inter
+        self.t_gate_up = QType.IQ1_S
+        self.t_down = QType.IQ1_S
+        self.n_routed = 6
+        self.slot = [ExpertSlot() for _ in range(kMaxRouted)]
+        self.weights = None
+        self.has_shared = True
+        self.t_shared = QType.Q6_K
+        self.shared = ExpertSlot()
+        self.x = None
+        self.y = None
+        self.scratch = None
+        self.swiglu_limit = 10.0
+
+    def _c(self):
+        a = _lib.MoeDecodeArgsC()
+        a.dim, a.inter = self.dim, self.inter
+        a.t_gate_up, a.t_down, a.t_shared = int(self.t_gate_up), int(self.t_down), int(self.t_shared)
+        a.n_routed, a.has_shared = self.n_routed, int(self.has_shared)
+        for i in range(min(self.n_routed, kMaxRouted)):
+            s = self.slot[i]
+            a.slot[i].gate, a.slot[i].up, a.slot[i].down = ptr(s.gate), ptr(s.up), ptr(s.down)
+        a.shared.gate, a.shared.up, a.shared.down = ptr(self.shared.gate), ptr(self.shared.up), ptr(self.shared.down)
+        a.weights, a.x, a.y = ptr(self.weights), ptr(self.x), ptr(self.y)
+        a.scratch = ptr(self.scratch)
+        a.scratch_bytes = self.scratch.numel() * self.scratch.element_size() if self.scratch is not None else 0
+        a.swiglu_limit = self.swiglu_limit
+        return a
+
+
+def moe_decode_scratch_bytes(inter=2304, max_routed=6):
+    return _lib.lib.msb_moe_decode_scratch_bytes(inter, max_routed)
+
+
+def encode_moe_decode(e: Enc, a: MoeDecodeArgs):
+    """Gate+up+SwiGLU for every expert, then down for every expert accumulated into y (quant.hpp:72-74)."""
+    c = a._c()
+    _lib.check(_lib.lib.msb_moe_decode(c, e.handle))
+
+
+def encode_moe_decode_table(e: Enc, a: MoeDecodeArgs, table):
+    encode_moe_decode_table_part(e, a, table, MoePart.All)
+
+
+def encode_moe_decode_table_part(e: Enc, a: MoeDecodeArgs, table, part):
+    """Routed matrices from `table`: n_routed x 3 device addresses {gate, up, down} (quant.hpp:75-85)."""
+    c = a._c()
+    _lib.check(_lib.lib.msb_moe_decode_table_part(c, ptr(table), int(part), e.handle))
+
+
+def encode_moe_decode_ids(e: Enc, a: MoeDecodeArgs, expert_table, ids, expert_lo, expert_hi, part=MoePart.All):
+    """HBM-resident experts: expert_table [n_experts][3] device addresses, ids = device int32 [n_routed] from the
+    router; only experts in [expert_lo, expert_hi) are computed on this GPU."""
+    c = a._c()
+    _lib.check(_lib.lib.msb_moe_decode_ids(c, ptr(expert_table), ptr(ids), expert_lo, expert_hi, int(part), e.handle))
