@@ -78,7 +78,9 @@ typedef struct {
   float swiglu_limit;                 /* clamp L; 0 selects the reference's 10 */
 } msb_moe_decode_args;
 enum { MSB_MOE_ALL = 0, MSB_MOE_SHARED_GU = 1, MSB_MOE_AFTER_SHARED_GU = 2, MSB_MOE_SHARED = 3, MSB_MOE_ROUTED = 4,
-       MSB_MOE_SHARED_DOWN = 5 };
+       MSB_MOE_SHARED_DOWN = 5,
+       /* not in the reference: the two launches of MSB_MOE_ALL one at a time (GU_ALL then DOWN_ALL == ALL, bit-identical) */
+       MSB_MOE_GU_ALL = 6, MSB_MOE_DOWN_ALL = 7 };
 size_t msb_moe_decode_scratch_bytes(int inter, int max_routed);
 int msb_moe_decode(const msb_moe_decode_args* a, void* stream);
 /* Routed matrices come from `table`: n_routed entries of 3 device addresses {gate, up, down} (uint64), a.slot[] is
@@ -104,6 +106,45 @@ int msb_router_topk(const float* logits, const float* bias, int* ids, float* w, 
 /* counts u32[E], offsets u32[E+1], entry/tok/slot_of u32[n*k], lw f32[n*k]; entries t*k+j ordered by (expert, entry). */
 int msb_route_lists(const int* ids, const float* w, int n_tokens, int k, int n_experts, uint32_t* counts,
                     uint32_t* offsets, uint32_t* entry, uint32_t* tok, float* lw, uint32_t* slot_of, void* stream);
+
+/* ---------------------------------------------------------------- lightning indexer (decode) and exact top-k
+ * ms::attn::encode_index_decode (src/kernels/attn.hpp:121-122, attn.mm:222-290); math spec tests/ref/attn_ref.cpp:163-202.
+ * Index keys: [len][128] rows, MSB_F16 (the reference's ikey cache, attn.hpp:69) or MSB_KEY_FP8_E4M3.
+ * heads = 32 (reference) or 64. */
+#define MSB_KEY_FP8_E4M3 101
+/* Query preparation (index_q): rope on the last 64 dims of each head with cs = (cos, sin)[32] of the query position,
+ * optional fp4 quant-dequant simulation (actq), head weights scaled by 128^-0.5 * heads^-0.5.  q: [heads][128]. */
+int msb_index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q, float* w,
+                   void* stream);
+/* scores[t] = sum_h relu(q_h . key_t) * w_h for t < len.  FP8 keys: the query is rounded to e4m3 for the tensor cores
+ * unless exact_query != 0 (then the keys are widened to f16 and the fp32 query is used as two f16 terms).
+ * topk_scratch (optional): when given, the histogram used by msb_topk(..., hist_ready = 1) is built on the fly. */
+int msb_index_scores(int key_type, const void* keys, int len, const float* q, const float* w, int heads, float* scores,
+                     void* topk_scratch, int exact_query, void* stream);
+/* Exact top-k (k <= 2048) among the finite entries of scores[0..n): ties -> lower index; out[k] sorted ascending by
+ * index, -1 padded (attn_ref.cpp:186-194).  scratch: msb_topk_scratch_bytes(n) bytes, ZERO-FILLED before its first
+ * use; every call leaves it zeroed again. */
+size_t msb_topk_scratch_bytes(int n_max);
+int msb_topk(const float* scores, int n, int k, int* out, void* scratch, size_t scratch_bytes, int hist_ready,
+             void* stream);
+/* Block maxima over bs consecutive scores, the newest block pinned to +inf: the input of the candidate-block top-k
+ * (attn_ref.cpp:196-202).  out[(len + bs - 1) / bs]. */
+int msb_block_max(const float* scores, int len, int bs, float* out, void* stream);
+/* prep + scores + top-k in one call (the sequence of encode_index_decode).  q_prep [heads][128] and w_prep [heads] are
+ * caller-owned work buffers. */
+int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw, const float* w_raw, const float* cs,
+                     int actq, int heads, int k, float* q_prep, float* w_prep, float* scores, int* topk_out,
+                     void* topk_scratch, size_t topk_scratch_bytes, int exact_query, void* stream);
+
+/* ---------------------------------------------------------------- sparse attention (decode)
+ * ms::attn::encode_sparse (src/kernels/attn.hpp:128-129, attn.mm:419-445); math spec tests/ref/attn_ref.cpp:204-230.
+ * q: F32 [heads][D] pre-rope; rows are K == V vectors of D elements (MSB_F16 or MSB_BF16), D = 512 or 576, rope on
+ * the last 64 dims; the attended set is win[0..n_win) followed by cache[topk[i]] for every topk[i] >= 0.
+ * out: F32 [heads][D] after the inverse rope.  scratch: msb_sparse_scratch_bytes(n_win + k, heads, D). */
+size_t msb_sparse_scratch_bytes(int total_rows_max, int heads, int D);
+int msb_sparse_decode(const float* q, const float* cs, const float* sinks, int elem_type, const void* win, int n_win,
+                      const void* cache, const int* topk, int k, int heads, int D, float* out, void* scratch,
+                      size_t scratch_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -14,6 +14,17 @@ int router_topk(const float* logits, const float* bias, int* ids, float* wts, in
                 float route_scale, cudaStream_t st);
 int route_lists(const int* ids, const float* w, int n, int k, int E, unsigned* counts, unsigned* offsets,
                 unsigned* entry, unsigned* tok, float* lw, unsigned* slot_of, cudaStream_t st);
+size_t topk_scratch_bytes(int n_max);
+int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, cudaStream_t st);
+int index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q, float* w,
+               cudaStream_t st);
+int index_scores(int key_type, const void* keys, int len, const float* q, const float* w, int heads, float* scores,
+                 unsigned* hist, int exact_query, cudaStream_t st);
+int block_max(const float* sc, int len, int bs, float* out, cudaStream_t st);
+size_t sparse_scratch_bytes(int total_rows_max, int H, int D);
+int sparse_decode(const float* q, const float* cs, const float* sinks, int elem_type, const void* win, int n_win,
+                  const void* cache, const int* topk, int k, int H, int D, float* out, void* scratch,
+                  size_t scratch_bytes, cudaStream_t st);
 }  // namespace msb
 #include "moe_decode_params.cuh"
 
@@ -119,6 +130,43 @@ int msb_router_topk(const float* logits, const float* bias, int* ids, float* w, 
 int msb_route_lists(const int* ids, const float* w, int n_tokens, int k, int n_experts, uint32_t* counts,
                     uint32_t* offsets, uint32_t* entry, uint32_t* tok, float* lw, uint32_t* slot_of, void* stream) {
   return route_lists(ids, w, n_tokens, k, n_experts, counts, offsets, entry, tok, lw, slot_of, (cudaStream_t)stream);
+}
+
+int msb_index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q, float* w,
+                   void* stream) {
+  return index_prep(q_raw, w_raw, cs, actq, heads, q, w, (cudaStream_t)stream);
+}
+int msb_index_scores(int key_type, const void* keys, int len, const float* q, const float* w, int heads, float* scores,
+                     void* topk_scratch, int exact_query, void* stream) {
+  return index_scores(key_type, keys, len, q, w, heads, scores, (unsigned*)topk_scratch, exact_query, (cudaStream_t)stream);
+}
+size_t msb_topk_scratch_bytes(int n_max) { return topk_scratch_bytes(n_max); }
+int msb_topk(const float* scores, int n, int k, int* out, void* scratch, size_t scratch_bytes, int hist_ready,
+             void* stream) {
+  return topk(scores, n, k, out, scratch, scratch_bytes, hist_ready != 0, (cudaStream_t)stream);
+}
+int msb_block_max(const float* scores, int len, int bs, float* out, void* stream) {
+  return block_max(scores, len, bs, out, (cudaStream_t)stream);
+}
+int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw, const float* w_raw, const float* cs,
+                     int actq, int heads, int k, float* q_prep, float* w_prep, float* scores, int* topk_out,
+                     void* topk_scratch, size_t topk_scratch_bytes_, int exact_query, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = index_prep(q_raw, w_raw, cs, actq, heads, q_prep, w_prep, st);
+  if (rc) return rc;
+  // the fused histogram exists on the direct FP8 path only
+  const bool fused = key_type == MSB_KEY_FP8_E4M3 && !exact_query && len > 0;
+  rc = index_scores(key_type, keys, len, q_prep, w_prep, heads, scores, fused ? (unsigned*)topk_scratch : nullptr,
+                    exact_query, st);
+  if (rc) return rc;
+  return topk(scores, len, k, topk_out, topk_scratch, topk_scratch_bytes_, fused, st);
+}
+size_t msb_sparse_scratch_bytes(int total_rows_max, int heads, int D) { return sparse_scratch_bytes(total_rows_max, heads, D); }
+int msb_sparse_decode(const float* q, const float* cs, const float* sinks, int elem_type, const void* win, int n_win,
+                      const void* cache, const int* topk_list, int k, int heads, int D, float* out, void* scratch,
+                      size_t scratch_bytes, void* stream) {
+  return sparse_decode(q, cs, sinks, elem_type, win, n_win, cache, topk_list, k, heads, D, out, scratch, scratch_bytes,
+                       (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,532 @@
+// Lightning indexer, decode side: query preparation, key scoring on the tensor cores, exact top-k.
+//   score[t] = sum_h relu(q_h . k_t) * w_h   for t < len          (tests/ref/attn_ref.cpp:172-184 is the math spec)
+//   top-k among finite scores, ties -> lower index, output sorted ascending by index, -1 padded (:186-194)
+// Replaces the reference's attn_idx_prep_thread / attn_idx_score_dec2 / attn_topk_compact / attn_topk_final Metal
+// kernels (src/kernels/attn_index.metal:129-145,616-677,703-797) behind ms::attn::encode_index_decode
+// (src/kernels/attn.hpp:121-122, attn.mm:222-290).
+//
+// Scoring is a [len x 128] x [128 x heads] contraction: FP8 (e4m3) keys go straight into mma.sync m16n8k32 with the
+// query held in registers as e4m3 B fragments; F16 keys use m16n8k16 with the fp32 query split into two f16 terms
+// (hi + lo) so that no query precision is lost.  fp32 accumulation throughout; heads are summed in a fixed order.
+// Selection: a 4096-bin histogram of the order-preserving key's top 12 bits (built by the scoring kernel) gives the
+// threshold bin; a grid-wide compaction collects everything above it plus the threshold bin's members; one block
+// finishes exactly (radix select on the remaining key bits, then on the index for ties) and sorts by index.
+#include <cuda_fp8.h>
+#include <algorithm>
+#include "msb_common.cuh"
+
+namespace msb {
+
+constexpr int kIdxDim = 128;
+constexpr int kKeyF16 = 1, kKeyFp8 = 101;
+constexpr int kHistBins = 4096;
+
+__device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ bool selectable(float f) { return f > -INFINITY; }   // finite or +inf; NaN never
+
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct IdxParams {
+  const uint8_t* keys;
+  const float* q;      // [H][128] prepared query
+  const float* w;      // [H] prepared head weights
+  float* scores;       // [len]
+  unsigned* hist;      // [4096] or null
+  int len;
+};
+
+__device__ __forceinline__ void hist_flush(unsigned* sh, unsigned* gh, int tid, int nthreads) {
+  __syncthreads();
+  for (int b = tid; b < kHistBins; b += nthreads) {
+    const unsigned v = sh[b];
+    if (v) atomicAdd(&gh[b], v);
+  }
+}
+
+// ---------------------------------------------------------------- FP8 keys: direct e4m3 MMA, query in registers
+// K permutation: lane (g, t) holds bytes 32t .. 32t+31 of key rows g and g+8; k-step s pairs words (2s, 2s+1) of the
+// row with the same bytes of the query, so the contraction covers every dimension once.
+template <int H>
+__global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p) {
+  constexpr int NT = H / 8;
+  __shared__ unsigned sh_hist[kHistBins];
+  const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (p.hist)
+    for (int b = tid; b < kHistBins; b += blockDim.x) sh_hist[b] = 0;
+  uint32_t B[NT][4][2];
+  float wr[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    const float* qr = p.q + (size_t)(nt * 8 + g) * kIdxDim + 32 * t;
+#pragma unroll
+    for (int s = 0; s < 4; s++)
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+          v |= (uint32_t)__nv_cvt_float_to_fp8(qr[8 * s + 4 * j + i], __NV_SATFINITE, __NV_E4M3) << (8 * i);
+        B[nt][s][j] = v;
+      }
+    wr[nt][0] = p.w[nt * 8 + 2 * t];
+    wr[nt][1] = p.w[nt * 8 + 2 * t + 1];
+  }
+  if (p.hist) __syncthreads();
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int ntiles = (p.len + 15) / 16;
+  for (int tile = blockIdx.x * (blockDim.x >> 5) + (tid >> 5); tile < ntiles; tile += warps) {
+    const int k0 = tile * 16 + g, k1 = k0 + 8;
+    uint4 r0a = make_uint4(0, 0, 0, 0), r0b = r0a, r1a = r0a, r1b = r0a;
+    if (k0 < p.len) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.keys + (size_t)k0 * kIdxDim + 32 * t);
+      r0a = __ldg(src); r0b = __ldg(src + 1);
+    }
+    if (k1 < p.len) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.keys + (size_t)k1 * kIdxDim + 32 * t);
+      r1a = __ldg(src); r1b = __ldg(src + 1);
+    }
+    const uint32_t A0[8] = {r0a.x, r0a.y, r0a.z, r0a.w, r0b.x, r0b.y, r0b.z, r0b.w};
+    const uint32_t A1[8] = {r1a.x, r1a.y, r1a.z, r1a.w, r1b.x, r1b.y, r1b.z, r1b.w};
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < 4; s++) mma_e4m3(c, A0[2 * s], A1[2 * s], A0[2 * s + 1], A1[2 * s + 1], B[nt][s][0], B[nt][s][1]);
+      s0 += fmaxf(c[0], 0.f) * wr[nt][0] + fmaxf(c[1], 0.f) * wr[nt][1];
+      s1 += fmaxf(c[2], 0.f) * wr[nt][0] + fmaxf(c[3], 0.f) * wr[nt][1];
+    }
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    if (t == 0) {
+      if (k0 < p.len) { p.scores[k0] = s0; if (p.hist && selectable(s0)) atomicAdd(&sh_hist[order_key(s0) >> 20], 1u); }
+      if (k1 < p.len) { p.scores[k1] = s1; if (p.hist && selectable(s1)) atomicAdd(&sh_hist[order_key(s1) >> 20], 1u); }
+    }
+  }
+  if (p.hist) hist_flush(sh_hist, p.hist, tid, blockDim.x);
+}
+
+// ---------------------------------------------------------------- F16 keys (or FP8 widened to F16): m16n8k16
+// Query columns: [0, H) = f16(q), and with SPLIT [H, 2H) = f16(q - f16(q)).  The B fragments live in shared memory as
+// Bs[n-tile][k-step][lane] = {b0, b1}; a warp scores 32 keys (two m-tiles) per pass over them.  (No fused histogram
+// here: the selection builds its own.)
+// K permutation: lane (g, t) holds elements 32t .. 32t+31 of its rows; k-step s uses elements 32t+4s .. 32t+4s+3.
+template <int H, bool FP8IN, bool SPLIT>
+__global__ void __launch_bounds__(256, 1) idx_score_f16_kernel(const IdxParams p) {
+  constexpr int NTH = H / 8;                 // n-tiles per term
+  constexpr int NT = SPLIT ? 2 * NTH : NTH;
+  __shared__ uint2 Bs[NT][8][32];
+  const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  for (int i = tid; i < NT * 8 * 32; i += blockDim.x) {
+    const int ln = i & 31, s = (i >> 5) & 7, nt = i >> 8;
+    const int gg = ln >> 2, tt = ln & 3;
+    const bool lo = SPLIT && nt >= NTH;
+    const float* qr = p.q + (size_t)((lo ? nt - NTH : nt) * 8 + gg) * kIdxDim + 32 * tt + 4 * s;
+    __half h[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const __half hi = __float2half_rn(qr[j]);
+      h[j] = lo ? __float2half_rn(qr[j] - __half2float(hi)) : hi;
+    }
+    uint2 v;
+    v.x = (uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
+    v.y = (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+    Bs[nt][s][ln] = v;
+  }
+  float wr[NTH][2];
+#pragma unroll
+  for (int nt = 0; nt < NTH; nt++) { wr[nt][0] = p.w[nt * 8 + 2 * t]; wr[nt][1] = p.w[nt * 8 + 2 * t + 1]; }
+  __syncthreads();
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int ntiles = (p.len + 31) / 32;
+  for (int tile = blockIdx.x * (blockDim.x >> 5) + (tid >> 5); tile < ntiles; tile += warps) {
+    uint32_t A[4][16];   // rows g, g+8, g+16, g+24 of the tile; 16 half2 each
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      const int k = tile * 32 + g + 8 * r;
+      if (k < p.len) {
+        if (FP8IN) {
+          const uint4* src = reinterpret_cast<const uint4*>(p.keys + (size_t)k * kIdxDim + 32 * t);
+          const uint4 a = __ldg(src), b = __ldg(src + 1);
+          const uint32_t wds[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const __half2_raw lo2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wds[i] & 0xFFFFu), __NV_E4M3);
+            const __half2_raw hi2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wds[i] >> 16), __NV_E4M3);
+            A[r][2 * i] = (uint32_t)lo2.x | ((uint32_t)lo2.y << 16);
+            A[r][2 * i + 1] = (uint32_t)hi2.x | ((uint32_t)hi2.y << 16);
+          }
+        } else {
+          const uint4* src = reinterpret_cast<const uint4*>(p.keys + ((size_t)k * kIdxDim + 32 * t) * 2);
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint4 a = __ldg(src + i);
+            A[r][4 * i] = a.x; A[r][4 * i + 1] = a.y; A[r][4 * i + 2] = a.z; A[r][4 * i + 3] = a.w;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) A[r][i] = 0;
+      }
+    }
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < NTH; nt++) {
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < 8; s++) {
+        const uint2 b = Bs[nt][s][lane];
+        mma_f16(c0, A[0][2 * s], A[1][2 * s], A[0][2 * s + 1], A[1][2 * s + 1], b.x, b.y);
+        mma_f16(c1, A[2][2 * s], A[3][2 * s], A[2][2 * s + 1], A[3][2 * s + 1], b.x, b.y);
+        if (SPLIT) {
+          const uint2 bl = Bs[nt + NTH][s][lane];
+          mma_f16(c0, A[0][2 * s], A[1][2 * s], A[0][2 * s + 1], A[1][2 * s + 1], bl.x, bl.y);
+          mma_f16(c1, A[2][2 * s], A[3][2 * s], A[2][2 * s + 1], A[3][2 * s + 1], bl.x, bl.y);
+        }
+      }
+      sc[0] += fmaxf(c0[0], 0.f) * wr[nt][0] + fmaxf(c0[1], 0.f) * wr[nt][1];
+      sc[1] += fmaxf(c0[2], 0.f) * wr[nt][0] + fmaxf(c0[3], 0.f) * wr[nt][1];
+      sc[2] += fmaxf(c1[0], 0.f) * wr[nt][0] + fmaxf(c1[1], 0.f) * wr[nt][1];
+      sc[3] += fmaxf(c1[2], 0.f) * wr[nt][0] + fmaxf(c1[3], 0.f) * wr[nt][1];
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      sc[r] += __shfl_xor_sync(0xffffffffu, sc[r], 1);
+      sc[r] += __shfl_xor_sync(0xffffffffu, sc[r], 2);
+      const int k = tile * 32 + g + 8 * r;
+      if (t == 0 && k < p.len) p.scores[k] = sc[r];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- query preparation (attn_ref.cpp:163-170)
+// rope on the last 64 dims of each head (interleaved pairs), optional fp4 (e2m1, power-of-two block-32 scale)
+// quant-dequant simulation, head weights scaled by dim^-0.5 * heads^-0.5.  One warp per head.
+__device__ __forceinline__ float pow2i(int e) { return __uint_as_float((uint32_t)(e + 127) << 23); }
+__device__ __forceinline__ float round_e2m1(float x) {
+  const float a = fabsf(x);
+  int e = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;
+  e = max(e, 0);
+  return copysignf(nearbyintf(a * pow2i(1 - e)) * pow2i(e - 1), x);
+}
+__global__ void idx_prep_kernel(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q,
+                                float* w) {
+  const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= heads) return;
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) v[i] = q_raw[(size_t)h * kIdxDim + 32 * i + lane];
+  // dims 64..127 are roped: pair (64 + 2j, 64 + 2j + 1) with (cos, sin) j.  Lane holds dims 64+lane and 96+lane.
+  {
+    const float o2 = __shfl_xor_sync(0xffffffffu, v[2], 1), o3 = __shfl_xor_sync(0xffffffffu, v[3], 1);
+    const int j2 = lane >> 1, j3 = 16 + (lane >> 1);
+    const float c2 = cs[2 * j2], s2 = cs[2 * j2 + 1], c3 = cs[2 * j3], s3 = cs[2 * j3 + 1];
+    // even element: a*c - b*s ; odd element: a*s + b*c  with (a, b) = (even, odd)
+    v[2] = (lane & 1) ? __fadd_rn(__fmul_rn(o2, s2), __fmul_rn(v[2], c2)) : __fsub_rn(__fmul_rn(v[2], c2), __fmul_rn(o2, s2));
+    v[3] = (lane & 1) ? __fadd_rn(__fmul_rn(o3, s3), __fmul_rn(v[3], c3)) : __fsub_rn(__fmul_rn(v[3], c3), __fmul_rn(o3, s3));
+  }
+  if (actq) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {   // block i = dims 32i .. 32i+31 = one value per lane
+      float amax = fabsf(v[i]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      amax = fmaxf(amax, 6.0f * 1.17549435e-38f);
+      const float r = __fmul_rn(amax, 1.0f / 6.0f);
+      const uint32_t rb = __float_as_uint(r);
+      const int e = (int)((rb >> 23) & 0xFF) - 127 + ((rb & 0x7FFFFF) ? 1 : 0);
+      const float s = pow2i(e), inv = pow2i(-e);
+      v[i] = __fmul_rn(round_e2m1(fminf(fmaxf(__fmul_rn(v[i], inv), -6.0f), 6.0f)), s);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) q[(size_t)h * kIdxDim + 32 * i + lane] = v[i];
+  if (lane == 0) w[h] = w_raw[h] * (float)(pow((double)kIdxDim, -0.5) * pow((double)heads, -0.5));
+}
+
+// ---------------------------------------------------------------- exact top-k
+struct TopkCtl { unsigned n_sel, n_cand, pad0, pad1; };
+
+__global__ void topk_hist_kernel(const float* sc, int n, unsigned* hist) {
+  __shared__ unsigned sh[kHistBins];
+  for (int b = threadIdx.x; b < kHistBins; b += blockDim.x) sh[b] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const float f = sc[i];
+    if (selectable(f)) atomicAdd(&sh[order_key(f) >> 20], 1u);
+  }
+  hist_flush(sh, hist, threadIdx.x, blockDim.x);
+}
+
+// threshold bin: the highest bin b with (count of bins > b) < k <= (count of bins >= b); -1 when fewer than k finite
+// scores exist (everything is selected).  Computed by every block of the compaction and by the final block.
+__device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024] */, unsigned* above_out) {
+  const int tid = threadIdx.x;   // blockDim.x == 1024 or 256; each thread owns a contiguous run of bins from the top
+  const int per = kHistBins / blockDim.x;
+  unsigned mine = 0;
+  for (int j = 0; j < per; j++) mine += hist[kHistBins - 1 - (tid * per + j)];
+  sh[tid] = mine;
+  __syncthreads();
+  for (int o = 1; o < (int)blockDim.x; o <<= 1) {   // inclusive scan over threads (descending bins)
+    const unsigned a = tid >= o ? sh[tid - o] : 0;
+    __syncthreads();
+    sh[tid] += a;
+    __syncthreads();
+  }
+  __shared__ int res_bin;
+  __shared__ unsigned res_above;
+  if (tid == 0) { res_bin = -1; res_above = sh[blockDim.x - 1]; }
+  __syncthreads();
+  const unsigned incl = sh[tid], excl = incl - mine;
+  if (excl < (unsigned)k && incl >= (unsigned)k) {   // the threshold lies in this thread's run
+    unsigned run = excl;
+    for (int j = 0; j < per; j++) {
+      const int b = kHistBins - 1 - (tid * per + j);
+      const unsigned c = hist[b];
+      if (run + c >= (unsigned)k) { res_bin = b; res_above = run; break; }
+      run += c;
+    }
+  }
+  __syncthreads();
+  *above_out = res_above;
+  return res_bin;
+}
+
+__global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int n, int k, const unsigned* hist, TopkCtl* ctl,
+                                                           int* sel, int* cand) {
+  __shared__ unsigned sh[1024];
+  __shared__ unsigned base_sel, base_cand, cnt_sel, cnt_cand;
+  unsigned above;
+  const int bstar = threshold_bin(hist, k, sh, &above);
+  const int per_block = (n + gridDim.x - 1) / gridDim.x;
+  const int i0 = blockIdx.x * per_block, i1 = min(n, i0 + per_block);
+  for (int base = i0; base < i1; base += blockDim.x) {
+    if (threadIdx.x == 0) { cnt_sel = 0; cnt_cand = 0; }
+    __syncthreads();
+    const int i = base + threadIdx.x;
+    int kind = 0;   // 1 = selected outright, 2 = threshold-bin candidate
+    unsigned slot = 0;
+    if (i < i1) {
+      const float f = sc[i];
+      if (selectable(f)) {
+        const int b = (int)(order_key(f) >> 20);
+        kind = b > bstar ? 1 : (b == bstar ? 2 : 0);
+      }
+    }
+    if (kind == 1) slot = atomicAdd(&cnt_sel, 1u);
+    if (kind == 2) slot = atomicAdd(&cnt_cand, 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      base_sel = cnt_sel ? atomicAdd(&ctl->n_sel, cnt_sel) : 0;
+      base_cand = cnt_cand ? atomicAdd(&ctl->n_cand, cnt_cand) : 0;
+    }
+    __syncthreads();
+    if (kind == 1) sel[base_sel + slot] = i;
+    if (kind == 2) cand[base_cand + slot] = i;
+    __syncthreads();
+  }
+}
+
+// One block of 1024 threads.  out[k] ascending, -1 padded.  Resets hist and ctl for the next call.
+__global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, TopkCtl* ctl,
+                                                          const int* sel, const int* cand, int* out) {
+  __shared__ unsigned sh[1024];
+  __shared__ int buf[2048];
+  __shared__ unsigned s_cnt, s_prefix, s_need, s_digit;
+  const int tid = threadIdx.x;
+  unsigned above;
+  const int bstar = threshold_bin(hist, k, sh, &above);
+  const unsigned n_sel = ctl->n_sel, n_cand = ctl->n_cand;
+  for (int i = tid; i < 2048; i += 1024) buf[i] = 0x7fffffff;
+  __syncthreads();
+  for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) buf[i] = sel[i];
+  unsigned filled = min(n_sel, 2048u);
+  if (bstar >= 0 && n_cand > 0) {
+    const unsigned need = (unsigned)k - above;   // how many of the threshold bin's members are taken
+    // radix select (descending) on the low 20 bits of the key: find T = the need-th largest key among candidates
+    unsigned prefix = 0, mask = 0, remaining = need;
+    for (int shift = 12; shift >= -4; shift -= 8) {
+      const int sft = shift < 0 ? 0 : shift;
+      const unsigned dmask = shift < 0 ? 0xFu : 0xFFu;
+      for (int b = tid; b < 256; b += 1024) sh[b] = 0;
+      __syncthreads();
+      for (unsigned i = tid; i < n_cand; i += 1024) {
+        const unsigned key = order_key(sc[cand[i]]) & 0xFFFFFu;
+        if ((key & mask) == prefix) atomicAdd(&sh[(key >> sft) & dmask], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned run = 0;
+        int d = (int)dmask;
+        for (; d > 0; d--) {
+          if (run + sh[d] >= remaining) break;
+          run += sh[d];
+        }
+        s_digit = (unsigned)d; s_need = remaining - run;
+      }
+      __syncthreads();
+      prefix |= s_digit << sft;
+      mask |= dmask << sft;
+      remaining = s_need;
+      __syncthreads();
+    }
+    const unsigned T = prefix;         // exact threshold key (low 20 bits); `remaining` members equal to T are taken
+    // ties at T: take the `remaining` lowest indices.  Radix select (ascending) on the index, 3 x 8 bits (n <= 2^24).
+    unsigned ip = 0, im = 0, irem = remaining;
+    for (int shift = 16; shift >= 0; shift -= 8) {
+      for (int b = tid; b < 256; b += 1024) sh[b] = 0;
+      __syncthreads();
+      for (unsigned i = tid; i < n_cand; i += 1024) {
+        const unsigned idx = (unsigned)cand[i];
+        if ((order_key(sc[idx]) & 0xFFFFFu) == T && (idx & im) == ip) atomicAdd(&sh[(idx >> shift) & 0xFFu], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned run = 0;
+        int d = 0;
+        for (; d < 255; d++) {
+          if (run + sh[d] >= irem) break;
+          run += sh[d];
+        }
+        s_digit = (unsigned)d; s_need = irem - run;
+      }
+      __syncthreads();
+      ip |= s_digit << shift;
+      im |= 0xFFu << shift;
+      irem = s_need;
+      __syncthreads();
+    }
+    const unsigned idxT = ip;          // members equal to T with index <= idxT are taken
+    if (tid == 0) s_cnt = filled;
+    __syncthreads();
+    for (unsigned i = tid; i < n_cand; i += 1024) {
+      const unsigned idx = (unsigned)cand[i];
+      const unsigned key = order_key(sc[idx]) & 0xFFFFFu;
+      if (key > T || (key == T && idx <= idxT)) {
+        const unsigned pos = atomicAdd(&s_cnt, 1u);
+        if (pos < 2048u) buf[pos] = (int)idx;
+      }
+    }
+    __syncthreads();
+    filled = min(s_cnt, 2048u);
+  }
+  __syncthreads();
+  // bitonic sort of 2048 slots ascending (unused slots hold INT_MAX)
+  for (int size = 2; size <= 2048; size <<= 1)
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < 1024; i += 1024) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = ((lo & size) == 0);
+        const int a = buf[lo], b = buf[hi];
+        if ((a > b) == up) { buf[lo] = b; buf[hi] = a; }
+      }
+      __syncthreads();
+    }
+  for (int i = tid; i < k; i += 1024) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
+  for (int b = tid; b < kHistBins; b += 1024) hist[b] = 0;
+  if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; }
+  (void)s_prefix; (void)n;
+}
+
+// block maxima over `bs` consecutive scores; the newest (possibly partial) block is pinned to +inf
+// (attn_ref.cpp:196-202)
+__global__ void block_max_kernel(const float* sc, int len, int bs, float* out, int nb) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nb) return;
+  float m = -INFINITY;
+  for (int i = b * bs; i < min(len, (b + 1) * bs); i++) m = fmaxf(m, sc[i]);
+  if (b == (len - 1) / bs) m = INFINITY;
+  out[b] = m;
+}
+
+// ---------------------------------------------------------------- host side
+size_t topk_scratch_bytes(int n_max) {
+  return sizeof(unsigned) * kHistBins + 64 + sizeof(int) * 2048 + sizeof(int) * (size_t)std::max(n_max, 1);
+}
+
+// scratch layout: hist[4096] | ctl (64 B) | sel[2048] | cand[n_max].  hist and ctl must be zero on entry; the final
+// kernel leaves them zero again.
+int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, cudaStream_t st) {
+  if (n < 0 || k <= 0 || k > 2048) return fail(kErrArg, "topk: n %d k %d (k must be 1..2048)", n, k);
+  if (!out || !scratch || (n > 0 && !sc)) return fail(kErrArg, "topk: null pointer");
+  if (scratch_bytes < topk_scratch_bytes(n)) return fail(kErrScratch, "topk: scratch too small");
+  unsigned* hist = reinterpret_cast<unsigned*>(scratch);
+  TopkCtl* ctl = reinterpret_cast<TopkCtl*>(hist + kHistBins);
+  int* sel = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ctl) + 64);
+  int* cand = sel + 2048;
+  int dev = 0, sms = 0;
+  MSB_CUDA(cudaGetDevice(&dev));
+  MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (n > 0) {
+    const int blocks = std::max(1, std::min(sms * 2, (n + 1023) / 1024));
+    if (!hist_ready) topk_hist_kernel<<<blocks, 256, 0, st>>>(sc, n, hist);
+    topk_compact_kernel<<<blocks, 256, 0, st>>>(sc, n, k, hist, ctl, sel, cand);
+  }
+  topk_final_kernel<<<1, 1024, 0, st>>>(sc, n, k, hist, ctl, sel, cand, out);
+  MSB_LAUNCH_CHECK("topk");
+  return kOk;
+}
+
+int index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q, float* w,
+               cudaStream_t st) {
+  if (heads <= 0 || !q_raw || !w_raw || !cs || !q || !w) return fail(kErrArg, "index_prep: bad arguments");
+  idx_prep_kernel<<<(heads + 3) / 4, 128, 0, st>>>(q_raw, w_raw, cs, actq, heads, q, w);
+  MSB_LAUNCH_CHECK("idx_prep_kernel");
+  return kOk;
+}
+
+int index_scores(int key_type, const void* keys, int len, const float* q, const float* w, int heads, float* scores,
+                 unsigned* hist, int exact_query, cudaStream_t st) {
+  if (len < 0 || (heads != 32 && heads != 64)) return fail(kErrArg, "index_scores: heads must be 32 or 64 (got %d)", heads);
+  if (key_type != kKeyF16 && key_type != kKeyFp8) return fail(kErrType, "index_scores: key type %d", key_type);
+  if (len == 0) return kOk;
+  if (!keys || !q || !w || !scores || (reinterpret_cast<uintptr_t>(keys) & 15))
+    return fail(kErrArg, "index_scores: null or misaligned pointer");
+  int dev = 0, sms = 0;
+  MSB_CUDA(cudaGetDevice(&dev));
+  MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len};
+  if (key_type == kKeyFp8 && !exact_query) {
+    const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));
+    if (heads == 64) idx_score_fp8_kernel<64><<<grid, 384, 0, st>>>(p);
+    else idx_score_fp8_kernel<32><<<grid, 384, 0, st>>>(p);
+  } else {
+    const int grid = std::max(1, std::min(sms, (len + 32 * 8 - 1) / (32 * 8)));
+    if (key_type == kKeyFp8) {
+      if (heads == 64) idx_score_f16_kernel<64, true, true><<<grid, 256, 0, st>>>(p);
+      else idx_score_f16_kernel<32, true, true><<<grid, 256, 0, st>>>(p);
+    } else {
+      if (heads == 64) idx_score_f16_kernel<64, false, true><<<grid, 256, 0, st>>>(p);
+      else idx_score_f16_kernel<32, false, true><<<grid, 256, 0, st>>>(p);
+    }
+  }
+  MSB_LAUNCH_CHECK("idx_score_kernel");
+  return kOk;
+}
+
+int block_max(const float* sc, int len, int bs, float* out, cudaStream_t st) {
+  if (len <= 0 || bs <= 0 || !sc || !out) return fail(kErrArg, "block_max: bad arguments");
+  const int nb = (len + bs - 1) / bs;
+  block_max_kernel<<<(nb + 255) / 256, 256, 0, st>>>(sc, len, bs, out, nb);
+  MSB_LAUNCH_CHECK("block_max_kernel");
+  return kOk;
+}
+
+}  // namespace msb

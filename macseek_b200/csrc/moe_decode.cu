@@ -421,7 +421,8 @@ size_t moe_decode_scratch_bytes(int inter, int max_routed) {
   return sizeof(float) * (size_t)(max_routed + 1) * inter;
 }
 
-// part: 0 All, 1 SharedGu, 2 AfterSharedGu, 3 Shared, 4 Routed, 5 SharedDown (the reference's MoePart, quant.hpp:83)
+// part: 0 All, 1 SharedGu, 2 AfterSharedGu, 3 Shared, 4 Routed, 5 SharedDown (the reference's MoePart, quant.hpp:83);
+// 6 = gate/up of every expert only, 7 = down of every expert only (the two launches of All, for timing one alone)
 int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, size_t scratch_bytes, cudaStream_t st) {
   if (p.n_routed < 0 || p.n_routed > kMaxRouted) return fail(kErrArg, "moe_decode: n_routed %d outside 0..%d", p.n_routed, kMaxRouted);
   if (!routed_type_ok(t_gate_up) || !routed_type_ok(t_down) || !shared_type_ok(t_shared))
@@ -429,13 +430,13 @@ int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, s
                 type_name(t_shared));
   if (p.dim <= 0 || p.inter <= 0 || p.dim % 256 || p.inter % 256) return fail(kErrArg, "moe_decode: dim/inter must be multiples of 256");
   if (scratch_bytes < moe_decode_scratch_bytes(p.inter, p.n_routed)) return fail(kErrScratch, "moe_decode: scratch too small");
-  if (part < 0 || part > 5) return fail(kErrArg, "moe_decode: bad part %d", part);
+  if (part < 0 || part > 7) return fail(kErrArg, "moe_decode: bad part %d", part);
   const bool shared_piece = part == 1 || part == 3 || part == 5;
   if (shared_piece && !p.has_shared) return kOk;
-  p.gu_r = part == 0 || part == 2 || part == 4;
-  p.gu_s = p.has_shared && (part == 0 || part == 1 || part == 3);
-  p.d_r = p.gu_r;
-  p.d_s = p.has_shared && (part == 0 || part == 2 || part == 3 || part == 5);
+  p.gu_r = part == 0 || part == 2 || part == 4 || part == 6;
+  p.gu_s = p.has_shared && (part == 0 || part == 1 || part == 3 || part == 6);
+  p.d_r = part == 0 || part == 2 || part == 4 || part == 7;
+  p.d_s = p.has_shared && (part == 0 || part == 2 || part == 3 || part == 5 || part == 7);
   if (p.n_routed == 0) p.gu_r = p.d_r = 0;
   if (!p.gu_r && !p.gu_s && !p.d_r && !p.d_s) return kOk;
   if (!p.x || !p.y || !p.h || (p.gu_r && !p.weights)) return fail(kErrArg, "moe_decode: null pointer");

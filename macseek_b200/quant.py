@@ -72,6 +72,8 @@ class MoePart(enum.IntEnum):
     Shared = 3
     Routed = 4
     SharedDown = 5
+    GuAll = 6       # not in the reference: the gate/up launch of All alone
+    DownAll = 7     # the down launch of All alone
 
 
 class MoeDecodeArgs:
