@@ -146,6 +146,22 @@ int msb_sparse_decode(const float* q, const float* cs, const float* sinks, int e
                       const void* cache, const int* topk, int k, int heads, int D, float* out, void* scratch,
                       size_t scratch_bytes, void* stream);
 
+/* ---------------------------------------------------------------- small per-token kernels between the hot-path calls
+ * y = x * rsqrt(mean(x^2) + eps) * w per row (w may be NULL); strides in floats, 0 = dim -- ms::arch::encode_rmsnorm
+ * (src/kernels/arch.hpp:128-130). */
+int msb_rmsnorm(const float* x, const float* w, float* y, int rows, int dim, float eps, int in_stride, int out_stride,
+                void* stream);
+/* Window KV row of one token: rmsnorm(kv) * norm_w -> rope on the last 64 dims -> optional fp8 quant-dequant
+ * simulation -> stored as D elements of elem_type (MSB_F16 / MSB_BF16) at out_row -- the n == 1 path of
+ * ms::attn::encode_kv_window (src/kernels/attn.hpp:113, attn.mm:186-193; math tests/ref/attn_ref.cpp:109-114). */
+int msb_kv_window(const float* kv, const float* norm_w, const float* cs, int actq, int D, int elem_type, void* out_row,
+                  void* stream);
+/* Greedy argmax, ties -> lowest index -- the temperature 0 case of ms::arch::encode_argmax (arch.hpp:107-112).
+ * out_val may be NULL. */
+int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream);
+/* y[i] += a[i] */
+int msb_add(float* y, const float* a, int n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

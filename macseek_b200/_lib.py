@@ -74,3 +74,8 @@ lib.msb_index_decode.argtypes = [_i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _v
 lib.msb_sparse_scratch_bytes.restype = C.c_size_t
 lib.msb_sparse_scratch_bytes.argtypes = [_i, _i, _i]
 lib.msb_sparse_decode.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, C.c_size_t, _vp]
+
+lib.msb_rmsnorm.argtypes = [_vp, _vp, _vp, _i, _i, _f, _i, _i, _vp]
+lib.msb_kv_window.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]
+lib.msb_argmax.argtypes = [_vp, _i, _vp, _vp, _vp]
+lib.msb_add.argtypes = [_vp, _vp, _i, _vp]

@@ -61,3 +61,19 @@ def encode_route_lists(e: Enc, ids, w, n, L: RouteLists):
         raise _lib.MsbError("route_lists: %d tokens > capacity %d" % (n, L.max_tokens))
     _lib.check(_lib.lib.msb_route_lists(ptr(ids), ptr(w), n, L.k, L.n_experts, ptr(L.counts), ptr(L.offsets),
                                         ptr(L.entry), ptr(L.tok), ptr(L.w), ptr(L.slot_of), e.handle))
+
+
+def encode_rmsnorm(e: Enc, x, w, y, rows, dim, eps, in_stride=0, out_stride=0):
+    """y = x * rsqrt(mean(x^2) + eps) * w (arch.hpp:128-130)."""
+    _lib.check(_lib.lib.msb_rmsnorm(ptr(x), ptr(w), ptr(y), rows, dim, eps, in_stride, out_stride, e.handle))
+
+
+def encode_argmax(e: Enc, logits, rows, V, out_idx, out_val=None):
+    """Greedy argmax per row, ties -> lowest index (arch.hpp:107-112, temperature 0)."""
+    for r in range(rows):
+        _lib.check(_lib.lib.msb_argmax(ptr(logits, r * V * 4), V, ptr(out_idx, r * 4),
+                                       ptr(out_val, r * 4) if out_val is not None else None, e.handle))
+
+
+def encode_add(e: Enc, y, a, n):
+    _lib.check(_lib.lib.msb_add(ptr(y), ptr(a), n, e.handle))

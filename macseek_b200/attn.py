@@ -113,3 +113,11 @@ def encode_sparse(e: Enc, s: DecodeState, q, sinks, out, pos, n_win=None):
     _lib.check(_lib.lib.msb_sparse_decode(ptr(q), ptr(s.rope[pos]), ptr(sinks), sh.elem_type, ptr(s.win), n_win,
                                           ptr(s.ckv), ptr(s.topk), sh.topk, sh.heads, sh.D, ptr(out),
                                           ptr(s.sparse_scratch), s.sparse_scratch.numel() * 4, e.handle))
+
+
+def encode_kv_window(e: Enc, s: DecodeState, kv, norm_w, pos, actq=False):
+    """Window KV row of the token at pos into the ring slot pos % window (attn.hpp:113, n == 1)."""
+    sh = s.shape
+    slot = pos % sh.window
+    _lib.check(_lib.lib.msb_kv_window(ptr(kv), ptr(norm_w), ptr(s.rope[pos]), int(actq), sh.D, sh.elem_type,
+                                      ptr(s.win[slot]), e.handle))

@@ -25,6 +25,12 @@ size_t sparse_scratch_bytes(int total_rows_max, int H, int D);
 int sparse_decode(const float* q, const float* cs, const float* sinks, int elem_type, const void* win, int n_win,
                   const void* cache, const int* topk, int k, int H, int D, float* out, void* scratch,
                   size_t scratch_bytes, cudaStream_t st);
+int rmsnorm(const float* x, const float* w, float* y, int rows, int dim, float eps, int in_stride, int out_stride,
+            cudaStream_t st);
+int kv_window(const float* kv, const float* norm_w, const float* cs, int actq, int D, int elem_type, void* out_row,
+              cudaStream_t st);
+int argmax(const float* x, int n, int* out_idx, float* out_val, cudaStream_t st);
+int vec_add(float* y, const float* a, int n, cudaStream_t st);
 }  // namespace msb
 #include "moe_decode_params.cuh"
 
@@ -168,5 +174,18 @@ int msb_sparse_decode(const float* q, const float* cs, const float* sinks, int e
   return sparse_decode(q, cs, sinks, elem_type, win, n_win, cache, topk_list, k, heads, D, out, scratch, scratch_bytes,
                        (cudaStream_t)stream);
 }
+
+int msb_rmsnorm(const float* x, const float* w, float* y, int rows, int dim, float eps, int in_stride, int out_stride,
+                void* stream) {
+  return rmsnorm(x, w, y, rows, dim, eps, in_stride, out_stride, (cudaStream_t)stream);
+}
+int msb_kv_window(const float* kv, const float* norm_w, const float* cs, int actq, int D, int elem_type, void* out_row,
+                  void* stream) {
+  return kv_window(kv, norm_w, cs, actq, D, elem_type, out_row, (cudaStream_t)stream);
+}
+int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream) {
+  return argmax(x, n, out_idx, out_val, (cudaStream_t)stream);
+}
+int msb_add(float* y, const float* a, int n, void* stream) { return vec_add(y, a, n, (cudaStream_t)stream); }
 
 }  // extern "C"

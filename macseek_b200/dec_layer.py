@@ -1,0 +1,213 @@
+"""Decode layer-forward call surface on synthetic weights: the order of hot-path calls that the reference's
+ds41::encode_dec_attn_side / encode_dec_moe_table / encode_head issue per token (src/model/dec_layer.hpp:107-118,
+dec_layer.mm:138-313, ds41.mm:491-503), re-expressed over CUDA streams and HBM-resident expert-parallel experts.
+
+Per layer:  rmsnorm -> q_a, kv, index-proj matvecs -> rmsnorm(q_a) -> q_b, index-q_b matvecs -> window KV row ->
+            indexer scores + exact top-k -> sparse attention -> o_a (block-diagonal) -> o_b (accumulated into h) ->
+            rmsnorm -> fused router -> MoE gate/up + down on the experts resident here (-> all-reduce under EP).
+What the reference does between these calls and is not on the measured path here (hyper-connection mixing, the
+compressor that produces new cache rows, engram) is left out; plain residual adds stand in for the hyper-connections.
+"""
+import numpy as np
+import torch
+
+from . import arch, attn, moe_layer as ml, quant as q, synthetic
+from .core import Enc
+
+
+class DecConfig:
+    """Shapes of the synthetic decode step (benchmark configuration: hidden 4096, 43 layers, 64 heads, KV rows of
+    512 + 64 rope dims in bf16, 64 x 128 FP8 index heads with top-k 2048 over a 200K KV, 384 experts top-8 + 1 shared,
+    expert inter 2048, vocab 129280 with a Q6_K head).  Projection shapes follow the reference's structure
+    (tests/dec_synth.hpp:113-132) scaled to this hidden size."""
+
+    def __init__(self, **kw):
+        self.dim = 4096
+        self.n_layers = 43
+        self.heads = 64
+        self.D = 576
+        self.q_lora = 1280
+        self.o_groups = 8
+        self.o_a_rows = 8192
+        self.window = 128
+        self.index_heads = 64
+        self.index_dim = 128
+        self.topk = 2048
+        self.kv_len = 200000
+        self.n_experts = 384
+        self.top_k = 8
+        self.inter = 2048
+        self.vocab = 129280
+        self.score_fn = arch.SCORE_SIGMOID
+        self.route_scale = 1.0
+        self.t_attn = q.QType.Q6_K
+        self.t_index = q.QType.BF16
+        self.t_gate_up = q.QType.IQ1_S
+        self.t_down = q.QType.IQ2_XXS
+        self.t_shared = q.QType.Q8_0
+        self.t_head = q.QType.Q6_K
+        self.key_type = attn.KEY_FP8
+        self.elem_type = attn.ELEM_BF16
+        self.norm_eps = 1e-6
+        for k, v in kw.items():
+            if not hasattr(self, k):
+                raise AttributeError(k)
+            setattr(self, k, v)
+
+    def attn_shape(self):
+        return attn.Shape(D=self.D, heads=self.heads, window=self.window, index_heads=self.index_heads, topk=self.topk,
+                          key_type=self.key_type, elem_type=self.elem_type)
+
+    # ---- byte model: what one token must read, per layer and for the head
+    def layer_bytes(self, local_expert_fraction=1.0):
+        rb = synthetic.row_bytes
+        hD = self.heads * self.D
+        attn_w = (rb(self.t_attn, self.dim) * (self.q_lora + self.D) + rb(self.t_attn, self.q_lora) * hD
+                  + rb(self.t_attn, hD // self.o_groups) * self.o_a_rows + rb(self.t_attn, self.o_a_rows) * self.dim)
+        idx_w = rb(self.t_index, self.dim) * self.index_heads + rb(self.t_index, self.q_lora) * self.index_heads * self.index_dim
+        keys = self.kv_len * self.index_dim * (1 if self.key_type == attn.KEY_FP8 else 2)
+        rows = (self.window + self.topk) * self.D * 2
+        expert = 2 * rb(self.t_gate_up, self.dim) * self.inter + rb(self.t_down, self.inter) * self.dim
+        shared = 2 * rb(self.t_shared, self.dim) * self.inter + rb(self.t_shared, self.inter) * self.dim
+        router = self.n_experts * self.dim * 4
+        moe = int(self.top_k * expert * local_expert_fraction) + shared + router
+        return {"attn_weights": attn_w, "index_weights": idx_w, "index_keys": keys, "kv_rows": rows, "moe": moe,
+                "total": attn_w + idx_w + keys + rows + moe}
+
+    def head_bytes(self):
+        return synthetic.row_bytes(self.t_head, self.dim) * self.vocab
+
+
+class LayerW:
+    """Weights of one layer (the reference's ds41::LayerW, dec_layer.hpp:18-50), all device tensors."""
+
+    def __init__(self, cfg: DecConfig, gen, ep_lo, ep_hi, moe_gen):
+        dev = gen.device
+        c = cfg
+        rw = lambda t, rows, cols: synthetic.random_weights(t, rows, cols, gen)
+        ones = lambda n: torch.ones(n, dtype=torch.float32, device=dev)
+        self.attn_norm, self.q_norm, self.kv_norm, self.ffn_norm = ones(c.dim), ones(c.q_lora), ones(c.D), ones(c.dim)
+        self.wq_a = rw(c.t_attn, c.q_lora, c.dim)
+        self.wkv = rw(c.t_attn, c.D, c.dim)
+        self.wq_b = rw(c.t_attn, c.heads * c.D, c.q_lora)
+        self.w_idx_proj = rw(c.t_index, c.index_heads, c.dim)
+        self.w_idx_qb = rw(c.t_index, c.index_heads * c.index_dim, c.q_lora)
+        self.wo_a = rw(c.t_attn, c.o_a_rows, c.heads * c.D // c.o_groups)
+        self.wo_b = rw(c.t_attn, c.dim, c.o_a_rows)
+        self.sinks = torch.zeros(c.heads, dtype=torch.float32, device=dev).normal_(0, 1, generator=gen)
+        self.moe = ml.MoeLayerWeights(c.dim, c.inter, c.n_experts, c.t_gate_up, c.t_down, c.t_shared, ep_lo, ep_hi, dev)
+        self.moe.randomize(moe_gen, router_gen=gen)
+
+
+class DecBufs:
+    """Activations of one token (the reference's ds41::DecBufs); everything F32 (SPEC.md:155)."""
+
+    def __init__(self, cfg: DecConfig, device):
+        f = lambda n: torch.zeros(n, dtype=torch.float32, device=device)
+        c = cfg
+        self.h, self.x = f(c.dim), f(c.dim)
+        self.qa, self.qan, self.kv = f(c.q_lora), f(c.q_lora), f(c.D)
+        self.qfull, self.attn_out = f(c.heads * c.D), f(c.heads * c.D)
+        self.iq, self.iw = f(c.index_heads * c.index_dim), f(c.index_heads)
+        self.oa = f(c.o_a_rows)
+        self.y_part = f(c.dim)
+        self.logits = f(c.vocab)
+        self.next_id = torch.zeros(1, dtype=torch.int32, device=device)
+        self.moe = ml.MoeLayerBufs(c.dim, c.inter, c.n_experts, c.top_k, device)
+
+
+class SyntheticModel:
+    """All layers resident in HBM: attention/dense weights replicated, experts [ep_rank * E / ep_world, ...) local."""
+
+    def __init__(self, cfg: DecConfig, seed=1234, device="cuda", ep_rank=0, ep_world=1, group=None):
+        self.cfg, self.device, self.ep_rank, self.ep_world, self.group = cfg, device, ep_rank, ep_world, group
+        c = cfg
+        per = c.n_experts // ep_world
+        self.ep_lo, self.ep_hi = ep_rank * per, (ep_rank + 1) * per
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed)                      # replicated tensors: the same stream on every rank
+        moe_gen = torch.Generator(device=device)
+        moe_gen.manual_seed(seed * 1000 + 17 + ep_rank)
+        rope = attn.make_rope_table(c.kv_len + 1, True)
+        self.rope = torch.from_numpy(rope).to(device)
+        self.layers, self.state = [], []
+        sh = c.attn_shape()
+        for _ in range(c.n_layers):
+            self.layers.append(LayerW(c, gen, self.ep_lo, self.ep_hi, moe_gen))
+            st = attn.DecodeState(sh, c.kv_len, self.rope, device)
+            # synthetic caches ~ N(0,1), as the reference fills them for its 200K benches (bench/attn200k.mm:60-66)
+            st.ckv.normal_(0, 1, generator=gen)
+            st.win.normal_(0, 1, generator=gen)
+            if c.key_type == attn.KEY_FP8:
+                tmp = torch.empty(st.ikey.shape, dtype=torch.bfloat16, device=device).normal_(0, 1, generator=gen)
+                st.ikey.copy_(tmp.to(torch.float8_e4m3fn).view(torch.uint8))
+                del tmp
+            else:
+                st.ikey.normal_(0, 1, generator=gen)
+            self.state.append(st)
+        self.out_norm = torch.ones(c.dim, dtype=torch.float32, device=device)
+        self.w_head = synthetic.random_weights(c.t_head, c.vocab, c.dim, gen)
+        self.bufs = DecBufs(c, device)
+        self.launches_per_token = 0
+
+    # ------------------------------------------------------------------ one layer
+    def encode_dec_attn_side(self, e: Enc, l, pos):
+        c, w, b, st = self.cfg, self.layers[l], self.bufs, self.state[l]
+        n = 0
+        arch.encode_rmsnorm(e, b.h, w.attn_norm, b.x, 1, c.dim, c.norm_eps); n += 1
+        q.encode_matvec(e, c.t_attn, w.wq_a, c.q_lora, c.dim, b.x, b.qa); n += 1
+        q.encode_matvec(e, c.t_attn, w.wkv, c.D, c.dim, b.x, b.kv); n += 1
+        q.encode_matvec(e, c.t_index, w.w_idx_proj, c.index_heads, c.dim, b.x, b.iw); n += 1
+        arch.encode_rmsnorm(e, b.qa, w.q_norm, b.qan, 1, c.q_lora, c.norm_eps); n += 1
+        q.encode_matvec(e, c.t_attn, w.wq_b, c.heads * c.D, c.q_lora, b.qan, b.qfull); n += 1
+        q.encode_matvec(e, c.t_index, w.w_idx_qb, c.index_heads * c.index_dim, c.q_lora, b.qan, b.iq); n += 1
+        attn.encode_kv_window(e, st, b.kv, w.kv_norm, pos); n += 1
+        attn.encode_index_decode(e, st, b.iq, b.iw, pos, c.kv_len, actq=False); n += 4
+        attn.encode_sparse(e, st, b.qfull, w.sinks, b.attn_out, pos); n += 2
+        q.encode_matvec(e, c.t_attn, w.wo_a, c.o_a_rows, c.heads * c.D // c.o_groups, b.attn_out, b.oa, False,
+                        c.o_groups); n += 1
+        q.encode_matvec(e, c.t_attn, w.wo_b, c.dim, c.o_a_rows, b.oa, b.h, True); n += 1     # h += o_b(...)
+        return n
+
+    def encode_dec_moe(self, e: Enc, l):
+        c, w, b = self.cfg, self.layers[l], self.bufs
+        n = 0
+        arch.encode_rmsnorm(e, b.h, w.ffn_norm, b.x, 1, c.dim, c.norm_eps); n += 1
+        if self.ep_world == 1:
+            ml.encode_moe_layer(e, w.moe, b.moe, b.x, b.h, c.score_fn, c.route_scale); n += 3
+            return n
+        # expert parallel: router and shared expert replicated (h += shared(x) locally), routed partial sums of the
+        # local experts combined over NVLink
+        arch.encode_router_fused(e, b.x, w.moe.router_w, w.moe.router_bias, b.moe.ids, b.moe.w, b.moe.router_scratch,
+                                 c.top_k, c.score_fn, c.route_scale); n += 1
+        a = q.MoeDecodeArgs(c.dim, c.inter)
+        a.t_gate_up, a.t_down, a.t_shared = c.t_gate_up, c.t_down, c.t_shared
+        a.n_routed, a.has_shared, a.shared = c.top_k, True, w.moe.shared
+        a.weights, a.x, a.scratch = b.moe.w, b.x, b.moe.moe_scratch
+        a.y = b.h
+        q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.Shared); n += 2
+        b.y_part.zero_()
+        a.y = b.y_part
+        q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.Routed); n += 2
+        import torch.distributed as dist
+        dist.all_reduce(b.y_part, group=self.group)
+        arch.encode_add(e, b.h, b.y_part, c.dim); n += 2
+        return n
+
+    def encode_head(self, e: Enc):
+        c, b = self.cfg, self.bufs
+        arch.encode_rmsnorm(e, b.h, self.out_norm, b.x, 1, c.dim, c.norm_eps)
+        q.encode_matvec(e, c.t_head, self.w_head, c.vocab, c.dim, b.x, b.logits)
+        arch.encode_argmax(e, b.logits, 1, c.vocab, b.next_id)
+        return 3
+
+    def forward_token(self, e: Enc, pos=None):
+        """Encode the whole step for the token whose hidden state is in bufs.h; returns the kernel launch count."""
+        pos = self.cfg.kv_len - 1 if pos is None else pos
+        n = 0
+        for l in range(self.cfg.n_layers):
+            n += self.encode_dec_attn_side(e, l, pos)
+            n += self.encode_dec_moe(e, l)
+        n += self.encode_head(e)
+        self.launches_per_token = n
+        return n
