@@ -46,6 +46,11 @@ int msb_dequant(int qtype, const void* blocks, int64_t n, float* out, void* stre
  * Preconditions as the reference (quant.mm:73): cols a multiple of the block size, rows % groups == 0. */
 int msb_matvec(int qtype, const void* W, int rows, int cols, const float* x, float* y, int accumulate, int groups,
                void* stream);
+/* y = W . (x * rsqrt(mean(x^2) + eps) * norm_w): the input RMSNorm fused into the activation load --
+ * ms::q::encode_matvec_rmsnorm (quant.hpp:19-26, quant.mm:107-127).  Every type is supported here (the reference
+ * excludes the IQ types). */
+int msb_matvec_rmsnorm(int qtype, const void* W, int rows, int cols, const float* x, const float* norm_w, float eps,
+                       float* y, void* stream);
 /* Y[n x rows] (+)= X[n x cols*groups] . W^T, 1 <= n <= 16 -- ms::q::encode_matvec_n (quant.hpp:32-35, quant.mm:129-156).
  * Row stride of X = cols*groups, of Y = rows. */
 int msb_matvec_n(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate,

@@ -6,7 +6,7 @@ namespace msb {
 const char* last_error_text();
 int dequant(int t, const void* src, int64_t n, float* out, cudaStream_t st);
 int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x_stride, float* Y, int64_t y_stride,
-             int n, int accumulate, int groups, cudaStream_t st);
+             int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st);
 size_t router_scratch_bytes(int E);
 int router_fused(const float* x, const float* W, const float* bias, int* ids, float* wts, void* scratch,
                  size_t scratch_bytes, int E, int dim, int k, int score_fn, float route_scale, cudaStream_t st);
@@ -67,13 +67,21 @@ int msb_dequant(int qtype, const void* blocks, int64_t n, float* out, void* stre
 
 int msb_matvec(int qtype, const void* W, int rows, int cols, const float* x, float* y, int accumulate, int groups,
                void* stream) {
-  return matvec_n(qtype, W, rows, cols, x, (int64_t)cols * groups, y, rows, 1, accumulate, groups, (cudaStream_t)stream);
+  return matvec_n(qtype, W, rows, cols, x, (int64_t)cols * groups, y, rows, 1, accumulate, groups, nullptr, 0.f,
+                  (cudaStream_t)stream);
+}
+
+int msb_matvec_rmsnorm(int qtype, const void* W, int rows, int cols, const float* x, const float* norm_w, float eps,
+                       float* y, void* stream) {
+  if (!norm_w) return fail(kErrArg, "matvec_rmsnorm: null norm_w");
+  return matvec_n(qtype, W, rows, cols, x, cols, y, rows, 1, 0, 1, norm_w, eps, (cudaStream_t)stream);
 }
 
 int msb_matvec_n(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate,
                  int groups, void* stream) {
   if (n < 1 || n > 16) return fail(kErrArg, "matvec_n: n = %d outside 1..16", n);
-  return matvec_n(qtype, W, rows, cols, X, (int64_t)cols * groups, Y, rows, n, accumulate, groups, (cudaStream_t)stream);
+  return matvec_n(qtype, W, rows, cols, X, (int64_t)cols * groups, Y, rows, n, accumulate, groups, nullptr, 0.f,
+                  (cudaStream_t)stream);
 }
 
 static int moe_fill(const msb_moe_decode_args* a, MoeParams* p) {

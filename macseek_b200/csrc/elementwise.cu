@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* x, int n, int
   __shared__ int si[32];
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+#pragma unroll 8
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {   // ascending i per thread: a strict compare keeps the lowest index
     const float v = x[i];
     if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
   }

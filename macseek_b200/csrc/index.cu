@@ -114,9 +114,16 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
     }
     s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
     s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-    if (t == 0) {
-      if (k0 < p.len) { p.scores[k0] = s0; if (p.hist && selectable(s0)) atomicAdd(&sh_hist[order_key(s0) >> 20], 1u); }
-      if (k1 < p.len) { p.scores[k1] = s1; if (p.hist && selectable(s1)) atomicAdd(&sh_hist[order_key(s1) >> 20], 1u); }
+    if (t == 0) {   // lanes 0, 4, ..., 28 hold the 16 scores of the tile
+      if (k0 < p.len) p.scores[k0] = s0;
+      if (k1 < p.len) p.scores[k1] = s1;
+      if (p.hist) {   // neighbouring scores mostly share a bin: one shared-memory atomic per distinct bin per warp
+        const uint32_t b0 = (k0 < p.len && selectable(s0)) ? order_key(s0) >> 20 : 0xFFFFFFFFu;
+        const uint32_t b1 = (k1 < p.len && selectable(s1)) ? order_key(s1) >> 20 : 0xFFFFFFFFu;
+        const unsigned m0 = __match_any_sync(0x11111111u, b0), m1 = __match_any_sync(0x11111111u, b1);
+        if (b0 != 0xFFFFFFFFu && lane == __ffs(m0) - 1) atomicAdd(&sh_hist[b0], (unsigned)__popc(m0));
+        if (b1 != 0xFFFFFFFFu && lane == __ffs(m1) - 1) atomicAdd(&sh_hist[b1], (unsigned)__popc(m1));
+      }
     }
   }
   if (p.hist) hist_flush(sh_hist, p.hist, tid, blockDim.x);
@@ -308,12 +315,15 @@ __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024]
   return res_bin;
 }
 
-__global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int n, int k, const unsigned* hist, TopkCtl* ctl,
-                                                           int* sel, int* cand) {
+__global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int n, int k, const unsigned* hist,
+                                                           unsigned* fine, TopkCtl* ctl, int* sel, int* cand) {
   __shared__ unsigned sh[1024];
+  __shared__ unsigned sh_fine[kHistBins];
   __shared__ unsigned base_sel, base_cand, cnt_sel, cnt_cand;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
+  for (int b = threadIdx.x; b < kHistBins; b += blockDim.x) sh_fine[b] = 0;
+  __syncthreads();
   const int per_block = (n + gridDim.x - 1) / gridDim.x;
   const int i0 = blockIdx.x * per_block, i1 = min(n, i0 + per_block);
   for (int base = i0; base < i1; base += blockDim.x) {
@@ -325,8 +335,10 @@ __global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int 
     if (i < i1) {
       const float f = sc[i];
       if (selectable(f)) {
-        const int b = (int)(order_key(f) >> 20);
+        const uint32_t key = order_key(f);
+        const int b = (int)(key >> 20);
         kind = b > bstar ? 1 : (b == bstar ? 2 : 0);
+        if (kind == 2) atomicAdd(&sh_fine[(key >> 8) & 0xFFFu], 1u);   // next 12 key bits of the threshold bin's members
       }
     }
     if (kind == 1) slot = atomicAdd(&cnt_sel, 1u);
@@ -341,96 +353,132 @@ __global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int 
     if (kind == 2) cand[base_cand + slot] = i;
     __syncthreads();
   }
+  hist_flush(sh_fine, fine, threadIdx.x, blockDim.x);
 }
 
-// One block of 1024 threads.  out[k] ascending, -1 padded.  Resets hist and ctl for the next call.
-__global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, TopkCtl* ctl,
-                                                          const int* sel, const int* cand, int* out) {
+// One block of 1024 threads.  out[k] ascending, -1 padded.  Resets the histograms and ctl for the next call.
+// The threshold bin's members are narrowed with the fine histogram (next 12 key bits); what remains in the fine
+// threshold bin (normally a handful) is ranked exactly by (key descending, index ascending).  More than 1024 of them
+// (massive ties) fall back to a radix select over all of the threshold bin's members, on the key then on the index.
+__global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
+                                                          TopkCtl* ctl, const int* sel, const int* cand, int* out) {
   __shared__ unsigned sh[1024];
   __shared__ int buf[2048];
-  __shared__ unsigned s_cnt, s_prefix, s_need, s_digit;
+  __shared__ unsigned long long c2[1024];
+  __shared__ unsigned s_cnt, s_c2, s_need, s_digit;
   const int tid = threadIdx.x;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
   const unsigned n_sel = ctl->n_sel, n_cand = ctl->n_cand;
   for (int i = tid; i < 2048; i += 1024) buf[i] = 0x7fffffff;
+  if (tid == 0) { s_cnt = min(n_sel, 2048u); s_c2 = 0; }
   __syncthreads();
   for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) buf[i] = sel[i];
-  unsigned filled = min(n_sel, 2048u);
   if (bstar >= 0 && n_cand > 0) {
     const unsigned need = (unsigned)k - above;   // how many of the threshold bin's members are taken
-    // radix select (descending) on the low 20 bits of the key: find T = the need-th largest key among candidates
-    unsigned prefix = 0, mask = 0, remaining = need;
-    for (int shift = 12; shift >= -4; shift -= 8) {
-      const int sft = shift < 0 ? 0 : shift;
-      const unsigned dmask = shift < 0 ? 0xFu : 0xFFu;
-      for (int b = tid; b < 256; b += 1024) sh[b] = 0;
-      __syncthreads();
-      for (unsigned i = tid; i < n_cand; i += 1024) {
-        const unsigned key = order_key(sc[cand[i]]) & 0xFFFFFu;
-        if ((key & mask) == prefix) atomicAdd(&sh[(key >> sft) & dmask], 1u);
-      }
-      __syncthreads();
-      if (tid == 0) {
-        unsigned run = 0;
-        int d = (int)dmask;
-        for (; d > 0; d--) {
-          if (run + sh[d] >= remaining) break;
-          run += sh[d];
-        }
-        s_digit = (unsigned)d; s_need = remaining - run;
-      }
-      __syncthreads();
-      prefix |= s_digit << sft;
-      mask |= dmask << sft;
-      remaining = s_need;
-      __syncthreads();
-    }
-    const unsigned T = prefix;         // exact threshold key (low 20 bits); `remaining` members equal to T are taken
-    // ties at T: take the `remaining` lowest indices.  Radix select (ascending) on the index, 3 x 8 bits (n <= 2^24).
-    unsigned ip = 0, im = 0, irem = remaining;
-    for (int shift = 16; shift >= 0; shift -= 8) {
-      for (int b = tid; b < 256; b += 1024) sh[b] = 0;
-      __syncthreads();
+    unsigned above2;
+    const int fstar = threshold_bin(fine, (int)need, sh, &above2);
+    const unsigned m2 = fstar >= 0 ? fine[fstar] : 0;
+    if (fstar >= 0 && m2 <= 1024u) {
+      const unsigned need2 = need - above2;
       for (unsigned i = tid; i < n_cand; i += 1024) {
         const unsigned idx = (unsigned)cand[i];
-        if ((order_key(sc[idx]) & 0xFFFFFu) == T && (idx & im) == ip) atomicAdd(&sh[(idx >> shift) & 0xFFu], 1u);
-      }
-      __syncthreads();
-      if (tid == 0) {
-        unsigned run = 0;
-        int d = 0;
-        for (; d < 255; d++) {
-          if (run + sh[d] >= irem) break;
-          run += sh[d];
+        const uint32_t key = order_key(sc[idx]);
+        const int fb = (int)((key >> 8) & 0xFFFu);
+        if (fb > fstar) {
+          const unsigned pos = atomicAdd(&s_cnt, 1u);
+          if (pos < 2048u) buf[pos] = (int)idx;
+        } else if (fb == fstar) {
+          const unsigned pos = atomicAdd(&s_c2, 1u);
+          if (pos < 1024u) c2[pos] = ((unsigned long long)(0xFFu - (key & 0xFFu)) << 32) | idx;   // ascending = better
         }
-        s_digit = (unsigned)d; s_need = irem - run;
       }
       __syncthreads();
-      ip |= s_digit << shift;
-      im |= 0xFFu << shift;
-      irem = s_need;
+      const unsigned m = min(s_c2, 1024u);
+      if ((unsigned)tid < m) {
+        const unsigned long long mine = c2[tid];
+        unsigned rank = 0;
+        for (unsigned j = 0; j < m; j++) rank += c2[j] < mine;
+        if (rank < need2) {
+          const unsigned pos = atomicAdd(&s_cnt, 1u);
+          if (pos < 2048u) buf[pos] = (int)(mine & 0xFFFFFFFFu);
+        }
+      }
+      __syncthreads();
+    } else {
+      // radix select (descending) on the low 20 bits of the key: find T = the need-th largest key among candidates
+      unsigned prefix = 0, mask = 0, remaining = need;
+      for (int shift = 12; shift >= -4; shift -= 8) {
+        const int sft = shift < 0 ? 0 : shift;
+        const unsigned dmask = shift < 0 ? 0xFu : 0xFFu;
+        for (int b = tid; b < 256; b += 1024) sh[b] = 0;
+        __syncthreads();
+        for (unsigned i = tid; i < n_cand; i += 1024) {
+          const unsigned key = order_key(sc[cand[i]]) & 0xFFFFFu;
+          if ((key & mask) == prefix) atomicAdd(&sh[(key >> sft) & dmask], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+          unsigned run = 0;
+          int d = (int)dmask;
+          for (; d > 0; d--) {
+            if (run + sh[d] >= remaining) break;
+            run += sh[d];
+          }
+          s_digit = (unsigned)d; s_need = remaining - run;
+        }
+        __syncthreads();
+        prefix |= s_digit << sft;
+        mask |= dmask << sft;
+        remaining = s_need;
+        __syncthreads();
+      }
+      const unsigned T = prefix;         // exact threshold key (low 20 bits); `remaining` members equal to T are taken
+      // ties at T: take the `remaining` lowest indices.  Radix select (ascending) on the index, 3 x 8 bits (n <= 2^24).
+      unsigned ip = 0, im = 0, irem = remaining;
+      for (int shift = 16; shift >= 0; shift -= 8) {
+        for (int b = tid; b < 256; b += 1024) sh[b] = 0;
+        __syncthreads();
+        for (unsigned i = tid; i < n_cand; i += 1024) {
+          const unsigned idx = (unsigned)cand[i];
+          if ((order_key(sc[idx]) & 0xFFFFFu) == T && (idx & im) == ip) atomicAdd(&sh[(idx >> shift) & 0xFFu], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+          unsigned run = 0;
+          int d = 0;
+          for (; d < 255; d++) {
+            if (run + sh[d] >= irem) break;
+            run += sh[d];
+          }
+          s_digit = (unsigned)d; s_need = irem - run;
+        }
+        __syncthreads();
+        ip |= s_digit << shift;
+        im |= 0xFFu << shift;
+        irem = s_need;
+        __syncthreads();
+      }
+      const unsigned idxT = ip;          // members equal to T with index <= idxT are taken
+      for (unsigned i = tid; i < n_cand; i += 1024) {
+        const unsigned idx = (unsigned)cand[i];
+        const unsigned key = order_key(sc[idx]) & 0xFFFFFu;
+        if (key > T || (key == T && idx <= idxT)) {
+          const unsigned pos = atomicAdd(&s_cnt, 1u);
+          if (pos < 2048u) buf[pos] = (int)idx;
+        }
+      }
       __syncthreads();
     }
-    const unsigned idxT = ip;          // members equal to T with index <= idxT are taken
-    if (tid == 0) s_cnt = filled;
-    __syncthreads();
-    for (unsigned i = tid; i < n_cand; i += 1024) {
-      const unsigned idx = (unsigned)cand[i];
-      const unsigned key = order_key(sc[idx]) & 0xFFFFFu;
-      if (key > T || (key == T && idx <= idxT)) {
-        const unsigned pos = atomicAdd(&s_cnt, 1u);
-        if (pos < 2048u) buf[pos] = (int)idx;
-      }
-    }
-    __syncthreads();
-    filled = min(s_cnt, 2048u);
   }
   __syncthreads();
-  // bitonic sort of 2048 slots ascending (unused slots hold INT_MAX)
-  for (int size = 2; size <= 2048; size <<= 1)
+  const unsigned filled = min(s_cnt, 2048u);
+  // bitonic sort of the used power-of-two prefix, ascending (unused slots hold INT_MAX)
+  int P = 32;
+  while (P < (int)filled) P <<= 1;
+  for (int size = 2; size <= P; size <<= 1)
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < 1024; i += 1024) {
+      for (int i = tid; i < P / 2; i += 1024) {
         const int lo = 2 * i - (i & (stride - 1));
         const int hi = lo + stride;
         const bool up = ((lo & size) == 0);
@@ -440,9 +488,9 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
       __syncthreads();
     }
   for (int i = tid; i < k; i += 1024) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
-  for (int b = tid; b < kHistBins; b += 1024) hist[b] = 0;
+  for (int b = tid; b < kHistBins; b += 1024) { hist[b] = 0; fine[b] = 0; }
   if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; }
-  (void)s_prefix; (void)n;
+  (void)n;
 }
 
 // block maxima over `bs` consecutive scores; the newest (possibly partial) block is pinned to +inf
@@ -458,17 +506,18 @@ __global__ void block_max_kernel(const float* sc, int len, int bs, float* out, i
 
 // ---------------------------------------------------------------- host side
 size_t topk_scratch_bytes(int n_max) {
-  return sizeof(unsigned) * kHistBins + 64 + sizeof(int) * 2048 + sizeof(int) * (size_t)std::max(n_max, 1);
+  return 2 * sizeof(unsigned) * kHistBins + 64 + sizeof(int) * 2048 + sizeof(int) * (size_t)std::max(n_max, 1);
 }
 
-// scratch layout: hist[4096] | ctl (64 B) | sel[2048] | cand[n_max].  hist and ctl must be zero on entry; the final
-// kernel leaves them zero again.
+// scratch layout: hist[4096] | fine[4096] | ctl (64 B) | sel[2048] | cand[n_max].  The histograms and ctl must be zero
+// on entry; the final kernel leaves them zero again.
 int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, cudaStream_t st) {
   if (n < 0 || k <= 0 || k > 2048) return fail(kErrArg, "topk: n %d k %d (k must be 1..2048)", n, k);
   if (!out || !scratch || (n > 0 && !sc)) return fail(kErrArg, "topk: null pointer");
   if (scratch_bytes < topk_scratch_bytes(n)) return fail(kErrScratch, "topk: scratch too small");
   unsigned* hist = reinterpret_cast<unsigned*>(scratch);
-  TopkCtl* ctl = reinterpret_cast<TopkCtl*>(hist + kHistBins);
+  unsigned* fine = hist + kHistBins;
+  TopkCtl* ctl = reinterpret_cast<TopkCtl*>(fine + kHistBins);
   int* sel = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ctl) + 64);
   int* cand = sel + 2048;
   int dev = 0, sms = 0;
@@ -477,9 +526,9 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   if (n > 0) {
     const int blocks = std::max(1, std::min(sms * 2, (n + 1023) / 1024));
     if (!hist_ready) topk_hist_kernel<<<blocks, 256, 0, st>>>(sc, n, hist);
-    topk_compact_kernel<<<blocks, 256, 0, st>>>(sc, n, k, hist, ctl, sel, cand);
+    topk_compact_kernel<<<blocks, 256, 0, st>>>(sc, n, k, hist, fine, ctl, sel, cand);
   }
-  topk_final_kernel<<<1, 1024, 0, st>>>(sc, n, k, hist, ctl, sel, cand, out);
+  topk_final_kernel<<<1, 1024, 0, st>>>(sc, n, k, hist, fine, ctl, sel, cand, out);
   MSB_LAUNCH_CHECK("topk");
   return kOk;
 }

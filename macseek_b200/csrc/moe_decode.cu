@@ -15,12 +15,15 @@ namespace msb {
 
 struct MoeSmemHead {
   uint64_t full[kMaxStages], empty[kMaxStages];
+  uint64_t lutbar, tilebar;
   int abort_flag;
   int n_local;
   int meta[kMaxStages];
   int local_slot[kMaxRouted];
   const uint8_t* p0[kMaxRouted];   // gate (gu kernel) or down (down kernel) of local routed slot i
   const uint8_t* p1[kMaxRouted];   // up
+  const uint8_t* srcs[kMaxStages][kMaxRouted];   // per ring slot: source addresses of the staged piece
+  float part[2][kMoeNW];           // down kernel: per-warp partial sums of a tile (double-buffered)
 };
 
 __device__ __forceinline__ float swiglu(float g, float u, float w, float limit) {
@@ -56,65 +59,83 @@ __device__ __forceinline__ void finish_block(unsigned* sched) {
   if (old == gridDim.x - 1) { sched[0] = 0; sched[1] = 0; __threadfence(); }
 }
 
-// ---------------------------------------------------------------------------------------------------- gate/up
-template <int T, int LPR, int NR>
-__device__ __forceinline__ void gu_tile_consume(const MoeParams& p, const Ring& ring, uint32_t& n, const MoeShape& sh,
-                                                const uint8_t* G, const uint8_t* Uw, int r0, int U, int warp, int lane,
-                                                const XqSmem (&xq)[1], const LaneLuts& L, float* hrow, float w,
-                                                bool& ok) {
-  constexpr int Gn = 32 / LPR, R = kMoeNW * Gn * NR;
-  const uint32_t rb = (uint32_t)row_bytes(T, p.dim);
-  float ag[NR][1], au[NR][1];
-#pragma unroll
-  for (int i = 0; i < NR; i++) { ag[i][0] = 0.f; au[i][0] = 0.f; }
-  const int nrows = min(R, p.inter - r0);
-  for (int u0 = 0; u0 < U && ok; u0 += sh.chunk) {
-    const int nu = min(sh.chunk, U - u0);
-    Piece pc;
-    pc.row_stride = rb; pc.bytes = units_bytes(T, nu); pc.nrows = nrows;
-    pc.src = G + (size_t)r0 * rb + units_bytes(T, u0);
-    if (!(ok = consumer_wait(ring, n))) break;
-    consume_piece<T, LPR, NR, 1>(ring, n, pc, sh.pitch, warp * Gn * NR, lane, xq, u0, nu, L, ag);
-    consumer_release(ring, n, lane); n++;
-    pc.src = Uw + (size_t)r0 * rb + units_bytes(T, u0);
-    if (!(ok = consumer_wait(ring, n))) break;
-    consume_piece<T, LPR, NR, 1>(ring, n, pc, sh.pitch, warp * Gn * NR, lane, xq, u0, nu, L, au);
-    consumer_release(ring, n, lane); n++;
-  }
-  if (!ok) return;
-  const int grp = lane / LPR, li = lane % LPR;
-#pragma unroll
-  for (int i = 0; i < NR; i++) {
-    const float g = group_sum<LPR>(ag[i][0]), u = group_sum<LPR>(au[i][0]);
-    const int lr = (warp * Gn + grp) * NR + i;
-    if (li == 0 && r0 + lr < p.inter) hrow[r0 + lr] = swiglu(g, u, w, p.limit);
+// Producer side of "first piece of a tile": wait for the slot, publish the tile id, then the piece.
+__device__ __forceinline__ bool announce_tile(const Ring& ring, uint32_t n, MoeSmemHead* hd, int tile, int lane) {
+  const int s = n % ring.stages;
+  if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return false;
+  if (lane == 0) *reinterpret_cast<volatile int*>(&hd->meta[s]) = tile;
+  __syncwarp();
+  return true;
+}
+__device__ __forceinline__ void end_of_tiles(const Ring& ring, uint32_t n, MoeSmemHead* hd, unsigned* sched, int lane) {
+  const int s = n % ring.stages;
+  if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return;
+  if (lane == 0) {
+    *reinterpret_cast<volatile int*>(&hd->meta[s]) = -1;
+    mbar_arrive(&ring.full[s]);
+    finish_block(sched);
   }
 }
 
+// ---------------------------------------------------------------------------------------------------- gate/up
+// A piece stages R gate rows and the same R up rows side by side; a lane group computes NR gate and NR up dot
+// products per activation load.
 template <int T, int LPR, int NR>
 __device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& ring, uint32_t& n, const MoeShape& sh,
-                                                const uint8_t* G, const uint8_t* Uw, int r0, int U, int lane, int tile,
+                                                const uint8_t* Gm, const uint8_t* Um, int r0, int U, int lane, int tile,
                                                 MoeSmemHead* hd) {
   constexpr int Gn = 32 / LPR, R = kMoeNW * Gn * NR;
   const uint32_t rb = (uint32_t)row_bytes(T, p.dim);
-  const int nrows = min(R, p.inter - r0);
+  Piece pc;
+  pc.nsrc = 2; pc.rows_per_src = R; pc.nrows = min(R, p.inter - r0); pc.row_stride = rb;
   bool first = true;
-  for (int u0 = 0; u0 < U; u0 += sh.chunk) {
+  for (int u0 = 0; u0 < U; u0 += sh.chunk, n++) {
     const int nu = min(sh.chunk, U - u0);
-    Piece pc;
-    pc.row_stride = rb; pc.bytes = units_bytes(T, nu); pc.nrows = nrows;
-    for (int m = 0; m < 2; m++, n++) {
-      pc.src = (m ? Uw : G) + (size_t)r0 * rb + units_bytes(T, u0);
-      if (first) {   // the first piece of a tile carries the tile id for the consumers
-        const int s = n % ring.stages;
-        if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty))
-          return false;
-        if (lane == 0) *reinterpret_cast<volatile int*>(&hd->meta[s]) = tile;
-        __syncwarp();
-        first = false;
-      }
-      if (!produce_piece(ring, n, pc, sh.pitch, lane)) return false;
+    const int s = n % ring.stages;
+    if (first) { if (!announce_tile(ring, n, hd, tile, lane)) return false; first = false; }
+    else if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return false;
+    if (lane == 0) {
+      hd->srcs[s][0] = Gm + (size_t)r0 * rb + units_bytes(T, u0);
+      hd->srcs[s][1] = Um + (size_t)r0 * rb + units_bytes(T, u0);
     }
+    __syncwarp();
+    pc.src = hd->srcs[s];
+    pc.bytes = units_bytes(T, nu);
+    if (!produce_piece(ring, n, pc, sh.pitch, lane)) return false;
+  }
+  return true;
+}
+
+template <int T, int LPR, int NR>
+__device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& ring, uint32_t& n, const MoeShape& sh,
+                                                const uint8_t* Gm, const uint8_t* Um, int r0, int U, int warp, int lane,
+                                                const XqSmem (&xq)[1], const LaneLuts& L, float* hrow, float w) {
+  constexpr int Gn = 32 / LPR, R = kMoeNW * Gn * NR;
+  const uint32_t rb = (uint32_t)row_bytes(T, p.dim);
+  const int grp = lane / LPR, li = lane % LPR;
+  const int lr0 = (warp * Gn + grp) * NR;
+  float acc[2 * NR][1];
+#pragma unroll
+  for (int i = 0; i < 2 * NR; i++) acc[i][0] = 0.f;
+  for (int u0 = 0; u0 < U; u0 += sh.chunk, n++) {
+    const int nu = min(sh.chunk, U - u0);
+    const saddr_t slot = smem_u32(ring.slot(n));
+    const uintptr_t ag = reinterpret_cast<uintptr_t>(Gm) + (size_t)r0 * rb + units_bytes(T, u0);
+    const uintptr_t au = reinterpret_cast<uintptr_t>(Um) + (size_t)r0 * rb + units_bytes(T, u0);
+    saddr_t rowp[2 * NR];
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+      rowp[i] = slot + (uint32_t)(lr0 + i) * sh.pitch + (uint32_t)((ag + (uintptr_t)(lr0 + i) * rb) & 15u);
+      rowp[NR + i] = slot + (uint32_t)(R + lr0 + i) * sh.pitch + (uint32_t)((au + (uintptr_t)(lr0 + i) * rb) & 15u);
+    }
+    if (!consumer_wait(ring, n)) return false;
+    consume_rows<T, LPR, 2 * NR, 1>(rowp, li, xq, u0, nu, L, acc);
+    consumer_release(ring, n, lane);
+  }
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const float g = group_sum<LPR>(acc[i][0]), u = group_sum<LPR>(acc[NR + i][0]);
+    if (li == 0 && r0 + lr0 + i < p.inter) hrow[r0 + lr0 + i] = swiglu(g, u, w, p.limit);
   }
   return true;
 }
@@ -122,7 +143,7 @@ __device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& 
 template <int TR, int TS, int LPR>
 __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeParams p) {
   constexpr int Gn = 32 / LPR;
-  constexpr int NR_R = 4, NR_S = 2;
+  constexpr int NR_R = 2, NR_S = 1;
   constexpr int R_R = kMoeNW * Gn * NR_R, R_S = kMoeNW * Gn * NR_S;
   extern __shared__ __align__(128) uint8_t smem[];
   MoeSmemHead* hd = reinterpret_cast<MoeSmemHead*>(smem);
@@ -134,23 +155,20 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
   cur += lut_bytes_for(TR);
   const int U = p.dim / 32;
   XqSmem xq[1];
-  xq[0].U = U;
-  xq[0].plane = reinterpret_cast<uint4*>(cur);
-  xq[0].scale = reinterpret_cast<float*>(cur + (size_t)U * 64);
-  xq[0].sumA = reinterpret_cast<int*>(cur + (size_t)U * 68);
-  xq[0].sumB = reinterpret_cast<int*>(cur + (size_t)U * 72);
-  xq[0].xf = nullptr;
-  cur += (size_t)U * 76;
+  xq_bind(xq[0], cur, U, false);
+  cur += xq_bytes(U, false);
   cur = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(cur) + 127) & ~(uintptr_t)127);
-  for (int s = 0; s < kMaxStages; s++) ring.slot[s] = cur + (size_t)s * p.stage_bytes;
+  ring.slot0 = cur; ring.slot_bytes = p.stage_bytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ring_init(ring, tid, kMoeNW);
-  if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
+  if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_fence_init(); resolve_local(p, hd, p.gu_r != 0, false); }
+  __syncthreads();
   LaneLuts L;
-  fill_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, blockDim.x, L, lane);
+  const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
   quantize_x(p.x, xq[0], tid, blockDim.x);
   __syncthreads();
+  if (!luts_ok) return;
 
   const int tiles_s = p.gu_s ? (p.inter + R_S - 1) / R_S : 0;
   const int tiles_r1 = (p.inter + R_R - 1) / R_R;
@@ -172,14 +190,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
       }
       if (!ok) return;
     }
-    // sentinel: an empty use that tells the consumers to stop
-    const int s = n % ring.stages;
-    if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return;
-    if (lane == 0) {
-      *reinterpret_cast<volatile int*>(&hd->meta[s]) = -1;
-      mbar_arrive(&ring.full[s]);
-      finish_block(p.sched);
-    }
+    end_of_tiles(ring, n, hd, p.sched, lane);
     return;
   }
   // ---------------- consumers
@@ -187,26 +198,29 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
     if (!consumer_wait(ring, n)) return;
     const int t = *reinterpret_cast<volatile int*>(&hd->meta[n % ring.stages]);
     if (t < 0) return;
-    bool ok = true;
+    bool ok;
     if (t < tiles_s) {
-      gu_tile_consume<TS, LPR, NR_S>(p, ring, n, p.gu_shared, p.sgate, p.sup, t * R_S, U, warp, lane, xq, L,
-                                     p.h + (size_t)p.n_routed * p.inter, 1.0f, ok);
+      ok = gu_tile_consume<TS, LPR, NR_S>(p, ring, n, p.gu_shared, p.sgate, p.sup, t * R_S, U, warp, lane, xq, L,
+                                          p.h + (size_t)p.n_routed * p.inter, 1.0f);
     } else {
       const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
       const int k = hd->local_slot[i];
-      gu_tile_consume<TR, LPR, NR_R>(p, ring, n, p.gu_routed, hd->p0[i], hd->p1[i], rt * R_R, U, warp, lane, xq, L,
-                                     p.h + (size_t)k * p.inter, __ldg(p.weights + k), ok);
+      ok = gu_tile_consume<TR, LPR, NR_R>(p, ring, n, p.gu_routed, hd->p0[i], hd->p1[i], rt * R_R, U, warp, lane, xq, L,
+                                          p.h + (size_t)k * p.inter, __ldg(p.weights + k));
     }
     if (!ok) return;
   }
 }
 
 // ---------------------------------------------------------------------------------------------------- down
+// Tile = 8 output rows.  One piece stages those 8 rows of every resident routed expert's down matrix side by side,
+// the next piece(s) the shared expert's rows.  Two warps share a row: the even warp takes the even sources (and the
+// first half of the shared expert's units), the odd warp the rest; the two partial sums meet in shared memory and
+// are added in a fixed order.
 template <int TR, int TS, int LPR>
 __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const MoeParams p) {
-  constexpr int Gn = 32 / LPR;
-  constexpr int NR = 1;
-  constexpr int R = kMoeNW * Gn * NR;
+  static_assert(LPR == 32 || LPR == 16 || LPR == 8, "lanes per row");
+  constexpr int R = kMoeNW / 2;
   extern __shared__ __align__(128) uint8_t smem[];
   MoeSmemHead* hd = reinterpret_cast<MoeSmemHead*>(smem);
   Ring ring;
@@ -218,23 +232,23 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   const int Ui = p.inter / 32;
   const int U = (p.n_routed + 1) * Ui;          // h rows of every slot, shared expert last
   XqSmem xq[1];
-  xq[0].U = U;
-  xq[0].plane = reinterpret_cast<uint4*>(cur);
-  xq[0].scale = reinterpret_cast<float*>(cur + (size_t)U * 64);
-  xq[0].sumA = reinterpret_cast<int*>(cur + (size_t)U * 68);
-  xq[0].sumB = reinterpret_cast<int*>(cur + (size_t)U * 72);
-  xq[0].xf = nullptr;
-  cur += (size_t)U * 76;
+  xq_bind(xq[0], cur, U, false);
+  cur += xq_bytes(U, false);
   cur = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(cur) + 127) & ~(uintptr_t)127);
-  for (int s = 0; s < kMaxStages; s++) ring.slot[s] = cur + (size_t)s * p.stage_bytes;
+  ring.slot0 = cur; ring.slot_bytes = p.stage_bytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ring_init(ring, tid, kMoeNW);
-  if (tid == 0) resolve_local(p, hd, p.d_r != 0, true);
+  if (tid == 0) {
+    mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, kMoeNW); mbar_fence_init();
+    resolve_local(p, hd, p.d_r != 0, true);
+  }
+  __syncthreads();
   LaneLuts L;
-  fill_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, blockDim.x, L, lane);
+  const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
   quantize_x(p.h, xq[0], tid, blockDim.x);
   __syncthreads();
+  if (!luts_ok) return;
 
   const int ntiles = (p.dim + R - 1) / R;
   const int n_local = hd->n_local;
@@ -246,73 +260,90 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
       if (lane == 0) t = (int)atomicAdd(&p.sched[0], 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
       if (t >= ntiles) break;
-      const int r0 = t * R, nrows = min(R, p.dim - r0);
+      const int r0 = t * R;
+      Piece pc;
+      pc.rows_per_src = R; pc.nrows = min(R, p.dim - r0);
       bool first = true;
-      for (int e = 0; e < n_local + (p.d_s ? 1 : 0); e++) {
-        const bool sh = e == n_local;
-        const MoeShape& shp = sh ? p.d_shared : p.d_routed;
-        const uint8_t* Wd = sh ? p.sdown : hd->p0[e];
-        const uint32_t rb = sh ? rb_s : rb_r;
-        for (int u0 = 0; u0 < Ui; u0 += shp.chunk, n++) {
-          const int nu = min(shp.chunk, Ui - u0);
-          Piece pc;
-          pc.row_stride = rb; pc.nrows = nrows;
-          pc.bytes = sh ? units_bytes(TS, nu) : units_bytes(TR, nu);
-          pc.src = Wd + (size_t)r0 * rb + (sh ? units_bytes(TS, u0) : units_bytes(TR, u0));
-          if (first) {
-            const int s = n % ring.stages;
-            if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty))
-              return;
-            if (lane == 0) *reinterpret_cast<volatile int*>(&hd->meta[s]) = t;
-            __syncwarp();
-            first = false;
-          }
-          if (!produce_piece(ring, n, pc, shp.pitch, lane)) return;
+      auto slot_ready = [&](int s) {
+        if (first) { first = false; return announce_tile(ring, n, hd, t, lane); }
+        return mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty);
+      };
+      if (n_local > 0) {
+        for (int u0 = 0; u0 < Ui; u0 += p.d_routed.chunk, n++) {
+          const int nu = min(p.d_routed.chunk, Ui - u0), s = n % ring.stages;
+          if (!slot_ready(s)) return;
+          for (int e = lane; e < n_local; e += 32) hd->srcs[s][e] = hd->p0[e] + (size_t)r0 * rb_r + units_bytes(TR, u0);
+          __syncwarp();
+          pc.src = hd->srcs[s]; pc.nsrc = n_local; pc.row_stride = rb_r; pc.bytes = units_bytes(TR, nu);
+          if (!produce_piece(ring, n, pc, p.d_routed.pitch, lane)) return;
+        }
+      }
+      if (p.d_s) {
+        for (int u0 = 0; u0 < Ui; u0 += p.d_shared.chunk, n++) {
+          const int nu = min(p.d_shared.chunk, Ui - u0), s = n % ring.stages;
+          if (!slot_ready(s)) return;
+          if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s + units_bytes(TS, u0);
+          __syncwarp();
+          pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s; pc.bytes = units_bytes(TS, nu);
+          if (!produce_piece(ring, n, pc, p.d_shared.pitch, lane)) return;
         }
       }
     }
-    const int s = n % ring.stages;
-    if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return;
-    if (lane == 0) {
-      *reinterpret_cast<volatile int*>(&hd->meta[s]) = -1;
-      mbar_arrive(&ring.full[s]);
-      finish_block(p.sched);
-    }
+    end_of_tiles(ring, n, hd, p.sched, lane);
     return;
   }
-  const int grp = lane / LPR, li = lane % LPR;
+  const int row = warp >> 1, half = warp & 1;
+  const int grp = lane / LPR, li = lane % LPR;   // LPR < 32: lane groups take alternate sources / unit runs
+  constexpr int Gn = 32 / LPR;
+  uint32_t tile_count = 0;
   for (;;) {
     if (!consumer_wait(ring, n)) return;
     const int t = *reinterpret_cast<volatile int*>(&hd->meta[n % ring.stages]);
     if (t < 0) return;
-    const int r0 = t * R, nrows = min(R, p.dim - r0);
-    float acc[NR][1];
-#pragma unroll
-    for (int i = 0; i < NR; i++) acc[i][0] = 0.f;
-    for (int e = 0; e < n_local + (p.d_s ? 1 : 0); e++) {
-      const bool sh = e == n_local;
-      const MoeShape& shp = sh ? p.d_shared : p.d_routed;
-      const uint8_t* Wd = sh ? p.sdown : hd->p0[e];
-      const uint32_t rb = sh ? rb_s : rb_r;
-      const int xunit = (sh ? p.n_routed : hd->local_slot[e]) * Ui;
-      for (int u0 = 0; u0 < Ui; u0 += shp.chunk, n++) {
-        const int nu = min(shp.chunk, Ui - u0);
-        Piece pc;
-        pc.row_stride = rb; pc.nrows = nrows;
-        pc.bytes = sh ? units_bytes(TS, nu) : units_bytes(TR, nu);
-        pc.src = Wd + (size_t)r0 * rb + (sh ? units_bytes(TS, u0) : units_bytes(TR, u0));
+    const int r0 = t * R;
+    float acc[1][1] = {{0.f}};
+    if (n_local > 0) {
+      for (int u0 = 0; u0 < Ui; u0 += p.d_routed.chunk, n++) {
+        const int nu = min(p.d_routed.chunk, Ui - u0);
         if (!consumer_wait(ring, n)) return;
-        if (sh) consume_piece<TS, LPR, NR, 1>(ring, n, pc, shp.pitch, warp * Gn * NR, lane, xq, xunit + u0, nu, L, acc);
-        else consume_piece<TR, LPR, NR, 1>(ring, n, pc, shp.pitch, warp * Gn * NR, lane, xq, xunit + u0, nu, L, acc);
+        const saddr_t slot = smem_u32(ring.slot(n));
+        for (int e = half * Gn + grp; e < n_local; e += 2 * Gn) {
+          const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)(r0 + row) * rb_r + units_bytes(TR, u0);
+          const saddr_t rowp[1] = {slot + (uint32_t)(e * R + row) * p.d_routed.pitch + (uint32_t)(a & 15u)};
+          consume_rows<TR, LPR, 1, 1>(rowp, li, xq, hd->local_slot[e] * Ui + u0, nu, L, acc);
+        }
         consumer_release(ring, n, lane);
       }
     }
-#pragma unroll
-    for (int i = 0; i < NR; i++) {
-      const float v = group_sum<LPR>(acc[i][0]);
-      const int lr = (warp * Gn + grp) * NR + i;
-      if (li == 0 && r0 + lr < p.dim) p.y[r0 + lr] += v;
+    if (p.d_s) {
+      for (int u0 = 0; u0 < Ui; u0 += p.d_shared.chunk, n++) {
+        const int nu = min(p.d_shared.chunk, Ui - u0);
+        if (!consumer_wait(ring, n)) return;
+        const saddr_t slot = smem_u32(ring.slot(n));
+        const uintptr_t a = reinterpret_cast<uintptr_t>(p.sdown) + (size_t)(r0 + row) * rb_s + units_bytes(TS, u0);
+        // the 2 * Gn lane groups that share this row split the chunk's units into equal runs of whole super-blocks
+        const int parts = 2 * Gn, me = half * Gn + grp;
+        const int step = block_elems(TS) == 256 ? 8 : 1;
+        const int per = ((nu + parts * step - 1) / (parts * step)) * step;
+        const int ua = min(nu, me * per), ub = min(nu, ua + per);
+        if (ub > ua) {
+          const saddr_t rowp[1] = {slot + (uint32_t)row * p.d_shared.pitch + (uint32_t)(a & 15u) + (uint32_t)units_bytes(TS, ua)};
+          consume_rows<TS, LPR, 1, 1>(rowp, li, xq, p.n_routed * Ui + u0 + ua, ub - ua, L, acc);
+        }
+        consumer_release(ring, n, lane);
+      }
     }
+    // combine: lane groups inside the warp (fixed order), then the two warps of the row
+    float v = group_sum<LPR>(acc[0][0]);
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int pb = tile_count & 1;
+    if (lane == 0) hd->part[pb][warp] = v;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&hd->tilebar);
+    if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return;
+    if (half == 0 && lane == 0 && r0 + row < p.dim) p.y[r0 + row] += hd->part[pb][warp] + hd->part[pb][warp + 1];
+    tile_count++;
   }
 }
 
@@ -322,16 +353,9 @@ namespace {
 bool routed_type_ok(int t) { return t == IQ1_S || t == IQ2_XXS; }
 bool shared_type_ok(int t) { return t == Q6_K || t == Q8_0; }
 
-// staged piece shape for R rows of `units` units of type t within a slot of slot_bytes
-bool shape_for(int t, int units, int R, int lpr, size_t slot_bytes, MoeShape* out) {
-  const bool sb = block_elems(t) == 256;
-  const int step = sb ? std::max(lpr, 8) : lpr;
-  const long per_row = (long)(slot_bytes / R) - 64;
-  if (per_row <= 0) return false;
-  const long by_bytes = sb ? per_row / block_bytes(t) * 8 : per_row / units_bytes(t, 1);
-  int chunk = (int)std::min<long>(by_bytes, units);
-  if (chunk < units && chunk >= step) chunk = chunk / step * step;
-  if (sb) chunk = chunk / 8 * 8;
+// staged piece shape for `rows` row pieces of `units` units of type t within a slot of slot_bytes
+bool shape_for(int t, int units, int rows, int lpr, size_t slot_bytes, MoeShape* out) {
+  const int chunk = chunk_units_for(t, units, rows, lpr, slot_bytes);
   if (chunk <= 0) return false;
   out->chunk = chunk;
   out->pitch = piece_pitch(units_bytes(t, chunk));
@@ -355,12 +379,12 @@ int set_smem(K kern, int dev, bool* done) {
 
 template <int TR, int TS, int LPR>
 int launch_gu(MoeParams& p, int sms, int dev, cudaStream_t st) {
-  constexpr int Gn = 32 / LPR, R_R = kMoeNW * Gn * 4, R_S = kMoeNW * Gn * 2;
+  constexpr int Gn = 32 / LPR, R_R = kMoeNW * Gn * 2, R_S = kMoeNW * Gn * 1;
   const int U = p.dim / 32;
-  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + (size_t)U * 76 + 128;
+  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false) + 128;
   for (int stages = kMaxStages; stages >= 2; stages--) {
     const size_t slot = std::min<size_t>(((size_t)kSmemLimit - fixed) / stages, 48 * 1024) & ~(size_t)127;
-    if (!shape_for(TR, U, R_R, LPR, slot, &p.gu_routed) || !shape_for(TS, U, R_S, LPR, slot, &p.gu_shared)) continue;
+    if (!shape_for(TR, U, 2 * R_R, LPR, slot, &p.gu_routed) || !shape_for(TS, U, 2 * R_S, LPR, slot, &p.gu_shared)) continue;
     p.stages = stages;
     p.stage_bytes = (uint32_t)slot;
     auto kern = moe_gu_kernel<TR, TS, LPR>;
@@ -378,13 +402,13 @@ int launch_gu(MoeParams& p, int sms, int dev, cudaStream_t st) {
 
 template <int TR, int TS, int LPR>
 int launch_down(MoeParams& p, int sms, int dev, cudaStream_t st) {
-  constexpr int Gn = 32 / LPR, R = kMoeNW * Gn;
+  constexpr int R = kMoeNW / 2;
   const int Ui = p.inter / 32, U = (p.n_routed + 1) * Ui;
-  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + (size_t)U * 76 + 128;
+  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false) + 128;
   for (int stages = kMaxStages; stages >= 2; stages--) {
     if (fixed + 8192 > (size_t)kSmemLimit) break;
     const size_t slot = std::min<size_t>(((size_t)kSmemLimit - fixed) / stages, 48 * 1024) & ~(size_t)127;
-    if (!shape_for(TR, Ui, R, LPR, slot, &p.d_routed) || !shape_for(TS, Ui, R, LPR, slot, &p.d_shared)) continue;
+    if (!shape_for(TR, Ui, R * std::max(1, p.n_routed), LPR, slot, &p.d_routed) || !shape_for(TS, Ui, R, LPR, slot, &p.d_shared)) continue;
     p.stages = stages;
     p.stage_bytes = (uint32_t)slot;
     auto kern = moe_down_kernel<TR, TS, LPR>;

@@ -5,7 +5,7 @@
 namespace msb {
 
 constexpr int kMaxRouted = 16;
-constexpr int kMoeNW = 8;
+constexpr int kMoeNW = 16;
 
 struct MoeShape { int chunk; uint32_t pitch; };   // staged piece shape for one (type, K) pair
 

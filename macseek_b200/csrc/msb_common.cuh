@@ -72,8 +72,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // every later wait of the block returns at once.  Returns false when the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
+  if (mbar_try_wait(bar, parity)) return true;    // fast path: no flag read, no clock read
   if (*abort_flag) return false;
-  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
@@ -124,17 +124,24 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 #endif  // __CUDACC__
 
 // ---------------------------------------------------------------- codebook tables (global memory, built at init)
-// IQ1_S : 2048 x u32, element j of the entry stored as (value + 1) in nibble (j < 4 ? 2j : 2(j-4)+1), so that
-//         v & 0x0F0F0F0F = elements 0..3 and (v >> 4) & 0x0F0F0F0F = elements 4..7, one byte each (0, 1 or 2).
-// IQ2_XXS: 256 x uint2 (8 unsigned bytes 8/25/43);  signs: 128 x uint2 (byte 0xFF where the element is negative).
-// IQ4_NL : 256 x u16: low byte = value of the low nibble, high byte = value of the high nibble.
+// Plain tables (dequant kernels):
+//   IQ2_XXS: 256 x uint2 (8 unsigned bytes 8/25/43);  signs: 128 x uint2 (byte 0xFF where the element is negative).
+//   IQ4_NL : 256 x u16: low byte = value of the low nibble, high byte = value of the high nibble.
+//   IQ1_S  : 2048 x 8 int8 values.
+// Shared-memory images (dot kernels), already replicated per bank group so that one bulk copy fills the block's LUT:
+//   img_iq1s  [2048][4 copies] uint2: 8 bytes (value + 1) of the entry        (64 KB)
+//   img_iq2g  [256][16 copies] uint2, img_iq2s [128][16 copies] uint2          (32 KB + 16 KB)
+//   img_iq4   [256][8 copies]  u32 (byte pair in the low 16 bits)               (8 KB)
 struct Tables {
-  const uint32_t* iq1s_nib;    // [2048]
   const uint2* iq2xxs_grid;    // [256]
   const uint2* iq2_signmask;   // [128]
   const uint16_t* iq4nl_pair;  // [256]
-  const int8_t* iq1s_i8;       // [2048][8] plain int8 values (dequant kernels)
-  int* status;                 // device failure word (kDev*)
+  const int8_t* iq1s_i8;       // [2048][8]
+  const uint8_t* img_iq1s;
+  const uint8_t* img_iq2g;
+  const uint8_t* img_iq2s;
+  const uint8_t* img_iq4;
+  int* status;                 // device failure word (kDev*) followed by library-owned scheduling counters
 };
 // Builds the tables on the current device the first time it is called for that device.
 int get_tables(Tables* out);

@@ -1,7 +1,7 @@
 // GGUF block decoders for sm_100a.  Two families per type:
 //   dequant8<T>  : exact dequantisation of 8 consecutive elements (bit-identical with the reference's CPU
 //                  ref::dequant_row, tests/ref/dequant.cpp:34-120: same float association, no FMA contraction).
-//   unit_dot<T>  : dot product of one 32-element unit of a weight row (staged in shared memory, 2-byte aligned) with
+//   decode_unit<T> / dot_unit<T> : dot product of one 32-element unit of a weight row (staged in shared memory, 2-byte aligned) with
 //                  the activation.  Quantised types multiply integer codes with a 16-bit fixed-point copy of the
 //                  activation (two int8 limbs, dp4a), exact in int32 inside the unit, scaled and accumulated in fp32.
 //                  Dense types (F32/F16/BF16) use fp32 FMAs.
@@ -15,10 +15,10 @@ namespace msb {
 
 // Shared-memory lookup tables are replicated so that lanes of a warp hit disjoint banks: copy c of entry i lives at
 // i * (entry_bytes * copies) + c * entry_bytes.
-constexpr int kIq1sCopies = 8;    // 2048 x 4 B x 8  = 64 KB
+constexpr int kIq1sCopies = 4;    // 2048 x 8 B x 4  = 64 KB
 constexpr int kIq2Copies = 16;    // 256 x 8 B x 16 = 32 KB (grid) + 128 x 8 B x 16 = 16 KB (signs)
 constexpr int kIq4Copies = 8;     // 256 x 4 B x 8  = 8 KB
-constexpr size_t kIq1sLutBytes = 2048 * 4 * kIq1sCopies;
+constexpr size_t kIq1sLutBytes = 2048 * 8 * kIq1sCopies;
 constexpr size_t kIq2GridLutBytes = 256 * 8 * kIq2Copies;
 constexpr size_t kIq2SignLutBytes = 128 * 8 * kIq2Copies;
 constexpr size_t kIq4LutBytes = 256 * 4 * kIq4Copies;
@@ -34,49 +34,80 @@ __host__ __device__ constexpr int units_bytes(int t, int units) {
 }
 
 #ifdef __CUDACC__
-struct LaneLuts {      // per-lane base pointers (already offset to the lane's copy)
-  const uint8_t* iq1s;
-  const uint8_t* iq2g;
-  const uint8_t* iq2s;
-  const uint8_t* iq4;
+// Every hot-path shared-memory read goes through explicit ld.shared with 32-bit shared-space addresses: pointers that
+// travel through structs lose their address space and would otherwise compile to generic loads.
+typedef uint32_t saddr_t;
+__device__ __forceinline__ uint32_t lds_u8(saddr_t a) { uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u16(saddr_t a) { uint32_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u32(saddr_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds_u64(saddr_t a) {
+  uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint4 lds_u128(saddr_t a) {
+  uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
+}
+__device__ __forceinline__ float4 lds_f128(saddr_t a) {
+  float4 v; asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v;
+}
+
+struct LaneLuts {      // per-lane shared-space base addresses (already offset to the lane's copy)
+  saddr_t iq1s, iq2g, iq2s, iq4;
 };
 
-// Quantised activation in shared memory: U units of 32 elements.  x ~= scale[u] * (256 * hi + lo), hi signed bytes,
+// Quantised activation in shared memory: U units of 32 elements.  x ~= scale * (256 * hi + lo), hi signed bytes,
 // lo unsigned bytes.  plane[0][u] / plane[1][u] = hi bytes of elements 0..15 / 16..31, plane[2..3] = lo bytes.
-// sumA / sumB = integer sums of the fixed-point values over elements 0..15 / 16..31.
+// meta[u] = {scale, scale * sum of the fixed-point values, (int) sum over elements 0..15, (int) sum over 16..31}.
 struct XqSmem {
-  uint4* plane;   // [4][U]
-  float* scale;   // [U]
-  int* sumA;      // [U]
-  int* sumB;      // [U]
+  uint4* plane;     // [4][U]
+  float4* meta;     // [U]
   const float* xf;  // dense types: fp32 copy of x [32 U]
+  saddr_t plane_s, meta_s, xf_s;   // the same locations as shared-space addresses
   int U;
 };
-__host__ __device__ inline size_t xq_bytes(int U, bool dense) {
-  return dense ? (size_t)U * 128 : (size_t)U * (64 + 12);
+constexpr int kXqUnitBytes = 80;
+__host__ __device__ inline size_t xq_bytes(int U, bool dense) { return dense ? (size_t)U * 128 : (size_t)U * kXqUnitBytes; }
+__device__ __forceinline__ void xq_bind(XqSmem& x, uint8_t* base, int U, bool dense) {
+  x.U = U;
+  x.plane_s = x.xf_s = smem_u32(base);
+  x.meta_s = x.plane_s + (uint32_t)U * 64u;
+  if (dense) { x.xf = reinterpret_cast<const float*>(base); x.plane = nullptr; x.meta = nullptr; }
+  else { x.plane = reinterpret_cast<uint4*>(base); x.meta = reinterpret_cast<float4*>(base + (size_t)U * 64); x.xf = nullptr; }
 }
-struct XRegs { uint32_t h[8], l[8]; float s; int sa, sb; };
+struct XRegs { uint32_t h[8], l[8]; float s, sx; int sa, sb; };
 
 __device__ __forceinline__ void load_xq(const XqSmem& x, int u, XRegs& r) {
-  const uint4 a = x.plane[u], b = x.plane[x.U + u], c = x.plane[2 * x.U + u], d = x.plane[3 * x.U + u];
+  const saddr_t pa = x.plane_s + 16u * (uint32_t)u, st = 16u * (uint32_t)x.U;
+  const uint4 a = lds_u128(pa), b = lds_u128(pa + st), c = lds_u128(pa + 2 * st), d = lds_u128(pa + 3 * st);
+  const float4 m = lds_f128(x.meta_s + 16u * (uint32_t)u);
   r.h[0] = a.x; r.h[1] = a.y; r.h[2] = a.z; r.h[3] = a.w; r.h[4] = b.x; r.h[5] = b.y; r.h[6] = b.z; r.h[7] = b.w;
   r.l[0] = c.x; r.l[1] = c.y; r.l[2] = c.z; r.l[3] = c.w; r.l[4] = d.x; r.l[5] = d.y; r.l[6] = d.z; r.l[7] = d.w;
-  r.s = x.scale[u]; r.sa = x.sumA[u]; r.sb = x.sumB[u];
+  r.s = m.x; r.sx = m.y; r.sa = __float_as_int(m.z); r.sb = __float_as_int(m.w);
 }
 
-// Quantise x[0 .. 32U) (global or shared fp32) into `q`.  Called by all `nthreads` threads of the block; 4 threads
-// cooperate on one unit (8 elements each).  Caller synchronises afterwards.
-__device__ __forceinline__ void quantize_x(const float* __restrict__ x, const XqSmem& q, int tid, int nthreads) {
+// Quantise x[0 .. 32U) (global or shared fp32, 16-byte aligned) into `q`, optionally scaling every element by
+// `mul` first (fused RMSNorm: mul = rstd, and by gain[i] when gain is given).  Called by all `nthreads` threads of the
+// block (a multiple of 32); 4 threads cooperate on one unit (8 elements each).  Caller synchronises afterwards.
+__device__ __forceinline__ void quantize_x(const float* __restrict__ x, const XqSmem& q, int tid, int nthreads,
+                                           float mul = 1.f, const float* __restrict__ gain = nullptr) {
   const int lane4 = tid & 3;
   for (int base = 0; base < q.U * 4; base += nthreads) {
     const int item = base + tid;           // one item = 8 elements
-    const bool live = item < q.U * 4;      // nthreads is a multiple of 32: whole quads are live or not
+    const bool live = item < q.U * 4;      // whole quads are live or not
     const int u = item >> 2;
     float v[8];
     if (live) {
       const float4 a = *reinterpret_cast<const float4*>(x + 8 * item);
       const float4 b = *reinterpret_cast<const float4*>(x + 8 * item + 4);
       v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      if (gain) {
+        const float4 ga = *reinterpret_cast<const float4*>(gain + 8 * item);
+        const float4 gb = *reinterpret_cast<const float4*>(gain + 8 * item + 4);
+        v[0] = v[0] * mul * ga.x; v[1] = v[1] * mul * ga.y; v[2] = v[2] * mul * ga.z; v[3] = v[3] * mul * ga.w;
+        v[4] = v[4] * mul * gb.x; v[5] = v[5] * mul * gb.y; v[6] = v[6] * mul * gb.z; v[7] = v[7] * mul * gb.w;
+      } else if (mul != 1.f) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] *= mul;
+      }
     } else {
 #pragma unroll
       for (int i = 0; i < 8; i++) v[i] = 0.f;
@@ -97,32 +128,32 @@ __device__ __forceinline__ void quantize_x(const float* __restrict__ x, const Xq
       hw[i >> 2] |= (uint32_t)((qv >> 8) & 0xFF) << (8 * (i & 3));
       lw[i >> 2] |= (uint32_t)(qv & 0xFF) << (8 * (i & 3));
     }
-    const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);   // lanes (0,1) -> sumA, (2,3) -> sumB
+    const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);   // lanes (0,1): elements 0..15, (2,3): 16..31
+    const int other = __shfl_xor_sync(0xffffffffu, pair, 2);
     if (live) {
       uint2* ph = reinterpret_cast<uint2*>(&q.plane[(lane4 >> 1) * q.U + u]) + (lane4 & 1);
       uint2* pl = reinterpret_cast<uint2*>(&q.plane[(2 + (lane4 >> 1)) * q.U + u]) + (lane4 & 1);
       *ph = make_uint2(hw[0], hw[1]);
       *pl = make_uint2(lw[0], lw[1]);
-      if (lane4 == 0) { q.scale[u] = amax * (1.0f / 32767.f); q.sumA[u] = pair; }
-      if (lane4 == 2) q.sumB[u] = pair;
+      if (lane4 == 0) {
+        const float sc = amax * (1.0f / 32767.f);
+        q.meta[u] = make_float4(sc, sc * (float)(pair + other), __int_as_float(pair), __int_as_float(other));
+      }
     }
   }
 }
 
-__device__ __forceinline__ uint32_t lds_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
-__device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t* p) { return lds_u16(p) | (lds_u16(p + 2) << 16); }
-__device__ __forceinline__ float lds_half(const uint8_t* p) {
-  return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(p)));
-}
+__device__ __forceinline__ uint32_t lds_u32_a2(saddr_t p) { return lds_u16(p) | (lds_u16(p + 2) << 16); }
+__device__ __forceinline__ float lds_half(saddr_t p) { return __half2float(__ushort_as_half((unsigned short)lds_u16(p))); }
 // N consecutive little-endian 32-bit words starting at a 2-byte aligned shared address (reads one word past the end
 // when the address is not 4-byte aligned; stage buffers are padded for that).
 template <int N>
-__device__ __forceinline__ void load_words(const uint8_t* p, uint32_t (&w)[N]) {
-  const uint32_t* a = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
-  const uint32_t sh = ((uint32_t)reinterpret_cast<uintptr_t>(p) & 2u) * 8u;
+__device__ __forceinline__ void load_words(saddr_t p, uint32_t (&w)[N]) {
+  const saddr_t a = p & ~3u;
+  const uint32_t sh = (p & 2u) * 8u;
   uint32_t t[N + 1];
 #pragma unroll
-  for (int i = 0; i <= N; i++) t[i] = a[i];
+  for (int i = 0; i <= N; i++) t[i] = lds_u32(a + 4u * i);
 #pragma unroll
   for (int i = 0; i < N; i++) w[i] = __funnelshift_r(t[i], t[i + 1], sh);
 }
@@ -135,23 +166,25 @@ template <int T> struct Dec { uint32_t w[8]; float a, b; };
 template <> struct Dec<Q6_K> { uint32_t w[8]; float a, s0, s1; };
 
 template <int T>
-__device__ __forceinline__ void decode_unit(const uint8_t* rowp, int u, const LaneLuts& L, Dec<T>& d);
+__device__ __forceinline__ void decode_unit(saddr_t rowp, int u, const LaneLuts& L, Dec<T>& d);
 template <int T>
 __device__ __forceinline__ float dot_unit(const Dec<T>& d, const XRegs& x);
 
 // ---- IQ1_S: codes + 1 (0,1,2) unsigned; sum (code + delta) x = sum (code + 1) x + (delta - 1) sum x
 template <>
-__device__ __forceinline__ void decode_unit<IQ1_S>(const uint8_t* rowp, int u, const LaneLuts& L, Dec<IQ1_S>& d) {
-  const uint8_t* blk = rowp + (u >> 3) * 50;
+__device__ __forceinline__ void decode_unit<IQ1_S>(saddr_t rowp, int u, const LaneLuts& L, Dec<IQ1_S>& d) {
+  const saddr_t blk = rowp + (uint32_t)(u >> 3) * 50u;
   const int ib = u & 7;
   const uint32_t qs = lds_u32_a2(blk + 2 + 4 * ib);
   const uint32_t qh = lds_u16(blk + 34 + 2 * ib);
+  // entry address = lut + 32 * (8-bit code) + 8192 * (3 high bits): the lane's copy is folded into L.iq1s
 #pragma unroll
   for (int l = 0; l < 4; l++) {
-    const uint32_t idx = ((qs >> (8 * l)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
-    const uint32_t v = *reinterpret_cast<const uint32_t*>(L.iq1s + idx * (4 * kIq1sCopies));
-    d.w[2 * l] = v & 0x0F0F0F0Fu;
-    d.w[2 * l + 1] = (v >> 4) & 0x0F0F0F0Fu;
+    const uint32_t lo = (l == 0 ? (qs << 5) : (qs >> (8 * l - 5))) & 0x1FE0u;
+    const uint32_t hi = (qh << (13 - 3 * l)) & 0xE000u;
+    const uint2 v = lds_u64(L.iq1s + lo + hi);
+    d.w[2 * l] = v.x;
+    d.w[2 * l + 1] = v.y;
   }
   d.a = lds_half(blk) * (float)(2 * ((qh >> 12) & 7u) + 1);
   d.b = (qh & 0x8000u) ? -1.125f : -0.875f;
@@ -161,19 +194,19 @@ __device__ __forceinline__ float dot_unit<IQ1_S>(const Dec<IQ1_S>& d, const XReg
   int sh = 0, sl = 0;
 #pragma unroll
   for (int i = 0; i < 8; i++) { sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl); }
-  return d.a * x.s * ((float)(sh * 256 + sl) + d.b * (float)(x.sa + x.sb));
+  return d.a * (x.s * (float)(sh * 256 + sl) + d.b * x.sx);
 }
 
 // ---- IQ2_XXS: signed bytes (+-8, +-25, +-43): negative elements are negated bytewise, (g ^ m) + (m & 1)
 template <>
-__device__ __forceinline__ void decode_unit<IQ2_XXS>(const uint8_t* rowp, int u, const LaneLuts& L, Dec<IQ2_XXS>& d) {
-  const uint8_t* blk = rowp + (u >> 3) * 66;
-  const uint8_t* a8 = blk + 2 + 8 * (u & 7);
+__device__ __forceinline__ void decode_unit<IQ2_XXS>(saddr_t rowp, int u, const LaneLuts& L, Dec<IQ2_XXS>& d) {
+  const saddr_t blk = rowp + (uint32_t)(u >> 3) * 66u;
+  const saddr_t a8 = blk + 2 + 8 * (u & 7);
   const uint32_t q = lds_u32_a2(a8), a1 = lds_u32_a2(a8 + 4);
 #pragma unroll
   for (int l = 0; l < 4; l++) {
-    const uint2 g = *reinterpret_cast<const uint2*>(L.iq2g + ((q >> (8 * l)) & 0xFFu) * (8 * kIq2Copies));
-    const uint2 m = *reinterpret_cast<const uint2*>(L.iq2s + ((a1 >> (7 * l)) & 127u) * (8 * kIq2Copies));
+    const uint2 g = lds_u64(L.iq2g + ((q >> (8 * l)) & 0xFFu) * (8 * kIq2Copies));
+    const uint2 m = lds_u64(L.iq2s + ((a1 >> (7 * l)) & 127u) * (8 * kIq2Copies));
     d.w[2 * l] = (g.x ^ m.x) + (m.x & 0x01010101u);
     d.w[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
   }
@@ -192,8 +225,8 @@ __device__ __forceinline__ float dot_unit<IQ2_XXS>(const Dec<IQ2_XXS>& d, const 
 
 // ---- Q8_0: the int8 codes as they are
 template <>
-__device__ __forceinline__ void decode_unit<Q8_0>(const uint8_t* rowp, int u, const LaneLuts&, Dec<Q8_0>& d) {
-  const uint8_t* blk = rowp + u * 34;
+__device__ __forceinline__ void decode_unit<Q8_0>(saddr_t rowp, int u, const LaneLuts&, Dec<Q8_0>& d) {
+  const saddr_t blk = rowp + (uint32_t)u * 34u;
   load_words<8>(blk + 2, d.w);
   d.a = lds_half(blk);
   d.b = 0.f;
@@ -203,8 +236,8 @@ __device__ __forceinline__ float dot_unit<Q8_0>(const Dec<Q8_0>& d, const XRegs&
 
 // ---- IQ4_NL: nibble -> signed level through the byte-pair table
 template <>
-__device__ __forceinline__ void decode_unit<IQ4_NL>(const uint8_t* rowp, int u, const LaneLuts& L, Dec<IQ4_NL>& d) {
-  const uint8_t* blk = rowp + u * 18;
+__device__ __forceinline__ void decode_unit<IQ4_NL>(saddr_t rowp, int u, const LaneLuts& L, Dec<IQ4_NL>& d) {
+  const saddr_t blk = rowp + (uint32_t)u * 18u;
   uint32_t q[4];
   load_words<4>(blk + 2, q);
 #pragma unroll
@@ -212,7 +245,7 @@ __device__ __forceinline__ void decode_unit<IQ4_NL>(const uint8_t* rowp, int u, 
     uint32_t r[4];
 #pragma unroll
     for (int k = 0; k < 4; k++)
-      r[k] = *reinterpret_cast<const uint32_t*>(L.iq4 + ((q[i] >> (8 * k)) & 0xFFu) * (4 * kIq4Copies));
+      r[k] = lds_u32(L.iq4 + ((q[i] >> (8 * k)) & 0xFFu) * (4 * kIq4Copies));
     const uint32_t t01 = __byte_perm(r[0], r[1], 0x5140), t23 = __byte_perm(r[2], r[3], 0x5140);
     d.w[i] = __byte_perm(t01, t23, 0x5410);       // low nibbles  -> elements 4i .. 4i+3
     d.w[4 + i] = __byte_perm(t01, t23, 0x7632);   // high nibbles -> elements 16+4i ..
@@ -225,8 +258,8 @@ __device__ __forceinline__ float dot_unit<IQ4_NL>(const Dec<IQ4_NL>& d, const XR
 
 // ---- Q6_K: codes 0..63 unsigned, two int8 scales per unit; sum (q - 32) x = sum q x - 32 sum x
 template <>
-__device__ __forceinline__ void decode_unit<Q6_K>(const uint8_t* rowp, int u, const LaneLuts&, Dec<Q6_K>& d) {
-  const uint8_t* blk = rowp + (u >> 3) * 210;
+__device__ __forceinline__ void decode_unit<Q6_K>(saddr_t rowp, int u, const LaneLuts&, Dec<Q6_K>& d) {
+  const saddr_t blk = rowp + (uint32_t)(u >> 3) * 210u;
   const int j = u & 7, half = j >> 2, q = j & 3;
   uint32_t a[8], b[8];
   load_words<8>(blk + 64 * half + 32 * (q & 1), a);
@@ -234,10 +267,10 @@ __device__ __forceinline__ void decode_unit<Q6_K>(const uint8_t* rowp, int u, co
   const int nsh = 4 * (q >> 1), hsh = 2 * q;
 #pragma unroll
   for (int i = 0; i < 8; i++) d.w[i] = ((a[i] >> nsh) & 0x0F0F0F0Fu) | (((b[i] >> hsh) & 0x03030303u) << 4);
-  const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192 + 8 * half + 2 * q);
+  const uint32_t sc = lds_u16(blk + 192 + 8 * half + 2 * q);   // two int8 scales (the address is even)
   d.a = lds_half(blk + 208);
-  d.s0 = (float)sc[0];
-  d.s1 = (float)sc[1];
+  d.s0 = (float)(int8_t)(sc & 0xFFu);
+  d.s1 = (float)(int8_t)(sc >> 8);
 }
 template <>
 __device__ __forceinline__ float dot_unit<Q6_K>(const Dec<Q6_K>& d, const XRegs& x) {
@@ -252,13 +285,17 @@ __device__ __forceinline__ float dot_unit<Q6_K>(const Dec<Q6_K>& d, const XRegs&
 
 // ---- Q5_K: codes 0..31 unsigned, y = (d * scale) q - dmin * min
 template <>
-__device__ __forceinline__ void decode_unit<Q5_K>(const uint8_t* rowp, int u, const LaneLuts&, Dec<Q5_K>& d) {
-  const uint8_t* blk = rowp + (u >> 3) * 176;
+__device__ __forceinline__ void decode_unit<Q5_K>(saddr_t rowp, int u, const LaneLuts&, Dec<Q5_K>& d) {
+  const saddr_t blk = rowp + (uint32_t)(u >> 3) * 176u;
   const int j = u & 7;
-  const uint8_t* sc = blk + 4;
+  const saddr_t sc = blk + 4;
   uint32_t scale, mn;
-  if (j < 4) { scale = sc[j] & 63u; mn = sc[j + 4] & 63u; }
-  else { scale = (sc[j + 4] & 0xFu) | ((uint32_t)(sc[j - 4] >> 6) << 4); mn = (sc[j + 4] >> 4) | ((uint32_t)(sc[j] >> 6) << 4); }
+  if (j < 4) { scale = lds_u8(sc + j) & 63u; mn = lds_u8(sc + j + 4) & 63u; }
+  else {
+    const uint32_t hi = lds_u8(sc + j + 4);
+    scale = (hi & 0xFu) | ((lds_u8(sc + j - 4) >> 6) << 4);
+    mn = (hi >> 4) | ((lds_u8(sc + j) >> 6) << 4);
+  }
   uint32_t a[8], b[8];
   load_words<8>(blk + 48 + 32 * (j >> 1), a);
   load_words<8>(blk + 16, b);
@@ -273,20 +310,20 @@ __device__ __forceinline__ float dot_unit<Q5_K>(const Dec<Q5_K>& d, const XRegs&
   int sh = 0, sl = 0;
 #pragma unroll
   for (int i = 0; i < 8; i++) { sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl); }
-  return x.s * (d.a * (float)(sh * 256 + sl) - d.b * (float)(x.sa + x.sb));
+  return d.a * (x.s * (float)(sh * 256 + sl)) - d.b * x.sx;
 }
 
 // dense types: fp32 activation from shared memory
 template <int T>
-__device__ __forceinline__ float unit_dot_dense(const uint8_t* rowp, int u, const float* xf) {
-  const float4* xv = reinterpret_cast<const float4*>(xf + 32 * u);
+__device__ __forceinline__ float unit_dot_dense(saddr_t rowp, int u, saddr_t xf) {
+  const saddr_t xv = xf + 128u * (uint32_t)u;
   float acc = 0.f;
   if (T == F32) {
     uint32_t w[32];
     load_words<32>(rowp + u * 128, w);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const float4 v = xv[i];
+      const float4 v = lds_f128(xv + 16u * i);
       acc = fmaf(__uint_as_float(w[4 * i]), v.x, acc); acc = fmaf(__uint_as_float(w[4 * i + 1]), v.y, acc);
       acc = fmaf(__uint_as_float(w[4 * i + 2]), v.z, acc); acc = fmaf(__uint_as_float(w[4 * i + 3]), v.w, acc);
     }
@@ -295,7 +332,7 @@ __device__ __forceinline__ float unit_dot_dense(const uint8_t* rowp, int u, cons
     load_words<16>(rowp + u * 64, w);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const float4 v = xv[i];
+      const float4 v = lds_f128(xv + 16u * i);
       float a0, a1, a2, a3;
       if (T == BF16) {
         a0 = __uint_as_float(w[2 * i] << 16); a1 = __uint_as_float(w[2 * i] & 0xFFFF0000u);

@@ -253,19 +253,33 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
 template <int D>
 __global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p) {
   __shared__ float xs[D];
+  __shared__ float fs[1024];      // per-split rescale factors exp(m_s - M)
+  __shared__ float s_den;
   const int h = blockIdx.x, d = threadIdx.x;
   const float sink = p.sinks[h];
+  // every thread needs M and the denominator: stage (m, l) of all splits once, then reduce from shared memory
+  for (int s = d; s < p.splits; s += D) fs[s] = p.part_ml[((size_t)s * p.H + h) * 2];
+  __syncthreads();
   float M = sink;
-  for (int s = 0; s < p.splits; s++) M = fmaxf(M, p.part_ml[((size_t)s * p.H + h) * 2]);
-  float den = expf(sink - M), acc = 0.f;
-  for (int s = 0; s < p.splits; s++) {
-    const float m = p.part_ml[((size_t)s * p.H + h) * 2], l = p.part_ml[((size_t)s * p.H + h) * 2 + 1];
-    if (m == -INFINITY) continue;
-    const float f = expf(m - M);
-    den += l * f;
-    acc += p.part_o[((size_t)s * p.H + h) * D + d] * f;
+  for (int s = 0; s < p.splits; s++) M = fmaxf(M, fs[s]);
+  __syncthreads();
+  for (int s = d; s < p.splits; s += D) {
+    const float m = p.part_ml[((size_t)s * p.H + h) * 2];
+    fs[s] = (m == -INFINITY) ? 0.f : expf(m - M);
   }
-  xs[d] = acc / den;
+  __syncthreads();
+  if (d == 0) {
+    float den = expf(sink - M);
+    for (int s = 0; s < p.splits; s++) den += p.part_ml[((size_t)s * p.H + h) * 2 + 1] * fs[s];
+    s_den = den;
+  }
+  float acc = 0.f;
+  const float* po = p.part_o + (size_t)h * D + d;
+  const size_t stride = (size_t)p.H * D;
+#pragma unroll 8
+  for (int s = 0; s < p.splits; s++) acc += po[(size_t)s * stride] * fs[s];
+  __syncthreads();
+  xs[d] = acc / s_den;
   __syncthreads();
   float v = xs[d];
   if (d >= D - 64) {
@@ -281,11 +295,11 @@ __global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p)
 static int splits_for(int total_rows, int H, int sms) {
   const int tiles = std::max(1, (total_rows + kSaRows - 1) / kSaRows);
   const int hg = H / kSaHeadsPerBlock;
-  return std::max(1, std::min(tiles, std::max(1, (2 * sms) / hg)));
+  return std::max(1, std::min(std::min(tiles, 1024), std::max(1, sms / hg)));
 }
 size_t sparse_scratch_bytes(int total_rows_max, int H, int D) {
   const int splits = std::max(1, (total_rows_max + kSaRows - 1) / kSaRows);   // upper bound, any device
-  return sizeof(float) * (size_t)std::min(splits, 1024) * H * (D + 2);
+  return sizeof(float) * (size_t)std::min(splits, 1024) * H * (D + 2);   // at most 1024 splits (combine kernel)
 }
 
 template <int D, bool BF>

@@ -1,7 +1,11 @@
 // Weight-streaming pipeline shared by the decode kernels (matvec, MoE gate/up, MoE down).
 //
+// One bulk copy costs the SM's copy engine a fixed ~60 ns whatever its size (measured: 272-byte copies stream at
+// 0.7 TB/s, 1 KB copies at 2.4 TB/s, 4 KB copies at 4.1 TB/s), so pieces are laid out as few, large, contiguous
+// copies: a tile of consecutive full rows is ONE copy.
+//
 // A block is (NW consumer warps + 1 producer warp).  The producer warp walks the block's list of "pieces" -- R rows x
-// a contiguous run of 32-element units of one weight matrix -- and brings each piece into one slot of a shared-memory
+// a contiguous run of 32-element units of one or several weight matrices -- and brings each piece into one slot of a shared-memory
 // ring with 1-D TMA bulk copies (one per row; the source is rounded down to 16 bytes and the copy length up, so raw
 // GGUF rows that are only 2-byte aligned still move as 16-byte bursts).  Consumer warps wait on the slot's "full"
 // mbarrier, decode their rows straight out of shared memory, and release the slot through its "empty" mbarrier.
@@ -14,20 +18,26 @@ namespace msb {
 constexpr int kMaxStages = 4;
 constexpr int kSmemLimit = 227 * 1024;
 
+// Scalar members only (no arrays): the struct must stay in registers, a dynamically indexed member would push it to
+// local memory.
 struct Ring {
-  uint8_t* slot[kMaxStages];
-  uint64_t* full;    // [stages]
-  uint64_t* empty;   // [stages]
+  uint8_t* slot0;        // slot s = slot0 + s * slot_bytes
+  uint32_t slot_bytes;
+  uint64_t* full;        // [stages]
+  uint64_t* empty;       // [stages]
   volatile int* abort_flag;
   int* status;
   int stages;
+  __device__ __forceinline__ uint8_t* slot(uint32_t n) const { return slot0 + (size_t)(n % stages) * slot_bytes; }
 };
 
 struct Piece {
-  const uint8_t* src;    // global address of the first row's first byte of the piece
-  uint32_t row_stride;   // bytes between consecutive rows in global memory
-  uint32_t bytes;        // bytes per row of the piece
-  int nrows;             // rows present (1 .. R)
+  const uint8_t* const* src;  // [nsrc] global address of each source's first row (array in shared or param memory)
+  int nsrc;                   // sources staged side by side in one slot (e.g. gate and up rows, or one per expert)
+  int rows_per_src;           // local rows reserved per source in the slot
+  int nrows;                  // rows present per source (1 .. rows_per_src)
+  uint32_t row_stride;        // bytes between consecutive rows in global memory
+  uint32_t bytes;             // bytes per row of the piece
 };
 
 __host__ __device__ inline uint32_t piece_pitch(uint32_t max_piece_bytes) {
@@ -47,15 +57,19 @@ __device__ __forceinline__ void ring_init(Ring& r, int tid, int consumer_warps) 
   }
 }
 
-// Producer warp: fill the slot for use number n (n counts pieces handled by this block).  Returns false after an
-// abandoned wait.
+// Producer warp: fill the slot for use number n (n counts pieces handled by this block).  Local row
+// lr = source * rows_per_src + row lands at slot + lr * pitch (+ the source address's low 4 bits).
+// Returns false after an abandoned wait.
 __device__ __forceinline__ bool produce_piece(const Ring& r, uint32_t n, const Piece& p, uint32_t pitch, int lane) {
   const int s = n % r.stages;
   const uint32_t ph = (n / r.stages) & 1u;
   if (!mbar_wait(&r.empty[s], ph ^ 1u, r.abort_flag, r.status, kDevWaitEmpty)) return false;
+  const int total_rows = p.nsrc * p.rows_per_src;
   uint32_t mine = 0;
-  for (int row = lane; row < p.nrows; row += 32) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p.src) + (uintptr_t)row * p.row_stride;
+  for (int lr = lane; lr < total_rows; lr += 32) {
+    const int si = lr / p.rows_per_src, row = lr - si * p.rows_per_src;
+    if (row >= p.nrows) continue;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p.src[si]) + (uintptr_t)row * p.row_stride;
     mine += (uint32_t)(((a & 15u) + p.bytes + 15u) & ~15u);
   }
   uint32_t total = mine;
@@ -63,10 +77,14 @@ __device__ __forceinline__ bool produce_piece(const Ring& r, uint32_t n, const P
   for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
   if (lane == 0) mbar_arrive_expect_tx(&r.full[s], total);
   __syncwarp();
-  for (int row = lane; row < p.nrows; row += 32) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p.src) + (uintptr_t)row * p.row_stride;
+  for (int lr = lane; lr < total_rows; lr += 32) {
+    const int si = lr / p.rows_per_src, row = lr - si * p.rows_per_src;
+    if (row >= p.nrows) continue;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p.src[si]) + (uintptr_t)row * p.row_stride;
     const uint32_t len = (uint32_t)(((a & 15u) + p.bytes + 15u) & ~15u);
-    tma_load_1d(r.slot[s] + (size_t)row * pitch, reinterpret_cast<const void*>(a & ~(uintptr_t)15), len, &r.full[s]);
+    uint8_t* dst = r.slot0 + (size_t)s * r.slot_bytes + (size_t)lr * pitch;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a & ~(uintptr_t)15);
+    for (uint32_t o = 0; o < len; o += 32768u) tma_load_1d(dst + o, src + o, min(32768u, len - o), &r.full[s]);
   }
   return true;
 }
@@ -78,66 +96,61 @@ __device__ __forceinline__ void consumer_release(const Ring& r, uint32_t n, int 
   __syncwarp();
   if (lane == 0) mbar_arrive(&r.empty[n % r.stages]);
 }
-// shared-memory address of local row `lr` of the piece held in the slot of use n
-__device__ __forceinline__ const uint8_t* piece_row(const Ring& r, uint32_t n, const Piece& p, uint32_t pitch, int lr) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p.src) + (uintptr_t)lr * p.row_stride;
-  return r.slot[n % r.stages] + (size_t)lr * pitch + (a & 15u);
+// shared-memory address of row `row` of source `si` of the piece held in the slot of use n
+__device__ __forceinline__ const uint8_t* piece_row(const Ring& r, uint32_t n, const Piece& p, uint32_t pitch, int si,
+                                                    int row) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p.src[si]) + (uintptr_t)row * p.row_stride;
+  return r.slot(n) + (size_t)(si * p.rows_per_src + row) * pitch + (a & 15u);
 }
 
-// Copy the lookup tables a type needs into shared memory (replicated per bank group) and return the lane's view.
-__device__ __forceinline__ void fill_luts(uint8_t* lut, bool iq1s, bool iq2, bool iq4, const Tables& tb, int tid, int nthreads,
-                                          LaneLuts& L, int lane) {
-  uint8_t* p = lut;
-  L.iq1s = L.iq2g = L.iq2s = L.iq4 = lut;
-  if (iq1s) {
-    uint32_t* d = reinterpret_cast<uint32_t*>(p);
-    for (int i = tid; i < 2048 * kIq1sCopies; i += nthreads) d[i] = __ldg(tb.iq1s_nib + i / kIq1sCopies);
-    L.iq1s = p + 4 * (lane % kIq1sCopies);
-    p += kIq1sLutBytes;
-  }
+// Bring the lookup tables a type needs into shared memory with bulk copies of the pre-replicated images and return
+// the lane's view.  `bar` is a dedicated mbarrier (initialised with count 1 by the caller before a __syncthreads);
+// every thread waits for the bytes (bounded).  Returns false after an abandoned wait.
+__device__ __forceinline__ bool load_luts(uint8_t* lut, bool iq1s, bool iq2, bool iq4, const Tables& tb, int tid,
+                                          uint64_t* bar, volatile int* abort_flag, LaneLuts& L, int lane) {
+  saddr_t p = smem_u32(lut);
+  L.iq1s = L.iq2g = L.iq2s = L.iq4 = p;
+  uint32_t total = 0;
+  if (iq1s) { L.iq1s = p + 8 * (lane % kIq1sCopies); p += kIq1sLutBytes; total += kIq1sLutBytes; }
   if (iq2) {
-    uint2* d = reinterpret_cast<uint2*>(p);
-    for (int i = tid; i < 256 * kIq2Copies; i += nthreads) d[i] = __ldg(tb.iq2xxs_grid + i / kIq2Copies);
-    L.iq2g = p + 8 * (lane % kIq2Copies);
-    p += kIq2GridLutBytes;
-    d = reinterpret_cast<uint2*>(p);
-    for (int i = tid; i < 128 * kIq2Copies; i += nthreads) d[i] = __ldg(tb.iq2_signmask + i / kIq2Copies);
-    L.iq2s = p + 8 * (lane % kIq2Copies);
-    p += kIq2SignLutBytes;
+    L.iq2g = p + 8 * (lane % kIq2Copies); p += kIq2GridLutBytes;
+    L.iq2s = p + 8 * (lane % kIq2Copies); p += kIq2SignLutBytes;
+    total += kIq2GridLutBytes + kIq2SignLutBytes;
   }
-  if (iq4) {
-    uint32_t* d = reinterpret_cast<uint32_t*>(p);
-    for (int i = tid; i < 256 * kIq4Copies; i += nthreads) d[i] = __ldg(tb.iq4nl_pair + i / kIq4Copies);
-    L.iq4 = p + 4 * (lane % kIq4Copies);
-    p += kIq4LutBytes;
+  if (iq4) { L.iq4 = p + 4 * (lane % kIq4Copies); p += kIq4LutBytes; total += kIq4LutBytes; }
+  if (total == 0) return true;
+  if (tid == 0) {
+    mbar_arrive_expect_tx(bar, total);
+    uint8_t* q = lut;
+    auto copy = [&](const uint8_t* src, uint32_t bytes) {
+      for (uint32_t o = 0; o < bytes; o += 16384) tma_load_1d(q + o, src + o, min(16384u, bytes - o), bar);
+      q += bytes;
+    };
+    if (iq1s) copy(tb.img_iq1s, kIq1sLutBytes);
+    if (iq2) { copy(tb.img_iq2g, kIq2GridLutBytes); copy(tb.img_iq2s, kIq2SignLutBytes); }
+    if (iq4) copy(tb.img_iq4, kIq4LutBytes);
   }
+  return mbar_wait(bar, 0, abort_flag, tb.status, kDevWaitFull);
 }
 
-// Partial dot products of one staged piece for the rows of this lane group.
-//   LPR lanes share a row; the warp covers G = 32 / LPR row groups x NR rows; NC activation columns.
-//   acc[r][c] += sum over the piece's units handled by this lane.
-template <int T, int LPR, int NR, int NC>
-__device__ __forceinline__ void consume_piece(const Ring& r, uint32_t n, const Piece& p, uint32_t pitch, int warp_row0,
-                                              int lane, const XqSmem (&xq)[NC], int unit0, int nunits,
-                                              const LaneLuts& L, float (&acc)[NR][NC]) {
-  constexpr int G = 32 / LPR;
-  const int grp = lane / LPR, li = lane % LPR;
-  const uint8_t* rowp[NR];
-#pragma unroll
-  for (int i = 0; i < NR; i++) rowp[i] = piece_row(r, n, p, pitch, warp_row0 + grp * NR + i);
-  (void)G;
+// Partial dot products of `nunits` staged units for NRT rows of one lane group: LPR lanes split the units, the x
+// registers of a unit are loaded once and shared by the NRT rows and NC activation columns.
+//   acc[i][c] += sum over this lane's units of  row_i[unit] . x_c[unit0 + unit]
+template <int T, int LPR, int NRT, int NC>
+__device__ __forceinline__ void consume_rows(const saddr_t (&rowp)[NRT], int li, const XqSmem (&xq)[NC], int unit0,
+                                             int nunits, const LaneLuts& L, float (&acc)[NRT][NC]) {
   for (int uu = li; uu < nunits; uu += LPR) {
     if constexpr (is_dense(T)) {
 #pragma unroll
-      for (int i = 0; i < NR; i++)
+      for (int i = 0; i < NRT; i++)
 #pragma unroll
-        for (int c = 0; c < NC; c++) acc[i][c] += unit_dot_dense<T>(rowp[i], uu, xq[c].xf + 32 * unit0);
+        for (int c = 0; c < NC; c++) acc[i][c] += unit_dot_dense<T>(rowp[i], uu, xq[c].xf_s + 128u * (uint32_t)unit0);
     } else {
       XRegs xr[NC];
 #pragma unroll
       for (int c = 0; c < NC; c++) load_xq(xq[c], unit0 + uu, xr[c]);
 #pragma unroll
-      for (int i = 0; i < NR; i++) {
+      for (int i = 0; i < NRT; i++) {
         Dec<T> d;
         decode_unit<T>(rowp[i], uu, L, d);
 #pragma unroll
@@ -154,5 +167,19 @@ __device__ __forceinline__ float group_sum(float v) {
   return v;
 }
 #endif
+
+// Largest staged chunk (in 32-element units) of a type-t row such that `rows` row pieces fit in slot_bytes; a multiple
+// of the lane stride and of a super-block where possible.  0 if nothing fits.
+inline int chunk_units_for(int t, int units, int rows, int lpr, size_t slot_bytes) {
+  const bool sb = block_elems(t) == 256;
+  const int step = sb ? (lpr > 8 ? lpr : 8) : lpr;
+  const long per_row = (long)(slot_bytes / rows) - 64;          // piece_pitch(b) <= b + 62
+  if (per_row <= 0) return 0;
+  const long by_bytes = sb ? per_row / block_bytes(t) * 8 : per_row / units_bytes(t, 1);
+  long chunk = by_bytes < units ? by_bytes : units;
+  if (chunk < units && chunk >= step) chunk = chunk / step * step;   // else: a short chunk, some lanes idle
+  if (sb) chunk = chunk / 8 * 8;
+  return (int)chunk;
+}
 
 }  // namespace msb

@@ -40,21 +40,21 @@ DevTables g_tables[kMaxDev];
 std::mutex g_mu;
 
 struct HostImage {
-  std::vector<uint32_t> iq1s_nib;
   std::vector<uint32_t> iq2_grid;   // 2 words per entry
   std::vector<uint32_t> iq2_sign;   // 2 words per entry
   std::vector<uint16_t> iq4_pair;
   std::vector<int8_t> iq1s_i8;
-  HostImage() : iq1s_nib(2048), iq2_grid(512), iq2_sign(256), iq4_pair(256), iq1s_i8(2048 * 8) {
+  std::vector<uint32_t> img_iq1s, img_iq2g, img_iq2s, img_iq4;
+  HostImage() : iq2_grid(512), iq2_sign(256), iq4_pair(256), iq1s_i8(2048 * 8) {
+    img_iq1s.assign(2048 * 4 * 2, 0);
     for (int i = 0; i < 2048; i++) {
-      uint32_t v = 0;
+      uint32_t w[2] = {0, 0};
       for (int j = 0; j < 8; j++) {
         const uint32_t f = (kMsbIq1sPacked[i] >> (2 * j)) & 3;   // value + 1
         iq1s_i8[i * 8 + j] = (int8_t)((int)f - 1);
-        const int nib = j < 4 ? 2 * j : 2 * (j - 4) + 1;
-        v |= f << (4 * nib);
+        w[j / 4] |= f << (8 * (j % 4));
       }
-      iq1s_nib[i] = v;
+      for (int c = 0; c < 4; c++) { img_iq1s[(i * 4 + c) * 2] = w[0]; img_iq1s[(i * 4 + c) * 2 + 1] = w[1]; }
     }
     static const uint32_t lv[4] = {8, 25, 43, 0};
     for (int i = 0; i < 256; i++)
@@ -66,6 +66,15 @@ struct HostImage {
     }
     for (int b = 0; b < 256; b++)
       iq4_pair[b] = (uint16_t)((uint8_t)kIq4nl[b & 15] | ((uint16_t)(uint8_t)kIq4nl[b >> 4] << 8));
+    img_iq2g.assign(256 * 16 * 2, 0);
+    img_iq2s.assign(128 * 16 * 2, 0);
+    img_iq4.assign(256 * 8, 0);
+    for (int i = 0; i < 256; i++)
+      for (int c = 0; c < 16; c++) { img_iq2g[(i * 16 + c) * 2] = iq2_grid[2 * i]; img_iq2g[(i * 16 + c) * 2 + 1] = iq2_grid[2 * i + 1]; }
+    for (int i = 0; i < 128; i++)
+      for (int c = 0; c < 16; c++) { img_iq2s[(i * 16 + c) * 2] = iq2_sign[2 * i]; img_iq2s[(i * 16 + c) * 2 + 1] = iq2_sign[2 * i + 1]; }
+    for (int i = 0; i < 256; i++)
+      for (int c = 0; c < 8; c++) img_iq4[i * 8 + c] = iq4_pair[i];
   }
 };
 
@@ -88,7 +97,10 @@ int get_tables(Tables* out) {
   DevTables& d = g_tables[dev];
   if (!d.ready) {
     static const HostImage img;
-    MSB_CUDA(upload(img.iq1s_nib, (const void**)&d.t.iq1s_nib));
+    MSB_CUDA(upload(img.img_iq1s, (const void**)&d.t.img_iq1s));
+    MSB_CUDA(upload(img.img_iq2g, (const void**)&d.t.img_iq2g));
+    MSB_CUDA(upload(img.img_iq2s, (const void**)&d.t.img_iq2s));
+    MSB_CUDA(upload(img.img_iq4, (const void**)&d.t.img_iq4));
     MSB_CUDA(upload(img.iq2_grid, (const void**)&d.t.iq2xxs_grid));
     MSB_CUDA(upload(img.iq2_sign, (const void**)&d.t.iq2_signmask));
     MSB_CUDA(upload(img.iq4_pair, (const void**)&d.t.iq4nl_pair));

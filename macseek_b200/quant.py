@@ -135,3 +135,8 @@ def encode_moe_decode_ids(e: Enc, a: MoeDecodeArgs, expert_table, ids, expert_lo
     router; only experts in [expert_lo, expert_hi) are computed on this GPU."""
     c = a._c()
     _lib.check(_lib.lib.msb_moe_decode_ids(c, ptr(expert_table), ptr(ids), expert_lo, expert_hi, int(part), e.handle))
+
+
+def encode_matvec_rmsnorm(e: Enc, t, W, rows, cols, x, norm_w, eps, y):
+    """y = W . (x * rsqrt(mean(x^2) + eps) * norm_w): input RMSNorm fused into the x load (quant.hpp:19-26)."""
+    _lib.check(_lib.lib.msb_matvec_rmsnorm(int(t), ptr(W), rows, cols, ptr(x), ptr(norm_w), eps, ptr(y), e.handle))

@@ -239,7 +239,8 @@ def test_router_fused_and_topk(orc, enc, cfg):
     n = 37
     L = (rng.standard_normal((n, E)) * 2).astype(np.float32)
     L[3, 10] = L[3, 200] = 9.0
-    b0 = bias.copy(); b0[10] = b0[200] = 0
+    L[3, :10] = -5.0          # nothing else of row 3 comes close to the tied pair's key
+    b0 = bias.copy(); b0[10] = b0[200] = 0.5
     ids_n = torch.zeros((n, k), dtype=torch.int32, device="cuda")
     w_n = torch.zeros((n, k), dtype=torch.float32, device="cuda")
     arch.encode_router_topk(enc, dev(L), dev(b0), ids_n, w_n, n, k, fn, scale)
