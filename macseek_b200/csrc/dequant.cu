@@ -37,7 +37,7 @@ int dequant(int t, const void* src, int64_t n, float* out, cudaStream_t st) {
   if (rc) return rc;
   const int threads = 256;
   if (is_dense(t)) {
-    widen_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, st>>>((const uint8_t*)src, out, n, t);
+    MSB_CUDA(launch_pdl(widen_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, st, (const uint8_t*)src, out, n, t));
   } else {
     const int64_t n8 = n / 8;
     const unsigned grid = (unsigned)((n8 + threads - 1) / threads);

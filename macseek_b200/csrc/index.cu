@@ -64,45 +64,61 @@ __device__ __forceinline__ void hist_flush(unsigned* sh, unsigned* gh, int tid, 
 // row with the same bytes of the query, so the contraction covers every dimension once.
 template <int H>
 __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int NT = H / 8;
   __shared__ unsigned sh_hist[kHistBins];
   const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
   if (p.hist)
     for (int b = tid; b < kHistBins; b += blockDim.x) sh_hist[b] = 0;
+  // the query goes through shared memory as e4m3 bytes: a coalesced, latency-parallel load instead of 256 dependent
+  // global loads per thread
+  __shared__ __align__(16) uint8_t q8[H * kIdxDim];
+  __shared__ float wsh[H];
+  for (int i = tid; i < H * kIdxDim / 4; i += blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(p.q)[i];
+    const uint32_t b = (uint32_t)__nv_cvt_float_to_fp8(v.x, __NV_SATFINITE, __NV_E4M3) |
+                       ((uint32_t)__nv_cvt_float_to_fp8(v.y, __NV_SATFINITE, __NV_E4M3) << 8) |
+                       ((uint32_t)__nv_cvt_float_to_fp8(v.z, __NV_SATFINITE, __NV_E4M3) << 16) |
+                       ((uint32_t)__nv_cvt_float_to_fp8(v.w, __NV_SATFINITE, __NV_E4M3) << 24);
+    reinterpret_cast<uint32_t*>(q8)[i] = b;
+  }
+  for (int i = tid; i < H; i += blockDim.x) wsh[i] = p.w[i];
+  __syncthreads();
   uint32_t B[NT][4][2];
   float wr[NT][2];
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
-    const float* qr = p.q + (size_t)(nt * 8 + g) * kIdxDim + 32 * t;
+    const uint32_t* qr = reinterpret_cast<const uint32_t*>(q8 + (size_t)(nt * 8 + g) * kIdxDim + 32 * t);
 #pragma unroll
-    for (int s = 0; s < 4; s++)
-#pragma unroll
-      for (int j = 0; j < 2; j++) {
-        uint32_t v = 0;
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-          v |= (uint32_t)__nv_cvt_float_to_fp8(qr[8 * s + 4 * j + i], __NV_SATFINITE, __NV_E4M3) << (8 * i);
-        B[nt][s][j] = v;
-      }
-    wr[nt][0] = p.w[nt * 8 + 2 * t];
-    wr[nt][1] = p.w[nt * 8 + 2 * t + 1];
+    for (int s = 0; s < 4; s++) { B[nt][s][0] = qr[2 * s]; B[nt][s][1] = qr[2 * s + 1]; }
+    wr[nt][0] = wsh[nt * 8 + 2 * t];
+    wr[nt][1] = wsh[nt * 8 + 2 * t + 1];
   }
   if (p.hist) __syncthreads();
   const int warps = gridDim.x * (blockDim.x >> 5);
   const int ntiles = (p.len + 15) / 16;
-  for (int tile = blockIdx.x * (blockDim.x >> 5) + (tid >> 5); tile < ntiles; tile += warps) {
+  // software pipeline: the next tile's 64 bytes per lane are requested before the current tile is multiplied
+  auto fetch = [&](int tile, uint4 (&r)[4]) {
     const int k0 = tile * 16 + g, k1 = k0 + 8;
-    uint4 r0a = make_uint4(0, 0, 0, 0), r0b = r0a, r1a = r0a, r1b = r0a;
-    if (k0 < p.len) {
+    r[0] = r[1] = r[2] = r[3] = make_uint4(0, 0, 0, 0);
+    if (tile < ntiles && k0 < p.len) {
       const uint4* src = reinterpret_cast<const uint4*>(p.keys + (size_t)k0 * kIdxDim + 32 * t);
-      r0a = __ldg(src); r0b = __ldg(src + 1);
+      r[0] = __ldg(src); r[1] = __ldg(src + 1);
     }
-    if (k1 < p.len) {
+    if (tile < ntiles && k1 < p.len) {
       const uint4* src = reinterpret_cast<const uint4*>(p.keys + (size_t)k1 * kIdxDim + 32 * t);
-      r1a = __ldg(src); r1b = __ldg(src + 1);
+      r[2] = __ldg(src); r[3] = __ldg(src + 1);
     }
-    const uint32_t A0[8] = {r0a.x, r0a.y, r0a.z, r0a.w, r0b.x, r0b.y, r0b.z, r0b.w};
-    const uint32_t A1[8] = {r1a.x, r1a.y, r1a.z, r1a.w, r1b.x, r1b.y, r1b.z, r1b.w};
+  };
+  uint4 cur[4], nxt[4];
+  int tile = blockIdx.x * (blockDim.x >> 5) + (tid >> 5);
+  fetch(tile, cur);
+  for (; tile < ntiles; tile += warps) {
+    fetch(tile + warps, nxt);
+    const int k0 = tile * 16 + g, k1 = k0 + 8;
+    const uint32_t A0[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
+    const uint32_t A1[8] = {cur[2].x, cur[2].y, cur[2].z, cur[2].w, cur[3].x, cur[3].y, cur[3].z, cur[3].w};
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
@@ -125,6 +141,8 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
         if (b1 != 0xFFFFFFFFu && lane == __ffs(m1) - 1) atomicAdd(&sh_hist[b1], (unsigned)__popc(m1));
       }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++) cur[i] = nxt[i];
   }
   if (p.hist) hist_flush(sh_hist, p.hist, tid, blockDim.x);
 }
@@ -136,6 +154,8 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
 // K permutation: lane (g, t) holds elements 32t .. 32t+31 of its rows; k-step s uses elements 32t+4s .. 32t+4s+3.
 template <int H, bool FP8IN, bool SPLIT>
 __global__ void __launch_bounds__(256, 1) idx_score_f16_kernel(const IdxParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int NTH = H / 8;                 // n-tiles per term
   constexpr int NT = SPLIT ? 2 * NTH : NTH;
   __shared__ uint2 Bs[NT][8][32];
@@ -234,6 +254,8 @@ __device__ __forceinline__ float round_e2m1(float x) {
 }
 __global__ void idx_prep_kernel(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q,
                                 float* w) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= heads) return;
   float v[4];
@@ -271,6 +293,8 @@ __global__ void idx_prep_kernel(const float* q_raw, const float* w_raw, const fl
 struct TopkCtl { unsigned n_sel, n_cand, pad0, pad1; };
 
 __global__ void topk_hist_kernel(const float* sc, int n, unsigned* hist) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned sh[kHistBins];
   for (int b = threadIdx.x; b < kHistBins; b += blockDim.x) sh[b] = 0;
   __syncthreads();
@@ -316,42 +340,49 @@ __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024]
 }
 
 __global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int n, int k, const unsigned* hist,
-                                                           unsigned* fine, TopkCtl* ctl, int* sel, int* cand) {
+                                                           unsigned* fine, TopkCtl* ctl, int* sel, uint2* cand) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned sh[1024];
   __shared__ unsigned sh_fine[kHistBins];
-  __shared__ unsigned base_sel, base_cand, cnt_sel, cnt_cand;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
   for (int b = threadIdx.x; b < kHistBins; b += blockDim.x) sh_fine[b] = 0;
   __syncthreads();
+  const int lane = threadIdx.x & 31;
   const int per_block = (n + gridDim.x - 1) / gridDim.x;
   const int i0 = blockIdx.x * per_block, i1 = min(n, i0 + per_block);
-  for (int base = i0; base < i1; base += blockDim.x) {
-    if (threadIdx.x == 0) { cnt_sel = 0; cnt_cand = 0; }
-    __syncthreads();
-    const int i = base + threadIdx.x;
-    int kind = 0;   // 1 = selected outright, 2 = threshold-bin candidate
-    unsigned slot = 0;
-    if (i < i1) {
-      const float f = sc[i];
-      if (selectable(f)) {
-        const uint32_t key = order_key(f);
+  // 4 independent loads per thread per trip; appends are aggregated per warp (one global atomic per warp and kind)
+  for (int base = i0; base < i1; base += blockDim.x * 4) {
+    float f[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int i = base + j * (int)blockDim.x + (int)threadIdx.x;
+      f[j] = i < i1 ? sc[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int i = base + j * (int)blockDim.x + (int)threadIdx.x;
+      int kind = 0;   // 1 = selected outright, 2 = threshold-bin candidate
+      uint32_t key = 0;
+      if (i < i1 && selectable(f[j])) {
+        key = order_key(f[j]);
         const int b = (int)(key >> 20);
         kind = b > bstar ? 1 : (b == bstar ? 2 : 0);
         if (kind == 2) atomicAdd(&sh_fine[(key >> 8) & 0xFFFu], 1u);   // next 12 key bits of the threshold bin's members
       }
+      const unsigned m1 = __ballot_sync(0xffffffffu, kind == 1), m2 = __ballot_sync(0xffffffffu, kind == 2);
+      unsigned b1 = 0, b2 = 0;
+      if (lane == 0) {
+        if (m1) b1 = atomicAdd(&ctl->n_sel, (unsigned)__popc(m1));
+        if (m2) b2 = atomicAdd(&ctl->n_cand, (unsigned)__popc(m2));
+      }
+      b1 = __shfl_sync(0xffffffffu, b1, 0);
+      b2 = __shfl_sync(0xffffffffu, b2, 0);
+      const unsigned lt = (1u << lane) - 1u;
+      if (kind == 1) { const unsigned pos = b1 + __popc(m1 & lt); if (pos < 2048u) sel[pos] = i; }
+      if (kind == 2) cand[b2 + __popc(m2 & lt)] = make_uint2((unsigned)i, key);
     }
-    if (kind == 1) slot = atomicAdd(&cnt_sel, 1u);
-    if (kind == 2) slot = atomicAdd(&cnt_cand, 1u);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      base_sel = cnt_sel ? atomicAdd(&ctl->n_sel, cnt_sel) : 0;
-      base_cand = cnt_cand ? atomicAdd(&ctl->n_cand, cnt_cand) : 0;
-    }
-    __syncthreads();
-    if (kind == 1) sel[base_sel + slot] = i;
-    if (kind == 2) cand[base_cand + slot] = i;
-    __syncthreads();
   }
   hist_flush(sh_fine, fine, threadIdx.x, blockDim.x);
 }
@@ -361,19 +392,29 @@ __global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int 
 // threshold bin (normally a handful) is ranked exactly by (key descending, index ascending).  More than 1024 of them
 // (massive ties) fall back to a radix select over all of the threshold bin's members, on the key then on the index.
 __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
-                                                          TopkCtl* ctl, const int* sel, const int* cand, int* out) {
+                                                          TopkCtl* ctl, const int* sel, const uint2* cand, int* out, int bm_words) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned sh[1024];
   __shared__ int buf[2048];
   __shared__ unsigned long long c2[1024];
   __shared__ unsigned s_cnt, s_c2, s_need, s_digit;
+  extern __shared__ unsigned bitmap[];          // bm_words words when the bitmap path is used (n <= 32 * bm_words)
   const int tid = threadIdx.x;
+  // chosen indices go into a bitmap of the n positions (read back in ascending order: no sort), or, for very long
+  // inputs that do not fit shared memory, into buf[] which is then sorted
+  auto emit = [&](unsigned idx) {
+    if (bm_words) atomicOr(&bitmap[idx >> 5], 1u << (idx & 31));
+    else { const unsigned pos = atomicAdd(&s_cnt, 1u); if (pos < 2048u) buf[pos] = (int)idx; }
+  };
+  for (int i = tid; i < bm_words; i += 1024) bitmap[i] = 0;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
   const unsigned n_sel = ctl->n_sel, n_cand = ctl->n_cand;
   for (int i = tid; i < 2048; i += 1024) buf[i] = 0x7fffffff;
-  if (tid == 0) { s_cnt = min(n_sel, 2048u); s_c2 = 0; }
+  if (tid == 0) { s_cnt = 0; s_c2 = 0; }
   __syncthreads();
-  for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) buf[i] = sel[i];
+  for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) emit((unsigned)sel[i]);
   if (bstar >= 0 && n_cand > 0) {
     const unsigned need = (unsigned)k - above;   // how many of the threshold bin's members are taken
     unsigned above2;
@@ -381,13 +422,14 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
     const unsigned m2 = fstar >= 0 ? fine[fstar] : 0;
     if (fstar >= 0 && m2 <= 1024u) {
       const unsigned need2 = need - above2;
+#pragma unroll 4
       for (unsigned i = tid; i < n_cand; i += 1024) {
-        const unsigned idx = (unsigned)cand[i];
-        const uint32_t key = order_key(sc[idx]);
+        const uint2 cd = cand[i];
+        const unsigned idx = cd.x;
+        const uint32_t key = cd.y;
         const int fb = (int)((key >> 8) & 0xFFFu);
         if (fb > fstar) {
-          const unsigned pos = atomicAdd(&s_cnt, 1u);
-          if (pos < 2048u) buf[pos] = (int)idx;
+          emit(idx);
         } else if (fb == fstar) {
           const unsigned pos = atomicAdd(&s_c2, 1u);
           if (pos < 1024u) c2[pos] = ((unsigned long long)(0xFFu - (key & 0xFFu)) << 32) | idx;   // ascending = better
@@ -399,10 +441,7 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
         const unsigned long long mine = c2[tid];
         unsigned rank = 0;
         for (unsigned j = 0; j < m; j++) rank += c2[j] < mine;
-        if (rank < need2) {
-          const unsigned pos = atomicAdd(&s_cnt, 1u);
-          if (pos < 2048u) buf[pos] = (int)(mine & 0xFFFFFFFFu);
-        }
+        if (rank < need2) emit((unsigned)(mine & 0xFFFFFFFFu));
       }
       __syncthreads();
     } else {
@@ -414,7 +453,7 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
         for (int b = tid; b < 256; b += 1024) sh[b] = 0;
         __syncthreads();
         for (unsigned i = tid; i < n_cand; i += 1024) {
-          const unsigned key = order_key(sc[cand[i]]) & 0xFFFFFu;
+          const unsigned key = cand[i].y & 0xFFFFFu;
           if ((key & mask) == prefix) atomicAdd(&sh[(key >> sft) & dmask], 1u);
         }
         __syncthreads();
@@ -440,8 +479,8 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
         for (int b = tid; b < 256; b += 1024) sh[b] = 0;
         __syncthreads();
         for (unsigned i = tid; i < n_cand; i += 1024) {
-          const unsigned idx = (unsigned)cand[i];
-          if ((order_key(sc[idx]) & 0xFFFFFu) == T && (idx & im) == ip) atomicAdd(&sh[(idx >> shift) & 0xFFu], 1u);
+          const uint2 cd = cand[i];
+          if ((cd.y & 0xFFFFFu) == T && (cd.x & im) == ip) atomicAdd(&sh[(cd.x >> shift) & 0xFFu], 1u);
         }
         __syncthreads();
         if (tid == 0) {
@@ -461,33 +500,59 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
       }
       const unsigned idxT = ip;          // members equal to T with index <= idxT are taken
       for (unsigned i = tid; i < n_cand; i += 1024) {
-        const unsigned idx = (unsigned)cand[i];
-        const unsigned key = order_key(sc[idx]) & 0xFFFFFu;
-        if (key > T || (key == T && idx <= idxT)) {
-          const unsigned pos = atomicAdd(&s_cnt, 1u);
-          if (pos < 2048u) buf[pos] = (int)idx;
-        }
+        const unsigned idx = cand[i].x;
+        const unsigned key = cand[i].y & 0xFFFFFu;
+        if (key > T || (key == T && idx <= idxT)) emit(idx);
       }
       __syncthreads();
     }
   }
   __syncthreads();
-  const unsigned filled = min(s_cnt, 2048u);
-  // bitonic sort of the used power-of-two prefix, ascending (unused slots hold INT_MAX)
-  int P = 32;
-  while (P < (int)filled) P <<= 1;
-  for (int size = 2; size <= P; size <<= 1)
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < P / 2; i += 1024) {
-        const int lo = 2 * i - (i & (stride - 1));
-        const int hi = lo + stride;
-        const bool up = ((lo & size) == 0);
-        const int a = buf[lo], b = buf[hi];
-        if ((a > b) == up) { buf[lo] = b; buf[hi] = a; }
-      }
+  if (bm_words) {
+    // ascending read-out: every thread owns a contiguous run of bitmap words; an exclusive scan of the run
+    // populations gives each run its offset in the output
+    const int per = (bm_words + 1023) / 1024;
+    const int w0 = min(bm_words, tid * per), w1 = min(bm_words, w0 + per);
+    unsigned cnt = 0;
+    for (int w = w0; w < w1; w++) cnt += __popc(bitmap[w]);
+    sh[tid] = cnt;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      const unsigned a = tid >= o ? sh[tid - o] : 0;
+      __syncthreads();
+      sh[tid] += a;
       __syncthreads();
     }
-  for (int i = tid; i < k; i += 1024) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
+    unsigned pos = sh[tid] - cnt;
+    const unsigned total = sh[1023];
+    for (int w = w0; w < w1; w++) {
+      unsigned m = bitmap[w];
+      while (m) {
+        const int bit = __ffs(m) - 1;
+        m &= m - 1;
+        if (pos < (unsigned)k) out[pos] = w * 32 + bit;
+        pos++;
+      }
+    }
+    for (int i = tid + (int)min(total, (unsigned)k); i < k; i += 1024) out[i] = -1;
+  } else {
+    const unsigned filled = min(s_cnt, 2048u);
+    // bitonic sort of the used power-of-two prefix, ascending (unused slots hold INT_MAX)
+    int P = 32;
+    while (P < (int)filled) P <<= 1;
+    for (int size = 2; size <= P; size <<= 1)
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int i = tid; i < P / 2; i += 1024) {
+          const int lo = 2 * i - (i & (stride - 1));
+          const int hi = lo + stride;
+          const bool up = ((lo & size) == 0);
+          const int a = buf[lo], b2 = buf[hi];
+          if ((a > b2) == up) { buf[lo] = b2; buf[hi] = a; }
+        }
+        __syncthreads();
+      }
+    for (int i = tid; i < k; i += 1024) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
+  }
   for (int b = tid; b < kHistBins; b += 1024) { hist[b] = 0; fine[b] = 0; }
   if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; }
   (void)n;
@@ -496,6 +561,8 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
 // block maxima over `bs` consecutive scores; the newest (possibly partial) block is pinned to +inf
 // (attn_ref.cpp:196-202)
 __global__ void block_max_kernel(const float* sc, int len, int bs, float* out, int nb) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= nb) return;
   float m = -INFINITY;
@@ -506,10 +573,10 @@ __global__ void block_max_kernel(const float* sc, int len, int bs, float* out, i
 
 // ---------------------------------------------------------------- host side
 size_t topk_scratch_bytes(int n_max) {
-  return 2 * sizeof(unsigned) * kHistBins + 64 + sizeof(int) * 2048 + sizeof(int) * (size_t)std::max(n_max, 1);
+  return 2 * sizeof(unsigned) * kHistBins + 64 + sizeof(int) * 2048 + sizeof(uint2) * (size_t)std::max(n_max, 1);
 }
 
-// scratch layout: hist[4096] | fine[4096] | ctl (64 B) | sel[2048] | cand[n_max].  The histograms and ctl must be zero
+// scratch layout: hist[4096] | fine[4096] | ctl (64 B) | sel[2048] | cand[n_max] as (index, key) pairs.  The histograms and ctl must be zero
 // on entry; the final kernel leaves them zero again.
 int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, cudaStream_t st) {
   if (n < 0 || k <= 0 || k > 2048) return fail(kErrArg, "topk: n %d k %d (k must be 1..2048)", n, k);
@@ -519,16 +586,24 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   unsigned* fine = hist + kHistBins;
   TopkCtl* ctl = reinterpret_cast<TopkCtl*>(fine + kHistBins);
   int* sel = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ctl) + 64);
-  int* cand = sel + 2048;
+  uint2* cand = reinterpret_cast<uint2*>(sel + 2048);
   int dev = 0, sms = 0;
   MSB_CUDA(cudaGetDevice(&dev));
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   if (n > 0) {
     const int blocks = std::max(1, std::min(sms * 2, (n + 1023) / 1024));
-    if (!hist_ready) topk_hist_kernel<<<blocks, 256, 0, st>>>(sc, n, hist);
-    topk_compact_kernel<<<blocks, 256, 0, st>>>(sc, n, k, hist, fine, ctl, sel, cand);
+    if (!hist_ready) MSB_CUDA(launch_pdl(topk_hist_kernel, dim3(blocks), dim3(256), 0, st, sc, n, hist));
+    MSB_CUDA(launch_pdl(topk_compact_kernel, dim3(blocks), dim3(256), 0, st, sc, n, k, hist, fine, ctl, sel, cand));
   }
-  topk_final_kernel<<<1, 1024, 0, st>>>(sc, n, k, hist, fine, ctl, sel, cand, out);
+  // positions bitmap in shared memory for n up to 1M (128 KB); longer inputs use the sorting read-out
+  const int bm_words = n <= (1 << 20) ? std::max(1, (n + 31) / 32) : 0;
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    MSB_CUDA(cudaFuncSetAttribute(topk_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+    configured[dev & 63] = true;
+  }
+  MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl, sel, cand,
+                      out, bm_words));
   MSB_LAUNCH_CHECK("topk");
   return kOk;
 }
@@ -536,7 +611,7 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
 int index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q, float* w,
                cudaStream_t st) {
   if (heads <= 0 || !q_raw || !w_raw || !cs || !q || !w) return fail(kErrArg, "index_prep: bad arguments");
-  idx_prep_kernel<<<(heads + 3) / 4, 128, 0, st>>>(q_raw, w_raw, cs, actq, heads, q, w);
+  MSB_CUDA(launch_pdl(idx_prep_kernel, dim3((heads + 3) / 4), dim3(128), 0, st, q_raw, w_raw, cs, actq, heads, q, w));
   MSB_LAUNCH_CHECK("idx_prep_kernel");
   return kOk;
 }
@@ -554,16 +629,16 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len};
   if (key_type == kKeyFp8 && !exact_query) {
     const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));
-    if (heads == 64) idx_score_fp8_kernel<64><<<grid, 384, 0, st>>>(p);
-    else idx_score_fp8_kernel<32><<<grid, 384, 0, st>>>(p);
+    if (heads == 64) MSB_CUDA(launch_pdl(idx_score_fp8_kernel<64>, dim3(grid), dim3(384), 0, st, p));
+    else MSB_CUDA(launch_pdl(idx_score_fp8_kernel<32>, dim3(grid), dim3(384), 0, st, p));
   } else {
     const int grid = std::max(1, std::min(sms, (len + 32 * 8 - 1) / (32 * 8)));
     if (key_type == kKeyFp8) {
-      if (heads == 64) idx_score_f16_kernel<64, true, true><<<grid, 256, 0, st>>>(p);
-      else idx_score_f16_kernel<32, true, true><<<grid, 256, 0, st>>>(p);
+      if (heads == 64) MSB_CUDA(launch_pdl(idx_score_f16_kernel<64, true, true>, dim3(grid), dim3(256), 0, st, p));
+      else MSB_CUDA(launch_pdl(idx_score_f16_kernel<32, true, true>, dim3(grid), dim3(256), 0, st, p));
     } else {
-      if (heads == 64) idx_score_f16_kernel<64, false, true><<<grid, 256, 0, st>>>(p);
-      else idx_score_f16_kernel<32, false, true><<<grid, 256, 0, st>>>(p);
+      if (heads == 64) MSB_CUDA(launch_pdl(idx_score_f16_kernel<64, false, true>, dim3(grid), dim3(256), 0, st, p));
+      else MSB_CUDA(launch_pdl(idx_score_f16_kernel<32, false, true>, dim3(grid), dim3(256), 0, st, p));
     }
   }
   MSB_LAUNCH_CHECK("idx_score_kernel");
@@ -573,7 +648,7 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
 int block_max(const float* sc, int len, int bs, float* out, cudaStream_t st) {
   if (len <= 0 || bs <= 0 || !sc || !out) return fail(kErrArg, "block_max: bad arguments");
   const int nb = (len + bs - 1) / bs;
-  block_max_kernel<<<(nb + 255) / 256, 256, 0, st>>>(sc, len, bs, out, nb);
+  MSB_CUDA(launch_pdl(block_max_kernel, dim3((nb + 255) / 256), dim3(256), 0, st, sc, len, bs, out, nb));
   MSB_LAUNCH_CHECK("block_max_kernel");
   return kOk;
 }

@@ -1,16 +1,21 @@
 // Decode matvec family: y[n][rows] (+)= X[n][cols (* groups)] . W^T with W as raw GGUF block rows.
-// Replaces the reference's q_mv / q_mvn Metal kernels (src/kernels/quant_mv.metal:7-39,148-202) behind
-// ms::q::encode_matvec / encode_matvec_n (src/kernels/quant.hpp:27-35, quant.mm:70-95,129-156).
+// Replaces the reference's q_mv / q_mv_rn / q_mvn Metal kernels (src/kernels/quant_mv.metal:7-39,68-129,148-202)
+// behind ms::q::encode_matvec / encode_matvec_rmsnorm / encode_matvec_n (src/kernels/quant.hpp:19-35,
+// quant.mm:70-156).
 //
 // Layout of the work: persistent blocks (16 consumer warps + 1 TMA producer warp); block b of group g walks row tiles
-// b, b + blocks_per_group, ... of that group.  A row tile is R = NW * (32 / LPR) * NR rows; each tile is streamed in K chunks through the TMA ring
-// (stream_pipe.cuh).  LPR lanes split the units of a row, partial sums are combined with warp shuffles in a fixed
-// order, so a row's result does not depend on the launch shape of other rows.
+// b, b + blocks_per_group, ... of that group.  A tile is R consecutive rows brought in as ONE contiguous bulk copy
+// (rows too long for a ring slot are streamed in K chunks, one large copy per row).  Short rows: each warp owns
+// G * NR whole rows (LPR lanes per row).  Long rows: KS warps share a row, each taking a contiguous run of units; their
+// partial sums meet in shared memory and are added in warp order.  A row's result never depends on which block
+// computed the other rows.
 #include <algorithm>
 #include <cstdlib>
 #include "stream_pipe.cuh"
 
 namespace msb {
+
+constexpr int kMvNW = 16;
 
 struct MvParams {
   const uint8_t* W;
@@ -23,28 +28,32 @@ struct MvParams {
   int64_t x_stride, y_stride;   // elements between activation columns / output columns
   uint32_t row_bytes;
   int accumulate;
+  int probe_skip_compute;       // tuning probe: stream the tiles, skip the arithmetic
   int units;                    // cols / 32
-  int chunk_units;              // units per staged piece
+  int ks;                       // warps sharing one row (1 = each warp owns whole rows)
+  int tile_rows;                // R
+  int chunk_units;              // units per staged piece (== units: whole rows, the tile is one contiguous copy)
   int blocks_per_group;
   int tiles_per_group;
   int stages;
-  uint32_t pitch;
+  uint32_t pitch;               // shared-memory distance between staged rows
   uint32_t stage_bytes;
   Tables tb;
 };
 
 struct MvSmemHead {
   uint64_t full[kMaxStages], empty[kMaxStages];
-  uint64_t lutbar;
+  uint64_t lutbar, tilebar;
   int abort_flag;
-  const uint8_t* src[1];
   float red[32];
+  float part[2][kMvNW][4];
 };
 
-template <int T, int LPR, int NR, int NC, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, 1) matvec_kernel(const MvParams p) {
+template <int T, int LPR, int NR, int NC>
+__global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvParams p) {
+  constexpr int NW = kMvNW;
   constexpr int G = 32 / LPR;
-  constexpr int R = NW * G * NR;
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t smem[];
   // [head][luts][xq columns][ring slots]
   MvSmemHead* hd = reinterpret_cast<MvSmemHead*>(smem);
@@ -64,10 +73,11 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) matvec_kernel(const MvParams
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = blockIdx.x / p.blocks_per_group, slot = blockIdx.x % p.blocks_per_group;
   ring_init(ring, tid, NW);
-  if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_fence_init(); hd->src[0] = nullptr; }
+  if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, NW); mbar_fence_init(); }
   __syncthreads();
   LaneLuts L;
   const bool luts_ok = load_luts(lut, T == IQ1_S, T == IQ2_XXS, T == IQ4_NL, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
+  pdl_wait();     // everything above is independent of the previous kernel; x (and y) are not
   // activation of this block's group -> shared (fixed point, or fp32 for dense weights), optionally RMS-normalised
 #pragma unroll
   for (int c = 0; c < NC; c++) {
@@ -104,21 +114,27 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) matvec_kernel(const MvParams
   __syncthreads();
   if (!luts_ok) return;
 
-  const int nchunks = (U + p.chunk_units - 1) / p.chunk_units;
+  const int R = p.tile_rows, KS = p.ks;
+  const bool whole = p.chunk_units >= U;             // whole rows per piece: the tile is one contiguous copy
+  const int nchunks = whole ? 1 : (U + p.chunk_units - 1) / p.chunk_units;
   const uint8_t* Wg = p.W + (size_t)group * p.rows_per_group * p.row_bytes;
   uint32_t n = 0;
   if (warp == NW) {
     // ---------------- producer warp
     const uint8_t* srcv[1];
     Piece pc;
-    pc.src = srcv; pc.nsrc = 1; pc.rows_per_src = R; pc.row_stride = p.row_bytes;
+    pc.src = srcv; pc.nsrc = 1; pc.row_stride = p.row_bytes;
     for (int t = slot; t < p.tiles_per_group; t += p.blocks_per_group) {
-      const int r0 = t * R;
-      pc.nrows = min(R, p.rows_per_group - r0);
+      const int r0 = t * R, nrows = min(R, p.rows_per_group - r0);
       for (int c = 0; c < nchunks; c++, n++) {
-        const int u0 = c * p.chunk_units, nu = min(p.chunk_units, U - u0);
-        srcv[0] = Wg + (size_t)r0 * p.row_bytes + units_bytes(T, u0);
-        pc.bytes = units_bytes(T, nu);
+        if (whole) {
+          srcv[0] = Wg + (size_t)r0 * p.row_bytes;
+          pc.rows_per_src = 1; pc.nrows = 1; pc.bytes = (uint32_t)nrows * p.row_bytes;
+        } else {
+          const int u0 = c * p.chunk_units, nu = min(p.chunk_units, U - u0);
+          srcv[0] = Wg + (size_t)r0 * p.row_bytes + units_bytes(T, u0);
+          pc.rows_per_src = R; pc.nrows = nrows; pc.bytes = units_bytes(T, nu);
+        }
         if (!produce_piece(ring, n, pc, p.pitch, lane)) return;
       }
     }
@@ -126,7 +142,11 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) matvec_kernel(const MvParams
   }
   // ---------------- consumer warps
   const int grp = lane / LPR, li = lane % LPR;
-  const int lr0 = (warp * G + grp) * NR;
+  // rows of this lane group inside the tile, and (KS > 1) this warp's share of the row's units
+  const int lr0 = KS > 1 ? warp / KS : (warp * G + grp) * NR;
+  const int kpart = KS > 1 ? warp % KS : 0;
+  const int step = block_elems(T) == 256 ? 8 : 1;
+  uint32_t tile_count = 0;
   for (int t = slot; t < p.tiles_per_group; t += p.blocks_per_group) {
     const int r0 = t * R;
     float acc[NR][NC];
@@ -135,25 +155,52 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) matvec_kernel(const MvParams
 #pragma unroll
       for (int c = 0; c < NC; c++) acc[i][c] = 0.f;
     for (int c = 0; c < nchunks; c++, n++) {
-      const int u0 = c * p.chunk_units, nu = min(p.chunk_units, U - u0);
+      const int u0 = whole ? 0 : c * p.chunk_units, nu = whole ? U : min(p.chunk_units, U - u0);
       const uintptr_t a0 = reinterpret_cast<uintptr_t>(Wg) + (size_t)r0 * p.row_bytes + units_bytes(T, u0);
       const saddr_t slot_s = smem_u32(ring.slot(n));
+      int ua = 0, ub = nu;                           // this warp's run of units inside the piece
+      if (KS > 1) {
+        const int per = ((nu + KS * step - 1) / (KS * step)) * step;
+        ua = min(nu, kpart * per); ub = min(nu, ua + per);
+      }
       saddr_t rowp[NR];
 #pragma unroll
-      for (int i = 0; i < NR; i++)
-        rowp[i] = slot_s + (uint32_t)(lr0 + i) * p.pitch + (uint32_t)((a0 + (uintptr_t)(lr0 + i) * p.row_bytes) & 15u);
+      for (int i = 0; i < NR; i++) {
+        const uint32_t mis = whole ? (uint32_t)(a0 & 15u) : (uint32_t)((a0 + (uintptr_t)(lr0 + i) * p.row_bytes) & 15u);
+        rowp[i] = slot_s + (uint32_t)(lr0 + i) * p.pitch + mis + (uint32_t)units_bytes(T, ua);
+      }
       if (!consumer_wait(ring, n)) return;
-      consume_rows<T, LPR, NR, NC>(rowp, li, xq, u0, nu, L, acc);
+      if (ub > ua && !p.probe_skip_compute) consume_rows<T, LPR, NR, NC>(rowp, li, xq, u0 + ua, ub - ua, L, acc);
       consumer_release(ring, n, lane);
     }
-#pragma unroll
-    for (int i = 0; i < NR; i++) {
+    if (KS > 1) {
+      // NR == 1, LPR == 32: one partial per warp and column; the first warp of the row adds them in warp order
+      const int pb = tile_count & 1;
 #pragma unroll
       for (int c = 0; c < NC; c++) {
-        const float v = group_sum<LPR>(acc[i][c]);
-        if (li == 0 && r0 + lr0 + i < p.rows_per_group) {
-          float* yp = p.y + (size_t)c * p.y_stride + (size_t)group * p.rows_per_group + r0 + lr0 + i;
-          *yp = p.accumulate ? *yp + v : v;
+        const float v = group_sum<32>(acc[0][c]);
+        if (lane == 0) hd->part[pb][warp][c] = v;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hd->tilebar);
+      if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return;
+      if (kpart == 0 && lane < NC && r0 + lr0 < p.rows_per_group) {
+        float v = 0.f;
+        for (int k = 0; k < KS; k++) v += hd->part[pb][warp + k][lane];
+        float* yp = p.y + (size_t)lane * p.y_stride + (size_t)group * p.rows_per_group + r0 + lr0;
+        *yp = p.accumulate ? *yp + v : v;
+      }
+      tile_count++;
+    } else {
+#pragma unroll
+      for (int i = 0; i < NR; i++) {
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+          const float v = group_sum<LPR>(acc[i][c]);
+          if (li == 0 && r0 + lr0 + i < p.rows_per_group) {
+            float* yp = p.y + (size_t)c * p.y_stride + (size_t)group * p.rows_per_group + r0 + lr0 + i;
+            *yp = p.accumulate ? *yp + v : v;
+          }
         }
       }
     }
@@ -162,7 +209,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) matvec_kernel(const MvParams
 
 // ---------------------------------------------------------------- host side
 namespace {
-constexpr int kNW = 16;
 
 // lanes per row: the largest of 32/16/8 that wastes the fewest lane iterations on this row length
 int pick_lpr(int units) {
@@ -177,57 +223,85 @@ int pick_lpr(int units) {
 }
 
 template <int T, int LPR, int NR, int NC>
-int launch_cfg(MvParams& p, cudaStream_t st, int dev, int sms) {
-  constexpr int G = 32 / LPR, R = kNW * G * NR;
-  const size_t fixed = ((sizeof(MvSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(T) + (size_t)NC * xq_bytes(p.units, is_dense(T)) + 128;
-  if (fixed + 2 * 4096 > (size_t)kSmemLimit)
-    return fail(kErrLimit, "matvec: cols %d x n %d does not fit in shared memory", p.cols, p.n);
-  int stages = kMaxStages, chunk = 0;
-  size_t slot_bytes = 0;
-  static const int env_chunk = getenv("MSB_MV_CHUNK") ? atoi(getenv("MSB_MV_CHUNK")) : 0;   // tuning probes
-  static const int env_stages = getenv("MSB_MV_STAGES") ? atoi(getenv("MSB_MV_STAGES")) : 0;
-  for (stages = env_stages ? env_stages : kMaxStages; stages >= 2; stages--) {
-    slot_bytes = std::min<size_t>(((size_t)kSmemLimit - fixed) / stages, env_chunk ? 200 * 1024 : 48 * 1024) & ~(size_t)127;
-    chunk = chunk_units_for(T, p.units, R, LPR, slot_bytes);
-    if (env_chunk && chunk > env_chunk) chunk = env_chunk;
-    if (chunk > 0) break;
-  }
-  if (chunk <= 0) return fail(kErrLimit, "matvec: no staging shape fits (type %s cols %d)", type_name(T), p.cols);
-  p.chunk_units = chunk;
-  p.stages = stages;
-  p.pitch = piece_pitch(units_bytes(T, chunk));
-  p.stage_bytes = (uint32_t)slot_bytes;
-  p.tiles_per_group = (p.rows_per_group + R - 1) / R;
-  p.blocks_per_group = std::max(1, std::min(p.tiles_per_group, sms / p.groups));
+int launch_cfg(MvParams& p, size_t fixed, int stages, size_t slot_bytes, cudaStream_t st, int dev) {
   const size_t smem = fixed + (size_t)stages * slot_bytes;
-  auto kern = matvec_kernel<T, LPR, NR, NC, kNW>;
+  auto kern = matvec_kernel<T, LPR, NR, NC>;
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
     MSB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     configured[dev & 63] = true;
   }
-  kern<<<p.blocks_per_group * p.groups, (kNW + 1) * 32, smem, st>>>(p);
+  p.stages = stages;
+  p.stage_bytes = (uint32_t)slot_bytes;
+  MSB_CUDA(launch_pdl(kern, dim3(p.blocks_per_group * p.groups), dim3((kMvNW + 1) * 32), smem, st, p));
   MSB_LAUNCH_CHECK("matvec_kernel");
   return kOk;
 }
 
-// rows per lane group: as many as the type's decode cost warrants (they share the activation registers), but few
-// enough that the matrix still spreads over every SM
+// Tile shape: as many consecutive whole rows as fit one ring slot (one contiguous copy), bounded by what the type's
+// decode cost warrants and by the need to spread the matrix over every SM.
 template <int T, int LPR, int NC>
 int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
   constexpr int G = 32 / LPR;
   constexpr int kMaxNR = (T == IQ1_S || T == IQ2_XXS) ? 4 : 2;
-  const int want_tiles = 2 * sms / p.groups;
-  int nr = NC > 1 ? std::min(kMaxNR, 2) : kMaxNR;
-  while (nr > 1 && (p.rows_per_group + kNW * G * nr - 1) / (kNW * G * nr) < want_tiles) nr >>= 1;
-  if (T == F32) nr = 1;
-  static const int env_nr = getenv("MSB_MV_NR") ? atoi(getenv("MSB_MV_NR")) : 0;
-  if (env_nr) nr = env_nr;
-  if (nr >= 4) {
-    if constexpr (kMaxNR >= 4 && NC == 1) return launch_cfg<T, LPR, 4, NC>(p, st, dev, sms);
+  const size_t fixed = ((sizeof(MvSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(T) +
+                       (size_t)NC * xq_bytes(p.units, is_dense(T)) + 128;
+  if (fixed + 2 * 8192 > (size_t)kSmemLimit)
+    return fail(kErrLimit, "matvec: cols %d x n %d does not fit in shared memory", p.cols, p.n);
+  const size_t avail = (size_t)kSmemLimit - fixed;
+  static const int env_slot = getenv("MSB_MV_SLOT_KB") ? atoi(getenv("MSB_MV_SLOT_KB")) : 0;   // tuning probes
+  static const int env_stages = getenv("MSB_MV_STAGES") ? atoi(getenv("MSB_MV_STAGES")) : 0;
+  int stages = avail / 4 >= 36 * 1024 ? 4 : (avail / 3 >= 24 * 1024 ? 3 : 2);
+  if (env_stages) stages = env_stages;
+  const size_t slot = std::min<size_t>(avail / stages, (size_t)(env_slot ? env_slot : (lut_bytes_for(T) ? 56 : 72)) * 1024) & ~(size_t)127;
+  const long rows_fit = ((long)slot - 64) / (long)p.row_bytes;
+  const int want_tiles = std::max(1, sms / p.groups);
+  auto tiles_of = [&](int r) { return (p.rows_per_group + r - 1) / r; };
+  p.chunk_units = p.units;
+  p.pitch = p.row_bytes;
+  int nr = 1, ks = 1, R = 0;
+  if (rows_fit >= 1) {
+    // whole rows per warp (KS = 1, R = 16 * G * NR), largest first
+    for (int cand : {4, 2, 1}) {
+      if (cand > kMaxNR || (NC > 1 && cand > 2)) continue;
+      const int r = kMvNW * G * cand;
+      if (r <= rows_fit && (tiles_of(r) >= want_tiles || cand == 1)) { R = r; nr = cand; break; }
+    }
+    // several warps per row when whole-row tiles do not fit or leave SMs idle
+    if (LPR == 32 && (R == 0 || tiles_of(R) < want_tiles)) {
+      for (int cand : {2, 4, 8, 16}) {
+        const int r = kMvNW / cand;
+        if (r > rows_fit) continue;
+        R = r; ks = cand; nr = 1;
+        if (tiles_of(r) >= want_tiles) break;
+      }
+    }
+    if (R == 0) {   // LPR < 32 and the smallest whole-row tile does not fit: per-row chunks instead
+      nr = 1; ks = 1;
+      R = kMvNW * G;
+      const int chunk = chunk_units_for(T, p.units, R, LPR, slot);
+      if (chunk <= 0) return fail(kErrLimit, "matvec: no staging shape fits (type %s cols %d)", type_name(T), p.cols);
+      p.chunk_units = chunk;
+      p.pitch = piece_pitch(units_bytes(T, chunk));
+    }
+  } else {
+    // one row does not fit a slot: all 16 warps share a row, K streamed in chunks (one large copy each)
+    if (LPR != 32) return fail(kErrLimit, "matvec: row of %u bytes does not fit (type %s)", p.row_bytes, type_name(T));
+    ks = kMvNW; nr = 1; R = 1;
+    const int chunk = chunk_units_for(T, p.units, 1, 32 * kMvNW, slot);
+    if (chunk <= 0) return fail(kErrLimit, "matvec: no staging shape fits (type %s cols %d)", type_name(T), p.cols);
+    p.chunk_units = chunk;
+    p.pitch = piece_pitch(units_bytes(T, chunk));
   }
-  if (nr >= 2) return launch_cfg<T, LPR, 2, NC>(p, st, dev, sms);
-  return launch_cfg<T, LPR, 1, NC>(p, st, dev, sms);
+  p.tile_rows = R;
+  p.ks = ks;
+  p.tiles_per_group = tiles_of(R);
+  p.blocks_per_group = std::max(1, std::min(p.tiles_per_group, sms / p.groups));
+  if (nr >= 4) {
+    if constexpr (kMaxNR >= 4 && NC == 1) return launch_cfg<T, LPR, 4, NC>(p, fixed, stages, slot, st, dev);
+  }
+  if (nr >= 2) return launch_cfg<T, LPR, 2, NC>(p, fixed, stages, slot, st, dev);
+  return launch_cfg<T, LPR, 1, NC>(p, fixed, stages, slot, st, dev);
 }
 
 template <int T, int NC>
@@ -282,6 +356,8 @@ int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x
   p.x_stride = x_stride; p.y_stride = y_stride;
   p.row_bytes = (uint32_t)row_bytes(t, cols);
   p.accumulate = accumulate;
+  static const int env_skip = getenv("MSB_MV_SKIP") ? atoi(getenv("MSB_MV_SKIP")) : 0;
+  p.probe_skip_compute = env_skip;
   p.units = cols / 32;
   for (int c0 = 0; c0 < n;) {
     const int left = n - c0;

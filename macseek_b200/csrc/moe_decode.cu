@@ -23,7 +23,7 @@ struct MoeSmemHead {
   const uint8_t* p0[kMaxRouted];   // gate (gu kernel) or down (down kernel) of local routed slot i
   const uint8_t* p1[kMaxRouted];   // up
   const uint8_t* srcs[kMaxStages][kMaxRouted];   // per ring slot: source addresses of the staged piece
-  float part[2][kMoeNW];           // down kernel: per-warp partial sums of a tile (double-buffered)
+  float part[2][kMoeNW][2];        // per-warp partial sums of a tile (double-buffered): down: [0]; gate/up: (g, u)
 };
 
 __device__ __forceinline__ float swiglu(float g, float u, float w, float limit) {
@@ -78,73 +78,84 @@ __device__ __forceinline__ void end_of_tiles(const Ring& ring, uint32_t n, MoeSm
 }
 
 // ---------------------------------------------------------------------------------------------------- gate/up
-// A piece stages R gate rows and the same R up rows side by side; a lane group computes NR gate and NR up dot
-// products per activation load.
-template <int T, int LPR, int NR>
-__device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& ring, uint32_t& n, const MoeShape& sh,
-                                                const uint8_t* Gm, const uint8_t* Um, int r0, int U, int lane, int tile,
-                                                MoeSmemHead* hd) {
-  constexpr int Gn = 32 / LPR, R = kMoeNW * Gn * NR;
-  const uint32_t rb = (uint32_t)row_bytes(T, p.dim);
+// A tile is R rows of one expert: the gate rows arrive as one contiguous piece, the same rows of the up matrix as the
+// next.  Routed experts (cheap bytes, expensive decode): each warp owns NR whole rows.  Shared expert (long rows):
+// KS warps share a row, each a contiguous run of units; the (gate, up) partial sums meet in shared memory.
+struct GuTile { const uint8_t* G; const uint8_t* U; int r0, R, KS; uint32_t rb; float* hrow; float w; };
+
+__device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& ring, uint32_t& n, const GuTile& tl,
+                                                int lane, int tile, MoeSmemHead* hd) {
   Piece pc;
-  pc.nsrc = 2; pc.rows_per_src = R; pc.nrows = min(R, p.inter - r0); pc.row_stride = rb;
-  bool first = true;
-  for (int u0 = 0; u0 < U; u0 += sh.chunk, n++) {
-    const int nu = min(sh.chunk, U - u0);
+  pc.nsrc = 1; pc.rows_per_src = 1; pc.nrows = 1; pc.row_stride = tl.rb;
+  pc.bytes = (uint32_t)min(tl.R, p.inter - tl.r0) * tl.rb;
+  for (int m = 0; m < 2; m++, n++) {
     const int s = n % ring.stages;
-    if (first) { if (!announce_tile(ring, n, hd, tile, lane)) return false; first = false; }
+    if (m == 0) { if (!announce_tile(ring, n, hd, tile, lane)) return false; }
     else if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return false;
-    if (lane == 0) {
-      hd->srcs[s][0] = Gm + (size_t)r0 * rb + units_bytes(T, u0);
-      hd->srcs[s][1] = Um + (size_t)r0 * rb + units_bytes(T, u0);
-    }
+    if (lane == 0) hd->srcs[s][0] = (m ? tl.U : tl.G) + (size_t)tl.r0 * tl.rb;
     __syncwarp();
     pc.src = hd->srcs[s];
-    pc.bytes = units_bytes(T, nu);
-    if (!produce_piece(ring, n, pc, sh.pitch, lane)) return false;
+    if (!produce_piece(ring, n, pc, 0, lane)) return false;
   }
   return true;
 }
 
 template <int T, int LPR, int NR>
-__device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& ring, uint32_t& n, const MoeShape& sh,
-                                                const uint8_t* Gm, const uint8_t* Um, int r0, int U, int warp, int lane,
-                                                const XqSmem (&xq)[1], const LaneLuts& L, float* hrow, float w) {
-  constexpr int Gn = 32 / LPR, R = kMoeNW * Gn * NR;
-  const uint32_t rb = (uint32_t)row_bytes(T, p.dim);
+__device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& ring, uint32_t& n, const GuTile& tl, int U,
+                                                int warp, int lane, const XqSmem (&xq)[1], const LaneLuts& L,
+                                                MoeSmemHead* hd, uint32_t& tile_count) {
+  constexpr int Gn = 32 / LPR;
   const int grp = lane / LPR, li = lane % LPR;
-  const int lr0 = (warp * Gn + grp) * NR;
-  float acc[2 * NR][1];
+  const int KS = tl.KS;
+  const int lr0 = KS > 1 ? warp / KS : (warp * Gn + grp) * NR;
+  const int kpart = KS > 1 ? warp % KS : 0;
+  constexpr int step = block_elems(T) == 256 ? 8 : 1;
+  int ua = 0, ub = U;
+  if (KS > 1) {
+    const int per = ((U + KS * step - 1) / (KS * step)) * step;
+    ua = min(U, kpart * per); ub = min(U, ua + per);
+  }
+  float acc[2][NR][1];
 #pragma unroll
-  for (int i = 0; i < 2 * NR; i++) acc[i][0] = 0.f;
-  for (int u0 = 0; u0 < U; u0 += sh.chunk, n++) {
-    const int nu = min(sh.chunk, U - u0);
-    const saddr_t slot = smem_u32(ring.slot(n));
-    const uintptr_t ag = reinterpret_cast<uintptr_t>(Gm) + (size_t)r0 * rb + units_bytes(T, u0);
-    const uintptr_t au = reinterpret_cast<uintptr_t>(Um) + (size_t)r0 * rb + units_bytes(T, u0);
-    saddr_t rowp[2 * NR];
+  for (int i = 0; i < NR; i++) { acc[0][i][0] = 0.f; acc[1][i][0] = 0.f; }
 #pragma unroll
-    for (int i = 0; i < NR; i++) {
-      rowp[i] = slot + (uint32_t)(lr0 + i) * sh.pitch + (uint32_t)((ag + (uintptr_t)(lr0 + i) * rb) & 15u);
-      rowp[NR + i] = slot + (uint32_t)(R + lr0 + i) * sh.pitch + (uint32_t)((au + (uintptr_t)(lr0 + i) * rb) & 15u);
-    }
+  for (int m = 0; m < 2; m++, n++) {
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(m ? tl.U : tl.G) + (size_t)tl.r0 * tl.rb;
+    const saddr_t base = smem_u32(ring.slot(n)) + (uint32_t)(a0 & 15u) + (uint32_t)units_bytes(T, ua);
+    saddr_t rowp[NR];
+#pragma unroll
+    for (int i = 0; i < NR; i++) rowp[i] = base + (uint32_t)(lr0 + i) * tl.rb;
     if (!consumer_wait(ring, n)) return false;
-    consume_rows<T, LPR, 2 * NR, 1>(rowp, li, xq, u0, nu, L, acc);
+    if (ub > ua) consume_rows<T, LPR, NR, 1>(rowp, li, xq, ua, ub - ua, L, acc[m]);
     consumer_release(ring, n, lane);
   }
+  if (KS > 1) {
+    const int pb = tile_count & 1;
+    const float g = group_sum<32>(acc[0][0][0]), u = group_sum<32>(acc[1][0][0]);
+    if (lane == 0) { hd->part[pb][warp][0] = g; hd->part[pb][warp][1] = u; }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&hd->tilebar);
+    if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return false;
+    if (kpart == 0 && lane == 0 && tl.r0 + lr0 < p.inter) {
+      float gs = 0.f, us = 0.f;
+      for (int k = 0; k < KS; k++) { gs += hd->part[pb][warp + k][0]; us += hd->part[pb][warp + k][1]; }
+      tl.hrow[tl.r0 + lr0] = swiglu(gs, us, tl.w, p.limit);
+    }
+    tile_count++;
+  } else {
 #pragma unroll
-  for (int i = 0; i < NR; i++) {
-    const float g = group_sum<LPR>(acc[i][0]), u = group_sum<LPR>(acc[NR + i][0]);
-    if (li == 0 && r0 + lr0 + i < p.inter) hrow[r0 + lr0 + i] = swiglu(g, u, w, p.limit);
+    for (int i = 0; i < NR; i++) {
+      const float g = group_sum<LPR>(acc[0][i][0]), u = group_sum<LPR>(acc[1][i][0]);
+      if (li == 0 && tl.r0 + lr0 + i < p.inter) tl.hrow[tl.r0 + lr0 + i] = swiglu(g, u, tl.w, p.limit);
+    }
   }
   return true;
 }
 
 template <int TR, int TS, int LPR>
 __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeParams p) {
-  constexpr int Gn = 32 / LPR;
-  constexpr int NR_R = 2, NR_S = 1;
-  constexpr int R_R = kMoeNW * Gn * NR_R, R_S = kMoeNW * Gn * NR_S;
+  constexpr int NR_R = 2;
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t smem[];
   MoeSmemHead* hd = reinterpret_cast<MoeSmemHead*>(smem);
   Ring ring;
@@ -162,65 +173,69 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ring_init(ring, tid, kMoeNW);
-  if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_fence_init(); resolve_local(p, hd, p.gu_r != 0, false); }
+  if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, kMoeNW); mbar_fence_init(); }
   __syncthreads();
   LaneLuts L;
   const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
+  pdl_wait();     // the router's ids / weights and x come from the previous kernels
+  if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
   quantize_x(p.x, xq[0], tid, blockDim.x);
   __syncthreads();
   if (!luts_ok) return;
 
+  const int R_R = p.gu_r_rows, R_S = p.gu_s_rows;
   const int tiles_s = p.gu_s ? (p.inter + R_S - 1) / R_S : 0;
   const int tiles_r1 = (p.inter + R_R - 1) / R_R;
   const int ntiles = tiles_s + hd->n_local * tiles_r1;
+  const uint32_t rb_r = (uint32_t)row_bytes(TR, p.dim), rb_s = (uint32_t)row_bytes(TS, p.dim);
+  // tile id -> what to stream: shared-expert tiles first (they are the largest), then the resident routed experts
+  auto tile_of = [&](int t) {
+    GuTile tl;
+    if (t < tiles_s) {
+      tl.G = p.sgate; tl.U = p.sup; tl.r0 = t * R_S; tl.R = R_S; tl.KS = p.gu_s_ks; tl.rb = rb_s;
+      tl.hrow = p.h + (size_t)p.n_routed * p.inter; tl.w = 1.0f;
+    } else {
+      const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
+      const int k = hd->local_slot[i];
+      tl.G = hd->p0[i]; tl.U = hd->p1[i]; tl.r0 = rt * R_R; tl.R = R_R; tl.KS = 1; tl.rb = rb_r;
+      tl.hrow = p.h + (size_t)k * p.inter; tl.w = __ldg(p.weights + k);
+    }
+    return tl;
+  };
   uint32_t n = 0;
   if (warp == kMoeNW) {
-    // ---------------- producer: pull tiles (shared-expert tiles first, they are the largest)
     for (;;) {
       int t = 0;
       if (lane == 0) t = (int)atomicAdd(&p.sched[0], 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
       if (t >= ntiles) break;
-      bool ok;
-      if (t < tiles_s) {
-        ok = gu_tile_produce<TS, LPR, NR_S>(p, ring, n, p.gu_shared, p.sgate, p.sup, t * R_S, U, lane, t, hd);
-      } else {
-        const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
-        ok = gu_tile_produce<TR, LPR, NR_R>(p, ring, n, p.gu_routed, hd->p0[i], hd->p1[i], rt * R_R, U, lane, t, hd);
-      }
-      if (!ok) return;
+      if (!gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
     }
     end_of_tiles(ring, n, hd, p.sched, lane);
     return;
   }
-  // ---------------- consumers
+  uint32_t tile_count = 0;
   for (;;) {
     if (!consumer_wait(ring, n)) return;
     const int t = *reinterpret_cast<volatile int*>(&hd->meta[n % ring.stages]);
     if (t < 0) return;
-    bool ok;
-    if (t < tiles_s) {
-      ok = gu_tile_consume<TS, LPR, NR_S>(p, ring, n, p.gu_shared, p.sgate, p.sup, t * R_S, U, warp, lane, xq, L,
-                                          p.h + (size_t)p.n_routed * p.inter, 1.0f);
-    } else {
-      const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
-      const int k = hd->local_slot[i];
-      ok = gu_tile_consume<TR, LPR, NR_R>(p, ring, n, p.gu_routed, hd->p0[i], hd->p1[i], rt * R_R, U, warp, lane, xq, L,
-                                          p.h + (size_t)k * p.inter, __ldg(p.weights + k));
-    }
+    const GuTile tl = tile_of(t);
+    const bool ok = t < tiles_s ? gu_tile_consume<TS, LPR, 1>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count)
+                                : gu_tile_consume<TR, LPR, NR_R>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count);
     if (!ok) return;
   }
 }
 
 // ---------------------------------------------------------------------------------------------------- down
-// Tile = 8 output rows.  One piece stages those 8 rows of every resident routed expert's down matrix side by side,
-// the next piece(s) the shared expert's rows.  Two warps share a row: the even warp takes the even sources (and the
-// first half of the shared expert's units), the odd warp the rest; the two partial sums meet in shared memory and
-// are added in a fixed order.
+// Tile = 8 output rows.  The first piece stages those 8 rows of every resident routed expert's down matrix (one
+// contiguous copy per expert, side by side), the second the shared expert's rows.  Two warps share a row: the even
+// warp takes the even sources (and the first half of the shared expert's units), the odd warp the rest; the two
+// partial sums meet in shared memory and are added in a fixed order.
 template <int TR, int TS, int LPR>
 __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const MoeParams p) {
-  static_assert(LPR == 32 || LPR == 16 || LPR == 8, "lanes per row");
   constexpr int R = kMoeNW / 2;
+  constexpr int Gn = 32 / LPR;
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t smem[];
   MoeSmemHead* hd = reinterpret_cast<MoeSmemHead*>(smem);
   Ring ring;
@@ -239,13 +254,12 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ring_init(ring, tid, kMoeNW);
-  if (tid == 0) {
-    mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, kMoeNW); mbar_fence_init();
-    resolve_local(p, hd, p.d_r != 0, true);
-  }
+  if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, kMoeNW); mbar_fence_init(); }
   __syncthreads();
   LaneLuts L;
   const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
+  pdl_wait();     // h comes from the gate/up kernel
+  if (tid == 0) resolve_local(p, hd, p.d_r != 0, true);
   quantize_x(p.h, xq[0], tid, blockDim.x);
   __syncthreads();
   if (!luts_ok) return;
@@ -260,33 +274,31 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
       if (lane == 0) t = (int)atomicAdd(&p.sched[0], 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
       if (t >= ntiles) break;
-      const int r0 = t * R;
+      const int r0 = t * R, nrows = min(R, p.dim - r0);
       Piece pc;
-      pc.rows_per_src = R; pc.nrows = min(R, p.dim - r0);
+      pc.rows_per_src = 1; pc.nrows = 1;
       bool first = true;
       auto slot_ready = [&](int s) {
         if (first) { first = false; return announce_tile(ring, n, hd, t, lane); }
         return mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty);
       };
       if (n_local > 0) {
-        for (int u0 = 0; u0 < Ui; u0 += p.d_routed.chunk, n++) {
-          const int nu = min(p.d_routed.chunk, Ui - u0), s = n % ring.stages;
-          if (!slot_ready(s)) return;
-          for (int e = lane; e < n_local; e += 32) hd->srcs[s][e] = hd->p0[e] + (size_t)r0 * rb_r + units_bytes(TR, u0);
-          __syncwarp();
-          pc.src = hd->srcs[s]; pc.nsrc = n_local; pc.row_stride = rb_r; pc.bytes = units_bytes(TR, nu);
-          if (!produce_piece(ring, n, pc, p.d_routed.pitch, lane)) return;
-        }
+        const int s = n % ring.stages;
+        if (!slot_ready(s)) return;
+        for (int e = lane; e < n_local; e += 32) hd->srcs[s][e] = hd->p0[e] + (size_t)r0 * rb_r;
+        __syncwarp();
+        pc.src = hd->srcs[s]; pc.nsrc = n_local; pc.row_stride = rb_r; pc.bytes = (uint32_t)nrows * rb_r;
+        if (!produce_piece(ring, n, pc, p.d_src_pitch, lane)) return;
+        n++;
       }
       if (p.d_s) {
-        for (int u0 = 0; u0 < Ui; u0 += p.d_shared.chunk, n++) {
-          const int nu = min(p.d_shared.chunk, Ui - u0), s = n % ring.stages;
-          if (!slot_ready(s)) return;
-          if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s + units_bytes(TS, u0);
-          __syncwarp();
-          pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s; pc.bytes = units_bytes(TS, nu);
-          if (!produce_piece(ring, n, pc, p.d_shared.pitch, lane)) return;
-        }
+        const int s = n % ring.stages;
+        if (!slot_ready(s)) return;
+        if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s;
+        __syncwarp();
+        pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s; pc.bytes = (uint32_t)nrows * rb_s;
+        if (!produce_piece(ring, n, pc, 0, lane)) return;
+        n++;
       }
     }
     end_of_tiles(ring, n, hd, p.sched, lane);
@@ -294,7 +306,6 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   }
   const int row = warp >> 1, half = warp & 1;
   const int grp = lane / LPR, li = lane % LPR;   // LPR < 32: lane groups take alternate sources / unit runs
-  constexpr int Gn = 32 / LPR;
   uint32_t tile_count = 0;
   for (;;) {
     if (!consumer_wait(ring, n)) return;
@@ -303,46 +314,42 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
     const int r0 = t * R;
     float acc[1][1] = {{0.f}};
     if (n_local > 0) {
-      for (int u0 = 0; u0 < Ui; u0 += p.d_routed.chunk, n++) {
-        const int nu = min(p.d_routed.chunk, Ui - u0);
-        if (!consumer_wait(ring, n)) return;
-        const saddr_t slot = smem_u32(ring.slot(n));
-        for (int e = half * Gn + grp; e < n_local; e += 2 * Gn) {
-          const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)(r0 + row) * rb_r + units_bytes(TR, u0);
-          const saddr_t rowp[1] = {slot + (uint32_t)(e * R + row) * p.d_routed.pitch + (uint32_t)(a & 15u)};
-          consume_rows<TR, LPR, 1, 1>(rowp, li, xq, hd->local_slot[e] * Ui + u0, nu, L, acc);
-        }
-        consumer_release(ring, n, lane);
+      if (!consumer_wait(ring, n)) return;
+      const saddr_t slot = smem_u32(ring.slot(n));
+      for (int e = half * Gn + grp; e < n_local; e += 2 * Gn) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)r0 * rb_r;
+        const saddr_t rowp[1] = {slot + (uint32_t)e * p.d_src_pitch + (uint32_t)(a & 15u) + (uint32_t)row * rb_r};
+        consume_rows<TR, LPR, 1, 1>(rowp, li, xq, hd->local_slot[e] * Ui, Ui, L, acc);
       }
+      consumer_release(ring, n, lane);
+      n++;
     }
     if (p.d_s) {
-      for (int u0 = 0; u0 < Ui; u0 += p.d_shared.chunk, n++) {
-        const int nu = min(p.d_shared.chunk, Ui - u0);
-        if (!consumer_wait(ring, n)) return;
-        const saddr_t slot = smem_u32(ring.slot(n));
-        const uintptr_t a = reinterpret_cast<uintptr_t>(p.sdown) + (size_t)(r0 + row) * rb_s + units_bytes(TS, u0);
-        // the 2 * Gn lane groups that share this row split the chunk's units into equal runs of whole super-blocks
-        const int parts = 2 * Gn, me = half * Gn + grp;
-        const int step = block_elems(TS) == 256 ? 8 : 1;
-        const int per = ((nu + parts * step - 1) / (parts * step)) * step;
-        const int ua = min(nu, me * per), ub = min(nu, ua + per);
-        if (ub > ua) {
-          const saddr_t rowp[1] = {slot + (uint32_t)row * p.d_shared.pitch + (uint32_t)(a & 15u) + (uint32_t)units_bytes(TS, ua)};
-          consume_rows<TS, LPR, 1, 1>(rowp, li, xq, p.n_routed * Ui + u0 + ua, ub - ua, L, acc);
-        }
-        consumer_release(ring, n, lane);
+      if (!consumer_wait(ring, n)) return;
+      const saddr_t slot = smem_u32(ring.slot(n));
+      const uintptr_t a = reinterpret_cast<uintptr_t>(p.sdown) + (size_t)r0 * rb_s;
+      // the 2 * Gn lane groups that share this row split its units into equal runs of whole super-blocks
+      const int parts = 2 * Gn, me = half * Gn + grp;
+      constexpr int step = block_elems(TS) == 256 ? 8 : 1;
+      const int per = ((Ui + parts * step - 1) / (parts * step)) * step;
+      const int ua = min(Ui, me * per), ub = min(Ui, ua + per);
+      if (ub > ua) {
+        const saddr_t rowp[1] = {slot + (uint32_t)(a & 15u) + (uint32_t)row * rb_s + (uint32_t)units_bytes(TS, ua)};
+        consume_rows<TS, LPR, 1, 1>(rowp, li, xq, p.n_routed * Ui + ua, ub - ua, L, acc);
       }
+      consumer_release(ring, n, lane);
+      n++;
     }
     // combine: lane groups inside the warp (fixed order), then the two warps of the row
     float v = group_sum<LPR>(acc[0][0]);
 #pragma unroll
     for (int o = LPR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     const int pb = tile_count & 1;
-    if (lane == 0) hd->part[pb][warp] = v;
+    if (lane == 0) hd->part[pb][warp][0] = v;
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->tilebar);
     if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return;
-    if (half == 0 && lane == 0 && r0 + row < p.dim) p.y[r0 + row] += hd->part[pb][warp] + hd->part[pb][warp + 1];
+    if (half == 0 && lane == 0 && r0 + row < p.dim) p.y[r0 + row] += hd->part[pb][warp][0] + hd->part[pb][warp + 1][0];
     tile_count++;
   }
 }
@@ -352,15 +359,6 @@ namespace {
 
 bool routed_type_ok(int t) { return t == IQ1_S || t == IQ2_XXS; }
 bool shared_type_ok(int t) { return t == Q6_K || t == Q8_0; }
-
-// staged piece shape for `rows` row pieces of `units` units of type t within a slot of slot_bytes
-bool shape_for(int t, int units, int rows, int lpr, size_t slot_bytes, MoeShape* out) {
-  const int chunk = chunk_units_for(t, units, rows, lpr, slot_bytes);
-  if (chunk <= 0) return false;
-  out->chunk = chunk;
-  out->pitch = piece_pitch(units_bytes(t, chunk));
-  return true;
-}
 
 int lpr_for(int units) {
   for (int lpr : {32, 16, 8})
@@ -379,25 +377,35 @@ int set_smem(K kern, int dev, bool* done) {
 
 template <int TR, int TS, int LPR>
 int launch_gu(MoeParams& p, int sms, int dev, cudaStream_t st) {
-  constexpr int Gn = 32 / LPR, R_R = kMoeNW * Gn * 2, R_S = kMoeNW * Gn * 1;
+  constexpr int Gn = 32 / LPR;
   const int U = p.dim / 32;
   const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false) + 128;
-  for (int stages = kMaxStages; stages >= 2; stages--) {
-    const size_t slot = std::min<size_t>(((size_t)kSmemLimit - fixed) / stages, 48 * 1024) & ~(size_t)127;
-    if (!shape_for(TR, U, 2 * R_R, LPR, slot, &p.gu_routed) || !shape_for(TS, U, 2 * R_S, LPR, slot, &p.gu_shared)) continue;
-    p.stages = stages;
-    p.stage_bytes = (uint32_t)slot;
-    auto kern = moe_gu_kernel<TR, TS, LPR>;
-    static bool done[64] = {};
-    int rc = set_smem(kern, dev, done);
-    if (rc) return rc;
-    const int tiles = (p.gu_s ? (p.inter + R_S - 1) / R_S : 0) + (p.gu_r ? p.n_routed : 0) * ((p.inter + R_R - 1) / R_R);
-    const int grid = std::max(1, std::min(sms, tiles));
-    kern<<<grid, (kMoeNW + 1) * 32, fixed + (size_t)stages * slot, st>>>(p);
-    MSB_LAUNCH_CHECK("moe_gu_kernel");
-    return kOk;
+  if (fixed + 3 * 8192 > (size_t)kSmemLimit) return fail(kErrLimit, "moe_decode: dim %d does not fit in shared memory", p.dim);
+  const int stages = 3;
+  const size_t slot = (((size_t)kSmemLimit - fixed) / stages) & ~(size_t)127;
+  const size_t rb_r = row_bytes(TR, p.dim), rb_s = row_bytes(TS, p.dim);
+  // routed tiles: every warp owns 2 whole rows per lane group
+  p.gu_r_rows = kMoeNW * Gn * 2;
+  if ((size_t)p.gu_r_rows * rb_r + 64 > slot) return fail(kErrLimit, "moe_decode: routed gate/up tile does not fit (dim %d)", p.dim);
+  // shared tiles: as many whole rows as fit, several warps per row when the rows are long
+  p.gu_s_ks = 0;
+  if ((size_t)kMoeNW * Gn * rb_s + 64 <= slot) { p.gu_s_rows = kMoeNW * Gn; p.gu_s_ks = 1; }
+  else if (LPR == 32) {
+    for (int ks : {2, 4, 8, 16})
+      if ((size_t)(kMoeNW / ks) * rb_s + 64 <= slot) { p.gu_s_rows = kMoeNW / ks; p.gu_s_ks = ks; break; }
   }
-  return fail(kErrLimit, "moe_decode: gate/up staging does not fit (dim %d)", p.dim);
+  if (!p.gu_s_ks) return fail(kErrLimit, "moe_decode: shared gate/up tile does not fit (dim %d)", p.dim);
+  p.stages = stages;
+  p.stage_bytes = (uint32_t)slot;
+  auto kern = moe_gu_kernel<TR, TS, LPR>;
+  static bool done[64] = {};
+  int rc = set_smem(kern, dev, done);
+  if (rc) return rc;
+  const int tiles = (p.gu_s ? (p.inter + p.gu_s_rows - 1) / p.gu_s_rows : 0) +
+                    (p.gu_r ? p.n_routed : 0) * ((p.inter + p.gu_r_rows - 1) / p.gu_r_rows);
+  MSB_CUDA(launch_pdl(kern, dim3(std::max(1, std::min(sms, tiles))), dim3((kMoeNW + 1) * 32), fixed + (size_t)stages * slot, st, p));
+  MSB_LAUNCH_CHECK("moe_gu_kernel");
+  return kOk;
 }
 
 template <int TR, int TS, int LPR>
@@ -405,10 +413,14 @@ int launch_down(MoeParams& p, int sms, int dev, cudaStream_t st) {
   constexpr int R = kMoeNW / 2;
   const int Ui = p.inter / 32, U = (p.n_routed + 1) * Ui;
   const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false) + 128;
+  const size_t rb_r = row_bytes(TR, p.inter), rb_s = row_bytes(TS, p.inter);
+  p.d_rows = R;
+  p.d_src_pitch = (uint32_t)((R * rb_r + 15 + 16 + 15) & ~(size_t)15);
+  const size_t need = std::max((size_t)std::max(1, p.n_routed) * p.d_src_pitch, R * rb_s + 64);
   for (int stages = kMaxStages; stages >= 2; stages--) {
-    if (fixed + 8192 > (size_t)kSmemLimit) break;
-    const size_t slot = std::min<size_t>(((size_t)kSmemLimit - fixed) / stages, 48 * 1024) & ~(size_t)127;
-    if (!shape_for(TR, Ui, R * std::max(1, p.n_routed), LPR, slot, &p.d_routed) || !shape_for(TS, Ui, R, LPR, slot, &p.d_shared)) continue;
+    if (fixed + (size_t)stages * need > (size_t)kSmemLimit) continue;
+    const size_t slot = std::min<size_t>(((size_t)kSmemLimit - fixed) / stages, need + 1024) & ~(size_t)127;
+    if (slot < need) continue;
     p.stages = stages;
     p.stage_bytes = (uint32_t)slot;
     auto kern = moe_down_kernel<TR, TS, LPR>;
@@ -416,7 +428,7 @@ int launch_down(MoeParams& p, int sms, int dev, cudaStream_t st) {
     int rc = set_smem(kern, dev, done);
     if (rc) return rc;
     const int tiles = (p.dim + R - 1) / R;
-    kern<<<std::max(1, std::min(sms, tiles)), (kMoeNW + 1) * 32, fixed + (size_t)stages * slot, st>>>(p);
+    MSB_CUDA(launch_pdl(kern, dim3(std::max(1, std::min(sms, tiles))), dim3((kMoeNW + 1) * 32), fixed + (size_t)stages * slot, st, p));
     MSB_LAUNCH_CHECK("moe_down_kernel");
     return kOk;
   }

@@ -7,7 +7,6 @@ namespace msb {
 constexpr int kMaxRouted = 16;
 constexpr int kMoeNW = 16;
 
-struct MoeShape { int chunk; uint32_t pitch; };   // staged piece shape for one (type, K) pair
 
 struct MoeParams {
   int dim, inter, n_routed, has_shared;
@@ -25,7 +24,11 @@ struct MoeParams {
   float* h;                               // [n_routed + 1][inter]
   unsigned* sched;                        // [2] tile counter, finished-block counter (zero between launches)
   float limit;
-  MoeShape gu_routed, gu_shared, d_routed, d_shared;
+  // tile shapes (whole rows, every piece one contiguous bulk copy per source)
+  int gu_r_rows;                          // routed gate/up tile rows (each warp owns whole rows)
+  int gu_s_rows, gu_s_ks;                 // shared gate/up tile rows, warps sharing a row
+  int d_rows;                             // down tile rows (two warps share a row)
+  uint32_t d_src_pitch;                   // shared-memory distance between the experts' row blocks of a down piece
   uint32_t stage_bytes;
   int stages;
   Tables tb;

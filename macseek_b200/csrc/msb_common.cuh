@@ -26,6 +26,24 @@ int cuda_fail(cudaError_t e, const char* what);
     if (_e != cudaSuccess) return ::msb::cuda_fail(_e, name);             \
   } while (0)
 
+// Launch with programmatic dependent launch allowed: the grid may be scheduled while the previous kernel of the stream
+// is still draining; every kernel of this library calls pdl_wait() before it touches anything a previous kernel wrote
+// (and before it writes anything), so only set-up work overlaps.  MSB_PDL=0 turns the attribute off.
+bool pdl_enabled();
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ggml type ids (the reference's ms::q::QType, src/kernels/quant_types.hpp:10-12)
 enum QType : int { F32 = 0, F16 = 1, Q8_0 = 8, Q5_K = 13, Q6_K = 14, IQ2_XXS = 16, IQ1_S = 19, IQ4_NL = 20, BF16 = 30 };
 __host__ __device__ constexpr int block_elems(int t) {

@@ -37,18 +37,17 @@ __host__ __device__ constexpr int units_bytes(int t, int units) {
 // Every hot-path shared-memory read goes through explicit ld.shared with 32-bit shared-space addresses: pointers that
 // travel through structs lose their address space and would otherwise compile to generic loads.
 typedef uint32_t saddr_t;
-__device__ __forceinline__ uint32_t lds_u8(saddr_t a) { uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint32_t lds_u16(saddr_t a) { uint32_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint32_t lds_u32(saddr_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint2 lds_u64(saddr_t a) {
-  uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v;
-}
-__device__ __forceinline__ uint4 lds_u128(saddr_t a) {
-  uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
-}
-__device__ __forceinline__ float4 lds_f128(saddr_t a) {
-  float4 v; asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v;
-}
+// Plain loads through a pointer rebuilt from the shared-space address: the compiler sees the address space (ld.shared),
+// folds constant offsets into the instruction and is free to schedule the loads; it will not move them across the
+// mbarrier waits, which are volatile asm with a memory clobber.
+template <typename V>
+__device__ __forceinline__ V lds_as(saddr_t a) { return *reinterpret_cast<const V*>(__cvta_shared_to_generic((size_t)a)); }
+__device__ __forceinline__ uint32_t lds_u8(saddr_t a) { return lds_as<uint8_t>(a); }
+__device__ __forceinline__ uint32_t lds_u16(saddr_t a) { return lds_as<uint16_t>(a); }
+__device__ __forceinline__ uint32_t lds_u32(saddr_t a) { return lds_as<uint32_t>(a); }
+__device__ __forceinline__ uint2 lds_u64(saddr_t a) { return lds_as<uint2>(a); }
+__device__ __forceinline__ uint4 lds_u128(saddr_t a) { return lds_as<uint4>(a); }
+__device__ __forceinline__ float4 lds_f128(saddr_t a) { return lds_as<float4>(a); }
 
 struct LaneLuts {      // per-lane shared-space base addresses (already offset to the lane's copy)
   saddr_t iq1s, iq2g, iq2s, iq4;
@@ -191,10 +190,13 @@ __device__ __forceinline__ void decode_unit<IQ1_S>(saddr_t rowp, int u, const La
 }
 template <>
 __device__ __forceinline__ float dot_unit<IQ1_S>(const Dec<IQ1_S>& d, const XRegs& x) {
-  int sh = 0, sl = 0;
+  int sh = 0, sl = 0, th = 0, tl = 0;      // two independent chains per limb
 #pragma unroll
-  for (int i = 0; i < 8; i++) { sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl); }
-  return d.a * (x.s * (float)(sh * 256 + sl) + d.b * x.sx);
+  for (int i = 0; i < 8; i += 2) {
+    sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl);
+    th = dp4a_us(d.w[i + 1], x.h[i + 1], th); tl = dp4a_uu(d.w[i + 1], x.l[i + 1], tl);
+  }
+  return d.a * (x.s * (float)((sh + th) * 256 + (sl + tl)) + d.b * x.sx);
 }
 
 // ---- IQ2_XXS: signed bytes (+-8, +-25, +-43): negative elements are negated bytewise, (g ^ m) + (m & 1)
@@ -215,10 +217,13 @@ __device__ __forceinline__ void decode_unit<IQ2_XXS>(saddr_t rowp, int u, const 
 }
 template <int T>
 __device__ __forceinline__ float dot_signed(const Dec<T>& d, const XRegs& x) {
-  int sh = 0, sl = 0;
+  int sh = 0, sl = 0, th = 0, tl = 0;
 #pragma unroll
-  for (int i = 0; i < 8; i++) { sh = dp4a_ss(d.w[i], x.h[i], sh); sl = dp4a_su(d.w[i], x.l[i], sl); }
-  return d.a * x.s * (float)(sh * 256 + sl);
+  for (int i = 0; i < 8; i += 2) {
+    sh = dp4a_ss(d.w[i], x.h[i], sh); sl = dp4a_su(d.w[i], x.l[i], sl);
+    th = dp4a_ss(d.w[i + 1], x.h[i + 1], th); tl = dp4a_su(d.w[i + 1], x.l[i + 1], tl);
+  }
+  return d.a * x.s * (float)((sh + th) * 256 + (sl + tl));
 }
 template <>
 __device__ __forceinline__ float dot_unit<IQ2_XXS>(const Dec<IQ2_XXS>& d, const XRegs& x) { return dot_signed(d, x); }
@@ -313,36 +318,33 @@ __device__ __forceinline__ float dot_unit<Q5_K>(const Dec<Q5_K>& d, const XRegs&
   return d.a * (x.s * (float)(sh * 256 + sl)) - d.b * x.sx;
 }
 
-// dense types: fp32 activation from shared memory
+// dense types: fp32 activation from shared memory; 16 bytes of weights per step (rows of dense matrices start on
+// 16-byte boundaries in practice; a 2-byte aligned row falls back to word loads + funnel shifts)
 template <int T>
 __device__ __forceinline__ float unit_dot_dense(saddr_t rowp, int u, saddr_t xf) {
   const saddr_t xv = xf + 128u * (uint32_t)u;
+  constexpr int kBytes = T == F32 ? 128 : 64;
+  const saddr_t wp = rowp + (uint32_t)u * kBytes;
   float acc = 0.f;
-  if (T == F32) {
-    uint32_t w[32];
-    load_words<32>(rowp + u * 128, w);
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const float4 v = lds_f128(xv + 16u * i);
-      acc = fmaf(__uint_as_float(w[4 * i]), v.x, acc); acc = fmaf(__uint_as_float(w[4 * i + 1]), v.y, acc);
-      acc = fmaf(__uint_as_float(w[4 * i + 2]), v.z, acc); acc = fmaf(__uint_as_float(w[4 * i + 3]), v.w, acc);
-    }
-  } else {
-    uint32_t w[16];
-    load_words<16>(rowp + u * 64, w);
+  for (int i = 0; i < kBytes / 16; i++) {
+    uint32_t w[4];
+    if ((wp & 15u) == 0) { const uint4 v = lds_u128(wp + 16u * i); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+    else load_words<4>(wp + 16u * i, w);
+    if (T == F32) {
+      const float4 x0 = lds_f128(xv + 16u * i);
+      acc = fmaf(__uint_as_float(w[0]), x0.x, acc); acc = fmaf(__uint_as_float(w[1]), x0.y, acc);
+      acc = fmaf(__uint_as_float(w[2]), x0.z, acc); acc = fmaf(__uint_as_float(w[3]), x0.w, acc);
+    } else {
+      const float4 x0 = lds_f128(xv + 32u * i), x1 = lds_f128(xv + 32u * i + 16u);
+      float a[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const float4 v = lds_f128(xv + 16u * i);
-      float a0, a1, a2, a3;
-      if (T == BF16) {
-        a0 = __uint_as_float(w[2 * i] << 16); a1 = __uint_as_float(w[2 * i] & 0xFFFF0000u);
-        a2 = __uint_as_float(w[2 * i + 1] << 16); a3 = __uint_as_float(w[2 * i + 1] & 0xFFFF0000u);
-      } else {
-        const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * i]));
-        const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * i + 1]));
-        a0 = p.x; a1 = p.y; a2 = r.x; a3 = r.y;
+      for (int k = 0; k < 4; k++) {
+        if (T == BF16) { a[2 * k] = __uint_as_float(w[k] << 16); a[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u); }
+        else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k])); a[2 * k] = f.x; a[2 * k + 1] = f.y; }
       }
-      acc = fmaf(a0, v.x, acc); acc = fmaf(a1, v.y, acc); acc = fmaf(a2, v.z, acc); acc = fmaf(a3, v.w, acc);
+      acc = fmaf(a[0], x0.x, acc); acc = fmaf(a[1], x0.y, acc); acc = fmaf(a[2], x0.z, acc); acc = fmaf(a[3], x0.w, acc);
+      acc = fmaf(a[4], x1.x, acc); acc = fmaf(a[5], x1.y, acc); acc = fmaf(a[6], x1.z, acc); acc = fmaf(a[7], x1.w, acc);
     }
   }
   return acc;

@@ -77,6 +77,8 @@ __device__ __forceinline__ void router_topk_warp(const float* logits, const floa
 // Fused decode router: every warp computes one (expert, K-slice) partial dot; the block that finishes last sums the
 // slices in a fixed order, writes the logits and selects.
 __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit = blockIdx.x * 8 + warp;
   const int slice = p.dim / kRouterKSplit;   // floats per slice, a multiple of 4
@@ -85,9 +87,19 @@ __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p)
     const float4* w = reinterpret_cast<const float4*>(p.W + (size_t)e * p.dim + (size_t)ks * slice);
     const float4* xv = reinterpret_cast<const float4*>(p.x + (size_t)ks * slice);
     float acc = 0.f;
-    for (int c = lane; c < slice / 4; c += 32) {
-      const float4 a = __ldg(w + c), b = xv[c];
-      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    for (int c0 = lane; c0 < slice / 4; c0 += 32 * 8) {   // 8 independent 16-byte loads in flight per lane
+      float4 a[8], b[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const int c = c0 + 32 * k;
+        a[k] = c < slice / 4 ? __ldg(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        b[k] = c < slice / 4 ? xv[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        acc = fmaf(a[k].x, b[k].x, acc); acc = fmaf(a[k].y, b[k].y, acc);
+        acc = fmaf(a[k].z, b[k].z, acc); acc = fmaf(a[k].w, b[k].w, acc);
+      }
     }
     acc = warp_sum(acc);
     if (lane == 0) p.partial[unit] = acc;
@@ -117,6 +129,8 @@ __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p)
 // logits [n][E] -> ids [n][k], weights [n][k]; one warp per token.
 __global__ void __launch_bounds__(128) router_topk_kernel(const float* logits, const float* bias, int* ids, float* wts,
                                                           int n, int E, int k, int score_fn, float route_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= n) return;
   router_topk_warp(logits + (size_t)t * E, bias, E, k, score_fn, route_scale, threadIdx.x & 31, ids + (size_t)t * k,
@@ -126,6 +140,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* logits, c
 // ---- routing lists: entries i = t*k + j sorted by (expert, i).  No atomics: a warp owns an expert and scans all
 // entries in order with ballots, so the lists are identical from run to run.
 __global__ void __launch_bounds__(256) route_count_kernel(const int* ids, unsigned* counts, int N, int E) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (e >= E) return;
   unsigned c = 0;
@@ -136,6 +152,8 @@ __global__ void __launch_bounds__(256) route_count_kernel(const int* ids, unsign
   if (lane == 0) counts[e] = c;
 }
 __global__ void __launch_bounds__(1024) route_scan_kernel(const unsigned* counts, unsigned* offsets, int E) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned buf[1024];
   const int tid = threadIdx.x;
   // E <= 1024 per pass; serial carry over passes
@@ -159,6 +177,8 @@ __global__ void __launch_bounds__(1024) route_scan_kernel(const unsigned* counts
 __global__ void __launch_bounds__(256) route_scatter_kernel(const int* ids, const float* w, const unsigned* offsets,
                                                             unsigned* entry, unsigned* tok, float* lw, unsigned* slot_of,
                                                             int N, int E, int k) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (e >= E) return;
   unsigned pos = offsets[e];
@@ -195,7 +215,7 @@ int router_fused(const float* x, const float* W, const float* bias, int* ids, fl
   p.ticket = reinterpret_cast<unsigned*>(tb.status) + 16;
   p.E = E; p.dim = dim; p.k = k; p.score_fn = score_fn; p.route_scale = route_scale;
   const int units = E * kRouterKSplit;
-  router_fused_kernel<<<(units + 7) / 8, 256, 0, st>>>(p);
+  MSB_CUDA(launch_pdl(router_fused_kernel, dim3((units + 7) / 8), dim3(256), 0, st, p));
   MSB_LAUNCH_CHECK("router_fused_kernel");
   return kOk;
 }
@@ -206,7 +226,7 @@ int router_topk(const float* logits, const float* bias, int* ids, float* wts, in
     return fail(kErrArg, "router_topk: bad shape (n %d E %d k %d)", n, E, k);
   if (n == 0) return kOk;
   if (!logits || !ids || !wts) return fail(kErrArg, "router_topk: null pointer");
-  router_topk_kernel<<<(n + 3) / 4, 128, 0, st>>>(logits, bias, ids, wts, n, E, k, score_fn, route_scale);
+  MSB_CUDA(launch_pdl(router_topk_kernel, dim3((n + 3) / 4), dim3(128), 0, st, logits, bias, ids, wts, n, E, k, score_fn, route_scale));
   MSB_LAUNCH_CHECK("router_topk_kernel");
   return kOk;
 }
@@ -216,9 +236,9 @@ int route_lists(const int* ids, const float* w, int n, int k, int E, unsigned* c
   if (n < 0 || k <= 0 || E <= 0) return fail(kErrArg, "route_lists: bad shape");
   if (!ids || !w || !counts || !offsets || !entry || !tok || !lw || !slot_of) return fail(kErrArg, "route_lists: null pointer");
   const int N = n * k;
-  route_count_kernel<<<(E + 7) / 8, 256, 0, st>>>(ids, counts, N, E);
-  route_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, E);
-  route_scatter_kernel<<<(E + 7) / 8, 256, 0, st>>>(ids, w, offsets, entry, tok, lw, slot_of, N, E, k);
+  MSB_CUDA(launch_pdl(route_count_kernel, dim3((E + 7) / 8), dim3(256), 0, st, ids, counts, N, E));
+  MSB_CUDA(launch_pdl(route_scan_kernel, dim3(1), dim3(1024), 0, st, counts, offsets, E));
+  MSB_CUDA(launch_pdl(route_scatter_kernel, dim3((E + 7) / 8), dim3(256), 0, st, ids, w, offsets, entry, tok, lw, slot_of, N, E, k));
   MSB_LAUNCH_CHECK("route_lists");
   return kOk;
 }

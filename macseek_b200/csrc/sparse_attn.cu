@@ -79,6 +79,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 template <int D, bool BF>
 __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparseParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int KS = D / 64;            // k-steps of 16 dims per warp (each warp contracts D / 4 dims)
   constexpr int NTW = D / 32;           // 8-wide output tiles per warp (each warp owns D / 4 output dims)
   constexpr int PITCH = D * 2 + 16;     // bytes per staged row (+16: rows start on different bank groups)
@@ -252,6 +254,8 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
 // combine the splits of one head, add the sink to the denominator, inverse rope on the last 64 dims
 template <int D>
 __global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float xs[D];
   __shared__ float fs[1024];      // per-split rescale factors exp(m_s - M)
   __shared__ float s_den;
@@ -312,8 +316,8 @@ static int launch_sparse(SparseParams& p, cudaStream_t st, int dev) {
     MSB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     done[dev & 63] = true;
   }
-  kern<<<dim3(p.H / kSaHeadsPerBlock, p.splits), 128, smem, st>>>(p);
-  sparse_combine_kernel<D><<<p.H, D, 0, st>>>(p);
+  MSB_CUDA(launch_pdl(kern, dim3(dim3(p.H / kSaHeadsPerBlock, p.splits)), dim3(128), smem, st, p));
+  MSB_CUDA(launch_pdl(sparse_combine_kernel<D>, dim3(p.H), dim3(D), 0, st, p));
   MSB_LAUNCH_CHECK("sparse attention");
   return kOk;
 }

@@ -1,5 +1,6 @@
 // Host-side status text and the per-device codebook tables of libmacseek_b200.
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -10,6 +11,11 @@ namespace msb {
 
 static thread_local char t_err[512] = "";
 const char* last_error_text() { return t_err; }
+
+bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("MSB_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -105,8 +111,8 @@ int get_tables(Tables* out) {
     MSB_CUDA(upload(img.iq2_sign, (const void**)&d.t.iq2_signmask));
     MSB_CUDA(upload(img.iq4_pair, (const void**)&d.t.iq4nl_pair));
     MSB_CUDA(upload(img.iq1s_i8, (const void**)&d.t.iq1s_i8));
-    MSB_CUDA(cudaMalloc((void**)&d.t.status, 256));
-    MSB_CUDA(cudaMemset(d.t.status, 0, 256));
+    MSB_CUDA(cudaMalloc((void**)&d.t.status, 2048));     // status word, scheduling counters, argmax partials
+    MSB_CUDA(cudaMemset(d.t.status, 0, 2048));
     d.ready = true;
   }
   *out = d.t;

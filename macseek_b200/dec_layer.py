@@ -2,7 +2,7 @@
 ds41::encode_dec_attn_side / encode_dec_moe_table / encode_head issue per token (src/model/dec_layer.hpp:107-118,
 dec_layer.mm:138-313, ds41.mm:491-503), re-expressed over CUDA streams and HBM-resident expert-parallel experts.
 
-Per layer:  rmsnorm -> q_a, kv, index-proj matvecs -> rmsnorm(q_a) -> q_b, index-q_b matvecs -> window KV row ->
+Per layer:  q_a, kv, index-proj matvecs (input RMSNorm fused) -> q_b, index-q_b matvecs (q RMSNorm fused) -> window KV row ->
             indexer scores + exact top-k -> sparse attention -> o_a (block-diagonal) -> o_b (accumulated into h) ->
             rmsnorm -> fused router -> MoE gate/up + down on the experts resident here (-> all-reduce under EP).
 What the reference does between these calls and is not on the measured path here (hyper-connection mixing, the
@@ -154,13 +154,13 @@ class SyntheticModel:
     def encode_dec_attn_side(self, e: Enc, l, pos):
         c, w, b, st = self.cfg, self.layers[l], self.bufs, self.state[l]
         n = 0
-        arch.encode_rmsnorm(e, b.h, w.attn_norm, b.x, 1, c.dim, c.norm_eps); n += 1
-        q.encode_matvec(e, c.t_attn, w.wq_a, c.q_lora, c.dim, b.x, b.qa); n += 1
-        q.encode_matvec(e, c.t_attn, w.wkv, c.D, c.dim, b.x, b.kv); n += 1
-        q.encode_matvec(e, c.t_index, w.w_idx_proj, c.index_heads, c.dim, b.x, b.iw); n += 1
-        arch.encode_rmsnorm(e, b.qa, w.q_norm, b.qan, 1, c.q_lora, c.norm_eps); n += 1
-        q.encode_matvec(e, c.t_attn, w.wq_b, c.heads * c.D, c.q_lora, b.qan, b.qfull); n += 1
-        q.encode_matvec(e, c.t_index, w.w_idx_qb, c.index_heads * c.index_dim, c.q_lora, b.qan, b.iq); n += 1
+        # the input RMSNorms are fused into the activation load of the matvecs that consume them
+        q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_a, c.q_lora, c.dim, b.h, w.attn_norm, c.norm_eps, b.qa); n += 1
+        q.encode_matvec_rmsnorm(e, c.t_attn, w.wkv, c.D, c.dim, b.h, w.attn_norm, c.norm_eps, b.kv); n += 1
+        q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_proj, c.index_heads, c.dim, b.h, w.attn_norm, c.norm_eps, b.iw); n += 1
+        q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_b, c.heads * c.D, c.q_lora, b.qa, w.q_norm, c.norm_eps, b.qfull); n += 1
+        q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_qb, c.index_heads * c.index_dim, c.q_lora, b.qa, w.q_norm,
+                                c.norm_eps, b.iq); n += 1
         attn.encode_kv_window(e, st, b.kv, w.kv_norm, pos); n += 1
         attn.encode_index_decode(e, st, b.iq, b.iw, pos, c.kv_len, actq=False); n += 4
         attn.encode_sparse(e, st, b.qfull, w.sinks, b.attn_out, pos); n += 2
@@ -196,10 +196,9 @@ class SyntheticModel:
 
     def encode_head(self, e: Enc):
         c, b = self.cfg, self.bufs
-        arch.encode_rmsnorm(e, b.h, self.out_norm, b.x, 1, c.dim, c.norm_eps)
-        q.encode_matvec(e, c.t_head, self.w_head, c.vocab, c.dim, b.x, b.logits)
+        q.encode_matvec_rmsnorm(e, c.t_head, self.w_head, c.vocab, c.dim, b.h, self.out_norm, c.norm_eps, b.logits)
         arch.encode_argmax(e, b.logits, 1, c.vocab, b.next_id)
-        return 3
+        return 2
 
     def forward_token(self, e: Enc, pos=None):
         """Encode the whole step for the token whose hidden state is in bufs.h; returns the kernel launch count."""

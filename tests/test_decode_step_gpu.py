@@ -42,13 +42,11 @@ def test_layer_stages_against_oracle():
     def mv(t, W, rows, cols, x, groups=1):
         return orc.matvec(int(t), raw(W), rows, cols, x, groups)
 
-    x = host(b.x)
-    assert np.allclose(x, orc.rmsnorm(host(h0), host(w.attn_norm), cfg.norm_eps), rtol=1e-5, atol=1e-6)
+    x = orc.rmsnorm(host(h0), host(w.attn_norm), cfg.norm_eps)       # the norm itself is fused into the matvecs
     for got, (ry, mag) in ((b.qa, mv(cfg.t_attn, w.wq_a, cfg.q_lora, cfg.dim, x)), (b.kv, mv(cfg.t_attn, w.wkv, cfg.D, cfg.dim, x)),
                            (b.iw, mv(cfg.t_index, w.w_idx_proj, cfg.index_heads, cfg.dim, x))):
         assert orc.max_norm_err(host(got), ry, mag) <= T
-    qan = host(b.qan)
-    assert np.allclose(qan, orc.rmsnorm(host(b.qa), host(w.q_norm), cfg.norm_eps), rtol=1e-5, atol=1e-6)
+    qan = orc.rmsnorm(host(b.qa), host(w.q_norm), cfg.norm_eps)
     ry, mag = mv(cfg.t_attn, w.wq_b, cfg.heads * cfg.D, cfg.q_lora, qan)
     assert orc.max_norm_err(host(b.qfull), ry, mag) <= T
     ry, mag = mv(cfg.t_index, w.w_idx_qb, cfg.index_heads * 128, cfg.q_lora, qan)

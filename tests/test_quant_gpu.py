@@ -171,3 +171,17 @@ def test_bad_arguments_fail_loudly(q, enc):
         q.encode_matvec(enc, 39, W, 8, 256, x, y)                # MXFP4: no kernel
     with pytest.raises(MsbError):
         q.encode_matvec(enc, ol.Q6_K, W, 9, 256, x, y, False, 2)  # rows % groups
+
+
+@pytest.mark.parametrize("t", (ol.Q6_K, ol.IQ1_S, ol.BF16, ol.Q8_0))
+def test_matvec_rmsnorm_fused(orc, q, enc, t):
+    # y = W . (x * rsqrt(mean(x^2) + eps) * norm_w)  (quant.hpp:19-26)
+    rows, cols = 1280, 4096
+    W = synth.random_weights(t, rows, cols, 21)
+    x = synth.randn(cols, 22, 3.0)
+    nw = (1 + 0.1 * synth.randn(cols, 23)).astype(np.float32)
+    y = torch.zeros(rows, device="cuda")
+    q.encode_matvec_rmsnorm(enc, t, dev(W), rows, cols, dev(x), dev(nw), 1e-6, y)
+    enc.wait()
+    ry, mag = orc.matvec(t, W, rows, cols, orc.rmsnorm(x, nw, 1e-6))
+    assert orc.max_norm_err(y.cpu().numpy(), ry, mag) <= TOL
