@@ -66,7 +66,7 @@ __global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvPar
   XqSmem xq[NC];
   const int U = p.units;
 #pragma unroll
-  for (int c = 0; c < NC; c++) { xq_bind(xq[c], cur, U, is_dense(T)); cur += xq_bytes(U, is_dense(T)); }
+  for (int c = 0; c < NC; c++) { xq_bind(xq[c], cur, U, is_dense(T), xq_padded(T)); cur += xq_bytes(U, is_dense(T), xq_padded(T)); }
   cur = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(cur) + 127) & ~(uintptr_t)127);
   ring.slot0 = cur; ring.slot_bytes = p.stage_bytes;
 
@@ -105,7 +105,9 @@ __global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvPar
           const float4 gw = reinterpret_cast<const float4*>(p.norm_w)[i];
           v.x = v.x * mul * gw.x; v.y = v.y * mul * gw.y; v.z = v.z * mul * gw.z; v.w = v.w * mul * gw.w;
         }
-        d[i] = v;
+        // 16-bit weights: one 16-byte weight granule spans 8 activations, kept as two float4 planes (elements
+        // 8g..8g+3 and 8g+4..8g+7 of granule g) so that lanes on consecutive granules read consecutive addresses
+        d[T == F32 ? i : (i & 1) * (U * 4) + (i >> 1)] = v;
       }
     } else {
       quantize_x(xg, xq[c], tid, blockDim.x, mul, p.norm_w);
@@ -245,15 +247,18 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
   constexpr int G = 32 / LPR;
   constexpr int kMaxNR = (T == IQ1_S || T == IQ2_XXS) ? 4 : 2;
   const size_t fixed = ((sizeof(MvSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(T) +
-                       (size_t)NC * xq_bytes(p.units, is_dense(T)) + 128;
+                       (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 128;
   if (fixed + 2 * 8192 > (size_t)kSmemLimit)
     return fail(kErrLimit, "matvec: cols %d x n %d does not fit in shared memory", p.cols, p.n);
   const size_t avail = (size_t)kSmemLimit - fixed;
-  static const int env_slot = getenv("MSB_MV_SLOT_KB") ? atoi(getenv("MSB_MV_SLOT_KB")) : 0;   // tuning probes
-  static const int env_stages = getenv("MSB_MV_STAGES") ? atoi(getenv("MSB_MV_STAGES")) : 0;
-  int stages = avail / 4 >= 36 * 1024 ? 4 : (avail / 3 >= 24 * 1024 ? 3 : 2);
-  if (env_stages) stages = env_stages;
-  const size_t slot = std::min<size_t>(avail / stages, (size_t)(env_slot ? env_slot : (lut_bytes_for(T) ? 56 : 72)) * 1024) & ~(size_t)127;
+  // tuning probes: cap the slot size (KB) / the ring depth
+  static const int env_slot = getenv("MSB_MV_SLOT_KB") ? atoi(getenv("MSB_MV_SLOT_KB")) : 0;
+  static const int env_stages = getenv("MSB_MV_STAGES") ? std::min(kMaxStages, std::max(2, atoi(getenv("MSB_MV_STAGES")))) : 0;
+  // A tile may take up to half of the free shared memory (a two-slot ring): rows that share a lane's activation
+  // registers cut the shared-memory traffic per weight, which matters more than ring depth once a slot holds tens of KB.
+  size_t slot = (avail / 2) & ~(size_t)127;
+  if (env_slot) slot = std::min<size_t>(slot, (size_t)env_slot * 1024);
+  int stages = 2;
   const long rows_fit = ((long)slot - 64) / (long)p.row_bytes;
   const int want_tiles = std::max(1, sms / p.groups);
   auto tiles_of = [&](int r) { return (p.rows_per_group + r - 1) / r; };
@@ -263,7 +268,7 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
   if (rows_fit >= 1) {
     // whole rows per warp (KS = 1, R = 16 * G * NR), largest first
     for (int cand : {4, 2, 1}) {
-      if (cand > kMaxNR || (NC > 1 && cand > 2)) continue;
+      if (cand > kMaxNR || (NC > 1 && cand > 2) || (T == Q6_K && NC > 2 && cand > 1)) continue;
       const int r = kMvNW * G * cand;
       if (r <= rows_fit && (tiles_of(r) >= want_tiles || cand == 1)) { R = r; nr = cand; break; }
     }
@@ -279,6 +284,8 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
     if (R == 0) {   // LPR < 32 and the smallest whole-row tile does not fit: per-row chunks instead
       nr = 1; ks = 1;
       R = kMvNW * G;
+      stages = 3;
+      slot = std::min(slot, (avail / 3) & ~(size_t)127);
       const int chunk = chunk_units_for(T, p.units, R, LPR, slot);
       if (chunk <= 0) return fail(kErrLimit, "matvec: no staging shape fits (type %s cols %d)", type_name(T), p.cols);
       p.chunk_units = chunk;
@@ -288,11 +295,19 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
     // one row does not fit a slot: all 16 warps share a row, K streamed in chunks (one large copy each)
     if (LPR != 32) return fail(kErrLimit, "matvec: row of %u bytes does not fit (type %s)", p.row_bytes, type_name(T));
     ks = kMvNW; nr = 1; R = 1;
+    stages = 3;
+    slot = std::min(slot, (avail / 3) & ~(size_t)127);
     const int chunk = chunk_units_for(T, p.units, 1, 32 * kMvNW, slot);
     if (chunk <= 0) return fail(kErrLimit, "matvec: no staging shape fits (type %s cols %d)", type_name(T), p.cols);
     p.chunk_units = chunk;
     p.pitch = piece_pitch(units_bytes(T, chunk));
   }
+  if (p.chunk_units >= p.units) {
+    // whole-row tiles: the slot is exactly one tile (plus the source's misalignment), the ring as deep as then fits
+    slot = ((size_t)R * p.row_bytes + 64 + 127) & ~(size_t)127;
+    stages = (int)std::min<size_t>(kMaxStages, avail / slot);
+  }
+  if (env_stages) stages = std::min(stages, env_stages);
   p.tile_rows = R;
   p.ks = ks;
   p.tiles_per_group = tiles_of(R);
@@ -306,7 +321,8 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
 
 template <int T, int NC>
 int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
-  switch (pick_lpr(p.units)) {
+  // Q6_K rows are split by half super-block (4 units), the other types by unit
+  switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units)) {
     case 32: return launch_rows<T, 32, NC>(p, st, dev, sms);
     case 16: return launch_rows<T, 16, NC>(p, st, dev, sms);
     default: return launch_rows<T, 8, NC>(p, st, dev, sms);

@@ -166,8 +166,8 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
   cur += lut_bytes_for(TR);
   const int U = p.dim / 32;
   XqSmem xq[1];
-  xq_bind(xq[0], cur, U, false);
-  cur += xq_bytes(U, false);
+  xq_bind(xq[0], cur, U, false, xq_padded(TR) || xq_padded(TS));
+  cur += xq_bytes(U, false, xq_padded(TR) || xq_padded(TS));
   cur = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(cur) + 127) & ~(uintptr_t)127);
   ring.slot0 = cur; ring.slot_bytes = p.stage_bytes;
 
@@ -247,8 +247,8 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   const int Ui = p.inter / 32;
   const int U = (p.n_routed + 1) * Ui;          // h rows of every slot, shared expert last
   XqSmem xq[1];
-  xq_bind(xq[0], cur, U, false);
-  cur += xq_bytes(U, false);
+  xq_bind(xq[0], cur, U, false, xq_padded(TR) || xq_padded(TS));
+  cur += xq_bytes(U, false, xq_padded(TR) || xq_padded(TS));
   cur = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(cur) + 127) & ~(uintptr_t)127);
   ring.slot0 = cur; ring.slot_bytes = p.stage_bytes;
 
@@ -379,7 +379,7 @@ template <int TR, int TS, int LPR>
 int launch_gu(MoeParams& p, int sms, int dev, cudaStream_t st) {
   constexpr int Gn = 32 / LPR;
   const int U = p.dim / 32;
-  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false) + 128;
+  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false, xq_padded(TR) || xq_padded(TS)) + 128;
   if (fixed + 3 * 8192 > (size_t)kSmemLimit) return fail(kErrLimit, "moe_decode: dim %d does not fit in shared memory", p.dim);
   const int stages = 3;
   const size_t slot = (((size_t)kSmemLimit - fixed) / stages) & ~(size_t)127;
@@ -412,7 +412,7 @@ template <int TR, int TS, int LPR>
 int launch_down(MoeParams& p, int sms, int dev, cudaStream_t st) {
   constexpr int R = kMoeNW / 2;
   const int Ui = p.inter / 32, U = (p.n_routed + 1) * Ui;
-  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false) + 128;
+  const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false, xq_padded(TR) || xq_padded(TS)) + 128;
   const size_t rb_r = row_bytes(TR, p.inter), rb_s = row_bytes(TS, p.inter);
   p.d_rows = R;
   p.d_src_pitch = (uint32_t)((R * rb_r + 15 + 16 + 15) & ~(size_t)15);

@@ -54,30 +54,42 @@ struct LaneLuts {      // per-lane shared-space base addresses (already offset t
 };
 
 // Quantised activation in shared memory: U units of 32 elements.  x ~= scale * (256 * hi + lo), hi signed bytes,
-// lo unsigned bytes.  plane[0][u] / plane[1][u] = hi bytes of elements 0..15 / 16..31, plane[2..3] = lo bytes.
-// meta[u] = {scale, scale * sum of the fixed-point values, (int) sum over elements 0..15, (int) sum over 16..31}.
+// lo unsigned bytes.  plane[0][.] / plane[1][.] = hi bytes of elements 0..15 / 16..31, plane[2..3] = lo bytes.
+// meta[.] = {scale, scale * sum of the fixed-point values, (int) sum over elements 0..15, (int) sum over 16..31}.
+// In the padded form (used when a Q6_K matrix reads it) unit u sits at slot u + u/8 of each array: one 16-byte slot
+// of padding per 8 units, so that lanes that each walk their own half super-block (unit stride 4) reach distinct banks,
+// as lanes on consecutive units do in either form.
 struct XqSmem {
-  uint4* plane;     // [4][U]
-  float4* meta;     // [U]
+  uint4* plane;     // [4][S], S = xq_slots(U)
+  float4* meta;     // [S]
   const float* xf;  // dense types: fp32 copy of x [32 U]
   saddr_t plane_s, meta_s, xf_s;   // the same locations as shared-space addresses
-  int U;
+  int U, S;
+  uint32_t padmask;   // all ones in the padded form, else 0
 };
-constexpr int kXqUnitBytes = 80;
-__host__ __device__ inline size_t xq_bytes(int U, bool dense) { return dense ? (size_t)U * 128 : (size_t)U * kXqUnitBytes; }
-__device__ __forceinline__ void xq_bind(XqSmem& x, uint8_t* base, int U, bool dense) {
+__host__ __device__ constexpr bool xq_padded(int t) { return t == Q6_K; }
+__host__ __device__ inline int xq_pos_padded(int u) { return u + (u >> 3); }
+__host__ __device__ inline int xq_slots(int U, bool padded) { return padded ? U + ((U + 7) >> 3) : U; }
+__host__ __device__ inline size_t xq_bytes(int U, bool dense, bool padded) {
+  return dense ? (size_t)U * 128 : (size_t)xq_slots(U, padded) * 80;
+}
+__device__ __forceinline__ int xq_pos(const XqSmem& x, int u) { return u + (int)((uint32_t)(u >> 3) & x.padmask); }
+__device__ __forceinline__ void xq_bind(XqSmem& x, uint8_t* base, int U, bool dense, bool padded) {
   x.U = U;
+  x.S = xq_slots(U, padded);
+  x.padmask = padded ? 0xFFFFFFFFu : 0u;
   x.plane_s = x.xf_s = smem_u32(base);
-  x.meta_s = x.plane_s + (uint32_t)U * 64u;
+  x.meta_s = x.plane_s + (uint32_t)x.S * 64u;
   if (dense) { x.xf = reinterpret_cast<const float*>(base); x.plane = nullptr; x.meta = nullptr; }
-  else { x.plane = reinterpret_cast<uint4*>(base); x.meta = reinterpret_cast<float4*>(base + (size_t)U * 64); x.xf = nullptr; }
+  else { x.plane = reinterpret_cast<uint4*>(base); x.meta = reinterpret_cast<float4*>(base + (size_t)x.S * 64); x.xf = nullptr; }
 }
 struct XRegs { uint32_t h[8], l[8]; float s, sx; int sa, sb; };
 
 __device__ __forceinline__ void load_xq(const XqSmem& x, int u, XRegs& r) {
-  const saddr_t pa = x.plane_s + 16u * (uint32_t)u, st = 16u * (uint32_t)x.U;
+  const uint32_t pos = (uint32_t)xq_pos(x, u);
+  const saddr_t pa = x.plane_s + 16u * pos, st = 16u * (uint32_t)x.S;
   const uint4 a = lds_u128(pa), b = lds_u128(pa + st), c = lds_u128(pa + 2 * st), d = lds_u128(pa + 3 * st);
-  const float4 m = lds_f128(x.meta_s + 16u * (uint32_t)u);
+  const float4 m = lds_f128(x.meta_s + 16u * pos);
   r.h[0] = a.x; r.h[1] = a.y; r.h[2] = a.z; r.h[3] = a.w; r.h[4] = b.x; r.h[5] = b.y; r.h[6] = b.z; r.h[7] = b.w;
   r.l[0] = c.x; r.l[1] = c.y; r.l[2] = c.z; r.l[3] = c.w; r.l[4] = d.x; r.l[5] = d.y; r.l[6] = d.z; r.l[7] = d.w;
   r.s = m.x; r.sx = m.y; r.sa = __float_as_int(m.z); r.sb = __float_as_int(m.w);
@@ -130,13 +142,14 @@ __device__ __forceinline__ void quantize_x(const float* __restrict__ x, const Xq
     const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);   // lanes (0,1): elements 0..15, (2,3): 16..31
     const int other = __shfl_xor_sync(0xffffffffu, pair, 2);
     if (live) {
-      uint2* ph = reinterpret_cast<uint2*>(&q.plane[(lane4 >> 1) * q.U + u]) + (lane4 & 1);
-      uint2* pl = reinterpret_cast<uint2*>(&q.plane[(2 + (lane4 >> 1)) * q.U + u]) + (lane4 & 1);
+      const int pos = xq_pos(q, u);
+      uint2* ph = reinterpret_cast<uint2*>(&q.plane[(lane4 >> 1) * q.S + pos]) + (lane4 & 1);
+      uint2* pl = reinterpret_cast<uint2*>(&q.plane[(2 + (lane4 >> 1)) * q.S + pos]) + (lane4 & 1);
       *ph = make_uint2(hw[0], hw[1]);
       *pl = make_uint2(lw[0], lw[1]);
       if (lane4 == 0) {
         const float sc = amax * (1.0f / 32767.f);
-        q.meta[u] = make_float4(sc, sc * (float)(pair + other), __int_as_float(pair), __int_as_float(other));
+        q.meta[pos] = make_float4(sc, sc * (float)(pair + other), __int_as_float(pair), __int_as_float(other));
       }
     }
   }
@@ -288,6 +301,88 @@ __device__ __forceinline__ float dot_unit<Q6_K>(const Dec<Q6_K>& d, const XRegs&
   return d.a * x.s * (d.s0 * (float)(h0 * 256 + l0 - 32 * x.sa) + d.s1 * (float)(h1 * 256 + l1 - 32 * x.sb));
 }
 
+// Q6_K, one half super-block (128 elements: units 4h .. 4h+3 of the block) of NRT rows against NC activation columns.
+// The half's 64 ql bytes and 32 qh bytes are each read once: ql[0..31] serves sub-blocks 0 (low nibbles) and 2 (high),
+// ql[32..63] sub-blocks 1 and 3, and qh supplies bits 4..5 of all four.  With m = 0x0F0F0F0F and
+// hx = (qh >> 0 or 2) & 0x33333333 the code words are (ql & m) | ((hx << 4) & ~m) and ((ql >> 4) & m) | (hx & ~m): one
+// shift and one three-input logic operation per word.  `blk[i]` = shared address of row i's block (2-byte aligned),
+// `u0` = index of the half's first unit in the activation.
+template <int NRT, int NC>
+__device__ __forceinline__ void q6k_half_block(const saddr_t (&blk)[NRT], int half, const XqSmem (&xq)[NC], int u0,
+                                               float (&acc)[NRT][NC]) {
+  constexpr uint32_t m = 0x0F0F0F0Fu;
+  uint32_t scw[NRT][2];
+  float d[NRT], part[NRT][NC];
+  uint32_t hk[NRT][8];
+#pragma unroll
+  for (int i = 0; i < NRT; i++) {
+    load_words<2>(blk[i] + 192 + 8 * half, scw[i]);
+    d[i] = lds_half(blk[i] + 208);
+    load_words<8>(blk[i] + 128 + 32 * half, hk[i]);
+#pragma unroll
+    for (int c = 0; c < NC; c++) part[i][c] = 0.f;
+  }
+#pragma unroll
+  for (int P = 0; P < 2; P++) {
+    uint32_t ql[NRT][8], hx[NRT][8];
+#pragma unroll
+    for (int i = 0; i < NRT; i++) {
+      load_words<8>(blk[i] + 64 * half + 32 * P, ql[i]);
+#pragma unroll
+      for (int g = 0; g < 8; g++) hx[i][g] = (P == 0 ? hk[i][g] : (hk[i][g] >> 2)) & 0x33333333u;
+    }
+#pragma unroll
+    for (int jj = 0; jj < 2; jj++) {
+      const int j = P + 2 * jj;                       // sub-block (unit) inside the half
+      const uint32_t pos = (uint32_t)xq_pos_padded(u0 + j);
+      float sub[NRT][NC];
+#pragma unroll
+      for (int i = 0; i < NRT; i++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) sub[i][c] = 0.f;
+      float xs[NC];
+#pragma unroll
+      for (int is = 0; is < 2; is++) {
+        uint32_t w[NRT][4];
+#pragma unroll
+        for (int i = 0; i < NRT; i++)
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const int g = 4 * is + k;
+            w[i][k] = jj == 0 ? ((ql[i][g] & m) | ((hx[i][g] << 4) & ~m)) : (((ql[i][g] >> 4) & m) | (hx[i][g] & ~m));
+          }
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+          const uint32_t st = 16u * (uint32_t)xq[c].S;
+          const uint4 xh = lds_u128(xq[c].plane_s + 16u * pos + st * is);
+          const uint4 xl = lds_u128(xq[c].plane_s + 16u * pos + st * (2 + is));
+          const float4 mt = lds_f128(xq[c].meta_s + 16u * pos);
+          xs[c] = mt.x;
+          const int s16 = __float_as_int(is == 0 ? mt.z : mt.w);
+#pragma unroll
+          for (int i = 0; i < NRT; i++) {
+            int h = dp4a_us(w[i][0], xh.x, 0), l = dp4a_uu(w[i][0], xl.x, 0);
+            h = dp4a_us(w[i][1], xh.y, h); l = dp4a_uu(w[i][1], xl.y, l);
+            h = dp4a_us(w[i][2], xh.z, h); l = dp4a_uu(w[i][2], xl.z, l);
+            h = dp4a_us(w[i][3], xh.w, h); l = dp4a_uu(w[i][3], xl.w, l);
+            const int sidx = 2 * j + is;
+            const float sc = (float)(int8_t)((scw[i][sidx >> 2] >> (8 * (sidx & 3))) & 0xFFu);
+            sub[i][c] = fmaf(sc, (float)(h * 256 + l - 32 * s16), sub[i][c]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < NRT; i++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) part[i][c] = fmaf(xs[c], sub[i][c], part[i][c]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NRT; i++)
+#pragma unroll
+    for (int c = 0; c < NC; c++) acc[i][c] = fmaf(d[i], part[i][c], acc[i][c]);
+}
+
 // ---- Q5_K: codes 0..31 unsigned, y = (d * scale) q - dmin * min
 template <>
 __device__ __forceinline__ void decode_unit<Q5_K>(saddr_t rowp, int u, const LaneLuts&, Dec<Q5_K>& d) {
@@ -316,38 +411,6 @@ __device__ __forceinline__ float dot_unit<Q5_K>(const Dec<Q5_K>& d, const XRegs&
 #pragma unroll
   for (int i = 0; i < 8; i++) { sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl); }
   return d.a * (x.s * (float)(sh * 256 + sl)) - d.b * x.sx;
-}
-
-// dense types: fp32 activation from shared memory; 16 bytes of weights per step (rows of dense matrices start on
-// 16-byte boundaries in practice; a 2-byte aligned row falls back to word loads + funnel shifts)
-template <int T>
-__device__ __forceinline__ float unit_dot_dense(saddr_t rowp, int u, saddr_t xf) {
-  const saddr_t xv = xf + 128u * (uint32_t)u;
-  constexpr int kBytes = T == F32 ? 128 : 64;
-  const saddr_t wp = rowp + (uint32_t)u * kBytes;
-  float acc = 0.f;
-#pragma unroll
-  for (int i = 0; i < kBytes / 16; i++) {
-    uint32_t w[4];
-    if ((wp & 15u) == 0) { const uint4 v = lds_u128(wp + 16u * i); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
-    else load_words<4>(wp + 16u * i, w);
-    if (T == F32) {
-      const float4 x0 = lds_f128(xv + 16u * i);
-      acc = fmaf(__uint_as_float(w[0]), x0.x, acc); acc = fmaf(__uint_as_float(w[1]), x0.y, acc);
-      acc = fmaf(__uint_as_float(w[2]), x0.z, acc); acc = fmaf(__uint_as_float(w[3]), x0.w, acc);
-    } else {
-      const float4 x0 = lds_f128(xv + 32u * i), x1 = lds_f128(xv + 32u * i + 16u);
-      float a[8];
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        if (T == BF16) { a[2 * k] = __uint_as_float(w[k] << 16); a[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u); }
-        else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k])); a[2 * k] = f.x; a[2 * k + 1] = f.y; }
-      }
-      acc = fmaf(a[0], x0.x, acc); acc = fmaf(a[1], x0.y, acc); acc = fmaf(a[2], x0.z, acc); acc = fmaf(a[3], x0.w, acc);
-      acc = fmaf(a[4], x1.x, acc); acc = fmaf(a[5], x1.y, acc); acc = fmaf(a[6], x1.z, acc); acc = fmaf(a[7], x1.w, acc);
-    }
-  }
-  return acc;
 }
 
 // ---------------------------------------------------------------- exact dequantisation of 8 consecutive elements

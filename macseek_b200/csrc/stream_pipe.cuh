@@ -139,23 +139,71 @@ __device__ __forceinline__ bool load_luts(uint8_t* lut, bool iq1s, bool iq2, boo
 template <int T, int LPR, int NRT, int NC>
 __device__ __forceinline__ void consume_rows(const saddr_t (&rowp)[NRT], int li, const XqSmem (&xq)[NC], int unit0,
                                              int nunits, const LaneLuts& L, float (&acc)[NRT][NC]) {
-  for (int uu = li; uu < nunits; uu += LPR) {
-    if constexpr (is_dense(T)) {
+  if constexpr (T == Q6_K) {
+    // lanes split the row's half super-blocks (the staged run starts on a super-block and holds whole ones)
+    for (int it = li; it < nunits / 4; it += LPR) {
+      saddr_t blk[NRT];
 #pragma unroll
-      for (int i = 0; i < NRT; i++)
+      for (int i = 0; i < NRT; i++) blk[i] = rowp[i] + (uint32_t)(it >> 1) * 210u;
+      q6k_half_block<NRT, NC>(blk, it & 1, xq, unit0 + 4 * it, acc);
+    }
+    return;
+  }
+  if constexpr (is_dense(T)) {
+    // lanes split the run's 16-byte weight granules (4 fp32 or 8 16-bit elements), consecutive lanes on consecutive
+    // granules; the activation is fp32 in shared memory (two planes for 16-bit weights, see the staging code)
+    constexpr int kGran = T == F32 ? 8 : 4;            // granules per 32-element unit
+    const int ng = nunits * kGran;
+    for (int g = li; g < ng; g += LPR) {
+      float xv[NC][8];
 #pragma unroll
-        for (int c = 0; c < NC; c++) acc[i][c] += unit_dot_dense<T>(rowp[i], uu, xq[c].xf_s + 128u * (uint32_t)unit0);
-    } else {
-      XRegs xr[NC];
-#pragma unroll
-      for (int c = 0; c < NC; c++) load_xq(xq[c], unit0 + uu, xr[c]);
+      for (int c = 0; c < NC; c++) {
+        const saddr_t xa = xq[c].xf_s + 16u * (uint32_t)(unit0 * kGran + g);
+        const float4 x0 = lds_f128(xa);
+        xv[c][0] = x0.x; xv[c][1] = x0.y; xv[c][2] = x0.z; xv[c][3] = x0.w;
+        if (T != F32) {
+          const float4 x1 = lds_f128(xa + 64u * (uint32_t)xq[c].U);
+          xv[c][4] = x1.x; xv[c][5] = x1.y; xv[c][6] = x1.z; xv[c][7] = x1.w;
+        }
+      }
 #pragma unroll
       for (int i = 0; i < NRT; i++) {
-        Dec<T> d;
-        decode_unit<T>(rowp[i], uu, L, d);
+        const saddr_t wp = rowp[i] + 16u * (uint32_t)g;
+        uint32_t w[4];
+        if ((wp & 15u) == 0) { const uint4 v = lds_u128(wp); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+        else load_words<4>(wp, w);
+        float a[8];
+        if (T == F32) {
 #pragma unroll
-        for (int c = 0; c < NC; c++) acc[i][c] += dot_unit<T>(d, xr[c]);
+          for (int k = 0; k < 4; k++) a[k] = __uint_as_float(w[k]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            if (T == BF16) { a[2 * k] = __uint_as_float(w[k] << 16); a[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u); }
+            else { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k])); a[2 * k] = f.x; a[2 * k + 1] = f.y; }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+          float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+          for (int k = 0; k < (T == F32 ? 4 : 8); k += 2) { s0 = fmaf(a[k], xv[c][k], s0); s1 = fmaf(a[k + 1], xv[c][k + 1], s1); }
+          acc[i][c] += s0 + s1;
+        }
       }
+    }
+    return;
+  }
+  for (int uu = li; uu < nunits; uu += LPR) {
+    XRegs xr[NC];
+#pragma unroll
+    for (int c = 0; c < NC; c++) load_xq(xq[c], unit0 + uu, xr[c]);
+#pragma unroll
+    for (int i = 0; i < NRT; i++) {
+      Dec<T> d;
+      decode_unit<T>(rowp[i], uu, L, d);
+#pragma unroll
+      for (int c = 0; c < NC; c++) acc[i][c] += dot_unit<T>(d, xr[c]);
     }
   }
 }

@@ -1,0 +1,158 @@
+"""Per-kernel timing of the decode path's kernels, outside the full decode step.
+
+    python -m macseek_b200.kernel_bench matvec Q6_K 129280 4096 [--n 1] [--groups 1]
+    python -m macseek_b200.kernel_bench moe {router|gu|down|all}
+    python -m macseek_b200.kernel_bench sweep
+
+Each case builds synthetic weights on the device (several copies, together larger than the 126 MB L2, used in
+rotation), records 20 launches into one CUDA graph and times graph replays with CUDA events on the replaying
+stream, so that the host's launch cost is not part of the figure.  ``--eager K`` instead issues K plain launches
+and exits: the form to put under a profiler, which should see few launches.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import arch, moe_layer as ml, quant as q, synthetic
+from .core import Enc
+
+
+def graph_time(fn, n_in_graph: int = 20, reps: int = 10):
+    """Median and minimum time (microseconds) of one call of ``fn(i)`` inside a replayed CUDA graph."""
+    fn(0)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(n_in_graph):
+                fn(i)
+        for _ in range(3):
+            g.replay()
+        s.synchronize()
+        ts = []
+        for _ in range(reps):
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record(s)
+            g.replay()
+            b.record(s)
+            s.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3 / n_in_graph)
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def run(fn, eager: int):
+    if eager:
+        for i in range(eager):
+            fn(i)
+        torch.cuda.synchronize()
+        return None
+    return graph_time(fn)
+
+
+def matvec_case(t: q.QType, rows: int, cols: int, n: int = 1, groups: int = 1, eager: int = 0):
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2)
+    nbytes = synthetic.row_bytes(t, cols) * rows
+    copies = min(max(2, int(600e6 // nbytes)), 20)
+    Ws = [synthetic.random_weights(t, rows, cols, gen) for _ in range(copies)]
+    x = torch.randn(n, cols * groups, device="cuda")
+    y = torch.zeros(n, rows, device="cuda")
+
+    def f(i):
+        e = Enc()
+        if n == 1:
+            q.encode_matvec(e, t, Ws[i % copies], rows, cols, x, y, False, groups)
+        else:
+            q.encode_matvec_n(e, t, Ws[i % copies], rows, cols, x, y, n, False, groups)
+
+    r = run(f, eager)
+    if r:
+        print(f"matvec {t.name:8s} {rows:6d}x{cols:6d} n={n} g={groups} median {r[0]:8.2f} us min {r[1]:8.2f}"
+              f"  {nbytes / r[0] / 1e3:8.1f} GB/s  ({nbytes / 1e6:.1f} MB x{copies})", flush=True)
+
+
+def moe_cases(which: str, eager: int = 0):
+    """The benchmark MoE layer: 8 of 384 routed experts (IQ1_S gate/up, IQ2_XXS down) + Q8_0 shared expert."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    L = 4
+    layers = [ml.MoeLayerWeights(4096, 2048, 384, q.QType.IQ1_S, q.QType.IQ2_XXS, q.QType.Q8_0).randomize(gen)
+              for _ in range(L)]
+    bufs = ml.MoeLayerBufs(4096, 2048, 384, 8)
+    xs = [torch.randn(4096, device="cuda", generator=gen) for _ in range(16)]
+    y = torch.zeros(4096, device="cuda")
+    idsets = [torch.randperm(384, device="cuda", generator=gen)[:8].int().contiguous() for _ in range(20)]
+    bufs.w.fill_(0.125)
+
+    def mk(part):
+        def f(i):
+            e = Enc()
+            lw = layers[i % L]
+            a = q.MoeDecodeArgs(4096, 2048)
+            a.t_gate_up, a.t_down, a.t_shared = lw.t_gate_up, lw.t_down, lw.t_shared
+            a.n_routed, a.has_shared, a.shared = 8, True, lw.shared
+            a.weights, a.x, a.y, a.scratch = bufs.w, xs[i % 16], y, bufs.moe_scratch
+            q.encode_moe_decode_ids(e, a, lw.table, idsets[i % 20], 0, 384, part)
+        return f
+
+    def router(i):
+        e = Enc()
+        lw = layers[i % L]
+        arch.encode_router_fused(e, xs[i % 16], lw.router_w, lw.router_bias, bufs.ids, bufs.w, bufs.router_scratch,
+                                 8, 1, 1.0)
+
+    iq1 = synthetic.row_bytes(q.QType.IQ1_S, 4096) * 2048
+    iq2 = synthetic.row_bytes(q.QType.IQ2_XXS, 2048) * 4096
+    q8a = synthetic.row_bytes(q.QType.Q8_0, 4096) * 2048
+    q8b = synthetic.row_bytes(q.QType.Q8_0, 2048) * 4096
+    gu_bytes = 8 * 2 * iq1 + 2 * q8a
+    d_bytes = 8 * iq2 + q8b
+    cases = {"router": (router, 384 * 4096 * 4), "gu": (mk(q.MoePart.GuAll), gu_bytes),
+             "down": (mk(q.MoePart.DownAll), d_bytes), "all": (mk(q.MoePart.All), gu_bytes + d_bytes)}
+    for name in (cases if which == "every" else [which]):
+        fn, nbytes = cases[name]
+        r = run(fn, eager)
+        if r:
+            print(f"moe {name:8s} median {r[0]:8.2f} us  min {r[1]:8.2f} us   {nbytes / r[0] / 1e3:8.1f} GB/s",
+                  flush=True)
+
+
+def sweep():
+    T = q.QType
+    moe_cases("every")
+    for t in (T.IQ1_S, T.IQ2_XXS, T.Q8_0, T.Q6_K, T.Q5_K, T.IQ4_NL, T.BF16, T.F32):
+        matvec_case(t, 16384, 4096)
+    # the decode step's own shapes
+    for t, r, c, g in ((T.Q6_K, 1280, 4096, 1), (T.Q6_K, 576, 4096, 1), (T.Q6_K, 36864, 1280, 1),
+                       (T.Q6_K, 8192, 4608, 8), (T.Q6_K, 4096, 8192, 1), (T.BF16, 8192, 1280, 1),
+                       (T.BF16, 64, 4096, 1), (T.Q6_K, 129280, 4096, 1), (T.Q6_K, 4096, 16384, 1)):
+        matvec_case(t, r, c, 1, g)
+    matvec_case(T.Q6_K, 16384, 4096, 4)
+    matvec_case(T.IQ2_XXS, 16384, 4096, 4)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("case", choices=["matvec", "moe", "sweep"])
+    ap.add_argument("args", nargs="*")
+    ap.add_argument("--n", type=int, default=1)
+    ap.add_argument("--groups", type=int, default=1)
+    ap.add_argument("--eager", type=int, default=0, help="issue this many plain launches and exit (no timing)")
+    a = ap.parse_args()
+    torch.cuda.set_device(0)
+    if a.case == "matvec":
+        matvec_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n, a.groups, a.eager)
+    elif a.case == "moe":
+        moe_cases(a.args[0] if a.args else "every", a.eager)
+    else:
+        sweep()
+    torch.cuda.synchronize()
+
+
+if __name__ == "__main__":
+    main()
