@@ -75,47 +75,6 @@ __global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvPar
   ring_init(ring, tid, NW);
   if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, NW); mbar_fence_init(); }
   __syncthreads();
-  LaneLuts L;
-  const bool luts_ok = load_luts(lut, T == IQ1_S, T == IQ2_XXS, T == IQ4_NL, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
-  pdl_wait();     // everything above is independent of the previous kernel; x (and y) are not
-  // activation of this block's group -> shared (fixed point, or fp32 for dense weights), optionally RMS-normalised
-#pragma unroll
-  for (int c = 0; c < NC; c++) {
-    const float* xg = p.x + (size_t)c * p.x_stride + (size_t)group * p.cols;
-    float mul = 1.f;
-    if (p.norm_w) {
-      float ss = 0.f;
-      for (int i = tid; i < p.cols / 4; i += blockDim.x) {
-        const float4 v = reinterpret_cast<const float4*>(xg)[i];
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) hd->red[warp] = ss;
-      __syncthreads();
-      float tot = 0.f;
-      for (int w = 0; w < NW + 1; w++) tot += hd->red[w];
-      __syncthreads();
-      mul = rsqrtf(tot / (float)p.cols + p.norm_eps);
-    }
-    if (is_dense(T)) {
-      float4* d = reinterpret_cast<float4*>(const_cast<float*>(xq[c].xf));
-      for (int i = tid; i < U * 8; i += blockDim.x) {
-        float4 v = reinterpret_cast<const float4*>(xg)[i];
-        if (p.norm_w) {
-          const float4 gw = reinterpret_cast<const float4*>(p.norm_w)[i];
-          v.x = v.x * mul * gw.x; v.y = v.y * mul * gw.y; v.z = v.z * mul * gw.z; v.w = v.w * mul * gw.w;
-        }
-        // 16-bit weights: one 16-byte weight granule spans 8 activations, kept as two float4 planes (elements
-        // 8g..8g+3 and 8g+4..8g+7 of granule g) so that lanes on consecutive granules read consecutive addresses
-        d[T == F32 ? i : (i & 1) * (U * 4) + (i >> 1)] = v;
-      }
-    } else {
-      quantize_x(xg, xq[c], tid, blockDim.x, mul, p.norm_w);
-    }
-  }
-  __syncthreads();
-  if (!luts_ok) return;
-
   const int R = p.tile_rows, KS = p.ks;
   const bool whole = p.chunk_units >= U;             // whole rows per piece: the tile is one contiguous copy
   const int nchunks = whole ? 1 : (U + p.chunk_units - 1) / p.chunk_units;
@@ -143,6 +102,49 @@ __global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvPar
     return;
   }
   // ---------------- consumer warps
+  LaneLuts L;
+  const bool luts_ok = load_luts(lut, T == IQ1_S, T == IQ2_XXS, T == IQ4_NL, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
+  // Everything up to here, and the producer warp's weight copies, is independent of the previous kernel (weights are
+  // constants); x (and y, when accumulating) are not.
+  pdl_wait();
+  // activation of this block's group -> shared (fixed point, or fp32 for dense weights), optionally RMS-normalised
+#pragma unroll
+  for (int c = 0; c < NC; c++) {
+    const float* xg = p.x + (size_t)c * p.x_stride + (size_t)group * p.cols;
+    float mul = 1.f;
+    if (p.norm_w) {
+      float ss = 0.f;
+      for (int i = tid; i < p.cols / 4; i += NW * 32) {
+        const float4 v = reinterpret_cast<const float4*>(xg)[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) hd->red[warp] = ss;
+      bar_sync_named(1, NW * 32);
+      float tot = 0.f;
+      for (int w = 0; w < NW; w++) tot += hd->red[w];
+      bar_sync_named(1, NW * 32);
+      mul = rsqrtf(tot / (float)p.cols + p.norm_eps);
+    }
+    if (is_dense(T)) {
+      float4* d = reinterpret_cast<float4*>(const_cast<float*>(xq[c].xf));
+      for (int i = tid; i < U * 8; i += NW * 32) {
+        float4 v = reinterpret_cast<const float4*>(xg)[i];
+        if (p.norm_w) {
+          const float4 gw = reinterpret_cast<const float4*>(p.norm_w)[i];
+          v.x = v.x * mul * gw.x; v.y = v.y * mul * gw.y; v.z = v.z * mul * gw.z; v.w = v.w * mul * gw.w;
+        }
+        // 16-bit weights: one 16-byte weight granule spans 8 activations, kept as two float4 planes (elements
+        // 8g..8g+3 and 8g+4..8g+7 of granule g) so that lanes on consecutive granules read consecutive addresses
+        d[T == F32 ? i : (i & 1) * (U * 4) + (i >> 1)] = v;
+      }
+    } else {
+      quantize_x(xg, xq[c], tid, NW * 32, mul, p.norm_w);
+    }
+  }
+  bar_sync_named(1, NW * 32);
+  if (!luts_ok) return;
+
   const int grp = lane / LPR, li = lane % LPR;
   // rows of this lane group inside the tile, and (KS > 1) this warp's share of the row's units
   const int lr0 = KS > 1 ? warp / KS : (warp * G + grp) * NR;
@@ -212,13 +214,16 @@ __global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvPar
 // ---------------------------------------------------------------- host side
 namespace {
 
-// lanes per row: the largest of 32/16/8 that wastes the fewest lane iterations on this row length
-int pick_lpr(int units) {
+// lanes per row: of 32/16/8 the one that wastes the fewest lane iterations on `items` work items per row, among
+// those whose smallest whole-row tile (16 warps x 32/lpr rows) fits `tile_cap` bytes; 32 when none does (long rows
+// are then shared by several warps or streamed in chunks)
+int pick_lpr(int items, size_t row_bytes, size_t tile_cap) {
   int best = 32;
   double best_eff = 0;
   for (int lpr : {32, 16, 8}) {
-    const int iters = (units + lpr - 1) / lpr;
-    const double eff = (double)units / (iters * lpr);
+    if (lpr < 32 && (size_t)kMvNW * (32 / lpr) * row_bytes + 192 > tile_cap) continue;
+    const int iters = (items + lpr - 1) / lpr;
+    const double eff = (double)items / (iters * lpr);
     if (eff > best_eff + 1e-9) { best_eff = eff; best = lpr; }
   }
   return best;
@@ -322,7 +327,9 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
 template <int T, int NC>
 int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
   // Q6_K rows are split by half super-block (4 units), the other types by unit
-  switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units)) {
+  const size_t fixed = lut_bytes_for(T) + (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 1024;
+  const size_t tile_cap = fixed < (size_t)kSmemLimit ? ((size_t)kSmemLimit - fixed) / 2 : 0;
+  switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, tile_cap)) {
     case 32: return launch_rows<T, 32, NC>(p, st, dev, sms);
     case 16: return launch_rows<T, 16, NC>(p, st, dev, sms);
     default: return launch_rows<T, 8, NC>(p, st, dev, sms);

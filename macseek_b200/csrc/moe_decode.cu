@@ -78,25 +78,27 @@ __device__ __forceinline__ void end_of_tiles(const Ring& ring, uint32_t n, MoeSm
 }
 
 // ---------------------------------------------------------------------------------------------------- gate/up
-// A tile is R rows of one expert: the gate rows arrive as one contiguous piece, the same rows of the up matrix as the
-// next.  Routed experts (cheap bytes, expensive decode): each warp owns NR whole rows.  Shared expert (long rows):
-// KS warps share a row, each a contiguous run of units; the (gate, up) partial sums meet in shared memory.
-struct GuTile { const uint8_t* G; const uint8_t* U; int r0, R, KS; uint32_t rb; float* hrow; float w; };
+// A tile is R rows of one expert's gate matrix and the same R rows of its up matrix, staged side by side in one ring
+// slot (two contiguous copies, one barrier): a lane decodes the gate and the up rows it owns against activation
+// registers loaded once.  Routed experts (cheap bytes, expensive decode): each warp owns NR whole row pairs.  Shared
+// expert (long rows): KS warps share a row pair, each a contiguous run of units; the (gate, up) partial sums meet in
+// shared memory.
+struct GuTile { const uint8_t* G; const uint8_t* U; int r0, R, KS; uint32_t rb, pitch; float* hrow; float w; };
 
 __device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& ring, uint32_t& n, const GuTile& tl,
                                                 int lane, int tile, MoeSmemHead* hd) {
-  Piece pc;
-  pc.nsrc = 1; pc.rows_per_src = 1; pc.nrows = 1; pc.row_stride = tl.rb;
-  pc.bytes = (uint32_t)min(tl.R, p.inter - tl.r0) * tl.rb;
-  for (int m = 0; m < 2; m++, n++) {
-    const int s = n % ring.stages;
-    if (m == 0) { if (!announce_tile(ring, n, hd, tile, lane)) return false; }
-    else if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return false;
-    if (lane == 0) hd->srcs[s][0] = (m ? tl.U : tl.G) + (size_t)tl.r0 * tl.rb;
-    __syncwarp();
-    pc.src = hd->srcs[s];
-    if (!produce_piece(ring, n, pc, 0, lane)) return false;
+  const int s = n % ring.stages;
+  if (!announce_tile(ring, n, hd, tile, lane)) return false;
+  if (lane == 0) {
+    hd->srcs[s][0] = tl.G + (size_t)tl.r0 * tl.rb;
+    hd->srcs[s][1] = tl.U + (size_t)tl.r0 * tl.rb;
   }
+  __syncwarp();
+  Piece pc;
+  pc.src = hd->srcs[s]; pc.nsrc = 2; pc.rows_per_src = 1; pc.nrows = 1; pc.row_stride = tl.rb;
+  pc.bytes = (uint32_t)min(tl.R, p.inter - tl.r0) * tl.rb;
+  if (!produce_piece(ring, n, pc, tl.pitch, lane)) return false;
+  n++;
   return true;
 }
 
@@ -115,23 +117,27 @@ __device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& 
     const int per = ((U + KS * step - 1) / (KS * step)) * step;
     ua = min(U, kpart * per); ub = min(U, ua + per);
   }
-  float acc[2][NR][1];
+  float acc[2 * NR][1];    // [0 .. NR): gate rows, [NR .. 2 NR): up rows
 #pragma unroll
-  for (int i = 0; i < NR; i++) { acc[0][i][0] = 0.f; acc[1][i][0] = 0.f; }
+  for (int i = 0; i < 2 * NR; i++) acc[i][0] = 0.f;
+  {
+    const uintptr_t ag = reinterpret_cast<uintptr_t>(tl.G) + (size_t)tl.r0 * tl.rb;
+    const uintptr_t au = reinterpret_cast<uintptr_t>(tl.U) + (size_t)tl.r0 * tl.rb;
+    const saddr_t slot = smem_u32(ring.slot(n)) + (uint32_t)units_bytes(T, ua);
+    saddr_t rowp[2 * NR];
 #pragma unroll
-  for (int m = 0; m < 2; m++, n++) {
-    const uintptr_t a0 = reinterpret_cast<uintptr_t>(m ? tl.U : tl.G) + (size_t)tl.r0 * tl.rb;
-    const saddr_t base = smem_u32(ring.slot(n)) + (uint32_t)(a0 & 15u) + (uint32_t)units_bytes(T, ua);
-    saddr_t rowp[NR];
-#pragma unroll
-    for (int i = 0; i < NR; i++) rowp[i] = base + (uint32_t)(lr0 + i) * tl.rb;
+    for (int i = 0; i < NR; i++) {
+      rowp[i] = slot + (uint32_t)(ag & 15u) + (uint32_t)(lr0 + i) * tl.rb;
+      rowp[NR + i] = slot + tl.pitch + (uint32_t)(au & 15u) + (uint32_t)(lr0 + i) * tl.rb;
+    }
     if (!consumer_wait(ring, n)) return false;
-    if (ub > ua) consume_rows<T, LPR, NR, 1>(rowp, li, xq, ua, ub - ua, L, acc[m]);
+    if (ub > ua) consume_rows<T, LPR, 2 * NR, 1>(rowp, li, xq, ua, ub - ua, L, acc);
     consumer_release(ring, n, lane);
+    n++;
   }
   if (KS > 1) {
     const int pb = tile_count & 1;
-    const float g = group_sum<32>(acc[0][0][0]), u = group_sum<32>(acc[1][0][0]);
+    const float g = group_sum<32>(acc[0][0]), u = group_sum<32>(acc[NR][0]);
     if (lane == 0) { hd->part[pb][warp][0] = g; hd->part[pb][warp][1] = u; }
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->tilebar);
@@ -145,16 +151,25 @@ __device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& 
   } else {
 #pragma unroll
     for (int i = 0; i < NR; i++) {
-      const float g = group_sum<LPR>(acc[0][i][0]), u = group_sum<LPR>(acc[1][i][0]);
+      const float g = group_sum<LPR>(acc[i][0]), u = group_sum<LPR>(acc[NR + i][0]);
       if (li == 0 && tl.r0 + lr0 + i < p.inter) tl.hrow[tl.r0 + lr0 + i] = swiglu(g, u, tl.w, p.limit);
     }
   }
   return true;
 }
 
+// Tile order: a block's first tile is its block index, later ones come from the launch's atomic counter (offset by the
+// grid size).  The producer warp stages that first tile before the grid dependency is resolved when it is a
+// shared-expert tile (constant data); everything that depends on the router's output waits for the consumers, which
+// resolve the dependency, the resident experts and the activation, at the block barrier.
+__device__ __forceinline__ int next_tile(unsigned* sched, int lane) {
+  int t = 0;
+  if (lane == 0) t = (int)(gridDim.x + atomicAdd(&sched[0], 1u));
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
 template <int TR, int TS, int LPR>
 __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeParams p) {
-  constexpr int NR_R = 2;
   pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t smem[];
   MoeSmemHead* hd = reinterpret_cast<MoeSmemHead*>(smem);
@@ -175,53 +190,59 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
   ring_init(ring, tid, kMoeNW);
   if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, kMoeNW); mbar_fence_init(); }
   __syncthreads();
-  LaneLuts L;
-  const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
-  pdl_wait();     // the router's ids / weights and x come from the previous kernels
-  if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
-  quantize_x(p.x, xq[0], tid, blockDim.x);
-  __syncthreads();
-  if (!luts_ok) return;
 
   const int R_R = p.gu_r_rows, R_S = p.gu_s_rows;
   const int tiles_s = p.gu_s ? (p.inter + R_S - 1) / R_S : 0;
   const int tiles_r1 = (p.inter + R_R - 1) / R_R;
-  const int ntiles = tiles_s + hd->n_local * tiles_r1;
   const uint32_t rb_r = (uint32_t)row_bytes(TR, p.dim), rb_s = (uint32_t)row_bytes(TS, p.dim);
   // tile id -> what to stream: shared-expert tiles first (they are the largest), then the resident routed experts
   auto tile_of = [&](int t) {
     GuTile tl;
     if (t < tiles_s) {
-      tl.G = p.sgate; tl.U = p.sup; tl.r0 = t * R_S; tl.R = R_S; tl.KS = p.gu_s_ks; tl.rb = rb_s;
+      tl.G = p.sgate; tl.U = p.sup; tl.r0 = t * R_S; tl.R = R_S; tl.KS = p.gu_s_ks; tl.rb = rb_s; tl.pitch = p.gu_s_pitch;
       tl.hrow = p.h + (size_t)p.n_routed * p.inter; tl.w = 1.0f;
     } else {
       const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
       const int k = hd->local_slot[i];
-      tl.G = hd->p0[i]; tl.U = hd->p1[i]; tl.r0 = rt * R_R; tl.R = R_R; tl.KS = 1; tl.rb = rb_r;
+      tl.G = hd->p0[i]; tl.U = hd->p1[i]; tl.r0 = rt * R_R; tl.R = R_R; tl.KS = 1; tl.rb = rb_r; tl.pitch = p.gu_r_pitch;
       tl.hrow = p.h + (size_t)k * p.inter; tl.w = __ldg(p.weights + k);
     }
     return tl;
   };
   uint32_t n = 0;
   if (warp == kMoeNW) {
-    for (;;) {
-      int t = 0;
-      if (lane == 0) t = (int)atomicAdd(&p.sched[0], 1u);
-      t = __shfl_sync(0xffffffffu, t, 0);
-      if (t >= ntiles) break;
+    int t = blockIdx.x;
+    const bool early = t < tiles_s;
+    if (early && !gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
+    __syncthreads();
+    pdl_wait();
+    const int ntiles = tiles_s + hd->n_local * tiles_r1;
+    if (early) t = next_tile(p.sched, lane);
+    while (t < ntiles) {
       if (!gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
+      t = next_tile(p.sched, lane);
     }
     end_of_tiles(ring, n, hd, p.sched, lane);
     return;
   }
+  LaneLuts L;
+  const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
+  pdl_wait();     // the router's ids / weights and x come from the previous kernels
+  if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
+  quantize_x(p.x, xq[0], tid, kMoeNW * 32);
+  __syncthreads();
+  if (!luts_ok) return;
+  const bool two_pairs = R_R == kMoeNW * (32 / LPR) * 2;   // row pairs per lane group of a routed tile: 2 or 1
   uint32_t tile_count = 0;
   for (;;) {
     if (!consumer_wait(ring, n)) return;
     const int t = *reinterpret_cast<volatile int*>(&hd->meta[n % ring.stages]);
     if (t < 0) return;
     const GuTile tl = tile_of(t);
-    const bool ok = t < tiles_s ? gu_tile_consume<TS, LPR, 1>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count)
-                                : gu_tile_consume<TR, LPR, NR_R>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count);
+    bool ok;
+    if (t < tiles_s) ok = gu_tile_consume<TS, LPR, 1>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count);
+    else if (two_pairs) ok = gu_tile_consume<TR, LPR, 2>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count);
+    else ok = gu_tile_consume<TR, LPR, 1>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count);
     if (!ok) return;
   }
 }
@@ -256,54 +277,62 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   ring_init(ring, tid, kMoeNW);
   if (tid == 0) { mbar_init(&hd->lutbar, 1); mbar_init(&hd->tilebar, kMoeNW); mbar_fence_init(); }
   __syncthreads();
-  LaneLuts L;
-  const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
-  pdl_wait();     // h comes from the gate/up kernel
-  if (tid == 0) resolve_local(p, hd, p.d_r != 0, true);
-  quantize_x(p.h, xq[0], tid, blockDim.x);
-  __syncthreads();
-  if (!luts_ok) return;
-
   const int ntiles = (p.dim + R - 1) / R;
-  const int n_local = hd->n_local;
   const uint32_t rb_r = (uint32_t)row_bytes(TR, p.inter), rb_s = (uint32_t)row_bytes(TS, p.inter);
   uint32_t n = 0;
   if (warp == kMoeNW) {
-    for (;;) {
-      int t = 0;
-      if (lane == 0) t = (int)atomicAdd(&p.sched[0], 1u);
-      t = __shfl_sync(0xffffffffu, t, 0);
-      if (t >= ntiles) break;
+    // Per tile: the shared expert's rows first (constant data: the first tile's are staged before the grid
+    // dependency is resolved), then the rows of every resident routed expert.
+    int t = blockIdx.x;                      // the grid has at most ntiles blocks
+    bool first_done = false;
+    Piece pc;
+    pc.rows_per_src = 1; pc.nrows = 1;
+    auto shared_piece = [&](bool announce) {
+      const int s = n % ring.stages;
       const int r0 = t * R, nrows = min(R, p.dim - r0);
-      Piece pc;
-      pc.rows_per_src = 1; pc.nrows = 1;
-      bool first = true;
-      auto slot_ready = [&](int s) {
-        if (first) { first = false; return announce_tile(ring, n, hd, t, lane); }
-        return mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty);
-      };
+      if (announce ? !announce_tile(ring, n, hd, t, lane)
+                   : !mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty))
+        return false;
+      if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s;
+      __syncwarp();
+      pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s; pc.bytes = (uint32_t)nrows * rb_s;
+      if (!produce_piece(ring, n, pc, 0, lane)) return false;
+      n++;
+      return true;
+    };
+    if (p.d_s) { if (!shared_piece(true)) return; first_done = true; }
+    __syncthreads();
+    pdl_wait();
+    const int n_local = hd->n_local;
+    while (t < ntiles) {
+      const int r0 = t * R, nrows = min(R, p.dim - r0);
+      bool announced = first_done;
+      if (p.d_s && !first_done) { if (!shared_piece(true)) return; announced = true; }
+      first_done = false;
       if (n_local > 0) {
         const int s = n % ring.stages;
-        if (!slot_ready(s)) return;
+        if (!announced ? !announce_tile(ring, n, hd, t, lane)
+                       : !mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty))
+          return;
         for (int e = lane; e < n_local; e += 32) hd->srcs[s][e] = hd->p0[e] + (size_t)r0 * rb_r;
         __syncwarp();
         pc.src = hd->srcs[s]; pc.nsrc = n_local; pc.row_stride = rb_r; pc.bytes = (uint32_t)nrows * rb_r;
         if (!produce_piece(ring, n, pc, p.d_src_pitch, lane)) return;
         n++;
       }
-      if (p.d_s) {
-        const int s = n % ring.stages;
-        if (!slot_ready(s)) return;
-        if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s;
-        __syncwarp();
-        pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s; pc.bytes = (uint32_t)nrows * rb_s;
-        if (!produce_piece(ring, n, pc, 0, lane)) return;
-        n++;
-      }
+      t = next_tile(p.sched, lane);
     }
     end_of_tiles(ring, n, hd, p.sched, lane);
     return;
   }
+  LaneLuts L;
+  const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
+  pdl_wait();     // h comes from the gate/up kernel
+  if (tid == 0) resolve_local(p, hd, p.d_r != 0, true);
+  quantize_x(p.h, xq[0], tid, kMoeNW * 32);
+  __syncthreads();
+  if (!luts_ok) return;
+  const int n_local = hd->n_local;
   const int row = warp >> 1, half = warp & 1;
   const int grp = lane / LPR, li = lane % LPR;   // LPR < 32: lane groups take alternate sources / unit runs
   uint32_t tile_count = 0;
@@ -313,17 +342,6 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
     if (t < 0) return;
     const int r0 = t * R;
     float acc[1][1] = {{0.f}};
-    if (n_local > 0) {
-      if (!consumer_wait(ring, n)) return;
-      const saddr_t slot = smem_u32(ring.slot(n));
-      for (int e = half * Gn + grp; e < n_local; e += 2 * Gn) {
-        const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)r0 * rb_r;
-        const saddr_t rowp[1] = {slot + (uint32_t)e * p.d_src_pitch + (uint32_t)(a & 15u) + (uint32_t)row * rb_r};
-        consume_rows<TR, LPR, 1, 1>(rowp, li, xq, hd->local_slot[e] * Ui, Ui, L, acc);
-      }
-      consumer_release(ring, n, lane);
-      n++;
-    }
     if (p.d_s) {
       if (!consumer_wait(ring, n)) return;
       const saddr_t slot = smem_u32(ring.slot(n));
@@ -336,6 +354,17 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
       if (ub > ua) {
         const saddr_t rowp[1] = {slot + (uint32_t)(a & 15u) + (uint32_t)row * rb_s + (uint32_t)units_bytes(TS, ua)};
         consume_rows<TS, LPR, 1, 1>(rowp, li, xq, p.n_routed * Ui + ua, ub - ua, L, acc);
+      }
+      consumer_release(ring, n, lane);
+      n++;
+    }
+    if (n_local > 0) {
+      if (!consumer_wait(ring, n)) return;
+      const saddr_t slot = smem_u32(ring.slot(n));
+      for (int e = half * Gn + grp; e < n_local; e += 2 * Gn) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)r0 * rb_r;
+        const saddr_t rowp[1] = {slot + (uint32_t)e * p.d_src_pitch + (uint32_t)(a & 15u) + (uint32_t)row * rb_r};
+        consume_rows<TR, LPR, 1, 1>(rowp, li, xq, hd->local_slot[e] * Ui, Ui, L, acc);
       }
       consumer_release(ring, n, lane);
       n++;
@@ -381,20 +410,31 @@ int launch_gu(MoeParams& p, int sms, int dev, cudaStream_t st) {
   const int U = p.dim / 32;
   const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(TR) + xq_bytes(U, false, xq_padded(TR) || xq_padded(TS)) + 128;
   if (fixed + 3 * 8192 > (size_t)kSmemLimit) return fail(kErrLimit, "moe_decode: dim %d does not fit in shared memory", p.dim);
-  const int stages = 3;
-  const size_t slot = (((size_t)kSmemLimit - fixed) / stages) & ~(size_t)127;
+  const size_t avail = (size_t)kSmemLimit - fixed;
   const size_t rb_r = row_bytes(TR, p.dim), rb_s = row_bytes(TS, p.dim);
-  // routed tiles: every warp owns 2 whole rows per lane group
-  p.gu_r_rows = kMoeNW * Gn * 2;
-  if ((size_t)p.gu_r_rows * rb_r + 64 > slot) return fail(kErrLimit, "moe_decode: routed gate/up tile does not fit (dim %d)", p.dim);
-  // shared tiles: as many whole rows as fit, several warps per row when the rows are long
+  // room for R rows of one matrix in a slot: the source's misalignment, rounded to 16, plus the word the decoders may
+  // read past the end
+  auto pitch_of = [](size_t bytes) { return (uint32_t)((bytes + 15 + 16 + 15) & ~(size_t)15); };
+  // routed tiles: every warp owns 2 whole row pairs (gate + up) per lane group, 1 when a two-deep ring of those does
+  // not fit
+  int stages = 0;
+  for (int pairs : {2, 1}) {
+    p.gu_r_rows = kMoeNW * Gn * pairs;
+    p.gu_r_pitch = pitch_of((size_t)p.gu_r_rows * rb_r);
+    stages = (int)std::min<size_t>(kMaxStages, avail / (2 * (size_t)p.gu_r_pitch + 128));
+    if (stages >= 2) break;
+  }
+  if (stages < 2) return fail(kErrLimit, "moe_decode: routed gate/up tile does not fit (dim %d)", p.dim);
+  const size_t slot = (avail / stages) & ~(size_t)127;
+  // shared tiles: as many whole row pairs as fit, several warps per row when the rows are long
   p.gu_s_ks = 0;
-  if ((size_t)kMoeNW * Gn * rb_s + 64 <= slot) { p.gu_s_rows = kMoeNW * Gn; p.gu_s_ks = 1; }
+  if (2 * (size_t)pitch_of((size_t)kMoeNW * Gn * rb_s) <= slot) { p.gu_s_rows = kMoeNW * Gn; p.gu_s_ks = 1; }
   else if (LPR == 32) {
     for (int ks : {2, 4, 8, 16})
-      if ((size_t)(kMoeNW / ks) * rb_s + 64 <= slot) { p.gu_s_rows = kMoeNW / ks; p.gu_s_ks = ks; break; }
+      if (2 * (size_t)pitch_of((size_t)(kMoeNW / ks) * rb_s) <= slot) { p.gu_s_rows = kMoeNW / ks; p.gu_s_ks = ks; break; }
   }
   if (!p.gu_s_ks) return fail(kErrLimit, "moe_decode: shared gate/up tile does not fit (dim %d)", p.dim);
+  p.gu_s_pitch = pitch_of((size_t)p.gu_s_rows * rb_s);
   p.stages = stages;
   p.stage_bytes = (uint32_t)slot;
   auto kern = moe_gu_kernel<TR, TS, LPR>;

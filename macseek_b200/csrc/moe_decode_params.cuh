@@ -22,10 +22,12 @@ struct MoeParams {
   const float* x;
   float* y;
   float* h;                               // [n_routed + 1][inter]
-  unsigned* sched;                        // [2] tile counter, finished-block counter (zero between launches)
+  unsigned* sched;                        // [2] counter of tiles handed out after each block's first (tile = its
+                                          // block index), finished-block counter; both zero between launches
   float limit;
   // tile shapes (whole rows, every piece one contiguous bulk copy per source)
   int gu_r_rows;                          // routed gate/up tile rows (each warp owns whole rows)
+  uint32_t gu_r_pitch, gu_s_pitch;        // shared-memory distance between a tile's gate rows and its up rows
   int gu_s_rows, gu_s_ks;                 // shared gate/up tile rows, warps sharing a row
   int d_rows;                             // down tile rows (two warps share a row)
   uint32_t d_src_pitch;                   // shared-memory distance between the experts' row blocks of a down piece

@@ -137,6 +137,10 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 // Programmatic dependent launch: let the next kernel of the stream start its prologue / wait for the previous one.
+// barrier over a subset of the block's warps (the producer warp of a streaming kernel never joins the consumers')
+__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif  // __CUDACC__
