@@ -25,6 +25,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 METRIC = "decode_tok_per_s_200k_ctx"
 UNIT = "tok/s"
+# DRAM bytes (read + write) of one moe_gu_kernel launch of the benchmark layer, all 8 routed experts resident:
+# measured once with ncu (profiles/moe_gu_kernel_cfg3_ncu_full.txt); the algorithmic bytes are 44,040,192
+NCU_GU_TRAFFIC_BYTES = 44_283_648
 
 
 def parse():
@@ -292,6 +295,20 @@ def run_ours(a):
         ids_now = b.moe.ids.cpu().tolist()
         n_local = sum(1 for i in ids_now if lw0.expert_lo <= i < lw0.expert_hi)
         gu_bytes = n_local * 2 * lw0.gu_bytes + (lw0.shared.gate.numel() + lw0.shared.up.numel())
+        # the output head (Q6_K 129280 x dim) alone: the one launch of the step that is purely a weight stream
+        hgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(hgraph, stream=stream):
+            for _ in range(4):
+                q.encode_matvec(Enc(torch.cuda.current_stream()), cfg.t_head, model.w_head, cfg.vocab, cfg.dim, b.x,
+                                b.logits, False, 1)
+        hgraph.replay()
+        stream.synchronize()
+        ev6, ev7 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev6.record(stream)
+        hgraph.replay()
+        ev7.record(stream)
+        stream.synchronize()
+        head_us = ev6.elapsed_time(ev7) * 1e3 / 4
         st = __import__("macseek_b200._lib", fromlist=["x"]).device_status()
         if st:
             raise RuntimeError("device-side failure word %d" % st)
@@ -323,7 +340,13 @@ def run_ours(a):
                 "roofline": {"bound": "hbm", "kernel": "moe_gu_kernel (gate/up + SwiGLU of the routed experts resident here + shared expert)",
                              "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_source": peak_src, "us_per_launch": gu_us, "bytes_per_launch": gu_bytes,
-                             "traffic": None},
+                             # dram__bytes_read.sum + dram__bytes_write.sum of one launch with all 8 routed
+                             # experts resident, from the ncu capture summarised under profiles/
+                             "traffic": NCU_GU_TRAFFIC_BYTES if world == 1 else None},
+                "roofline_head": {"bound": "hbm", "kernel": "matvec_kernel<Q6_K> output head %d x %d" % (cfg.vocab, cfg.dim),
+                                  "achieved": cfg.head_bytes() / head_us / 1e3, "peak": peak, "unit": "GB/s",
+                                  "frac": cfg.head_bytes() / head_us / 1e3 / peak, "us_per_launch": head_us,
+                                  "bytes_per_launch": cfg.head_bytes()},
                 "step_bytes": {"per_token_this_rank": token_bytes, "gbs_whole_step": token_bytes / (ms / a.steps) / 1e6}}
         if world == 1 and not a.no_cpu_baseline:
             try:
