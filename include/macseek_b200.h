@@ -6,6 +6,11 @@
  * commit/wait)" (src/kernels/quant.hpp:3, arch.hpp:4-5, attn.hpp:3-4); a reference Buffer{buf, off} becomes the
  * device pointer buf + off, an Enc becomes the stream, and die()/abort() becomes a status code.
  * All pointers are device pointers unless a parameter is documented as host memory.  There is no CPU fallback.
+ *
+ * Weight matrices (W, expert matrices, expert tables) are treated as CONSTANTS: a kernel may start copying weight rows
+ * before earlier work on the stream has finished (launches use programmatic stream serialization), so weights must be
+ * in place and synchronised before the first call that reads them.  Activations, ids, scratch and outputs are ordered
+ * on the stream as usual.
  */
 #ifndef MACSEEK_B200_H
 #define MACSEEK_B200_H
@@ -88,6 +93,14 @@ enum { MSB_MOE_ALL = 0, MSB_MOE_SHARED_GU = 1, MSB_MOE_AFTER_SHARED_GU = 2, MSB_
        MSB_MOE_GU_ALL = 6, MSB_MOE_DOWN_ALL = 7 };
 size_t msb_moe_decode_scratch_bytes(int inter, int max_routed);
 int msb_moe_decode(const msb_moe_decode_args* a, void* stream);
+/* NO COUNTERPART IN THE REFERENCE.  msb_moe_decode for callers that cannot allocate device memory: a.scratch and
+ * a.scratch_bytes are ignored, the h rows go to an array inside the library (static device memory, one instance per
+ * device).  Nothing is allocated on this path, now or on first use: msb_init() must have run on the device before
+ * (else MSB_E_DEVICE), and the first call per device only looks the array's address up (cudaGetSymbolAddress) -- make
+ * that first call before any stream capture.  Limits: inter <= 4096 and n_routed <= 16, beyond them MSB_E_LIMIT.
+ * Nothing in the array has to start at zero (the gate/up launch writes every h row the down launch reads).  Calls
+ * that overlap in time on one device (two streams) share the array and race: serialise them. */
+int msb_moe_decode_noalloc(const msb_moe_decode_args* a, void* stream);
 /* Routed matrices come from `table`: n_routed entries of 3 device addresses {gate, up, down} (uint64), a.slot[] is
  * ignored -- encode_moe_decode_table_part (quant.hpp:75-85). */
 int msb_moe_decode_table_part(const msb_moe_decode_args* a, const uint64_t* table, int part, void* stream);

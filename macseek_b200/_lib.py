@@ -56,6 +56,7 @@ class MoeDecodeArgsC(C.Structure):
 lib.msb_moe_decode_scratch_bytes.restype = C.c_size_t
 lib.msb_moe_decode_scratch_bytes.argtypes = [_i, _i]
 lib.msb_moe_decode.argtypes = [C.POINTER(MoeDecodeArgsC), _vp]
+lib.msb_moe_decode_noalloc.argtypes = [C.POINTER(MoeDecodeArgsC), _vp]
 lib.msb_moe_decode_table_part.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _i, _vp]
 lib.msb_moe_decode_ids.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _vp, _i, _i, _i, _vp]
 lib.msb_router_scratch_bytes.restype = C.c_size_t

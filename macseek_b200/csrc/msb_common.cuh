@@ -167,5 +167,6 @@ struct Tables {
 };
 // Builds the tables on the current device the first time it is called for that device.
 int get_tables(Tables* out);
+bool tables_ready();
 
 }  // namespace msb

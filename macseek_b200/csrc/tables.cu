@@ -119,4 +119,12 @@ int get_tables(Tables* out) {
   return kOk;
 }
 
+// Whether this device's tables and status buffer already exist (nothing is created here).
+bool tables_ready() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return false;
+  std::lock_guard<std::mutex> lk(g_mu);
+  return g_tables[dev].ready;
+}
+
 }  // namespace msb

@@ -120,6 +120,12 @@ def encode_moe_decode(e: Enc, a: MoeDecodeArgs):
     _lib.check(_lib.lib.msb_moe_decode(c, e.handle))
 
 
+def encode_moe_decode_noalloc(e: Enc, a: MoeDecodeArgs):
+    """encode_moe_decode with the library's own static scratch (a.scratch is ignored); no reference counterpart."""
+    c = a._c()
+    _lib.check(_lib.lib.msb_moe_decode_noalloc(c, e.handle))
+
+
 def encode_moe_decode_table(e: Enc, a: MoeDecodeArgs, table):
     encode_moe_decode_table_part(e, a, table, MoePart.All)
 
