@@ -11,7 +11,7 @@ compressor that produces new cache rows, engram) is left out; plain residual add
 import numpy as np
 import torch
 
-from . import arch, attn, moe_layer as ml, quant as q, synthetic
+from . import arch, attn, ep, moe_layer as ml, quant as q, synthetic
 from .core import Enc
 
 
@@ -122,8 +122,7 @@ class SyntheticModel:
     def __init__(self, cfg: DecConfig, seed=1234, device="cuda", ep_rank=0, ep_world=1, group=None):
         self.cfg, self.device, self.ep_rank, self.ep_world, self.group = cfg, device, ep_rank, ep_world, group
         c = cfg
-        per = c.n_experts // ep_world
-        self.ep_lo, self.ep_hi = ep_rank * per, (ep_rank + 1) * per
+        self.ep_lo, self.ep_hi = ep.expert_range(c.n_experts, ep_world, ep_rank)
         gen = torch.Generator(device=device)
         gen.manual_seed(seed)                      # replicated tensors: the same stream on every rank
         moe_gen = torch.Generator(device=device)
@@ -189,8 +188,7 @@ class SyntheticModel:
         b.y_part.zero_()
         a.y = b.y_part
         q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.Routed); n += 2
-        import torch.distributed as dist
-        dist.all_reduce(b.y_part, group=self.group)
+        ep.combine_routed(b.y_part, self.group)
         arch.encode_add(e, b.h, b.y_part, c.dim); n += 2
         return n
 

@@ -1,0 +1,100 @@
+"""Expert-parallel host logic on CPU: two gloo ranks each evaluate (with the oracle) only the routed experts they hold,
+sum their partial outputs through macseek_b200.ep.combine_routed, and must reproduce the single-rank oracle result.
+Mirrors what the GPU ranks do per layer (router + shared expert replicated, routed partials all-reduced)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle_lib as ol
+import synth
+
+D, I, E, K = 512, 256, 8, 4
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _case():
+    G = [synth.random_weights(ol.IQ1_S, I, D, 10 + 3 * e) for e in range(E)]
+    U = [synth.random_weights(ol.IQ1_S, I, D, 11 + 3 * e) for e in range(E)]
+    Dn = [synth.random_weights(ol.IQ2_XXS, D, I, 12 + 3 * e) for e in range(E)]
+    sh = (synth.random_weights(ol.Q8_0, I, D, 900), synth.random_weights(ol.Q8_0, I, D, 901),
+          synth.random_weights(ol.Q8_0, D, I, 902))
+    x = synth.randn(D, 5)
+    y0 = synth.randn(D, 6)
+    logits = synth.randn(E, 7)
+    return G, U, Dn, sh, x, y0, logits
+
+
+def _rank_main(rank, world, port, out):
+    from macseek_b200 import ep
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        orc = ol.Oracle()
+        G, U, Dn, sh, x, y0, logits = _case()
+        ids, w = orc.router(logits, np.zeros(E, np.float32), K, score_fn=1, route_scale=1.0)   # replicated
+        lo, hi = ep.expert_range(E, world, rank)
+        mine = ep.local_slots(ids, lo, hi)
+        # routed experts resident here, into a zero partial
+        _, part, _, _ = orc.moe_decode(D, I, ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, [G[ids[k]] for k in mine],
+                                       [U[ids[k]] for k in mine], [Dn[ids[k]] for k in mine], w[mine] if mine else None,
+                                       x, np.zeros(D), has_shared=False)
+        t = torch.from_numpy(np.asarray(part, dtype=np.float64))
+        ep.combine_routed(t)
+        # shared expert replicated: every rank adds it to its copy of the hidden state
+        _, y_sh, _, _ = orc.moe_decode(D, I, ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, [sh[0]], [sh[1]], [sh[2]], None, x, y0,
+                                       has_shared=True)
+        y = y_sh + t.numpy()
+        gathered = [torch.zeros(D, dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(y))
+        if rank == 0:
+            _, want, mag, _ = orc.moe_decode(D, I, ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, [G[i] for i in ids] + [sh[0]],
+                                             [U[i] for i in ids] + [sh[1]], [Dn[i] for i in ids] + [sh[2]], w, x, y0,
+                                             has_shared=True)
+            err = float(np.max(np.abs(y - want) / mag))
+            same = all(np.array_equal(gathered[0].numpy(), g.numpy()) for g in gathered)
+            covered = sorted(k for r in range(world) for k in ep.local_slots(ids, *ep.expert_range(E, world, r)))
+            out.put((err, same, covered == list(range(K))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_range_partitions():
+    from macseek_b200 import ep
+    for world in (1, 2, 4, 8):
+        r = [ep.expert_range(384, world, k) for k in range(world)]
+        assert r[0][0] == 0 and r[-1][1] == 384
+        assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(hi - lo == 384 // world for lo, hi in r)
+    with pytest.raises(ValueError):
+        ep.expert_range(384, 5, 0)
+    with pytest.raises(ValueError):
+        ep.expert_range(384, 2, 2)
+
+
+def test_two_rank_combine_matches_single_rank():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    err, same, covered = out.get(timeout=10)
+    assert covered, "every routed slot must be owned by exactly one rank"
+    assert same, "ranks disagree on the combined output"
+    assert err < 1e-12, err
