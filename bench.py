@@ -354,9 +354,20 @@ def run_ours(a):
                 line["cpu_baseline"] = dict(info, value=1.0 / sec, unit=UNIT)
             except Exception as ex:      # the oracle is test infrastructure: never let it break the GPU number
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "error": str(ex)[:200]}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tear down in dependency order: the captured graphs hold NCCL kernels, so they go before the communicator
+        # (destroying the process group while such graphs are alive blocks forever).  Every rank is idle here.
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        del graph, ggraph, hgraph
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # the communicator itself is released with the process: its destructor waits on a watchdog thread that can
+        # outlive the work, and a benchmark that has printed its line must not hang at exit
+        os._exit(0)
 
 
 def main():

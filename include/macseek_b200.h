@@ -119,6 +119,12 @@ int msb_moe_decode_ids(const msb_moe_decode_args* a, const uint64_t* expert_tabl
 size_t msb_router_scratch_bytes(int n_experts);
 int msb_router_fused(const float* x, const float* W, const float* bias, int* ids, float* w, void* scratch,
                      size_t scratch_bytes, int n_experts, int dim, int k, int score_fn, float route_scale, void* stream);
+/* The same with the RMSNorm that precedes the router fused in (the reference runs arch::encode_rmsnorm,
+ * src/kernels/arch.hpp:99-104, as its own dispatch): logits = W . (h * rsqrt(mean(h^2) + eps) * norm_w); the normalised
+ * vector is also written to x_out (may be NULL) for the MoE kernels that read it next. */
+int msb_router_fused_rmsnorm(const float* h, const float* norm_w, float eps, float* x_out, const float* W,
+                             const float* bias, int* ids, float* w, void* scratch, size_t scratch_bytes, int n_experts,
+                             int dim, int k, int score_fn, float route_scale, void* stream);
 int msb_router_topk(const float* logits, const float* bias, int* ids, float* w, int n_tokens, int n_experts, int k,
                     int score_fn, float route_scale, void* stream);
 /* counts u32[E], offsets u32[E+1], entry/tok/slot_of u32[n*k], lw f32[n*k]; entries t*k+j ordered by (expert, entry). */

@@ -115,6 +115,15 @@ inline void encode_router_fused(Enc& e, Buffer x, Buffer W, Buffer bias, Buffer 
                          (float*)w.ptr(), s.router.ptr(), s.router.size, s.n_experts, dim, k, score_fn, route_scale,
                          e.stream), "encode_router_fused");
 }
+// rmsnorm (arch.hpp:99-104) + router in one launch; x_out receives the normalised vector
+inline void encode_router_fused_rmsnorm(Enc& e, Buffer h, Buffer norm_w, float eps, Buffer x_out, Buffer W, Buffer bias,
+                                        Buffer ids, Buffer w, const Scratch& s, int dim = 5120, int k = 6,
+                                        int score_fn = 0, float route_scale = 1.5f) {
+  check(msb_router_fused_rmsnorm((const float*)h.ptr(), (const float*)norm_w.ptr(), eps, (float*)x_out.ptr(),
+                                 (const float*)W.ptr(), (const float*)bias.ptr(), (int*)ids.ptr(), (float*)w.ptr(),
+                                 s.router.ptr(), s.router.size, s.n_experts, dim, k, score_fn, route_scale, e.stream),
+        "encode_router_fused_rmsnorm");
+}
 inline void encode_router_topk(Enc& e, Buffer logits, Buffer bias, Buffer ids, Buffer w, int n, int n_experts = 384,
                                int k = 6, int score_fn = 0, float route_scale = 1.5f) {
   check(msb_router_topk((const float*)logits.ptr(), (const float*)bias.ptr(), (int*)ids.ptr(), (float*)w.ptr(), n,

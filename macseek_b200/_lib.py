@@ -62,6 +62,7 @@ lib.msb_moe_decode_ids.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _vp, _i, _i, 
 lib.msb_router_scratch_bytes.restype = C.c_size_t
 lib.msb_router_scratch_bytes.argtypes = [_i]
 lib.msb_router_fused.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _i, _f, _vp]
+lib.msb_router_fused_rmsnorm.argtypes = [_vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _i, _f, _vp]
 lib.msb_router_topk.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]
 lib.msb_route_lists.argtypes = [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
 

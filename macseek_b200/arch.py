@@ -32,6 +32,15 @@ def encode_router_fused(e: Enc, x, W, bias, ids, w, s: Scratch, k=kTopK, score_f
                                          E, dim, k, score_fn, route_scale, e.handle))
 
 
+def encode_router_fused_rmsnorm(e: Enc, h, norm_w, eps, x_out, W, bias, ids, w, s: Scratch, k=kTopK,
+                                score_fn=SCORE_SQRT_SOFTPLUS, route_scale=kRouteScale):
+    """encode_rmsnorm(h -> x_out) + encode_router_fused(x_out) in one launch; x_out may be None."""
+    E, dim = W.shape
+    _lib.check(_lib.lib.msb_router_fused_rmsnorm(ptr(h), ptr(norm_w), eps, ptr(x_out), ptr(W), ptr(bias), ptr(ids),
+                                                 ptr(w), ptr(s.buf), s.buf.numel() * 4, E, dim, k, score_fn,
+                                                 route_scale, e.handle))
+
+
 def encode_router_topk(e: Enc, logits, bias, ids, w, n, k=kTopK, score_fn=SCORE_SQRT_SOFTPLUS, route_scale=kRouteScale):
     """From precomputed logits [n][E] (arch.hpp:85)."""
     E = logits.shape[-1]

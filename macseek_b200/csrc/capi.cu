@@ -8,8 +8,9 @@ int dequant(int t, const void* src, int64_t n, float* out, cudaStream_t st);
 int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x_stride, float* Y, int64_t y_stride,
              int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st);
 size_t router_scratch_bytes(int E);
-int router_fused(const float* x, const float* W, const float* bias, int* ids, float* wts, void* scratch,
-                 size_t scratch_bytes, int E, int dim, int k, int score_fn, float route_scale, cudaStream_t st);
+int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_out, const float* W, const float* bias,
+                 int* ids, float* wts, void* scratch, size_t scratch_bytes, int E, int dim, int k, int score_fn,
+                 float route_scale, cudaStream_t st);
 int router_topk(const float* logits, const float* bias, int* ids, float* wts, int n, int E, int k, int score_fn,
                 float route_scale, cudaStream_t st);
 int route_lists(const int* ids, const float* w, int n, int k, int E, unsigned* counts, unsigned* offsets,
@@ -165,8 +166,15 @@ int msb_moe_decode_noalloc(const msb_moe_decode_args* a, void* stream) {
 size_t msb_router_scratch_bytes(int n_experts) { return router_scratch_bytes(n_experts); }
 int msb_router_fused(const float* x, const float* W, const float* bias, int* ids, float* w, void* scratch,
                      size_t scratch_bytes, int n_experts, int dim, int k, int score_fn, float route_scale, void* stream) {
-  return router_fused(x, W, bias, ids, w, scratch, scratch_bytes, n_experts, dim, k, score_fn, route_scale,
-                      (cudaStream_t)stream);
+  return router_fused(x, nullptr, 0.f, nullptr, W, bias, ids, w, scratch, scratch_bytes, n_experts, dim, k, score_fn,
+                      route_scale, (cudaStream_t)stream);
+}
+int msb_router_fused_rmsnorm(const float* h, const float* norm_w, float eps, float* x_out, const float* W, const float* bias,
+                             int* ids, float* w, void* scratch, size_t scratch_bytes, int n_experts, int dim, int k,
+                             int score_fn, float route_scale, void* stream) {
+  if (!norm_w) return fail(kErrArg, "router_fused_rmsnorm: null norm weights");
+  return router_fused(h, norm_w, eps, x_out, W, bias, ids, w, scratch, scratch_bytes, n_experts, dim, k, score_fn,
+                      route_scale, (cudaStream_t)stream);
 }
 int msb_router_topk(const float* logits, const float* bias, int* ids, float* w, int n_tokens, int n_experts, int k,
                     int score_fn, float route_scale, void* stream) {

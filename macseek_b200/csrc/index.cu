@@ -49,6 +49,7 @@ struct IdxParams {
   float* scores;       // [len]
   unsigned* hist;      // [4096] or null
   int len;
+  int probe;           // tuning probe: 1 = fetch the keys but skip the tensor-core work
 };
 
 __device__ __forceinline__ void hist_flush(unsigned* sh, unsigned* gh, int tid, int nthreads) {
@@ -69,33 +70,6 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
   constexpr int NT = H / 8;
   __shared__ unsigned sh_hist[kHistBins];
   const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  if (p.hist)
-    for (int b = tid; b < kHistBins; b += blockDim.x) sh_hist[b] = 0;
-  // the query goes through shared memory as e4m3 bytes: a coalesced, latency-parallel load instead of 256 dependent
-  // global loads per thread
-  __shared__ __align__(16) uint8_t q8[H * kIdxDim];
-  __shared__ float wsh[H];
-  for (int i = tid; i < H * kIdxDim / 4; i += blockDim.x) {
-    const float4 v = reinterpret_cast<const float4*>(p.q)[i];
-    const uint32_t b = (uint32_t)__nv_cvt_float_to_fp8(v.x, __NV_SATFINITE, __NV_E4M3) |
-                       ((uint32_t)__nv_cvt_float_to_fp8(v.y, __NV_SATFINITE, __NV_E4M3) << 8) |
-                       ((uint32_t)__nv_cvt_float_to_fp8(v.z, __NV_SATFINITE, __NV_E4M3) << 16) |
-                       ((uint32_t)__nv_cvt_float_to_fp8(v.w, __NV_SATFINITE, __NV_E4M3) << 24);
-    reinterpret_cast<uint32_t*>(q8)[i] = b;
-  }
-  for (int i = tid; i < H; i += blockDim.x) wsh[i] = p.w[i];
-  __syncthreads();
-  uint32_t B[NT][4][2];
-  float wr[NT][2];
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) {
-    const uint32_t* qr = reinterpret_cast<const uint32_t*>(q8 + (size_t)(nt * 8 + g) * kIdxDim + 32 * t);
-#pragma unroll
-    for (int s = 0; s < 4; s++) { B[nt][s][0] = qr[2 * s]; B[nt][s][1] = qr[2 * s + 1]; }
-    wr[nt][0] = wsh[nt * 8 + 2 * t];
-    wr[nt][1] = wsh[nt * 8 + 2 * t + 1];
-  }
-  if (p.hist) __syncthreads();
   const int warps = gridDim.x * (blockDim.x >> 5);
   const int ntiles = (p.len + 15) / 16;
   // software pipeline: the next tile's 64 bytes per lane are requested before the current tile is multiplied
@@ -111,15 +85,61 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
       r[2] = __ldg(src); r[3] = __ldg(src + 1);
     }
   };
-  uint4 cur[4], nxt[4];
+  // three tiles of keys per warp in flight (48 registers): requested before the query is staged, so that the first
+  // round trips to HBM overlap the prologue
+  uint4 cur[4], nx1[4], nx2[4];
   int tile = blockIdx.x * (blockDim.x >> 5) + (tid >> 5);
   fetch(tile, cur);
+  fetch(tile + warps, nx1);
+  fetch(tile + 2 * warps, nx2);
+  if (p.hist)
+    for (int b = tid; b < kHistBins; b += blockDim.x) sh_hist[b] = 0;
+  // the query goes through shared memory as e4m3 bytes: a coalesced, latency-parallel load instead of 256 dependent
+  // global loads per thread
+  __shared__ __align__(16) uint8_t q8[H * kIdxDim];
+  __shared__ float wsh[H];
+  {
+    constexpr int kQ4 = (H * kIdxDim / 4 + 383) / 384;   // 16-byte pieces per thread (block of 384)
+    float4 v[kQ4];
+#pragma unroll
+    for (int j = 0; j < kQ4; j++) {                      // all loads in flight before the first conversion
+      const int i = tid + 384 * j;
+      v[j] = i < H * kIdxDim / 4 ? reinterpret_cast<const float4*>(p.q)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kQ4; j++) {
+      const int i = tid + 384 * j;
+      const uint32_t b = (uint32_t)__nv_cvt_float_to_fp8(v[j].x, __NV_SATFINITE, __NV_E4M3) |
+                         ((uint32_t)__nv_cvt_float_to_fp8(v[j].y, __NV_SATFINITE, __NV_E4M3) << 8) |
+                         ((uint32_t)__nv_cvt_float_to_fp8(v[j].z, __NV_SATFINITE, __NV_E4M3) << 16) |
+                         ((uint32_t)__nv_cvt_float_to_fp8(v[j].w, __NV_SATFINITE, __NV_E4M3) << 24);
+      if (i < H * kIdxDim / 4) reinterpret_cast<uint32_t*>(q8)[i] = b;
+    }
+  }
+  for (int i = tid; i < H; i += blockDim.x) wsh[i] = p.w[i];
+  __syncthreads();
+  uint32_t B[NT][4][2];
+  float wr[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    const uint32_t* qr = reinterpret_cast<const uint32_t*>(q8 + (size_t)(nt * 8 + g) * kIdxDim + 32 * t);
+#pragma unroll
+    for (int s = 0; s < 4; s++) { B[nt][s][0] = qr[2 * s]; B[nt][s][1] = qr[2 * s + 1]; }
+    wr[nt][0] = wsh[nt * 8 + 2 * t];
+    wr[nt][1] = wsh[nt * 8 + 2 * t + 1];
+  }
+  if (p.hist) __syncthreads();
   for (; tile < ntiles; tile += warps) {
-    fetch(tile + warps, nxt);
+    uint4 nx3[4];
+    fetch(tile + 3 * warps, nx3);
     const int k0 = tile * 16 + g, k1 = k0 + 8;
     const uint32_t A0[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
     const uint32_t A1[8] = {cur[2].x, cur[2].y, cur[2].z, cur[2].w, cur[3].x, cur[3].y, cur[3].z, cur[3].w};
     float s0 = 0.f, s1 = 0.f;
+    if (p.probe == 1) {
+      s0 = __uint_as_float((A0[0] ^ A0[1] ^ A0[2] ^ A0[3] ^ A0[4] ^ A0[5] ^ A0[6] ^ A0[7]) & 0x3FFFFFFFu);
+      s1 = __uint_as_float((A1[0] ^ A1[1] ^ A1[2] ^ A1[3] ^ A1[4] ^ A1[5] ^ A1[6] ^ A1[7]) & 0x3FFFFFFFu);
+    } else
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
       float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -142,7 +162,7 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
       }
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) cur[i] = nxt[i];
+    for (int i = 0; i < 4; i++) { cur[i] = nx1[i]; nx1[i] = nx2[i]; nx2[i] = nx3[i]; }
   }
   if (p.hist) hist_flush(sh_hist, p.hist, tid, blockDim.x);
 }
@@ -307,31 +327,56 @@ __global__ void topk_hist_kernel(const float* sc, int n, unsigned* hist) {
 
 // threshold bin: the highest bin b with (count of bins > b) < k <= (count of bins >= b); -1 when fewer than k finite
 // scores exist (everything is selected).  Computed by every block of the compaction and by the final block.
+// Inclusive scan of one value per thread over the block (a multiple of 32 threads, at most 1024): warp shuffles, then
+// the warp totals.  `wsum` is 32 words of shared memory; the caller synchronises before reusing it.
+__device__ __forceinline__ unsigned block_scan_incl(unsigned v, unsigned* wsum, unsigned* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  unsigned x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) wsum[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned s = lane < nw ? wsum[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned y = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += y;
+    }
+    wsum[lane] = s;
+  }
+  __syncthreads();
+  *total = wsum[nw - 1];
+  return x + (warp ? wsum[warp - 1] : 0u);
+}
+
 __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024] */, unsigned* above_out) {
   const int tid = threadIdx.x;   // blockDim.x == 1024 or 256; each thread owns a contiguous run of bins from the top
   const int per = kHistBins / blockDim.x;
+  unsigned c[kHistBins / 256];
   unsigned mine = 0;
-  for (int j = 0; j < per; j++) mine += hist[kHistBins - 1 - (tid * per + j)];
-  sh[tid] = mine;
-  __syncthreads();
-  for (int o = 1; o < (int)blockDim.x; o <<= 1) {   // inclusive scan over threads (descending bins)
-    const unsigned a = tid >= o ? sh[tid - o] : 0;
-    __syncthreads();
-    sh[tid] += a;
-    __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kHistBins / 256; j++) {
+    c[j] = j < per ? hist[kHistBins - 1 - (tid * per + j)] : 0u;
+    mine += c[j];
   }
+  unsigned total;
+  const unsigned incl = block_scan_incl(mine, sh, &total), excl = incl - mine;
   __shared__ int res_bin;
   __shared__ unsigned res_above;
-  if (tid == 0) { res_bin = -1; res_above = sh[blockDim.x - 1]; }
+  if (tid == 0) { res_bin = -1; res_above = total; }
   __syncthreads();
-  const unsigned incl = sh[tid], excl = incl - mine;
   if (excl < (unsigned)k && incl >= (unsigned)k) {   // the threshold lies in this thread's run
     unsigned run = excl;
-    for (int j = 0; j < per; j++) {
-      const int b = kHistBins - 1 - (tid * per + j);
-      const unsigned c = hist[b];
-      if (run + c >= (unsigned)k) { res_bin = b; res_above = run; break; }
-      run += c;
+#pragma unroll
+    for (int j = 0; j < kHistBins / 256; j++) {
+      if (j < per) {
+        if (run + c[j] >= (unsigned)k) { res_bin = kHistBins - 1 - (tid * per + j); res_above = run; break; }
+        run += c[j];
+      }
     }
   }
   __syncthreads();
@@ -515,16 +560,8 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
     const int w0 = min(bm_words, tid * per), w1 = min(bm_words, w0 + per);
     unsigned cnt = 0;
     for (int w = w0; w < w1; w++) cnt += __popc(bitmap[w]);
-    sh[tid] = cnt;
-    __syncthreads();
-    for (int o = 1; o < 1024; o <<= 1) {
-      const unsigned a = tid >= o ? sh[tid - o] : 0;
-      __syncthreads();
-      sh[tid] += a;
-      __syncthreads();
-    }
-    unsigned pos = sh[tid] - cnt;
-    const unsigned total = sh[1023];
+    unsigned total;
+    unsigned pos = block_scan_incl(cnt, sh, &total) - cnt;
     for (int w = w0; w < w1; w++) {
       unsigned m = bitmap[w];
       while (m) {
@@ -626,7 +663,8 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   int dev = 0, sms = 0;
   MSB_CUDA(cudaGetDevice(&dev));
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len};
+  static const int env_probe = getenv("MSB_IDX_PROBE") ? atoi(getenv("MSB_IDX_PROBE")) : 0;
+  IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len, env_probe};
   if (key_type == kKeyFp8 && !exact_query) {
     const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));
     if (heads == 64) MSB_CUDA(launch_pdl(idx_score_fp8_kernel<64>, dim3(grid), dim3(384), 0, st, p));

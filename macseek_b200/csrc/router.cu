@@ -14,6 +14,9 @@ constexpr int kRouterKSplit = 4;   // K slices per expert row in the fused kerne
 
 struct RouterParams {
   const float* x;
+  const float* norm_w;   // not null: x is RMS-normalised with this gain before use (fused RMSNorm)
+  float* x_out;          // with norm_w: the normalised x is also written here (may be null)
+  float norm_eps;
   const float* W;
   const float* bias;     // may be null
   float* logits;         // [E] (written by the fused kernel; diagnostic, as the reference's Scratch::router_logits)
@@ -78,22 +81,53 @@ __device__ __forceinline__ void router_topk_warp(const float* logits, const floa
 // slices in a fixed order, writes the logits and selects.
 __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p) {
   pdl_launch_dependents();
-  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit = blockIdx.x * 8 + warp;
   const int slice = p.dim / kRouterKSplit;   // floats per slice, a multiple of 4
-  if (unit < p.E * kRouterKSplit) {
-    const int e = unit / kRouterKSplit, ks = unit % kRouterKSplit;
-    const float4* w = reinterpret_cast<const float4*>(p.W + (size_t)e * p.dim + (size_t)ks * slice);
+  const bool live = unit < p.E * kRouterKSplit;
+  const int e = unit / kRouterKSplit, ks = unit % kRouterKSplit;
+  const float4* w = reinterpret_cast<const float4*>(p.W + (size_t)(live ? e : 0) * p.dim + (size_t)ks * slice);
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  // the router matrix is constant: its first 8 x 16 bytes per lane are requested before the grid dependency resolves
+  float4 a[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const int c = lane + 32 * k;
+    a[k] = (live && c < slice / 4) ? __ldg(w + c) : zero4;
+  }
+  pdl_wait();
+  float mul = 1.f;
+  if (p.norm_w) {   // every block needs 1/rms of the whole vector: dim floats from L2, summed in a fixed order
+    __shared__ float red[8];
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < p.dim / 4; i += 256) {
+      const float4 v = reinterpret_cast<const float4*>(p.x)[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    mul = rsqrtf(tot / (float)p.dim + p.norm_eps);
+  }
+  if (live) {
     const float4* xv = reinterpret_cast<const float4*>(p.x + (size_t)ks * slice);
+    const float4* gv = reinterpret_cast<const float4*>(p.norm_w ? p.norm_w + (size_t)ks * slice : p.x);
     float acc = 0.f;
     for (int c0 = lane; c0 < slice / 4; c0 += 32 * 8) {   // 8 independent 16-byte loads in flight per lane
-      float4 a[8], b[8];
+      float4 b[8];
 #pragma unroll
       for (int k = 0; k < 8; k++) {
         const int c = c0 + 32 * k;
-        a[k] = c < slice / 4 ? __ldg(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        b[k] = c < slice / 4 ? xv[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c0 != lane) a[k] = c < slice / 4 ? __ldg(w + c) : zero4;
+        b[k] = c < slice / 4 ? xv[c] : zero4;
+        if (p.norm_w && c < slice / 4) {
+          const float4 g = __ldg(gv + c);
+          b[k].x = b[k].x * mul * g.x; b[k].y = b[k].y * mul * g.y; b[k].z = b[k].z * mul * g.z; b[k].w = b[k].w * mul * g.w;
+          if (e == 0 && p.x_out) reinterpret_cast<float4*>(p.x_out + (size_t)ks * slice)[c] = b[k];
+        }
       }
 #pragma unroll
       for (int k = 0; k < 8; k++) {
@@ -197,8 +231,9 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int* ids, cons
 // ---------------------------------------------------------------- host side
 size_t router_scratch_bytes(int E) { return sizeof(float) * (size_t)E * (1 + kRouterKSplit); }
 
-int router_fused(const float* x, const float* W, const float* bias, int* ids, float* wts, void* scratch,
-                 size_t scratch_bytes, int E, int dim, int k, int score_fn, float route_scale, cudaStream_t st) {
+int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_out, const float* W, const float* bias,
+                 int* ids, float* wts, void* scratch, size_t scratch_bytes, int E, int dim, int k, int score_fn,
+                 float route_scale, cudaStream_t st) {
   if (E <= 0 || E > kRouterMaxE || k <= 0 || k > kRouterMaxK || k > E || dim <= 0 || dim % (4 * kRouterKSplit))
     return fail(kErrArg, "router: bad shape (E %d dim %d k %d)", E, dim, k);
   if (!x || !W || !ids || !wts || !scratch) return fail(kErrArg, "router: null pointer");
@@ -209,7 +244,10 @@ int router_fused(const float* x, const float* W, const float* bias, int* ids, fl
   int rc = get_tables(&tb);
   if (rc) return rc;
   RouterParams p;
-  p.x = x; p.W = W; p.bias = bias; p.ids = ids; p.wts = wts;
+  if ((norm_w && (reinterpret_cast<uintptr_t>(norm_w) & 15)) || (x_out && (reinterpret_cast<uintptr_t>(x_out) & 15)))
+    return fail(kErrArg, "router: norm_w and x_out must be 16-byte aligned");
+  p.x = x; p.norm_w = norm_w; p.norm_eps = norm_eps; p.x_out = norm_w ? x_out : nullptr;
+  p.W = W; p.bias = bias; p.ids = ids; p.wts = wts;
   p.logits = reinterpret_cast<float*>(scratch);
   p.partial = p.logits + E;
   p.ticket = reinterpret_cast<unsigned*>(tb.status) + 16;

@@ -98,46 +98,66 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
   const int nit = v1 > v0 ? (v1 - v0 + kSaRows - 1) / kSaRows : 0;
   const int kbase = 16 * KS * warp;     // first contracted dim of this warp == first output dim of this warp
 
+  // four threads per row: the row's source is resolved once per thread (one dependent load, all rows in parallel),
+  // then the thread copies every fourth 16-byte chunk of it
   auto gather = [&](int it, int buf) {
-    const int vb = v0 + it * kSaRows;
-    for (int i = tid; i < kSaRows * CH; i += 128) {
-      const int r = i / CH, c = i % CH;
-      const int v = vb + r;
-      const uint8_t* src = nullptr;
-      if (v < v1) {
-        if (v < p.n_win) src = p.win + (size_t)v * D * 2;
-        else {
-          const int idx = __ldg(p.topk + (v - p.n_win));
-          if (idx >= 0) src = p.cache + (size_t)idx * D * 2;
-        }
+    const int r = tid >> 2, v = v0 + it * kSaRows + r;
+    const uint8_t* src = nullptr;
+    if (v < v1) {
+      if (v < p.n_win) src = p.win + (size_t)v * D * 2;
+      else {
+        const int idx = __ldg(p.topk + (v - p.n_win));
+        if (idx >= 0) src = p.cache + (size_t)idx * D * 2;
       }
-      uint8_t* dst = rows[buf] + r * PITCH + c * 16;
-      if (src) cp_async16(smem_u32(dst), src + c * 16);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-      if (c == 0) rowvalid[buf * kSaRows + r] = src != nullptr;
     }
+    uint8_t* dst = rows[buf] + r * PITCH;
+#pragma unroll
+    for (int c = tid & 3; c < CH; c += 4) {
+      if (src) cp_async16(smem_u32(dst + c * 16), src + c * 16);
+      else *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    if ((tid & 3) == 0) rowvalid[buf * kSaRows + r] = src != nullptr;
     cp_async_commit();
   };
 
-  // ---- query fragments for this warp's contraction range, roped, as hi + lo terms
+  // the first tile's rows are requested before anything else: the round trip overlaps the query prologue
+  if (nit > 0) gather(0, 0);
+  // ---- query fragments for this warp's contraction range, roped, as hi + lo terms.  The 16 heads' queries pass
+  // through the (still unused) second row buffer with coalesced 16-byte loads.
+  {
+    float4* qs4 = reinterpret_cast<float4*>(rows[1]);
+    const float4* src = reinterpret_cast<const float4*>(p.q + (size_t)hg * kSaHeadsPerBlock * D);
+    constexpr int kQ4 = kSaHeadsPerBlock * D / 4 / 128;   // 16-byte pieces per thread (16 or 18)
+    static_assert(kSaHeadsPerBlock * D / 4 % 128 == 0, "query staging assumes a whole number of pieces per thread");
+    float4 v[kQ4];
+#pragma unroll
+    for (int i = 0; i < kQ4; i++) v[i] = src[tid + 128 * i];       // all loads in flight before the first store
+#pragma unroll
+    for (int i = 0; i < kQ4; i++) qs4[tid + 128 * i] = v[i];
+  }
+  __syncthreads();
   uint32_t qh[KS][4], ql[KS][4];
+  {
+    const float* qs = reinterpret_cast<const float*>(rows[1]);
 #pragma unroll
-  for (int s = 0; s < KS; s++)
+    for (int s = 0; s < KS; s++)
 #pragma unroll
-    for (int j = 0; j < 2; j++)
+      for (int j = 0; j < 2; j++)
 #pragma unroll
-      for (int r = 0; r < 2; r++) {
-        const int d = kbase + 16 * s + 8 * j + 2 * t;
-        const int head = hg * kSaHeadsPerBlock + g + 8 * r;
-        float a = p.q[(size_t)head * D + d], b = p.q[(size_t)head * D + d + 1];
-        if (d >= D - 64) {
-          const int i = (d - (D - 64)) >> 1;
-          const float c = p.cs[2 * i], sn = p.cs[2 * i + 1];
-          const float ra = a * c - b * sn, rb = a * sn + b * c;
-          a = ra; b = rb;
+        for (int r = 0; r < 2; r++) {
+          const int d = kbase + 16 * s + 8 * j + 2 * t;
+          const float2 v = *reinterpret_cast<const float2*>(qs + (g + 8 * r) * D + d);
+          float a = v.x, b = v.y;
+          if (d >= D - 64) {
+            const int i = (d - (D - 64)) >> 1;
+            const float c = p.cs[2 * i], sn = p.cs[2 * i + 1];
+            const float ra = a * c - b * sn, rb = a * sn + b * c;
+            a = ra; b = rb;
+          }
+          split2<BF>(a, b, qh[s][j * 2 + r], ql[s][j * 2 + r]);
         }
-        split2<BF>(a, b, qh[s][j * 2 + r], ql[s][j * 2 + r]);
-      }
+  }
+  __syncthreads();   // the second row buffer is free again
 
   float o[NTW][4];
 #pragma unroll
@@ -145,7 +165,6 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const float scale = 1.0f / sqrtf((float)D);
 
-  if (nit > 0) gather(0, 0);
   for (int it = 0; it < nit; it++) {
     const int buf = it & 1;
     if (it + 1 < nit) { gather(it + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
@@ -258,32 +277,29 @@ __global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p)
   pdl_wait();
   __shared__ float xs[D];
   __shared__ float fs[1024];      // per-split rescale factors exp(m_s - M)
-  __shared__ float s_den;
   const int h = blockIdx.x, d = threadIdx.x;
   const float sink = p.sinks[h];
-  // every thread needs M and the denominator: stage (m, l) of all splits once, then reduce from shared memory
-  for (int s = d; s < p.splits; s += D) fs[s] = p.part_ml[((size_t)s * p.H + h) * 2];
+  // every thread needs M and the denominator: stage (m, l) of all splits once, then every thread reduces them from
+  // shared memory in the same order
+  __shared__ float ls[1024];
+  for (int s = d; s < p.splits; s += D) {
+    const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((size_t)s * p.H + h) * 2);
+    fs[s] = ml.x; ls[s] = ml.y;
+  }
   __syncthreads();
   float M = sink;
   for (int s = 0; s < p.splits; s++) M = fmaxf(M, fs[s]);
   __syncthreads();
-  for (int s = d; s < p.splits; s += D) {
-    const float m = p.part_ml[((size_t)s * p.H + h) * 2];
-    fs[s] = (m == -INFINITY) ? 0.f : expf(m - M);
-  }
+  for (int s = d; s < p.splits; s += D) { const float m = fs[s]; fs[s] = (m == -INFINITY) ? 0.f : expf(m - M); }
   __syncthreads();
-  if (d == 0) {
-    float den = expf(sink - M);
-    for (int s = 0; s < p.splits; s++) den += p.part_ml[((size_t)s * p.H + h) * 2 + 1] * fs[s];
-    s_den = den;
-  }
+  float den = expf(sink - M);
+  for (int s = 0; s < p.splits; s++) den += ls[s] * fs[s];
   float acc = 0.f;
   const float* po = p.part_o + (size_t)h * D + d;
   const size_t stride = (size_t)p.H * D;
 #pragma unroll 8
   for (int s = 0; s < p.splits; s++) acc += po[(size_t)s * stride] * fs[s];
-  __syncthreads();
-  xs[d] = acc / s_den;
+  xs[d] = acc / den;
   __syncthreads();
   float v = xs[d];
   if (d >= D - 64) {
@@ -299,7 +315,9 @@ __global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p)
 static int splits_for(int total_rows, int H, int sms) {
   const int tiles = std::max(1, (total_rows + kSaRows - 1) / kSaRows);
   const int hg = H / kSaHeadsPerBlock;
-  return std::max(1, std::min(std::min(tiles, 1024), std::max(1, sms / hg)));
+  // two blocks fit an SM: one row tile per block while that gives at most two blocks per SM (the chain gather ->
+  // scores -> softmax -> output is latency-bound, so more blocks beat longer ones)
+  return std::max(1, std::min(std::min(tiles, 1024), std::max(1, 2 * sms / hg)));
 }
 size_t sparse_scratch_bytes(int total_rows_max, int H, int D) {
   const int splits = std::max(1, (total_rows_max + kSaRows - 1) / kSaRows);   // upper bound, any device

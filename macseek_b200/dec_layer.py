@@ -87,8 +87,10 @@ class LayerW:
         rw = lambda t, rows, cols: synthetic.random_weights(t, rows, cols, gen)
         ones = lambda n: torch.ones(n, dtype=torch.float32, device=dev)
         self.attn_norm, self.q_norm, self.kv_norm, self.ffn_norm = ones(c.dim), ones(c.q_lora), ones(c.D), ones(c.dim)
-        self.wq_a = rw(c.t_attn, c.q_lora, c.dim)
-        self.wkv = rw(c.t_attn, c.D, c.dim)
+        # q_a and kv read the same normalised hidden state: their rows are stored back to back and run as one matvec
+        self.wq_a_kv = torch.cat([rw(c.t_attn, c.q_lora, c.dim), rw(c.t_attn, c.D, c.dim)])
+        nb = synthetic.row_bytes(c.t_attn, c.dim) * c.q_lora
+        self.wq_a, self.wkv = self.wq_a_kv[:nb], self.wq_a_kv[nb:]
         self.wq_b = rw(c.t_attn, c.heads * c.D, c.q_lora)
         self.w_idx_proj = rw(c.t_index, c.index_heads, c.dim)
         self.w_idx_qb = rw(c.t_index, c.index_heads * c.index_dim, c.q_lora)
@@ -106,7 +108,8 @@ class DecBufs:
         f = lambda n: torch.zeros(n, dtype=torch.float32, device=device)
         c = cfg
         self.h, self.x = f(c.dim), f(c.dim)
-        self.qa, self.qan, self.kv = f(c.q_lora), f(c.q_lora), f(c.D)
+        self.qa_kv = f(c.q_lora + c.D)                      # one output buffer of the fused q_a / kv matvec
+        self.qa, self.kv, self.qan = self.qa_kv[:c.q_lora], self.qa_kv[c.q_lora:], f(c.q_lora)
         self.qfull, self.attn_out = f(c.heads * c.D), f(c.heads * c.D)
         self.iq, self.iw = f(c.index_heads * c.index_dim), f(c.index_heads)
         self.oa = f(c.o_a_rows)
@@ -154,8 +157,7 @@ class SyntheticModel:
         c, w, b, st = self.cfg, self.layers[l], self.bufs, self.state[l]
         n = 0
         # the input RMSNorms are fused into the activation load of the matvecs that consume them
-        q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_a, c.q_lora, c.dim, b.h, w.attn_norm, c.norm_eps, b.qa); n += 1
-        q.encode_matvec_rmsnorm(e, c.t_attn, w.wkv, c.D, c.dim, b.h, w.attn_norm, c.norm_eps, b.kv); n += 1
+        q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_a_kv, c.q_lora + c.D, c.dim, b.h, w.attn_norm, c.norm_eps, b.qa_kv); n += 1
         q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_proj, c.index_heads, c.dim, b.h, w.attn_norm, c.norm_eps, b.iw); n += 1
         q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_b, c.heads * c.D, c.q_lora, b.qa, w.q_norm, c.norm_eps, b.qfull); n += 1
         q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_qb, c.index_heads * c.index_dim, c.q_lora, b.qa, w.q_norm,
@@ -171,14 +173,16 @@ class SyntheticModel:
     def encode_dec_moe(self, e: Enc, l):
         c, w, b = self.cfg, self.layers[l], self.bufs
         n = 0
-        arch.encode_rmsnorm(e, b.h, w.ffn_norm, b.x, 1, c.dim, c.norm_eps); n += 1
+        # the FFN RMSNorm (h -> x) runs inside the router launch
         if self.ep_world == 1:
-            ml.encode_moe_layer(e, w.moe, b.moe, b.x, b.h, c.score_fn, c.route_scale); n += 3
+            ml.encode_moe_layer(e, w.moe, b.moe, b.x, b.h, c.score_fn, c.route_scale, norm_in=b.h, norm_w=w.ffn_norm,
+                                norm_eps=c.norm_eps); n += 3
             return n
         # expert parallel: router and shared expert replicated (h += shared(x) locally), routed partial sums of the
         # local experts combined over NVLink
-        arch.encode_router_fused(e, b.x, w.moe.router_w, w.moe.router_bias, b.moe.ids, b.moe.w, b.moe.router_scratch,
-                                 c.top_k, c.score_fn, c.route_scale); n += 1
+        arch.encode_router_fused_rmsnorm(e, b.h, w.ffn_norm, c.norm_eps, b.x, w.moe.router_w, w.moe.router_bias,
+                                         b.moe.ids, b.moe.w, b.moe.router_scratch, c.top_k, c.score_fn,
+                                         c.route_scale); n += 1
         a = q.MoeDecodeArgs(c.dim, c.inter)
         a.t_gate_up, a.t_down, a.t_shared = c.t_gate_up, c.t_down, c.t_shared
         a.n_routed, a.has_shared, a.shared = c.top_k, True, w.moe.shared

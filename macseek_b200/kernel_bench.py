@@ -2,6 +2,7 @@
 
     python -m macseek_b200.kernel_bench matvec Q6_K 129280 4096 [--n 1] [--groups 1]
     python -m macseek_b200.kernel_bench moe {router|gu|down|all}
+    python -m macseek_b200.kernel_bench attn {index|scores|topk|sparse|all} [--kv-len 200000]
     python -m macseek_b200.kernel_bench sweep
 
 Each case builds synthetic weights on the device (several copies, together larger than the 126 MB L2, used in
@@ -15,7 +16,8 @@ import argparse
 
 import torch
 
-from . import arch, moe_layer as ml, quant as q, synthetic
+from . import _lib, arch, attn, moe_layer as ml, quant as q, synthetic
+from .core import ptr
 from .core import Enc
 
 
@@ -122,9 +124,63 @@ def moe_cases(which: str, eager: int = 0):
                   flush=True)
 
 
+def attn_cases(which: str, kv_len: int = 200000, eager: int = 0):
+    """The benchmark attention side: 64 x 128 FP8 index heads over kv_len keys, exact top-2048, sparse attention of 64
+    heads over 128 window rows + the 2048 selected rows of 576 bf16.  Six KV sources are used in rotation so that the
+    keys (25.6 MB per source at 200K) come from HBM, not from L2."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3)
+    sh = attn.Shape.benchmark()
+    rope = torch.from_numpy(attn.make_rope_table(kv_len + 1, True)).cuda()
+    states = []
+    for _ in range(6):
+        st = attn.DecodeState(sh, kv_len, rope, "cuda")
+        st.ckv.normal_(0, 1, generator=gen)
+        st.win.normal_(0, 1, generator=gen)
+        tmp = torch.empty(st.ikey.shape, dtype=torch.bfloat16, device="cuda").normal_(0, 1, generator=gen)
+        st.ikey.copy_(tmp.to(torch.float8_e4m3fn).view(torch.uint8))
+        states.append(st)
+    iq = torch.randn(sh.index_heads * sh.index_dim, device="cuda", generator=gen)
+    iw = torch.randn(sh.index_heads, device="cuda", generator=gen)
+    qf = torch.randn(sh.heads * sh.D, device="cuda", generator=gen)
+    sinks = torch.randn(sh.heads, device="cuda", generator=gen)
+    out = torch.zeros(sh.heads * sh.D, device="cuda")
+    pos = kv_len - 1
+    for st in states:                      # a valid top-k list and scores in every source
+        attn.encode_index_decode(Enc(), st, iq, iw, pos, kv_len, actq=False)
+    torch.cuda.synchronize()
+
+    def index(i):
+        attn.encode_index_decode(Enc(), states[i % 6], iq, iw, pos, kv_len, actq=False)
+
+    def scores(i):
+        st = states[i % 6]
+        _lib.check(_lib.lib.msb_index_scores(sh.key_type, ptr(st.ikey), kv_len, ptr(st.q_prep), ptr(st.w_prep),
+                                             sh.index_heads, ptr(st.dec_scores), None, 0,
+                                             torch.cuda.current_stream().cuda_stream))
+
+    def topk(i):
+        st = states[i % 6]
+        attn.encode_topk(Enc(), st.dec_scores, kv_len, sh.topk, st.topk, st.topk_scratch)
+
+    def sparse(i):
+        attn.encode_sparse(Enc(), states[i % 6], qf, sinks, out, pos)
+
+    key_bytes = kv_len * sh.index_dim
+    cases = {"index": (index, key_bytes), "scores": (scores, key_bytes), "topk": (topk, kv_len * 4),
+             "sparse": (sparse, (sh.window + sh.topk) * sh.D * 2)}
+    for name in (cases if which in ("every", "all") else [which]):
+        fn, nbytes = cases[name]
+        r = run(fn, eager)
+        if r:
+            print(f"attn {name:8s} median {r[0]:8.2f} us  min {r[1]:8.2f} us   {nbytes / r[0] / 1e3:8.1f} GB/s",
+                  flush=True)
+
+
 def sweep():
     T = q.QType
     moe_cases("every")
+    attn_cases("every")
     for t in (T.IQ1_S, T.IQ2_XXS, T.Q8_0, T.Q6_K, T.Q5_K, T.IQ4_NL, T.BF16, T.F32):
         matvec_case(t, 16384, 4096)
     # the decode step's own shapes
@@ -138,10 +194,11 @@ def sweep():
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["matvec", "moe", "sweep"])
+    ap.add_argument("case", choices=["matvec", "moe", "attn", "sweep"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--groups", type=int, default=1)
+    ap.add_argument("--kv-len", type=int, default=200000)
     ap.add_argument("--eager", type=int, default=0, help="issue this many plain launches and exit (no timing)")
     a = ap.parse_args()
     torch.cuda.set_device(0)
@@ -149,6 +206,8 @@ def main():
         matvec_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n, a.groups, a.eager)
     elif a.case == "moe":
         moe_cases(a.args[0] if a.args else "every", a.eager)
+    elif a.case == "attn":
+        attn_cases(a.args[0] if a.args else "every", a.kv_len, a.eager)
     else:
         sweep()
     torch.cuda.synchronize()

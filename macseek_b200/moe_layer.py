@@ -87,9 +87,16 @@ class MoeLayerBufs:
         self.moe_scratch = torch.zeros(q.moe_decode_scratch_bytes(inter, k) // 4, dtype=torch.float32, device=device)
 
 
-def encode_moe_layer(e: Enc, lw: MoeLayerWeights, b: MoeLayerBufs, x, y, score_fn, route_scale, add_shared=True):
-    """y += MoE(x): fused router, then the two MoE kernels on the experts resident here (ids resolved on the GPU)."""
-    arch.encode_router_fused(e, x, lw.router_w, lw.router_bias, b.ids, b.w, b.router_scratch, b.k, score_fn, route_scale)
+def encode_moe_layer(e: Enc, lw: MoeLayerWeights, b: MoeLayerBufs, x, y, score_fn, route_scale, add_shared=True,
+                     norm_in=None, norm_w=None, norm_eps=0.0):
+    """y += MoE(x): fused router, then the two MoE kernels on the experts resident here (ids resolved on the GPU).
+    With norm_in, x is first produced as RMSNorm(norm_in) * norm_w inside the router launch."""
+    if norm_in is not None:
+        arch.encode_router_fused_rmsnorm(e, norm_in, norm_w, norm_eps, x, lw.router_w, lw.router_bias, b.ids, b.w,
+                                         b.router_scratch, b.k, score_fn, route_scale)
+    else:
+        arch.encode_router_fused(e, x, lw.router_w, lw.router_bias, b.ids, b.w, b.router_scratch, b.k, score_fn,
+                                 route_scale)
     a = q.MoeDecodeArgs(lw.dim, lw.inter)
     a.t_gate_up, a.t_down, a.t_shared = lw.t_gate_up, lw.t_down, lw.t_shared
     a.n_routed, a.has_shared = b.k, add_shared

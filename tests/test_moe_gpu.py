@@ -270,3 +270,30 @@ def test_route_lists_bit_exact(orc, enc):
             for g, r, nm in zip(got, ref, ("counts", "offsets", "entry", "tok", "w", "slot_of")):
                 gn = g.cpu().numpy()
                 assert np.array_equal(gn.view(np.uint32), r.view(np.uint32)), (n, nm)
+
+
+def test_router_fused_rmsnorm(orc, enc):
+    """RMSNorm folded into the router launch: logits of the normalised vector, and the normalised vector itself."""
+    from macseek_b200 import arch
+    E, dim, k = 384, 4096, 8
+    rng = np.random.default_rng(11)
+    W = (rng.standard_normal((E, dim)) * 0.02).astype(np.float32)
+    gain = (1.0 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    s = arch.Scratch.create(E)
+    Wd, gd = dev(W), dev(gain)
+    ids = torch.zeros(k, dtype=torch.int32, device="cuda")
+    w = torch.zeros(k, dtype=torch.float32, device="cuda")
+    xo = torch.zeros(dim, dtype=torch.float32, device="cuda")
+    for trial in range(5):
+        h = synth.randn(dim, 2000 + trial, 0.5 + trial)
+        arch.encode_router_fused_rmsnorm(enc, dev(h), gd, 1e-6, xo, Wd, None, ids, w, s, k, 1, 1.0)
+        enc.wait()
+        xn = orc.rmsnorm(h, gain, 1e-6)
+        got_x = xo.cpu().numpy()
+        assert np.max(np.abs(got_x - xn)) <= 1e-5 * np.max(np.abs(xn))
+        logits = W.astype(np.float64) @ xn.astype(np.float64)
+        got_logits = s.router_logits.cpu().numpy()
+        assert np.max(np.abs(got_logits - logits)) <= 1e-4 * (np.abs(W) @ np.abs(xn)).max()
+        rid, rw = orc.router(got_logits, np.zeros(E, np.float32), k, 1, 1.0)
+        assert np.array_equal(ids.cpu().numpy(), rid)
+        assert np.max(np.abs(w.cpu().numpy() - rw) / rw) <= 1e-5
