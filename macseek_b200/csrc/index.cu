@@ -21,6 +21,10 @@ constexpr int kIdxDim = 128;
 constexpr int kKeyF16 = 1, kKeyFp8 = 101;
 constexpr int kHistBins = 4096;
 
+// tcgen05 scoring kernel for FP8 keys (index_tc.cu)
+int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
+                    cudaStream_t st);
+
 __device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
   const uint32_t u = __float_as_uint(f);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
@@ -665,6 +669,8 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   static const int env_probe = getenv("MSB_IDX_PROBE") ? atoi(getenv("MSB_IDX_PROBE")) : 0;
   IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len, env_probe};
+  static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;   // mma.sync path
+  if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, st);
   if (key_type == kKeyFp8 && !exact_query) {
     const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));
     if (heads == 64) MSB_CUDA(launch_pdl(idx_score_fp8_kernel<64>, dim3(grid), dim3(384), 0, st, p));
