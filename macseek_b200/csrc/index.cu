@@ -314,7 +314,7 @@ __global__ void idx_prep_kernel(const float* q_raw, const float* w_raw, const fl
 }
 
 // ---------------------------------------------------------------- exact top-k
-struct TopkCtl { unsigned n_sel, n_cand, pad0, pad1; };
+struct TopkCtl { unsigned n_sel, n_cand, ticket, pad1; };
 
 __global__ void topk_hist_kernel(const float* sc, int n, unsigned* hist) {
   pdl_launch_dependents();
@@ -364,7 +364,7 @@ __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024]
   unsigned mine = 0;
 #pragma unroll
   for (int j = 0; j < kHistBins / 256; j++) {
-    c[j] = j < per ? hist[kHistBins - 1 - (tid * per + j)] : 0u;
+    c[j] = j < per ? __ldcg(hist + (kHistBins - 1 - (tid * per + j))) : 0u;
     mine += c[j];
   }
   unsigned total;
@@ -388,12 +388,20 @@ __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024]
   return res_bin;
 }
 
-__global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int n, int k, const unsigned* hist,
-                                                           unsigned* fine, TopkCtl* ctl, int* sel, uint2* cand) {
+// forward declaration: the last step, run by the compaction block that finishes last
+__device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, unsigned* fine, TopkCtl* ctl,
+                                 const int* sel, const uint2* cand, int* out, int bm_words);
+
+// Compaction over the whole grid (blocks of 1024 threads), then the exact finish in the block that takes the last
+// ticket: one launch for the whole selection after the histogram.
+__global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
+                                                           TopkCtl* ctl, int* sel, uint2* cand, int* out, int bm_words,
+                                                           int fused) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ unsigned sh[1024];
   __shared__ unsigned sh_fine[kHistBins];
+  __shared__ int is_last;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
   for (int b = threadIdx.x; b < kHistBins; b += blockDim.x) sh_fine[b] = 0;
@@ -434,16 +442,29 @@ __global__ void __launch_bounds__(256) topk_compact_kernel(const float* sc, int 
     }
   }
   hist_flush(sh_fine, fine, threadIdx.x, blockDim.x);
+  if (!fused) return;
+  // the block that takes the last ticket sees every other block's lists and finishes the selection
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&ctl->ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words);
 }
 
-// One block of 1024 threads.  out[k] ascending, -1 padded.  Resets the histograms and ctl for the next call.
-// The threshold bin's members are narrowed with the fine histogram (next 12 key bits); what remains in the fine
-// threshold bin (normally a handful) is ranked exactly by (key descending, index ascending).  More than 1024 of them
-// (massive ties) fall back to a radix select over all of the threshold bin's members, on the key then on the index.
+// the last step as its own launch (one block)
 __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
                                                           TopkCtl* ctl, const int* sel, const uint2* cand, int* out, int bm_words) {
   pdl_launch_dependents();
   pdl_wait();
+  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words);
+}
+
+// The selection's last step, run by ONE block of 1024 threads (the compaction block that finishes last).
+// out[k] ascending, -1 padded.  Resets the histograms and ctl for the next call.
+__device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, unsigned* fine, TopkCtl* ctl,
+                                 const int* sel, const uint2* cand, int* out, int bm_words) {
   __shared__ unsigned sh[1024];
   __shared__ int buf[2048];
   __shared__ unsigned long long c2[1024];
@@ -459,21 +480,22 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
   for (int i = tid; i < bm_words; i += 1024) bitmap[i] = 0;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
-  const unsigned n_sel = ctl->n_sel, n_cand = ctl->n_cand;
+  const unsigned n_sel = *reinterpret_cast<volatile unsigned*>(&ctl->n_sel);
+  const unsigned n_cand = *reinterpret_cast<volatile unsigned*>(&ctl->n_cand);
   for (int i = tid; i < 2048; i += 1024) buf[i] = 0x7fffffff;
   if (tid == 0) { s_cnt = 0; s_c2 = 0; }
   __syncthreads();
-  for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) emit((unsigned)sel[i]);
+  for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) emit((unsigned)__ldcg(sel + i));
   if (bstar >= 0 && n_cand > 0) {
     const unsigned need = (unsigned)k - above;   // how many of the threshold bin's members are taken
     unsigned above2;
     const int fstar = threshold_bin(fine, (int)need, sh, &above2);
-    const unsigned m2 = fstar >= 0 ? fine[fstar] : 0;
+    const unsigned m2 = fstar >= 0 ? __ldcg(fine + fstar) : 0;
     if (fstar >= 0 && m2 <= 1024u) {
       const unsigned need2 = need - above2;
 #pragma unroll 4
       for (unsigned i = tid; i < n_cand; i += 1024) {
-        const uint2 cd = cand[i];
+        const uint2 cd = __ldcg(cand + i);
         const unsigned idx = cd.x;
         const uint32_t key = cd.y;
         const int fb = (int)((key >> 8) & 0xFFFu);
@@ -502,7 +524,7 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
         for (int b = tid; b < 256; b += 1024) sh[b] = 0;
         __syncthreads();
         for (unsigned i = tid; i < n_cand; i += 1024) {
-          const unsigned key = cand[i].y & 0xFFFFFu;
+          const unsigned key = __ldcg(cand + i).y & 0xFFFFFu;
           if ((key & mask) == prefix) atomicAdd(&sh[(key >> sft) & dmask], 1u);
         }
         __syncthreads();
@@ -528,7 +550,7 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
         for (int b = tid; b < 256; b += 1024) sh[b] = 0;
         __syncthreads();
         for (unsigned i = tid; i < n_cand; i += 1024) {
-          const uint2 cd = cand[i];
+          const uint2 cd = __ldcg(cand + i);
           if ((cd.y & 0xFFFFFu) == T && (cd.x & im) == ip) atomicAdd(&sh[(cd.x >> shift) & 0xFFu], 1u);
         }
         __syncthreads();
@@ -549,8 +571,9 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
       }
       const unsigned idxT = ip;          // members equal to T with index <= idxT are taken
       for (unsigned i = tid; i < n_cand; i += 1024) {
-        const unsigned idx = cand[i].x;
-        const unsigned key = cand[i].y & 0xFFFFFu;
+        const uint2 cd = __ldcg(cand + i);
+        const unsigned idx = cd.x;
+        const unsigned key = cd.y & 0xFFFFFu;
         if (key > T || (key == T && idx <= idxT)) emit(idx);
       }
       __syncthreads();
@@ -595,7 +618,7 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
     for (int i = tid; i < k; i += 1024) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
   }
   for (int b = tid; b < kHistBins; b += 1024) { hist[b] = 0; fine[b] = 0; }
-  if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; }
+  if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; ctl->ticket = 0; }
   (void)n;
 }
 
@@ -631,20 +654,29 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   int dev = 0, sms = 0;
   MSB_CUDA(cudaGetDevice(&dev));
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (n > 0) {
-    const int blocks = std::max(1, std::min(sms * 2, (n + 1023) / 1024));
-    if (!hist_ready) MSB_CUDA(launch_pdl(topk_hist_kernel, dim3(blocks), dim3(256), 0, st, sc, n, hist));
-    MSB_CUDA(launch_pdl(topk_compact_kernel, dim3(blocks), dim3(256), 0, st, sc, n, k, hist, fine, ctl, sel, cand));
-  }
   // positions bitmap in shared memory for n up to 1M (128 KB); longer inputs use the sorting read-out
   const int bm_words = n <= (1 << 20) ? std::max(1, (n + 31) / 32) : 0;
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
+    MSB_CUDA(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
     MSB_CUDA(cudaFuncSetAttribute(topk_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
     configured[dev & 63] = true;
   }
-  MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl, sel, cand,
-                      out, bm_words));
+  static const int fused = getenv("MSB_TOPK_FUSED") ? atoi(getenv("MSB_TOPK_FUSED")) : 1;   // tuning probe
+  static const int env_blocks = getenv("MSB_TOPK_BLOCKS") ? atoi(getenv("MSB_TOPK_BLOCKS")) : 0;
+  // one element per thread and up to two blocks per SM: the per-block fixed work (threshold, fine histogram) is small
+  // next to the latency of a longer per-thread loop
+  int blocks = std::max(1, std::min(2 * sms, (n + 1023) / 1024));
+  if (env_blocks) blocks = std::max(1, std::min(env_blocks, (n + 1023) / 1024));
+  if (n > 0 && !hist_ready) MSB_CUDA(launch_pdl(topk_hist_kernel, dim3(std::max(1, std::min(sms * 2, (n + 1023) / 1024))), dim3(256), 0, st, sc, n, hist));
+  if (fused) {
+    MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl, sel,
+                        cand, out, bm_words, 1));
+  } else {
+    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), 0, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0));
+    MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl,
+                        (const int*)sel, (const uint2*)cand, out, bm_words));
+  }
   MSB_LAUNCH_CHECK("topk");
   return kOk;
 }
