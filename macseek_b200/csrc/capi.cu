@@ -7,6 +7,8 @@ const char* last_error_text();
 int dequant(int t, const void* src, int64_t n, float* out, cudaStream_t st);
 int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x_stride, float* Y, int64_t y_stride,
              int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st);
+int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
+                    int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st);
 size_t router_scratch_bytes(int E);
 int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_out, const float* W, const float* bias,
                  int* ids, float* wts, void* scratch, size_t scratch_bytes, int E, int dim, int k, int score_fn,
@@ -205,12 +207,21 @@ int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw
                      int actq, int heads, int k, float* q_prep, float* w_prep, float* scores, int* topk_out,
                      void* topk_scratch, size_t topk_scratch_bytes_, int exact_query, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = index_prep(q_raw, w_raw, cs, actq, heads, q_prep, w_prep, st);
-  if (rc) return rc;
   // the fused histogram exists on the direct FP8 path only
   const bool fused = key_type == MSB_KEY_FP8_E4M3 && !exact_query && len > 0;
-  rc = index_scores(key_type, keys, len, q_prep, w_prep, heads, scores, fused ? (unsigned*)topk_scratch : nullptr,
-                    exact_query, st);
+  static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;
+  int rc;
+  if (fused && !legacy && (heads == 32 || heads == 64)) {
+    // tcgen05 path: the query preparation runs inside the scoring kernel (q_prep / w_prep are still written)
+    if (!keys || !q_raw || !w_raw || !cs || !q_prep || !w_prep || !scores || (reinterpret_cast<uintptr_t>(keys) & 15))
+      return fail(kErrArg, "index_decode: null or misaligned pointer");
+    rc = index_scores_tc(keys, len, q_raw, w_raw, heads, scores, (unsigned*)topk_scratch, 1, cs, actq, q_prep, w_prep, st);
+  } else {
+    rc = index_prep(q_raw, w_raw, cs, actq, heads, q_prep, w_prep, st);
+    if (rc) return rc;
+    rc = index_scores(key_type, keys, len, q_prep, w_prep, heads, scores, fused ? (unsigned*)topk_scratch : nullptr,
+                      exact_query, st);
+  }
   if (rc) return rc;
   return topk(scores, len, k, topk_out, topk_scratch, topk_scratch_bytes_, fused, st);
 }

@@ -23,7 +23,7 @@ constexpr int kHistBins = 4096;
 
 // tcgen05 scoring kernel for FP8 keys (index_tc.cu)
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
-                    cudaStream_t st);
+                    int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st);
 
 __device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
   const uint32_t u = __float_as_uint(f);
@@ -702,7 +702,7 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   static const int env_probe = getenv("MSB_IDX_PROBE") ? atoi(getenv("MSB_IDX_PROBE")) : 0;
   IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len, env_probe};
   static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;   // mma.sync path
-  if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, st);
+  if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, 0, nullptr, 0, nullptr, nullptr, st);
   if (key_type == kKeyFp8 && !exact_query) {
     const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));
     if (heads == 64) MSB_CUDA(launch_pdl(idx_score_fp8_kernel<64>, dim3(grid), dim3(384), 0, st, p));

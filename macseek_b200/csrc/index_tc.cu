@@ -19,6 +19,7 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 #include <algorithm>
+#include <cmath>
 #include "msb_common.cuh"
 
 namespace msb {
@@ -33,8 +34,13 @@ constexpr uint32_t kTcSbo = 1024;          // bytes between 8-row groups of the 
 
 struct IdxTcParams {
   CUtensorMap keys;    // [len][128] bytes, box 128 x 128, 128-byte swizzle
-  const float* q;      // [H][128] prepared query
-  const float* w;      // [H] prepared head weights
+  const float* q;      // [H][128] query: prepared, or raw when prep != 0
+  const float* w;      // [H] head weights: prepared, or raw when prep != 0
+  const float* cs;     // prep: [32][2] (cos, sin) of the query position
+  float* q_out;        // prep: the prepared query is also written here (block 0), as index_prep would
+  float* w_out;        // prep: likewise the prepared head weights
+  float wscale;        // prep: dim^-0.5 * heads^-0.5
+  int prep, actq;      // prep: fold the query preparation (rope, optional fp4 simulation, weight scale) in
   float* scores;       // [len]
   unsigned* hist;      // [4096] or null
   int* status;         // device failure word
@@ -89,6 +95,14 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float tc_pow2i(int e) { return __uint_as_float((uint32_t)(e + 127) << 23); }
+__device__ __forceinline__ float tc_round_e2m1(float x) {   // as round_e2m1 of index.cu (attn_ref.cpp:93-100)
+  const float a = fabsf(x);
+  int e = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;
+  e = max(e, 0);
+  return copysignf(nearbyintf(a * tc_pow2i(1 - e)) * tc_pow2i(e - 1), x);
+}
 
 template <int H>
 __global__ void __launch_bounds__(kTcThreads, 1) idx_score_tc_kernel(const __grid_constant__ IdxTcParams p) {
@@ -169,6 +183,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) idx_score_tc_kernel(const __gri
         const float4* src = reinterpret_cast<const float4*>(p.q + (size_t)n * kTcDim + j * 16);
         f[i][0] = src[0]; f[i][1] = src[1]; f[i][2] = src[2]; f[i][3] = src[3];
       }
+      if (p.prep) {
+        // query preparation of index_prep (attn_ref.cpp:163-170) on this thread's 16 dims: rope on dims 64..127
+        // (interleaved pairs), then the optional e2m1 simulation with a power-of-two scale per 32 dims (= this
+        // thread's chunk and its neighbour's)
+#pragma unroll
+        for (int i = 0; i < kPer; i++) {
+          const int c = tid + 128 * i, n = c >> 3, j = c & 7;
+          float* v = reinterpret_cast<float*>(&f[i][0]);
+          if (j >= 4) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+              const int pi = (16 * j - 64) / 2 + e;
+              const float cc = p.cs[2 * pi], sn = p.cs[2 * pi + 1];
+              const float a = v[2 * e], b = v[2 * e + 1];
+              v[2 * e] = __fsub_rn(__fmul_rn(a, cc), __fmul_rn(b, sn));
+              v[2 * e + 1] = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, cc));
+            }
+          }
+          if (p.actq) {
+            float amax = 0.f;
+#pragma unroll
+            for (int e = 0; e < 16; e++) amax = fmaxf(amax, fabsf(v[e]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, 6.0f * 1.17549435e-38f);
+            const float r = __fmul_rn(amax, 1.0f / 6.0f);
+            const uint32_t rb = __float_as_uint(r);
+            const int ex = (int)((rb >> 23) & 0xFF) - 127 + ((rb & 0x7FFFFF) ? 1 : 0);
+            const float sc = tc_pow2i(ex), inv = tc_pow2i(-ex);
+#pragma unroll
+            for (int e = 0; e < 16; e++)
+              v[e] = __fmul_rn(tc_round_e2m1(fminf(fmaxf(__fmul_rn(v[e], inv), -6.0f), 6.0f)), sc);
+          }
+          if (blockIdx.x == 0 && p.q_out) {
+            float4* dst = reinterpret_cast<float4*>(p.q_out + (size_t)n * kTcDim + j * 16);
+            dst[0] = f[i][0]; dst[1] = f[i][1]; dst[2] = f[i][2]; dst[3] = f[i][3];
+          }
+        }
+      }
       auto pack = [](const float4& v) {
         return (uint32_t)__nv_cvt_float_to_fp8(v.x, __NV_SATFINITE, __NV_E4M3) |
                ((uint32_t)__nv_cvt_float_to_fp8(v.y, __NV_SATFINITE, __NV_E4M3) << 8) |
@@ -188,8 +240,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) idx_score_tc_kernel(const __gri
     float wr[H];                                   // head weights in registers
 #pragma unroll
     for (int h = 0; h < H; h += 4) {
-      const float4 w4 = __ldg(reinterpret_cast<const float4*>(p.w + h));
+      const float4 w4 = *reinterpret_cast<const float4*>(p.w + h);
       wr[h] = w4.x; wr[h + 1] = w4.y; wr[h + 2] = w4.z; wr[h + 3] = w4.w;
+    }
+    if (p.prep) {
+#pragma unroll
+      for (int h = 0; h < H; h++) wr[h] *= p.wscale;
+      if (blockIdx.x == 0 && p.w_out && tid < H) p.w_out[tid] = p.w[tid] * p.wscale;
     }
     for (int i = 0; i < my_tiles; i++) {
       const int buf = i & 1;
@@ -257,8 +314,10 @@ EncodeTiledFn encode_tiled_fn() {
 }  // namespace
 
 // FP8 keys, heads 32 or 64.  Returns kOk or an error code; the caller has validated the pointers (keys 16-byte aligned).
+// prep != 0: q / w are the raw projections and the preparation of index_prep is folded in (cs, actq; the prepared
+// values are also written to q_out / w_out when those are given).
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
-                    cudaStream_t st) {
+                    int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st) {
   Tables tb;
   int rc = get_tables(&tb);
   if (rc) return rc;
@@ -277,6 +336,8 @@ int index_scores_tc(const void* keys, int len, const float* q, const float* w, i
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fail(kErrCuda, "index_scores: tensor map encode failed (%d)", (int)cr);
   p.q = q; p.w = w; p.scores = scores; p.hist = hist; p.status = tb.status; p.len = len;
+  p.prep = prep; p.cs = cs; p.actq = actq; p.q_out = q_out; p.w_out = w_out;
+  p.wscale = (float)(pow((double)kTcDim, -0.5) * pow((double)heads, -0.5));
   const int ntiles = (len + kTcTile - 1) / kTcTile;
   const int grid = std::max(1, std::min(sms, ntiles));
   const size_t smem = idx_score_tc_smem(heads);
