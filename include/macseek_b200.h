@@ -61,6 +61,18 @@ int msb_matvec_rmsnorm(int qtype, const void* W, int rows, int cols, const float
 int msb_matvec_n(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate,
                  int groups, void* stream);
 
+/* ---- prefill projections: ms::q::encode_matmul / encode_f32_to_f16 / encode_matmul_h (src/kernels/quant.hpp:37-46).
+ * Y[n x rows] (+)= X[n x cols] . W^T with half operands and fp32 accumulation on the tensor cores (tcgen05), as the
+ * reference's Metal tensor path does.  The reference keeps module-owned scratch for the half copies of X and W
+ * (quant.mm:175-184); here the caller passes it: msb_matmul_scratch_bytes(..., with_x) bytes (with_x = 1 for msb_matmul,
+ * which converts X itself; 0 for msb_matmul_h, whose X16 is already half with row stride x_stride, 0 = cols). */
+int msb_f32_to_f16(const float* x, void* x16, size_t count, void* stream);   /* count % 4 == 0 */
+size_t msb_matmul_scratch_bytes(int qtype, int rows, int cols, int n, int with_x);
+int msb_matmul_h(int qtype, const void* W, int rows, int cols, const void* X16, int x_stride, float* Y, int n, int accumulate,
+                 void* scratch, size_t scratch_bytes, void* stream);
+int msb_matmul(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate, void* scratch,
+               size_t scratch_bytes, void* stream);
+
 /* ---------------------------------------------------------------- MoE decode (one token)
  * ms::q::MoeDecodeArgs / ExpertSlot / moe_decode_scratch_bytes / encode_moe_decode[_table[_part]] / MoePart
  * (src/kernels/quant.hpp:49-85, quant.mm:264-369).  dim and inter are run-time here (the reference fixes 5120 / 2304).

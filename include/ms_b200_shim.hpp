@@ -61,6 +61,24 @@ inline void encode_matvec_n(Enc& e, QType t, const Buffer& W, int rows, int cols
 }
 
 constexpr int kMaxRouted = MSB_MAX_ROUTED;
+// prefill projections (quant.hpp:37-46).  The reference's module-owned X16 / W16 scratch becomes an explicit Buffer.
+inline size_t matmul_scratch_bytes(QType t, int rows, int cols, int n, bool with_x = true) {
+  return msb_matmul_scratch_bytes((int)t, rows, cols, n, with_x ? 1 : 0);
+}
+inline void encode_f32_to_f16(Enc& e, const Buffer& X, const Buffer& X16, size_t count) {
+  check(msb_f32_to_f16((const float*)X.ptr(), X16.ptr(), count, e.stream), "encode_f32_to_f16");
+}
+inline void encode_matmul_h(Enc& e, QType t, const Buffer& W, int rows, int cols, const Buffer& X16, const Buffer& Y, int n,
+                            const Buffer& scratch, bool accumulate = false, int x_stride = 0) {
+  check(msb_matmul_h((int)t, W.ptr(), rows, cols, X16.ptr(), x_stride, (float*)Y.ptr(), n, accumulate ? 1 : 0, scratch.ptr(),
+                     scratch.size, e.stream), "encode_matmul_h");
+}
+inline void encode_matmul(Enc& e, QType t, const Buffer& W, int rows, int cols, const Buffer& X, const Buffer& Y, int n,
+                          const Buffer& scratch, bool accumulate = false) {
+  check(msb_matmul((int)t, W.ptr(), rows, cols, (const float*)X.ptr(), (float*)Y.ptr(), n, accumulate ? 1 : 0, scratch.ptr(),
+                   scratch.size, e.stream), "encode_matmul");
+}
+
 struct ExpertSlot { Buffer gate, up, down; };
 enum class MoePart { All, SharedGu, AfterSharedGu, Shared, Routed, SharedDown };
 struct MoeDecodeArgs {     // quant.hpp:54-70, with dim / inter as fields (the reference: 5120 / 2304)

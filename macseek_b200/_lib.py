@@ -53,6 +53,11 @@ class MoeDecodeArgsC(C.Structure):
                 ("y", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("swiglu_limit", C.c_float)]
 
 
+lib.msb_f32_to_f16.argtypes = [_vp, _vp, C.c_size_t, _vp]
+lib.msb_matmul_scratch_bytes.restype = C.c_size_t
+lib.msb_matmul_scratch_bytes.argtypes = [_i, _i, _i, _i, _i]
+lib.msb_matmul_h.argtypes = [_i, _vp, _i, _i, _vp, _i, _vp, _i, _i, _vp, C.c_size_t, _vp]
+lib.msb_matmul.argtypes = [_i, _vp, _i, _i, _vp, _vp, _i, _i, _vp, C.c_size_t, _vp]
 lib.msb_moe_decode_scratch_bytes.restype = C.c_size_t
 lib.msb_moe_decode_scratch_bytes.argtypes = [_i, _i]
 lib.msb_moe_decode.argtypes = [C.POINTER(MoeDecodeArgsC), _vp]

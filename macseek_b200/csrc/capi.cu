@@ -9,6 +9,12 @@ int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x
              int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st);
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
                     int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st);
+int f32_to_f16(const float* x, void* x16, size_t count, cudaStream_t st);
+size_t matmul_scratch_bytes(int t, int rows, int cols, int n, bool with_x);
+int matmul_h(int t, const void* W, int rows, int cols, const void* X16, int x_stride, float* Y, int n, bool accumulate,
+             void* scratch, size_t scratch_bytes, cudaStream_t st);
+int matmul(int t, const void* W, int rows, int cols, const float* X, float* Y, int n, bool accumulate, void* scratch,
+           size_t scratch_bytes, cudaStream_t st);
 size_t router_scratch_bytes(int E);
 int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_out, const float* W, const float* bias,
                  int* ids, float* wts, void* scratch, size_t scratch_bytes, int E, int dim, int k, int score_fn,
@@ -102,6 +108,19 @@ static int moe_fill(const msb_moe_decode_args* a, MoeParams* p) {
   if (reinterpret_cast<uintptr_t>(a->scratch) & 15 || reinterpret_cast<uintptr_t>(a->x) & 15)
     return fail(kErrArg, "moe_decode: x and scratch must be 16-byte aligned");
   return kOk;
+}
+
+int msb_f32_to_f16(const float* x, void* x16, size_t count, void* stream) { return f32_to_f16(x, x16, count, (cudaStream_t)stream); }
+size_t msb_matmul_scratch_bytes(int qtype, int rows, int cols, int n, int with_x) {
+  return matmul_scratch_bytes(qtype, rows, cols, n, with_x != 0);
+}
+int msb_matmul_h(int qtype, const void* W, int rows, int cols, const void* X16, int x_stride, float* Y, int n, int accumulate,
+                 void* scratch, size_t scratch_bytes, void* stream) {
+  return matmul_h(qtype, W, rows, cols, X16, x_stride, Y, n, accumulate != 0, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+int msb_matmul(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate, void* scratch,
+               size_t scratch_bytes, void* stream) {
+  return matmul(qtype, W, rows, cols, X, Y, n, accumulate != 0, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
 size_t msb_moe_decode_scratch_bytes(int inter, int max_routed) { return moe_decode_scratch_bytes(inter, max_routed); }

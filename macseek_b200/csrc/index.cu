@@ -409,7 +409,16 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
   const int lane = threadIdx.x & 31;
   const int per_block = (n + gridDim.x - 1) / gridDim.x;
   const int i0 = blockIdx.x * per_block, i1 = min(n, i0 + per_block);
-  // 4 independent loads per thread per trip; appends are aggregated per warp (one global atomic per warp and kind)
+  // The block's picks are collected in shared memory first (dynamic region: per_block ints for the outright selections,
+  // per_block (index, key) pairs for the threshold bin's members) and appended to the global lists with ONE atomic per
+  // kind and block: thousands of same-address atomics from individual warps were the bulk of this kernel's time.
+  extern __shared__ unsigned dyn_smem[];
+  int* sel_buf = reinterpret_cast<int*>(dyn_smem);
+  uint2* cand_buf = reinterpret_cast<uint2*>(dyn_smem + ((per_block + 1) & ~1));
+  __shared__ unsigned s_n1, s_n2, s_g1, s_g2;
+  if (threadIdx.x == 0) { s_n1 = 0; s_n2 = 0; }
+  __syncthreads();
+  // 4 independent loads per thread per trip
   for (int base = i0; base < i1; base += blockDim.x * 4) {
     float f[4];
 #pragma unroll
@@ -431,16 +440,24 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
       const unsigned m1 = __ballot_sync(0xffffffffu, kind == 1), m2 = __ballot_sync(0xffffffffu, kind == 2);
       unsigned b1 = 0, b2 = 0;
       if (lane == 0) {
-        if (m1) b1 = atomicAdd(&ctl->n_sel, (unsigned)__popc(m1));
-        if (m2) b2 = atomicAdd(&ctl->n_cand, (unsigned)__popc(m2));
+        if (m1) b1 = atomicAdd(&s_n1, (unsigned)__popc(m1));
+        if (m2) b2 = atomicAdd(&s_n2, (unsigned)__popc(m2));
       }
       b1 = __shfl_sync(0xffffffffu, b1, 0);
       b2 = __shfl_sync(0xffffffffu, b2, 0);
       const unsigned lt = (1u << lane) - 1u;
-      if (kind == 1) { const unsigned pos = b1 + __popc(m1 & lt); if (pos < 2048u) sel[pos] = i; }
-      if (kind == 2) cand[b2 + __popc(m2 & lt)] = make_uint2((unsigned)i, key);
+      if (kind == 1) sel_buf[b1 + __popc(m1 & lt)] = i;
+      if (kind == 2) cand_buf[b2 + __popc(m2 & lt)] = make_uint2((unsigned)i, key);
     }
   }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_g1 = s_n1 ? atomicAdd(&ctl->n_sel, s_n1) : 0u;
+    s_g2 = s_n2 ? atomicAdd(&ctl->n_cand, s_n2) : 0u;
+  }
+  __syncthreads();
+  for (unsigned i = threadIdx.x; i < s_n1; i += blockDim.x) { const unsigned pos = s_g1 + i; if (pos < 2048u) sel[pos] = sel_buf[i]; }
+  for (unsigned i = threadIdx.x; i < s_n2; i += blockDim.x) cand[s_g2 + i] = cand_buf[i];
   hist_flush(sh_fine, fine, threadIdx.x, blockDim.x);
   if (!fused) return;
   // the block that takes the last ticket sees every other block's lists and finishes the selection
@@ -668,12 +685,16 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   // next to the latency of a longer per-thread loop
   int blocks = std::max(1, std::min(2 * sms, (n + 1023) / 1024));
   if (env_blocks) blocks = std::max(1, std::min(env_blocks, (n + 1023) / 1024));
+  // staging of a block's picks: per_block ints + per_block (index, key) pairs; blocks are added until that fits
+  auto stage_of = [&](int nb) { const size_t pb = ((size_t)n + nb - 1) / nb; return ((pb + 1) & ~(size_t)1) * 4 + pb * 8 + 16; };
+  while (stage_of(blocks) > 100 * 1024) blocks *= 2;
+  const size_t stage_bytes = stage_of(blocks);
   if (n > 0 && !hist_ready) MSB_CUDA(launch_pdl(topk_hist_kernel, dim3(std::max(1, std::min(sms * 2, (n + 1023) / 1024))), dim3(256), 0, st, sc, n, hist));
   if (fused) {
-    MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl, sel,
-                        cand, out, bm_words, 1));
+    MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), std::max((size_t)bm_words * 4, stage_bytes), st, sc, n, k, hist,
+                        fine, ctl, sel, cand, out, bm_words, 1));
   } else {
-    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), 0, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0));
+    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), stage_bytes, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0));
     MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl,
                         (const int*)sel, (const uint2*)cand, out, bm_words));
   }

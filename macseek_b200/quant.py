@@ -57,6 +57,29 @@ def encode_matvec_n(e: Enc, t, W, rows, cols, X, Y, n, accumulate=False, groups=
 kMaxRouted = 16
 
 
+def matmul_scratch_bytes(t, rows, cols, n, with_x=True):
+    return _lib.lib.msb_matmul_scratch_bytes(int(t), rows, cols, n, int(with_x))
+
+
+def encode_f32_to_f16(e: Enc, X, X16, count):
+    """F32 -> half (quant.hpp:43); count % 4 == 0."""
+    _lib.check(_lib.lib.msb_f32_to_f16(ptr(X), ptr(X16), count, e.handle))
+
+
+def encode_matmul_h(e: Enc, t, W, rows, cols, X16, Y, n, accumulate=False, x_stride=0, scratch=None):
+    """Prefill: Y[n x rows] (+)= X16[n x cols] . W^T, X16 half with row stride x_stride (quant.hpp:45-46).  scratch:
+    matmul_scratch_bytes(t, rows, cols, n, with_x=False) bytes (the reference's module-owned W16)."""
+    _lib.check(_lib.lib.msb_matmul_h(int(t), ptr(W), rows, cols, ptr(X16), x_stride, ptr(Y), n, int(accumulate),
+                                     ptr(scratch), scratch.numel() * scratch.element_size() if scratch is not None else 0,
+                                     e.handle))
+
+
+def encode_matmul(e: Enc, t, W, rows, cols, X, Y, n, accumulate=False, scratch=None):
+    """Prefill: Y[n x rows] (+)= X[n x cols] . W^T with X F32, converted to half internally (quant.hpp:41-42)."""
+    _lib.check(_lib.lib.msb_matmul(int(t), ptr(W), rows, cols, ptr(X), ptr(Y), n, int(accumulate), ptr(scratch),
+                                   scratch.numel() * scratch.element_size() if scratch is not None else 0, e.handle))
+
+
 class ExpertSlot:
     """Three raw-block matrices of one expert: gate [inter x dim], up [inter x dim], down [dim x inter]."""
 
