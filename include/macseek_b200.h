@@ -128,6 +128,33 @@ int msb_moe_decode_ids(const msb_moe_decode_args* a, const uint64_t* expert_tabl
  * arch.mm:173-239).  E experts (<= 512), top-k (<= 16); score_fn 0 = sqrt(softplus(logit)) (arch_router.metal:16-24),
  * 1 = sigmoid (reference/inference/model.py:816-817); key = score + bias (bias may be NULL); ties -> lowest id;
  * w = score / (sum + 1e-20) * route_scale; ids / w in descending key order. */
+/* ---- MoE prefill: ms::q::MoePrefillArgs / moe_prefill_scratch_bytes / encode_moe_prefill (src/kernels/quant.hpp:87-118).
+ * Grouped expert GEMMs on the tensor cores (tcgen05) with half operands and fp32 accumulation, as the reference's tensor
+ * path.  Routing is expert-sorted: routed expert j owns entries [offs[j], offs[j+1]) of tok[] (token row in X) and wt[];
+ * slot_of[t * k_per_token + k] = entry of token t's k-th expert (-1 = none);
+ *   Y[t] += shared(t) + sum_k Z[slot_of[t][k]]   in that fixed order (run-to-run bit-identical).
+ * slots and offs are HOST arrays (as in the reference, whose host side writes the tile tables at encode time); they are
+ * read before the call returns.  Do not capture this call into a CUDA graph (the tables are copied from host memory). */
+typedef struct {
+  int dim, inter;                     /* the reference: 5120, 2304 */
+  int t_gate_up, t_down, t_shared;
+  int n_tokens, n_exp;
+  const msb_expert_slot* slots;       /* host [n_exp], device addresses inside */
+  const int* offs;                    /* host [n_exp + 1], offs[0] = 0, offs[n_exp] = total */
+  const int* tok;                     /* device int32[total] */
+  const float* wt;                    /* device F32[total] */
+  const int* slot_of;                 /* device int32[n_tokens * k_per_token] */
+  int k_per_token, has_shared;
+  msb_expert_slot shared;
+  const float* X;                     /* F32[n_tokens x dim] */
+  float* Y;                           /* F32[n_tokens x dim], accumulated */
+  void* scratch;
+  size_t scratch_bytes;               /* >= msb_moe_prefill_scratch_bytes(total, n_tokens, n_exp, dim, inter) */
+  float swiglu_limit;                 /* 0 selects the reference's 10 */
+} msb_moe_prefill_args;
+size_t msb_moe_prefill_scratch_bytes(int total_entries, int n_tokens, int n_exp, int dim, int inter);
+int msb_moe_prefill(const msb_moe_prefill_args* a, void* stream);
+
 size_t msb_router_scratch_bytes(int n_experts);
 int msb_router_fused(const float* x, const float* W, const float* bias, int* ids, float* w, void* scratch,
                      size_t scratch_bytes, int n_experts, int dim, int k, int score_fn, float route_scale, void* stream);

@@ -9,6 +9,7 @@
 //   die() -> abort()                        check(): prints msb_last_error() and aborts
 // Header-only; needs only <cuda_runtime_api.h>-free C: the stream is carried as void*.
 #pragma once
+#include <vector>
 #include <cstddef>
 #include <cstdint>
 #include <cstdio>
@@ -122,6 +123,36 @@ inline void encode_moe_decode_ids(Enc& e, const MoeDecodeArgs& a, const Buffer& 
   const msb_moe_decode_args c = to_c(a);
   check(msb_moe_decode_ids(&c, (const uint64_t*)expert_table.ptr(), (const int*)ids.ptr(), expert_lo, expert_hi,
                            (int)part, e.stream), "encode_moe_decode_ids");
+}
+// prefill MoE (quant.hpp:87-118), with dim / inter as fields
+struct MoePrefillArgs {
+  int dim = 5120, inter = 2304;
+  QType t_gate_up = QType::IQ1_S, t_down = QType::IQ1_S;
+  int n_tokens = 0, n_exp = 0;
+  const ExpertSlot* slots = nullptr;   // host [n_exp]
+  const int* offs = nullptr;           // host [n_exp + 1]
+  Buffer tok, wt, slot_of;
+  int k_per_token = 6;
+  bool has_shared = true;
+  QType t_shared = QType::Q6_K;
+  ExpertSlot shared;
+  Buffer X, Y, scratch;
+};
+inline size_t moe_prefill_scratch_bytes(int total_entries, int n_tokens, int n_exp = 384, int dim = 5120, int inter = 2304) {
+  return msb_moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim, inter);
+}
+inline void encode_moe_prefill(Enc& e, const MoePrefillArgs& a) {
+  std::vector<msb_expert_slot> slots((size_t)(a.n_exp > 0 ? a.n_exp : 1));
+  for (int j = 0; j < a.n_exp; j++) slots[(size_t)j] = msb_expert_slot{a.slots[j].gate.ptr(), a.slots[j].up.ptr(), a.slots[j].down.ptr()};
+  msb_moe_prefill_args c{};
+  c.dim = a.dim; c.inter = a.inter;
+  c.t_gate_up = (int)a.t_gate_up; c.t_down = (int)a.t_down; c.t_shared = (int)a.t_shared;
+  c.n_tokens = a.n_tokens; c.n_exp = a.n_exp; c.slots = slots.data(); c.offs = a.offs;
+  c.tok = (const int*)a.tok.ptr(); c.wt = (const float*)a.wt.ptr(); c.slot_of = (const int*)a.slot_of.ptr();
+  c.k_per_token = a.k_per_token; c.has_shared = a.has_shared ? 1 : 0;
+  c.shared = msb_expert_slot{a.shared.gate.ptr(), a.shared.up.ptr(), a.shared.down.ptr()};
+  c.X = (const float*)a.X.ptr(); c.Y = (float*)a.Y.ptr(); c.scratch = a.scratch.ptr(); c.scratch_bytes = a.scratch.size;
+  check(msb_moe_prefill(&c, e.stream), "encode_moe_prefill");
 }
 }  // namespace q
 

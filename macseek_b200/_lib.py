@@ -53,6 +53,17 @@ class MoeDecodeArgsC(C.Structure):
                 ("y", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("swiglu_limit", C.c_float)]
 
 
+class MoePrefillArgsC(C.Structure):
+    _fields_ = [("dim", C.c_int), ("inter", C.c_int), ("t_gate_up", C.c_int), ("t_down", C.c_int), ("t_shared", C.c_int),
+                ("n_tokens", C.c_int), ("n_exp", C.c_int), ("slots", C.POINTER(ExpertSlotC)), ("offs", C.POINTER(C.c_int)),
+                ("tok", C.c_void_p), ("wt", C.c_void_p), ("slot_of", C.c_void_p), ("k_per_token", C.c_int),
+                ("has_shared", C.c_int), ("shared", ExpertSlotC), ("X", C.c_void_p), ("Y", C.c_void_p),
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("swiglu_limit", C.c_float)]
+
+
+lib.msb_moe_prefill_scratch_bytes.restype = C.c_size_t
+lib.msb_moe_prefill_scratch_bytes.argtypes = [_i, _i, _i, _i, _i]
+lib.msb_moe_prefill.argtypes = [C.POINTER(MoePrefillArgsC), _vp]
 lib.msb_f32_to_f16.argtypes = [_vp, _vp, C.c_size_t, _vp]
 lib.msb_matmul_scratch_bytes.restype = C.c_size_t
 lib.msb_matmul_scratch_bytes.argtypes = [_i, _i, _i, _i, _i]

@@ -1,4 +1,6 @@
 // extern "C" surface of libmacseek_b200 (declared in include/macseek_b200.h).
+#include <vector>
+#include <algorithm>
 #include "msb_common.cuh"
 #include "../../include/macseek_b200.h"
 
@@ -15,6 +17,23 @@ int matmul_h(int t, const void* W, int rows, int cols, const void* X16, int x_st
              void* scratch, size_t scratch_bytes, cudaStream_t st);
 int matmul(int t, const void* W, int rows, int cols, const float* X, float* Y, int n, bool accumulate, void* scratch,
            size_t scratch_bytes, cudaStream_t st);
+struct MoePrefillArgs {
+  int dim, inter, t_gate_up, t_down, t_shared, n_tokens, n_exp;
+  const uint64_t* slot_ptrs;
+  const int* offs;
+  const int* tok;
+  const float* wt;
+  const int* slot_of;
+  int k_per_token, has_shared;
+  uint64_t shared_ptrs[3];
+  const float* X;
+  float* Y;
+  void* scratch;
+  size_t scratch_bytes;
+  float limit;
+};
+size_t moe_prefill_scratch_bytes(int total, int n_tokens, int n_exp, int dim, int inter);
+int moe_prefill(const MoePrefillArgs& a, cudaStream_t st);
 size_t router_scratch_bytes(int E);
 int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_out, const float* W, const float* bias,
                  int* ids, float* wts, void* scratch, size_t scratch_bytes, int E, int dim, int k, int score_fn,
@@ -182,6 +201,28 @@ int msb_moe_decode_noalloc(const msb_moe_decode_args* a, void* stream) {
   b.scratch = g_noalloc_addr[dev];
   b.scratch_bytes = sizeof(float) * (size_t)(kMaxRouted + 1) * kNoAllocMaxInter;
   return msb_moe_decode(&b, stream);
+}
+
+size_t msb_moe_prefill_scratch_bytes(int total_entries, int n_tokens, int n_exp, int dim, int inter) {
+  return moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim, inter);
+}
+int msb_moe_prefill(const msb_moe_prefill_args* a, void* stream) {
+  if (!a) return fail(kErrArg, "moe_prefill: null args");
+  if (a->n_exp < 0 || (a->n_exp > 0 && !a->slots)) return fail(kErrArg, "moe_prefill: bad expert list");
+  std::vector<uint64_t> ptrs((size_t)std::max(a->n_exp, 1) * 3, 0);
+  for (int j = 0; j < a->n_exp; j++) {
+    ptrs[(size_t)j * 3] = (uint64_t)(uintptr_t)a->slots[j].gate;
+    ptrs[(size_t)j * 3 + 1] = (uint64_t)(uintptr_t)a->slots[j].up;
+    ptrs[(size_t)j * 3 + 2] = (uint64_t)(uintptr_t)a->slots[j].down;
+  }
+  MoePrefillArgs m;
+  m.dim = a->dim; m.inter = a->inter; m.t_gate_up = a->t_gate_up; m.t_down = a->t_down; m.t_shared = a->t_shared;
+  m.n_tokens = a->n_tokens; m.n_exp = a->n_exp; m.slot_ptrs = ptrs.data(); m.offs = a->offs; m.tok = a->tok; m.wt = a->wt;
+  m.slot_of = a->slot_of; m.k_per_token = a->k_per_token; m.has_shared = a->has_shared;
+  m.shared_ptrs[0] = (uint64_t)(uintptr_t)a->shared.gate; m.shared_ptrs[1] = (uint64_t)(uintptr_t)a->shared.up;
+  m.shared_ptrs[2] = (uint64_t)(uintptr_t)a->shared.down;
+  m.X = a->X; m.Y = a->Y; m.scratch = a->scratch; m.scratch_bytes = a->scratch_bytes; m.limit = a->swiglu_limit;
+  return moe_prefill(m, (cudaStream_t)stream);
 }
 
 size_t msb_router_scratch_bytes(int n_experts) { return router_scratch_bytes(n_experts); }

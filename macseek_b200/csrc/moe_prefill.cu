@@ -1,0 +1,506 @@
+// MoE prefill: grouped expert GEMMs on the 5th-generation tensor cores.
+// Replaces the reference's prefill MoE kernels (src/kernels/quant_moe_prefill.metal:22-344) behind
+// ms::q::encode_moe_prefill (src/kernels/quant.hpp:87-118, quant.mm:427-612).  Same arithmetic as the reference's
+// tensor path: activations, expert weights and the intermediate H as half operands, fp32 accumulation;
+//   H[e][r] = half( silu(min(g,10)) * clamp(u,-10,10) * wt[e] ),  Z[e] = H[e] . down^T,
+//   Y[t] += Z[shared row of t] + sum_k Z[slot_of[t][k]]   in that fixed order.
+//
+// Routing arrives expert-sorted (entries [offs[j], offs[j+1]) of tok[] / wt[] belong to routed expert j).  Launches:
+//   gather      Xg[entry] = half(X[tok[entry]]); the shared expert's rows (every token, weight 1) follow the routed ones
+//   gate/up     one grouped GEMM per weight type (routed experts, shared expert): tile = 128 entries x (64 gate rows +
+//               the same 64 up rows), SwiGLU in the epilogue, H stored as half
+//   down        the same grouped GEMM with 128 down rows per tile, Z stored as fp32
+//   combine     the fixed-order sum into Y
+// Grouped GEMM kernel, one persistent CTA per SM, 14 warps: warps 0..3 epilogue (TMEM lane = entry), warp 4 one
+// MMA-issuing thread (tcgen05.mma kind::f16, M 128, N 128, K 16), warp 5 one TMA thread for the activation tiles
+// (128-byte swizzle), warps 6..13 dequantise the tile's weight rows from the raw GGUF blocks straight into the swizzled
+// shared-memory operand layout (no half copy of the experts in HBM: every expert weight is used by one tile row block
+// only).  Tiles come from a table the host builds from offs[].  Every mbarrier wait is bounded.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <algorithm>
+#include <vector>
+#include "quant_blocks.cuh"
+
+namespace msb {
+
+constexpr int kMpBM = 128, kMpBN = 128, kMpBK = 64;
+constexpr int kMpABytes = kMpBM * kMpBK * 2, kMpBBytes = kMpBN * kMpBK * 2;
+constexpr int kMpStages = 5;
+constexpr int kMpProducerWarps = 8;
+constexpr int kMpThreads = (4 + 1 + 1 + kMpProducerWarps) * 32;
+
+struct MpTile { int slot, row0, rows, n0; };   // expert slot, first entry row, valid rows (<= 128), first weight row
+
+struct MpGemmParams {
+  CUtensorMap a_map;        // activations [rows_total][K] half, box 64 x 128
+  const MpTile* tiles;
+  const uint64_t* wptr;     // [slots][3] device addresses {gate, up, down}
+  const float* wt;          // [rows_total] routing weight per entry row (mode 0)
+  __half* h;                // mode 0 output [rows_total][n_out]
+  float* z;                 // mode 1 output [rows_total][n_out]
+  int* status;
+  int ntiles, K, n_out;     // K = contraction length (dim / inter), n_out = output row width (inter / dim)
+  float limit;
+  Tables tb;
+};
+
+struct MpHead {
+  uint64_t full[kMpStages], empty[kMpStages], accfull[2], accempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint64_t mp_desc(uint32_t saddr) {   // K-major, 128-byte swizzle, 8-row groups 1024 B apart
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void mp_tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void mp_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void mp_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mp_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mp_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mp_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void mp_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// MODE 0: gate/up + SwiGLU -> H (half);  MODE 1: down -> Z (fp32).  T = weight type of every tile of the launch.
+template <int T, int MODE>
+__global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_constant__ MpGemmParams p) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(1024) uint8_t mp_smem_raw[];
+  uint8_t* smem = mp_smem_raw + ((1024u - (smem_u32(mp_smem_raw) & 1023u)) & 1023u);
+  MpHead* hd = reinterpret_cast<MpHead*>(smem);
+  uint8_t* stage0 = smem + 1024;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t kCols = 2 * kMpBN;
+
+  if (tid == 0) {
+    for (int s = 0; s < kMpStages; s++) { mbar_init(&hd->full[s], 1 + kMpProducerWarps); mbar_init(&hd->empty[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&hd->accfull[b], 1); mbar_init(&hd->accempty[b], 4); }
+    hd->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hd->tmem_base)), "r"(kCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  mp_fence_before();
+  __syncthreads();
+  mp_fence_after();
+  const uint32_t tmem = hd->tmem_base;
+  volatile int* abort_flag = &hd->abort_flag;
+  const int kb = p.K / kMpBK;
+  const int my_tiles = p.ntiles > (int)blockIdx.x ? (p.ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  pdl_wait();
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA thread: activation tiles
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < my_tiles; i++) {
+        const MpTile tl = p.tiles[(int)blockIdx.x + i * (int)gridDim.x];
+        for (int k = 0; k < kb; k++, it++) {
+          const int s = it % kMpStages;
+          if (!mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty)) { ok = false; break; }
+          mbar_arrive_expect_tx(&hd->full[s], kMpABytes);
+          mp_tma_2d(stage0 + (size_t)s * (kMpABytes + kMpBBytes), &p.a_map, k * kMpBK, tl.row0, &hd->full[s]);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kMpBN >> 3) << 17) | ((uint32_t)(kMpBM >> 4) << 24);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < my_tiles; i++) {
+        const int buf = i & 1;
+        if (!mbar_wait(&hd->accempty[buf], ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty)) break;
+        for (int k = 0; k < kb; k++, it++) {
+          const int s = it % kMpStages;
+          if (!mbar_wait(&hd->full[s], (it / kMpStages) & 1u, abort_flag, p.status, kDevWaitFull)) { ok = false; break; }
+          mp_fence_after();
+          const uint32_t a_s = smem_u32(stage0 + (size_t)s * (kMpABytes + kMpBBytes)), b_s = a_s + kMpABytes;
+#pragma unroll
+          for (int ks = 0; ks < kMpBK / 16; ks++)
+            mp_mma_f16(tmem + (uint32_t)(buf * kMpBN), mp_desc(a_s + ks * 32), mp_desc(b_s + ks * 32), idesc,
+                       (k > 0 || ks > 0) ? 1u : 0u);
+          mp_commit(&hd->empty[s]);
+        }
+        if (ok) mp_commit(&hd->accfull[buf]);
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ weight producers: raw blocks -> half operand tile
+    // chunk c = (tile row r, 8-element group j of the 64-wide K block); 8 consecutive threads share a row (one block
+    // of the raw matrix), a warp writes four whole 128-byte rows: conflict-free stores at the swizzled positions
+    const int pt = tid - 6 * 32;
+    const size_t rb = row_bytes(T, p.K);
+    constexpr int per_block = block_elems(T) / 8;          // 8-element groups per raw block
+    uint32_t it = 0;
+    bool ok = true;
+    for (int i = 0; ok && i < my_tiles; i++) {
+      const MpTile tl = p.tiles[(int)blockIdx.x + i * (int)gridDim.x];
+      const uint64_t* wp = p.wptr + (size_t)tl.slot * 3;
+      const uint8_t* w0 = reinterpret_cast<const uint8_t*>(MODE == 0 ? wp[0] : wp[2]);   // gate | down
+      const uint8_t* w1 = reinterpret_cast<const uint8_t*>(wp[1]);                        // up (mode 0)
+      for (int k = 0; k < kb; k++, it++) {
+        const int s = it % kMpStages;
+        if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
+          ok = false;
+          break;
+        }
+        uint8_t* bt = stage0 + (size_t)s * (kMpABytes + kMpBBytes) + kMpABytes;
+#pragma unroll
+        for (int q = 0; q < kMpBN * 8 / (kMpProducerWarps * 32); q++) {
+          const int c = pt + q * kMpProducerWarps * 32, r = c >> 3, j = c & 7;
+          // mode 0: tile rows 0..63 = gate rows n0.., 64..127 = the same up rows; mode 1: down rows n0..n0+127
+          const uint8_t* base = (MODE == 0 && r >= 64) ? w1 : w0;
+          const int wrow = tl.n0 + (MODE == 0 ? (r & 63) : r);
+          uint4 out = make_uint4(0, 0, 0, 0);
+          if (wrow < p.n_out) {
+            const int e8 = k * (kMpBK / 8) + j;            // 8-element group index inside the weight row
+            float y[8];
+            if constexpr (is_dense(T)) {
+#pragma unroll
+              for (int e = 0; e < 8; e++) y[e] = 0.f;      // dense expert weights are not a reference combination
+            } else {
+              dequant8<T>(base + (size_t)wrow * rb + (size_t)(e8 / per_block) * block_bytes(T), e8 % per_block, p.tb, y);
+            }
+            __half2 hh[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) hh[e] = __floats2half2_rn(y[2 * e], y[2 * e + 1]);
+            out = *reinterpret_cast<uint4*>(hh);
+          }
+          *reinterpret_cast<uint4*>(bt + r * 128 + ((j ^ (r & 7)) << 4)) = out;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hd->full[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: TMEM lane = entry row
+    for (int i = 0; i < my_tiles; i++) {
+      const int buf = i & 1;
+      const MpTile tl = p.tiles[(int)blockIdx.x + i * (int)gridDim.x];
+      if (!__all_sync(0xffffffffu, mbar_wait(&hd->accfull[buf], (i >> 1) & 1u, abort_flag, p.status, kDevWaitFull))) break;
+      mp_fence_after();
+      const int lrow = 32 * warp + lane;
+      const bool live = lrow < tl.rows;
+      const size_t grow = (size_t)tl.row0 + lrow;
+      const uint32_t taddr = tmem + ((uint32_t)(32 * warp) << 16) + (uint32_t)(buf * kMpBN);
+      if (MODE == 0) {
+        const float wt = live ? p.wt[grow] : 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t g[32], u[32];
+          mp_ld32(taddr + c0, g);
+          mp_ld32(taddr + 64 + c0, u);
+          mp_wait_ld();
+          if (live) {
+            __half2 hh[16];
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              float hv[2];
+#pragma unroll
+              for (int e = 0; e < 2; e++) {
+                const float gg = fminf(__uint_as_float(g[2 * q + e]), p.limit);
+                const float uu = fminf(fmaxf(__uint_as_float(u[2 * q + e]), -p.limit), p.limit);
+                hv[e] = gg / (1.f + expf(-gg)) * uu * wt;
+              }
+              hh[q] = __floats2half2_rn(hv[0], hv[1]);
+            }
+            const int col0 = tl.n0 + c0;
+            __half* dst = p.h + grow * p.n_out + col0;
+            if (col0 + 32 <= p.n_out) {
+#pragma unroll
+              for (int q = 0; q < 4; q++) reinterpret_cast<uint4*>(dst)[q] = reinterpret_cast<uint4*>(hh)[q];
+            } else {
+              for (int q = 0; q < 32; q++)
+                if (col0 + q < p.n_out) dst[q] = reinterpret_cast<__half*>(hh)[q];
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kMpBN; c0 += 32) {
+          uint32_t r[32];
+          mp_ld32(taddr + c0, r);
+          mp_wait_ld();
+          const int col0 = tl.n0 + c0;
+          if (live && col0 < p.n_out) {
+            float* dst = p.z + grow * p.n_out + col0;
+            if (col0 + 32 <= p.n_out) {
+#pragma unroll
+              for (int q = 0; q < 8; q++)
+                reinterpret_cast<float4*>(dst)[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+            } else {
+              for (int q = 0; q < 32; q++)
+                if (col0 + q < p.n_out) dst[q] = __uint_as_float(r[q]);
+            }
+          }
+        }
+      }
+      mp_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hd->accempty[buf]);
+    }
+  }
+  mp_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    mp_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kCols) : "memory");
+  }
+}
+
+// Xg[row] = half(X[src token]); rows [0, total) follow tok[], rows [total, total + n_tokens) are the tokens in order
+// (the shared expert's entries); their routing weight 1 is written to wt_all.
+__global__ void __launch_bounds__(256) moep_gather_kernel(const float* __restrict__ X, const int* __restrict__ tok,
+                                                          const float* __restrict__ wt, __half* __restrict__ xg,
+                                                          float* __restrict__ wt_all, int total, int n_tokens, int dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int t = row < total ? tok[row] : row - total;
+  if (threadIdx.x == 0) wt_all[row] = row < total ? wt[row] : 1.0f;
+  const float4* src = reinterpret_cast<const float4*>(X + (size_t)t * dim);
+  uint2* dst = reinterpret_cast<uint2*>(xg + (size_t)row * dim);
+  for (int i = threadIdx.x; i < dim / 4; i += 256) {
+    const float4 v = src[i];
+    __half2 h[2] = {__floats2half2_rn(v.x, v.y), __floats2half2_rn(v.z, v.w)};
+    dst[i] = *reinterpret_cast<uint2*>(h);
+  }
+}
+
+// Y[t] += Z[total + t] (shared, if any) + sum over k of Z[slot_of[t * kpt + k]] (slots < 0 skipped), in that order
+__global__ void __launch_bounds__(256) moep_combine_kernel(const float* __restrict__ z, const int* __restrict__ slot_of,
+                                                           float* __restrict__ Y, int total, int n_tokens, int kpt, int dim,
+                                                           int has_shared) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < dim / 4; i += 256) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (has_shared) acc = reinterpret_cast<const float4*>(z + (size_t)(total + t) * dim)[i];
+    for (int k = 0; k < kpt; k++) {
+      const int e = slot_of[(size_t)t * kpt + k];
+      if (e < 0) continue;
+      const float4 v = reinterpret_cast<const float4*>(z + (size_t)e * dim)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float4 y = reinterpret_cast<float4*>(Y + (size_t)t * dim)[i];
+    y.x += acc.x; y.y += acc.y; y.z += acc.z; y.w += acc.w;
+    reinterpret_cast<float4*>(Y + (size_t)t * dim)[i] = y;
+  }
+}
+
+// ---------------------------------------------------------------- host side
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn mp_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols) {
+  EncodeTiledFn encode = mp_encode_fn();
+  if (!encode) return fail(kErrCuda, "moe_prefill: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kMpBK, (cuuint32_t)kMpBM};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult cr = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fail(kErrCuda, "moe_prefill: tensor map encode failed (%d)", (int)cr);
+  return kOk;
+}
+
+template <int T, int MODE>
+int mp_launch(MpGemmParams& p, int sms, int dev, cudaStream_t st) {
+  if (p.ntiles <= 0) return kOk;
+  const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes);
+  auto kern = moep_gemm_kernel<T, MODE>;
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    MSB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev & 63] = true;
+  }
+  MSB_CUDA(launch_pdl(kern, dim3(std::max(1, std::min(sms, p.ntiles))), dim3(kMpThreads), smem, st, p));
+  MSB_LAUNCH_CHECK("moep_gemm_kernel");
+  return kOk;
+}
+template <int MODE>
+int mp_launch_type(int t, MpGemmParams& p, int sms, int dev, cudaStream_t st) {
+  switch (t) {
+    case IQ1_S: return mp_launch<IQ1_S, MODE>(p, sms, dev, st);
+    case IQ2_XXS: return mp_launch<IQ2_XXS, MODE>(p, sms, dev, st);
+    case Q6_K: return mp_launch<Q6_K, MODE>(p, sms, dev, st);
+    case Q8_0: return mp_launch<Q8_0, MODE>(p, sms, dev, st);
+  }
+  return fail(kErrType, "moe_prefill: unsupported expert weight type %s", type_name(t));
+}
+size_t al256(size_t b) { return (b + 255) & ~(size_t)255; }
+// upper bounds of the tile counts
+size_t mp_row_tiles(int total, int n_exp, int n_tokens) {
+  return (size_t)(total + kMpBM - 1) / kMpBM + (size_t)n_exp + (size_t)(n_tokens + kMpBM - 1) / kMpBM + 1;
+}
+}  // namespace
+
+struct MoePrefillArgs {
+  int dim, inter, t_gate_up, t_down, t_shared, n_tokens, n_exp;
+  const uint64_t* slot_ptrs;   // host [n_exp][3] device addresses {gate, up, down}
+  const int* offs;             // host [n_exp + 1]
+  const int* tok;              // device [total]
+  const float* wt;             // device [total]
+  const int* slot_of;          // device [n_tokens * k_per_token]
+  int k_per_token, has_shared;
+  uint64_t shared_ptrs[3];
+  const float* X;
+  float* Y;
+  void* scratch;
+  size_t scratch_bytes;
+  float limit;
+};
+
+size_t moe_prefill_scratch_bytes(int total, int n_tokens, int n_exp, int dim, int inter) {
+  const size_t rows = (size_t)total + n_tokens;
+  const size_t rt = mp_row_tiles(total, n_exp, n_tokens);
+  size_t b = 256;
+  b += al256(rt * ((inter + 63) / 64) * sizeof(MpTile)) + al256(rt * ((dim + 127) / 128) * sizeof(MpTile));
+  b += al256((size_t)(n_exp + 1) * 3 * sizeof(uint64_t)) + al256(rows * sizeof(float));
+  b += al256(rows * dim * 2) + al256(rows * inter * 2) + al256(rows * dim * 4);
+  return b;
+}
+
+int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
+  if (a.dim <= 0 || a.inter <= 0 || a.dim % 256 || a.inter % 256) return fail(kErrArg, "moe_prefill: dim/inter must be multiples of 256");
+  if (a.n_tokens < 0 || a.n_exp < 0 || a.k_per_token <= 0) return fail(kErrArg, "moe_prefill: bad counts");
+  if (a.n_tokens == 0) return kOk;
+  if (a.n_exp > 0 && (!a.slot_ptrs || !a.offs || !a.tok || !a.wt)) return fail(kErrArg, "moe_prefill: null routing arrays");
+  if (!a.slot_of || !a.X || !a.Y || !a.scratch) return fail(kErrArg, "moe_prefill: null pointer");
+  const int total = a.n_exp > 0 ? a.offs[a.n_exp] : 0;
+  if (a.n_exp > 0 && a.offs[0] != 0) return fail(kErrArg, "moe_prefill: offs[0] must be 0");
+  for (int j = 0; j < a.n_exp; j++)
+    if (a.offs[j + 1] < a.offs[j]) return fail(kErrArg, "moe_prefill: offs must not decrease");
+  if (a.scratch_bytes < moe_prefill_scratch_bytes(total, a.n_tokens, a.n_exp, a.dim, a.inter))
+    return fail(kErrScratch, "moe_prefill: scratch too small");
+  Tables tb;
+  int rc = get_tables(&tb);
+  if (rc) return rc;
+  int dev = 0, sms = 0;
+  MSB_CUDA(cudaGetDevice(&dev));
+  MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int n_sh = a.has_shared ? a.n_tokens : 0;
+  const size_t rows = (size_t)total + n_sh;
+  // tile tables: per expert, weight-row tiles outer, entry tiles inner (CTAs that run together share a weight tile)
+  std::vector<MpTile> t1r, t1s, t2r, t2s;
+  auto add_tiles = [&](std::vector<MpTile>& v, int slot, int row0, int m, int n_out, int step) {
+    for (int n0 = 0; n0 < n_out; n0 += step)
+      for (int m0 = 0; m0 < m; m0 += kMpBM) v.push_back(MpTile{slot, row0 + m0, std::min(kMpBM, m - m0), n0});
+  };
+  for (int j = 0; j < a.n_exp; j++) {
+    const int m = a.offs[j + 1] - a.offs[j];
+    if (m <= 0) continue;
+    add_tiles(t1r, j, a.offs[j], m, a.inter, 64);
+    add_tiles(t2r, j, a.offs[j], m, a.dim, kMpBN);
+  }
+  if (n_sh) {
+    add_tiles(t1s, a.n_exp, total, n_sh, a.inter, 64);
+    add_tiles(t2s, a.n_exp, total, n_sh, a.dim, kMpBN);
+  }
+  std::vector<uint64_t> wptr((size_t)(a.n_exp + 1) * 3, 0);
+  for (int j = 0; j < a.n_exp; j++)
+    for (int q = 0; q < 3; q++) {
+      wptr[(size_t)j * 3 + q] = a.slot_ptrs[(size_t)j * 3 + q];
+      if (!wptr[(size_t)j * 3 + q] && a.offs[j + 1] > a.offs[j]) return fail(kErrArg, "moe_prefill: null matrix of expert slot %d", j);
+    }
+  for (int q = 0; q < 3; q++) wptr[(size_t)a.n_exp * 3 + q] = a.shared_ptrs[q];
+  if (n_sh && (!a.shared_ptrs[0] || !a.shared_ptrs[1] || !a.shared_ptrs[2])) return fail(kErrArg, "moe_prefill: null shared expert matrix");
+  // scratch carve-up
+  uint8_t* cur = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(a.scratch) + 255) & ~(uintptr_t)255);
+  const size_t rt = mp_row_tiles(total, a.n_exp, a.n_tokens);
+  MpTile* d_t1 = reinterpret_cast<MpTile*>(cur); cur += al256(rt * ((a.inter + 63) / 64) * sizeof(MpTile));
+  MpTile* d_t2 = reinterpret_cast<MpTile*>(cur); cur += al256(rt * ((a.dim + 127) / 128) * sizeof(MpTile));
+  uint64_t* d_wptr = reinterpret_cast<uint64_t*>(cur); cur += al256((size_t)(a.n_exp + 1) * 3 * sizeof(uint64_t));
+  float* d_wt = reinterpret_cast<float*>(cur); cur += al256(rows * sizeof(float));
+  __half* d_xg = reinterpret_cast<__half*>(cur); cur += al256(rows * a.dim * 2);
+  __half* d_h = reinterpret_cast<__half*>(cur); cur += al256(rows * a.inter * 2);
+  float* d_z = reinterpret_cast<float*>(cur);
+  // the tables go to the device (pageable source: the runtime stages them before returning)
+  auto upload = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {
+    return bytes ? cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st) : cudaSuccess;
+  };
+  MSB_CUDA(upload(d_t1, t1r.data(), t1r.size() * sizeof(MpTile)));
+  MSB_CUDA(upload(d_t1 + t1r.size(), t1s.data(), t1s.size() * sizeof(MpTile)));
+  MSB_CUDA(upload(d_t2, t2r.data(), t2r.size() * sizeof(MpTile)));
+  MSB_CUDA(upload(d_t2 + t2r.size(), t2s.data(), t2s.size() * sizeof(MpTile)));
+  MSB_CUDA(upload(d_wptr, wptr.data(), wptr.size() * sizeof(uint64_t)));
+  if (rows == 0) return kOk;
+  MSB_CUDA(launch_pdl(moep_gather_kernel, dim3((unsigned)rows), dim3(256), 0, st, a.X, a.tok, a.wt, d_xg, d_wt, total, n_sh,
+                      a.dim));
+  MpGemmParams p;
+  p.wptr = d_wptr; p.wt = d_wt; p.h = d_h; p.z = d_z; p.status = tb.status; p.limit = a.limit > 0.f ? a.limit : 10.f; p.tb = tb;
+  // gate/up + SwiGLU
+  rc = mp_make_map(&p.a_map, d_xg, (int64_t)rows, a.dim);
+  if (rc) return rc;
+  p.K = a.dim; p.n_out = a.inter;
+  p.tiles = d_t1; p.ntiles = (int)t1r.size();
+  rc = mp_launch_type<0>(a.t_gate_up, p, sms, dev, st);
+  if (rc) return rc;
+  p.tiles = d_t1 + t1r.size(); p.ntiles = (int)t1s.size();
+  rc = mp_launch_type<0>(a.t_shared, p, sms, dev, st);
+  if (rc) return rc;
+  // down
+  rc = mp_make_map(&p.a_map, d_h, (int64_t)rows, a.inter);
+  if (rc) return rc;
+  p.K = a.inter; p.n_out = a.dim;
+  p.tiles = d_t2; p.ntiles = (int)t2r.size();
+  rc = mp_launch_type<1>(a.t_down, p, sms, dev, st);
+  if (rc) return rc;
+  p.tiles = d_t2 + t2r.size(); p.ntiles = (int)t2s.size();
+  rc = mp_launch_type<1>(a.t_shared, p, sms, dev, st);
+  if (rc) return rc;
+  MSB_CUDA(launch_pdl(moep_combine_kernel, dim3((unsigned)a.n_tokens), dim3(256), 0, st, (const float*)d_z, a.slot_of, a.Y, total,
+                      a.n_tokens, a.k_per_token, a.dim, a.has_shared ? 1 : 0));
+  MSB_LAUNCH_CHECK("moe_prefill");
+  return kOk;
+}
+
+}  // namespace msb

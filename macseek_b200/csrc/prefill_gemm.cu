@@ -338,7 +338,7 @@ size_t matmul_scratch_bytes(int t, int rows, int cols, int n, bool with_x) {
   size_t b = t == F16 ? 0 : (size_t)rows * cols * 2;
   b = (b + 255) & ~(size_t)255;
   if (with_x) b += ((size_t)n * cols * 2 + 255) & ~(size_t)255;
-  return b + 256;
+  return b ? b + 256 : 0;   // + room to align the base
 }
 
 int matmul_h(int t, const void* W, int rows, int cols, const void* X16, int x_stride, float* Y, int n, bool accumulate,

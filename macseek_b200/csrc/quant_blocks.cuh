@@ -444,9 +444,12 @@ __device__ __forceinline__ void dequant8<IQ1_S>(const uint8_t* blk, int e8, cons
   const float dl = __fmul_rn(ldg_half(blk), (float)(2 * ((qh >> 12) & 7u) + 1));
   const float delta = (qh & 0x8000u) ? -0.125f : 0.125f;
   const uint32_t idx = __ldg(blk + 2 + 4 * ib + l) | (((qh >> (3 * l)) & 7u) << 8);
-  const int8_t* g = tb.iq1s_i8 + idx * 8;
+  const uint2 gv = __ldg(reinterpret_cast<const uint2*>(tb.iq1s_i8 + idx * 8));   // the entry's 8 signed bytes at once
 #pragma unroll
-  for (int j = 0; j < 8; j++) y[j] = __fmul_rn(dl, __fadd_rn((float)__ldg(g + j), delta));
+  for (int j = 0; j < 8; j++) {
+    const int8_t gj = (int8_t)(((j < 4 ? gv.x : gv.y) >> (8 * (j & 3))) & 0xFFu);
+    y[j] = __fmul_rn(dl, __fadd_rn((float)gj, delta));
+  }
 }
 template <>
 __device__ __forceinline__ void dequant8<IQ2_XXS>(const uint8_t* blk, int e8, const Tables& tb, float (&y)[8]) {

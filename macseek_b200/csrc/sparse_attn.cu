@@ -270,19 +270,22 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
   }
 }
 
-// combine the splits of one head, add the sink to the denominator, inverse rope on the last 64 dims
+// combine the splits of one head, add the sink to the denominator, inverse rope on the last 64 dims.  A head's D
+// outputs are spread over 4 blocks (D / 4 threads each): the kernel streams splits x H x D partials and is bounded by
+// how many of those loads are in flight, so it wants every SM, not one block per head.
 template <int D>
-__global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p) {
+__global__ void __launch_bounds__(D / 4) sparse_combine_kernel(const SparseParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float xs[D];
+  constexpr int DQ = D / 4;
+  __shared__ float xs[DQ];
   __shared__ float fs[1024];      // per-split rescale factors exp(m_s - M)
-  const int h = blockIdx.x, d = threadIdx.x;
+  __shared__ float ls[1024];
+  const int h = blockIdx.x, t = threadIdx.x, d = blockIdx.y * DQ + t;
   const float sink = p.sinks[h];
   // every thread needs M and the denominator: stage (m, l) of all splits once, then every thread reduces them from
   // shared memory in the same order
-  __shared__ float ls[1024];
-  for (int s = d; s < p.splits; s += D) {
+  for (int s = t; s < p.splits; s += DQ) {
     const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((size_t)s * p.H + h) * 2);
     fs[s] = ml.x; ls[s] = ml.y;
   }
@@ -290,23 +293,23 @@ __global__ void __launch_bounds__(D) sparse_combine_kernel(const SparseParams p)
   float M = sink;
   for (int s = 0; s < p.splits; s++) M = fmaxf(M, fs[s]);
   __syncthreads();
-  for (int s = d; s < p.splits; s += D) { const float m = fs[s]; fs[s] = (m == -INFINITY) ? 0.f : expf(m - M); }
+  for (int s = t; s < p.splits; s += DQ) { const float m = fs[s]; fs[s] = (m == -INFINITY) ? 0.f : expf(m - M); }
   __syncthreads();
   float den = expf(sink - M);
   for (int s = 0; s < p.splits; s++) den += ls[s] * fs[s];
   float acc = 0.f;
   const float* po = p.part_o + (size_t)h * D + d;
   const size_t stride = (size_t)p.H * D;
-#pragma unroll 8
+#pragma unroll 16
   for (int s = 0; s < p.splits; s++) acc += po[(size_t)s * stride] * fs[s];
-  xs[d] = acc / den;
+  xs[t] = acc / den;
   __syncthreads();
-  float v = xs[d];
-  if (d >= D - 64) {
+  float v = xs[t];
+  if (d >= D - 64) {    // rope pairs (d, d ^ 1) sit in the same block: DQ is even
     const int i = (d - (D - 64)) >> 1;
     const float c = p.cs[2 * i], sn = -p.cs[2 * i + 1];
-    const float a = xs[d & ~1], b = xs[d | 1];
-    v = (d & 1) ? a * sn + b * c : a * c - b * sn;
+    const float a = xs[t & ~1], b2 = xs[t | 1];
+    v = (d & 1) ? a * sn + b2 * c : a * c - b2 * sn;
   }
   p.out[(size_t)h * D + d] = v;
 }
@@ -335,7 +338,7 @@ static int launch_sparse(SparseParams& p, cudaStream_t st, int dev) {
     done[dev & 63] = true;
   }
   MSB_CUDA(launch_pdl(kern, dim3(dim3(p.H / kSaHeadsPerBlock, p.splits)), dim3(128), smem, st, p));
-  MSB_CUDA(launch_pdl(sparse_combine_kernel<D>, dim3(p.H), dim3(D), 0, st, p));
+  MSB_CUDA(launch_pdl(sparse_combine_kernel<D>, dim3(p.H, 4), dim3(D / 4), 0, st, p));
   MSB_LAUNCH_CHECK("sparse attention");
   return kOk;
 }

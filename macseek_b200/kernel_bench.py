@@ -3,6 +3,8 @@
     python -m macseek_b200.kernel_bench matvec Q6_K 129280 4096 [--n 1] [--groups 1]
     python -m macseek_b200.kernel_bench moe {router|gu|down|all}
     python -m macseek_b200.kernel_bench attn {index|scores|topk|sparse|all} [--kv-len 200000]
+    python -m macseek_b200.kernel_bench gemm Q6_K 4096 4096 --n 4096
+    python -m macseek_b200.kernel_bench moe_prefill [--n 4096]
     python -m macseek_b200.kernel_bench sweep
 
 Each case builds synthetic weights on the device (several copies, together larger than the 126 MB L2, used in
@@ -177,6 +179,91 @@ def attn_cases(which: str, kv_len: int = 200000, eager: int = 0):
                   flush=True)
 
 
+def gemm_case(t: q.QType, rows: int, cols: int, n: int, eager: int = 0):
+    """Prefill projection Y[n x rows] = X[n x cols] . W^T: the contraction alone (half weights given) and the whole
+    call (weight dequantisation to half + contraction)."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4)
+    W = synthetic.random_weights(t, rows, cols, gen)
+    W16 = synthetic.random_weights(q.QType.F16, rows, cols, gen)
+    X16 = torch.randn(n, cols, device="cuda", generator=gen).half()
+    Y = torch.zeros(n, rows, device="cuda")
+    scratch = torch.zeros(q.matmul_scratch_bytes(t, rows, cols, n, False), dtype=torch.uint8, device="cuda")
+    flop = 2.0 * n * rows * cols
+
+    def dense(i):
+        q.encode_matmul_h(Enc(), q.QType.F16, W16, rows, cols, X16, Y, n, False, 0, None)
+
+    def whole(i):
+        q.encode_matmul_h(Enc(), t, W, rows, cols, X16, Y, n, False, 0, scratch)
+
+    for name, fn in (("contraction (F16 weights)", dense), ("dequant + contraction (%s)" % t.name, whole)):
+        r = run(fn, eager) if eager else graph_time(fn, 4, 5)
+        if r:
+            print(f"gemm {n}x{rows}x{cols} {name:34s} median {r[0]:9.2f} us   {flop / r[0] / 1e6:8.1f} TFLOP/s", flush=True)
+
+
+def moe_prefill_case(n: int = 4096, eager: int = 0):
+    """The benchmark prefill layer: n tokens, top-8 of 384 experts (IQ1_S gate/up, IQ2_XXS down) + Q8_0 shared expert,
+    dim 4096, inter 2048; logits N(0,1) plus a log-Zipf(1.1) popularity bias over a seeded expert permutation."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    D, I, E, K = 4096, 2048, 384, 8
+    lw = ml.MoeLayerWeights(D, I, E, q.QType.IQ1_S, q.QType.IQ2_XXS, q.QType.Q8_0).randomize(gen)
+    perm = torch.randperm(E, device="cuda", generator=gen)
+    bias = torch.empty(E, device="cuda")
+    bias[perm] = -1.1 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
+    logits = torch.randn(n, E, device="cuda", generator=gen) + bias
+    ids = torch.topk(logits, K, dim=1).indices                                   # [n][K]
+    w = torch.softmax(torch.gather(logits, 1, ids), dim=1).float()
+    flat_e = ids.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)                                   # entries sorted by (expert, token*K+k)
+    tok = (order // K).int().contiguous()
+    wt = w.reshape(-1)[order].contiguous()
+    slot_of = torch.empty(n * K, dtype=torch.int32, device="cuda")
+    slot_of[order] = torch.arange(n * K, dtype=torch.int32, device="cuda")
+    counts = torch.bincount(flat_e, minlength=E).cpu().tolist()
+    used = [e for e in range(E) if counts[e] > 0]
+    offs = [0]
+    for e in used:
+        offs.append(offs[-1] + counts[e])
+
+    def slot_of_expert(ex):
+        sl = q.ExpertSlot()
+        sl.gate, sl.up, sl.down = lw.expert_views(ex)
+        return sl
+    a = q.MoePrefillArgs(D, I)
+    a.t_gate_up, a.t_down, a.t_shared = lw.t_gate_up, lw.t_down, lw.t_shared
+    a.n_tokens, a.k_per_token, a.has_shared = n, K, True
+    a.slots = [slot_of_expert(ex) for ex in used]
+    a.shared = lw.shared
+    a.offs = offs
+    a.tok, a.wt, a.slot_of = tok, wt, slot_of
+    a.X = torch.randn(n, D, device="cuda", generator=gen)
+    a.Y = torch.zeros(n, D, device="cuda")
+    a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(offs[-1], n, len(used), D, I), dtype=torch.uint8, device="cuda")
+    cs = sorted(counts)
+    print(f"moe_prefill n={n}: {len(used)} experts hit, tokens/expert min {cs[0]} median {cs[len(cs) // 2]} max {cs[-1]}", flush=True)
+    e = Enc()
+    for _ in range(2):
+        q.encode_moe_prefill(e, a)
+    e.wait()
+    if eager:
+        return
+    ts = []
+    for _ in range(5):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        q.encode_moe_prefill(e, a)
+        t1.record()
+        torch.cuda.synchronize()
+        ts.append(t0.elapsed_time(t1))
+    ts.sort()
+    flop = 2.0 * 3 * D * I * (n * K + n)
+    print(f"moe_prefill n={n} median {ts[2]:8.3f} ms   {flop / ts[2] / 1e9:8.1f} TFLOP/s (algorithmic 2*3*D*I*(entries+tokens))",
+          flush=True)
+
+
 def sweep():
     T = q.QType
     moe_cases("every")
@@ -194,7 +281,7 @@ def sweep():
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["matvec", "moe", "attn", "sweep"])
+    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "sweep"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--groups", type=int, default=1)
@@ -206,6 +293,10 @@ def main():
         matvec_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n, a.groups, a.eager)
     elif a.case == "moe":
         moe_cases(a.args[0] if a.args else "every", a.eager)
+    elif a.case == "moe_prefill":
+        moe_prefill_case(a.n if a.n > 1 else 4096, a.eager)
+    elif a.case == "gemm":
+        gemm_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n if a.n > 1 else 4096, a.eager)
     elif a.case == "attn":
         attn_cases(a.args[0] if a.args else "every", a.kv_len, a.eager)
     else:

@@ -169,3 +169,47 @@ def encode_moe_decode_ids(e: Enc, a: MoeDecodeArgs, expert_table, ids, expert_lo
 def encode_matvec_rmsnorm(e: Enc, t, W, rows, cols, x, norm_w, eps, y):
     """y = W . (x * rsqrt(mean(x^2) + eps) * norm_w): input RMSNorm fused into the x load (quant.hpp:19-26)."""
     _lib.check(_lib.lib.msb_matvec_rmsnorm(int(t), ptr(W), rows, cols, ptr(x), ptr(norm_w), eps, ptr(y), e.handle))
+
+
+def moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim=5120, inter=2304):
+    return _lib.lib.msb_moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim, inter)
+
+
+class MoePrefillArgs:
+    """ms::q::MoePrefillArgs (quant.hpp:96-116) with dim / inter as fields.  slots: list of ExpertSlot (device tensors),
+    offs: host list of n_exp + 1 entry offsets; tok / wt / slot_of / X / Y / scratch: device tensors."""
+
+    def __init__(self, dim=5120, inter=2304):
+        self.dim, self.inter = dim, inter
+        self.t_gate_up = self.t_down = QType.IQ1_S
+        self.t_shared = QType.Q6_K
+        self.n_tokens = 0
+        self.slots, self.offs = [], [0]
+        self.tok = self.wt = self.slot_of = None
+        self.k_per_token = 6
+        self.has_shared = True
+        self.shared = ExpertSlot()
+        self.X = self.Y = self.scratch = None
+        self.swiglu_limit = 10.0
+
+
+def encode_moe_prefill(e: Enc, a: MoePrefillArgs):
+    """Grouped expert GEMMs of a prefill chunk, Y accumulated (quant.hpp:118)."""
+    import ctypes as C
+    n_exp = len(a.slots)
+    c = _lib.MoePrefillArgsC()
+    c.dim, c.inter = a.dim, a.inter
+    c.t_gate_up, c.t_down, c.t_shared = int(a.t_gate_up), int(a.t_down), int(a.t_shared)
+    c.n_tokens, c.n_exp = a.n_tokens, n_exp
+    slots = (_lib.ExpertSlotC * max(n_exp, 1))()
+    for j, s in enumerate(a.slots):
+        slots[j].gate, slots[j].up, slots[j].down = ptr(s.gate), ptr(s.up), ptr(s.down)
+    offs = (C.c_int * (n_exp + 1))(*[int(v) for v in a.offs])
+    c.slots, c.offs = slots, offs
+    c.tok, c.wt, c.slot_of = ptr(a.tok), ptr(a.wt), ptr(a.slot_of)
+    c.k_per_token, c.has_shared = a.k_per_token, int(a.has_shared)
+    c.shared.gate, c.shared.up, c.shared.down = ptr(a.shared.gate), ptr(a.shared.up), ptr(a.shared.down)
+    c.X, c.Y, c.scratch = ptr(a.X), ptr(a.Y), ptr(a.scratch)
+    c.scratch_bytes = a.scratch.numel() * a.scratch.element_size() if a.scratch is not None else 0
+    c.swiglu_limit = a.swiglu_limit
+    _lib.check(_lib.lib.msb_moe_prefill(C.byref(c), e.handle))

@@ -1,0 +1,175 @@
+"""GPU parity of the MoE prefill (grouped expert GEMMs on tcgen05) against the reference's own check
+(tests/test_quant_moe_prefill.mm): half-emulated reference error <= 1e-3, pure-F32 reference error <= 5e-3, both
+normalised by the summed magnitudes, and run-to-run bit identity.  Routing patterns follow the reference's test
+(:70-110): a popular expert that spans several tiles, explicit expert sizes around the tile boundaries, Zipf."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as ol
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def orc():
+    return ol.Oracle()
+
+
+def r16(a):
+    return a.astype(np.float16).astype(np.float64)
+
+
+SIZES = [1, 1, 2, 15, 16, 17, 31, 32, 33, 47, 48, 49, 63, 64, 65, 100, 129, 200, 300]
+
+
+def make_routing(kind, n, k, n_exp, seed):
+    rng = np.random.default_rng(seed)
+    rt = [[] for _ in range(n)]
+    if kind == "popular":          # slot 0 -> expert 0 for every token, other slots random distinct
+        for t in range(n):
+            perm = rng.permutation(np.arange(1, n_exp))
+            rt[t] = [0] + [int(v) for v in perm[:k - 1]]
+    elif kind == "sizes":          # expert 0 takes every token, the rest have the listed sizes
+        for t in range(n):
+            rt[t].append(0)
+        nxt = 0
+        for j in range(1, n_exp):
+            for _ in range(SIZES[j - 1]):
+                t = nxt
+                while len(rt[t]) >= k:
+                    t = (t + 1) % n
+                rt[t].append(j)
+                nxt = (t + 7) % n
+    else:                          # Zipf(0.8) popularity, k distinct experts per token
+        perm = rng.permutation(n_exp)
+        pw = np.zeros(n_exp)
+        pw[perm] = 1.0 / np.power(np.arange(1, n_exp + 1), 0.8)
+        for t in range(n):
+            rt[t] = [int(v) for v in rng.choice(n_exp, size=k, replace=False, p=pw / pw.sum())]
+    rw = [[0.1 + 0.2 * ((t * 7 + kk * 3) % 5) / 5 for kk in range(len(rt[t]))] for t in range(n)]
+    offs, tok, wt = [0] * (n_exp + 1), [], []
+    slot_of = -np.ones(n * k, dtype=np.int32)
+    for j in range(n_exp):
+        offs[j] = len(tok)
+        for t in range(n):
+            for kk, e in enumerate(rt[t]):
+                if e == j:
+                    slot_of[t * k + kk] = len(tok)
+                    tok.append(t)
+                    wt.append(rw[t][kk])
+    offs[n_exp] = len(tok)
+    return offs, np.array(tok, np.int32), np.array(wt, np.float32), slot_of
+
+
+# (gate/up type, down type, shared type, n, k, n_exp, shared, routing, tokens checked (0 = all), dim, inter)
+# The first three cases use the reference's layer shape (5120 / 2304); the many-expert routings run on a smaller layer so
+# that the CPU reference stays cheap (the contraction still spans 16 / 8 K-blocks and several weight-row tiles).
+CASES = [
+    (ol.IQ1_S, ol.IQ1_S, ol.Q6_K, 80, 2, 5, True, "popular", 0, 5120, 2304),
+    (ol.IQ2_XXS, ol.IQ2_XXS, ol.Q8_0, 70, 2, 4, True, "popular", 0, 5120, 2304),
+    (ol.IQ1_S, ol.IQ2_XXS, ol.Q6_K, 40, 3, 4, False, "popular", 0, 5120, 2304),
+    (ol.IQ1_S, ol.IQ1_S, ol.Q6_K, 600, 6, 20, True, "sizes", 40, 1024, 512),
+    (ol.IQ2_XXS, ol.IQ1_S, ol.Q8_0, 256, 6, 64, True, "zipf", 40, 1024, 512),
+    (ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, 300, 8, 12, True, "zipf", 30, 4096, 2048),      # the benchmark's layer shape
+]
+
+
+@pytest.mark.parametrize("c", CASES, ids=lambda c: "%s-%s-%s-n%d-k%d-e%d-%s" % (ol.TYPE_NAMES[c[0]], ol.TYPE_NAMES[c[1]], ol.TYPE_NAMES[c[2]], c[3], c[4], c[5], c[7]))
+def test_moe_prefill_reference_cases(orc, c):
+    from macseek_b200 import quant as q
+    from macseek_b200.core import Enc
+    gu, dn, sh, n, k, n_exp, shared, kind, n_check, D, I = c
+    offs, tok, wt, slot_of = make_routing(kind, n, k, n_exp, 42 + n)
+    total = offs[-1]
+    ne_all = n_exp + (1 if shared else 0)
+    G, U, Dn = [], [], []
+    for j in range(ne_all):
+        tg, td = (sh, sh) if j == n_exp else (gu, dn)
+        G.append(synth.random_weights(tg, I, D, 500 + 3 * j))
+        U.append(synth.random_weights(tg, I, D, 501 + 3 * j))
+        Dn.append(synth.random_weights(td, D, I, 502 + 3 * j))
+    X = synth.randn(n * D, 9).reshape(n, D)
+    Y0 = synth.randn(n * D, 10).reshape(n, D)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    a = q.MoePrefillArgs(D, I)
+    a.t_gate_up, a.t_down, a.t_shared = gu, dn, sh
+    a.n_tokens, a.k_per_token, a.has_shared = n, k, shared
+    keep = []
+    for j in range(ne_all):
+        s = q.ExpertSlot()
+        s.gate, s.up, s.down = dev(G[j]), dev(U[j]), dev(Dn[j])
+        keep.append(s)
+        if j == n_exp:
+            a.shared = s
+        else:
+            a.slots.append(s)
+    a.offs = offs
+    a.tok, a.wt, a.slot_of = dev(tok), dev(wt), dev(slot_of)
+    a.X = dev(X)
+    a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(total, n, n_exp, D, I), dtype=torch.uint8, device="cuda")
+    e = Enc()
+    outs = []
+    for _ in range(2):
+        a.Y = dev(Y0)
+        q.encode_moe_prefill(e, a)
+        e.wait()
+        outs.append(a.Y.cpu().numpy())
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32)), "repeat differs"
+    got = outs[0].astype(np.float64)
+    # tokens to check
+    if n_check <= 0:
+        chk = list(range(n))
+    else:
+        on = np.zeros(n, bool)
+        for j in range(n_exp):
+            if offs[j + 1] - offs[j] <= 2:
+                on[tok[offs[j]:offs[j + 1]]] = True
+        for t in (0, 15, 16, 31, 32, 47, 48, 63, 64, 65, 127, 128, 511, 512, 513, n - 1):
+            if t < n:
+                on[t] = True
+        on[np.random.default_rng(1).integers(0, n, n_check)] = True
+        chk = [t for t in range(n) if on[t]]
+    ci = -np.ones(n, dtype=np.int64)
+    ci[chk] = np.arange(len(chk))
+    yh = Y0[chk].astype(np.float64)
+    yf = yh.copy()
+    ym = np.abs(yh)
+    for j in range(ne_all):
+        if j == n_exp:
+            toks, ws = np.array(chk), np.ones(len(chk))
+        else:
+            ent = [i for i in range(offs[j], offs[j + 1]) if ci[tok[i]] >= 0]
+            toks, ws = tok[ent], wt[ent].astype(np.float64)
+        if len(toks) == 0:
+            continue
+        tg, td = (sh, sh) if j == n_exp else (gu, dn)
+        wg = orc.dequant(tg, G[j], I * D).reshape(I, D).astype(np.float64)
+        wu = orc.dequant(tg, U[j], I * D).reshape(I, D).astype(np.float64)
+        wd = orc.dequant(td, Dn[j], I * D).reshape(D, I).astype(np.float64)
+        for hv in (0, 1):
+            xin = X[toks].astype(np.float64)
+            if hv:
+                xin = r16(xin)
+            g = xin @ (r16(wg) if hv else wg).T
+            u = xin @ (r16(wu) if hv else wu).T
+            gg = np.minimum(g, 10.0)
+            uu = np.clip(u, -10.0, 10.0)
+            h = (gg / (1 + np.exp(-gg)) * uu * ws[:, None]).astype(np.float32).astype(np.float64)
+            if hv:
+                h = r16(h)
+            wdd = r16(wd) if hv else wd
+            o = h @ wdd.T
+            if hv:
+                yh[ci[toks]] += o
+                ym[ci[toks]] += np.abs(h) @ np.abs(wdd).T
+            else:
+                yf[ci[toks]] += o
+    err_h = float(np.max(np.abs(got[chk] - yh) / (ym + 1e-9)))
+    err_f = float(np.max(np.abs(got[chk] - yf) / (ym + 1e-9)))
+    assert np.all(np.isfinite(got))
+    assert err_h <= 1e-3, (err_h, err_f)
+    assert err_f <= 5e-3, (err_h, err_f)
+    # tokens the reference check did not look at must at least have moved from Y0 when they have any expert
+    assert not np.array_equal(outs[0], Y0)
