@@ -331,7 +331,7 @@ def run_ours(a):
         token_bytes = lb["total"] * cfg.n_layers + cfg.head_bytes()
         line = {"metric": METRIC, "value": a.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": a.steps,
                 "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "u8 codes x int16 fixed-point activations (dp4a), f32 accumulate; fp8/bf16 mma for attention",
+                "vs_baseline": None, "dtype": "u8 codes x int16 fixed-point activations (dp4a), f32 accumulate; fp8 tcgen05 (indexer) and bf16 mma (attention)",
                 "data": "synthetic", "config": workload_config(a, world),
                 "e2e": {"value": a.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": cfg.dim * 4,
                         "d2h_bytes_per_step": 4},

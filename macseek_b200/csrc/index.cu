@@ -487,22 +487,22 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
   __shared__ unsigned long long c2[1024];
   __shared__ unsigned s_cnt, s_c2, s_need, s_digit;
   extern __shared__ unsigned bitmap[];          // bm_words words when the bitmap path is used (n <= 32 * bm_words)
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, NT = blockDim.x;   // any multiple of 32 from 256 to 1024
   // chosen indices go into a bitmap of the n positions (read back in ascending order: no sort), or, for very long
   // inputs that do not fit shared memory, into buf[] which is then sorted
   auto emit = [&](unsigned idx) {
     if (bm_words) atomicOr(&bitmap[idx >> 5], 1u << (idx & 31));
     else { const unsigned pos = atomicAdd(&s_cnt, 1u); if (pos < 2048u) buf[pos] = (int)idx; }
   };
-  for (int i = tid; i < bm_words; i += 1024) bitmap[i] = 0;
+  for (int i = tid; i < bm_words; i += NT) bitmap[i] = 0;
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
   const unsigned n_sel = *reinterpret_cast<volatile unsigned*>(&ctl->n_sel);
   const unsigned n_cand = *reinterpret_cast<volatile unsigned*>(&ctl->n_cand);
-  for (int i = tid; i < 2048; i += 1024) buf[i] = 0x7fffffff;
+  for (int i = tid; i < 2048; i += NT) buf[i] = 0x7fffffff;
   if (tid == 0) { s_cnt = 0; s_c2 = 0; }
   __syncthreads();
-  for (unsigned i = tid; i < n_sel && i < 2048u; i += 1024) emit((unsigned)__ldcg(sel + i));
+  for (unsigned i = tid; i < n_sel && i < 2048u; i += NT) emit((unsigned)__ldcg(sel + i));
   if (bstar >= 0 && n_cand > 0) {
     const unsigned need = (unsigned)k - above;   // how many of the threshold bin's members are taken
     unsigned above2;
@@ -511,7 +511,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
     if (fstar >= 0 && m2 <= 1024u) {
       const unsigned need2 = need - above2;
 #pragma unroll 4
-      for (unsigned i = tid; i < n_cand; i += 1024) {
+      for (unsigned i = tid; i < n_cand; i += NT) {
         const uint2 cd = __ldcg(cand + i);
         const unsigned idx = cd.x;
         const uint32_t key = cd.y;
@@ -525,8 +525,8 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
       }
       __syncthreads();
       const unsigned m = min(s_c2, 1024u);
-      if ((unsigned)tid < m) {
-        const unsigned long long mine = c2[tid];
+      for (unsigned e2 = tid; e2 < m; e2 += NT) {
+        const unsigned long long mine = c2[e2];
         unsigned rank = 0;
         for (unsigned j = 0; j < m; j++) rank += c2[j] < mine;
         if (rank < need2) emit((unsigned)(mine & 0xFFFFFFFFu));
@@ -538,9 +538,9 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
       for (int shift = 12; shift >= -4; shift -= 8) {
         const int sft = shift < 0 ? 0 : shift;
         const unsigned dmask = shift < 0 ? 0xFu : 0xFFu;
-        for (int b = tid; b < 256; b += 1024) sh[b] = 0;
+        for (int b = tid; b < 256; b += NT) sh[b] = 0;
         __syncthreads();
-        for (unsigned i = tid; i < n_cand; i += 1024) {
+        for (unsigned i = tid; i < n_cand; i += NT) {
           const unsigned key = __ldcg(cand + i).y & 0xFFFFFu;
           if ((key & mask) == prefix) atomicAdd(&sh[(key >> sft) & dmask], 1u);
         }
@@ -564,9 +564,9 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
       // ties at T: take the `remaining` lowest indices.  Radix select (ascending) on the index, 3 x 8 bits (n <= 2^24).
       unsigned ip = 0, im = 0, irem = remaining;
       for (int shift = 16; shift >= 0; shift -= 8) {
-        for (int b = tid; b < 256; b += 1024) sh[b] = 0;
+        for (int b = tid; b < 256; b += NT) sh[b] = 0;
         __syncthreads();
-        for (unsigned i = tid; i < n_cand; i += 1024) {
+        for (unsigned i = tid; i < n_cand; i += NT) {
           const uint2 cd = __ldcg(cand + i);
           if ((cd.y & 0xFFFFFu) == T && (cd.x & im) == ip) atomicAdd(&sh[(cd.x >> shift) & 0xFFu], 1u);
         }
@@ -587,7 +587,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
         __syncthreads();
       }
       const unsigned idxT = ip;          // members equal to T with index <= idxT are taken
-      for (unsigned i = tid; i < n_cand; i += 1024) {
+      for (unsigned i = tid; i < n_cand; i += NT) {
         const uint2 cd = __ldcg(cand + i);
         const unsigned idx = cd.x;
         const unsigned key = cd.y & 0xFFFFFu;
@@ -600,7 +600,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
   if (bm_words) {
     // ascending read-out: every thread owns a contiguous run of bitmap words; an exclusive scan of the run
     // populations gives each run its offset in the output
-    const int per = (bm_words + 1023) / 1024;
+    const int per = (bm_words + NT - 1) / NT;
     const int w0 = min(bm_words, tid * per), w1 = min(bm_words, w0 + per);
     unsigned cnt = 0;
     for (int w = w0; w < w1; w++) cnt += __popc(bitmap[w]);
@@ -615,7 +615,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
         pos++;
       }
     }
-    for (int i = tid + (int)min(total, (unsigned)k); i < k; i += 1024) out[i] = -1;
+    for (int i = tid + (int)min(total, (unsigned)k); i < k; i += NT) out[i] = -1;
   } else {
     const unsigned filled = min(s_cnt, 2048u);
     // bitonic sort of the used power-of-two prefix, ascending (unused slots hold INT_MAX)
@@ -623,7 +623,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
     while (P < (int)filled) P <<= 1;
     for (int size = 2; size <= P; size <<= 1)
       for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        for (int i = tid; i < P / 2; i += 1024) {
+        for (int i = tid; i < P / 2; i += NT) {
           const int lo = 2 * i - (i & (stride - 1));
           const int hi = lo + stride;
           const bool up = ((lo & size) == 0);
@@ -632,9 +632,9 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
         }
         __syncthreads();
       }
-    for (int i = tid; i < k; i += 1024) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
+    for (int i = tid; i < k; i += NT) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
   }
-  for (int b = tid; b < kHistBins; b += 1024) { hist[b] = 0; fine[b] = 0; }
+  for (int b = tid; b < kHistBins; b += NT) { hist[b] = 0; fine[b] = 0; }
   if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; ctl->ticket = 0; }
   (void)n;
 }
@@ -681,9 +681,11 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   }
   static const int fused = getenv("MSB_TOPK_FUSED") ? atoi(getenv("MSB_TOPK_FUSED")) : 1;   // tuning probe
   static const int env_blocks = getenv("MSB_TOPK_BLOCKS") ? atoi(getenv("MSB_TOPK_BLOCKS")) : 0;
+  static const int env_threads = getenv("MSB_TOPK_THREADS") ? atoi(getenv("MSB_TOPK_THREADS")) : 0;
+  const int nthreads = (env_threads == 256 || env_threads == 512) ? env_threads : 1024;
   // one element per thread and up to two blocks per SM: the per-block fixed work (threshold, fine histogram) is small
   // next to the latency of a longer per-thread loop
-  int blocks = std::max(1, std::min(2 * sms, (n + 1023) / 1024));
+  int blocks = std::max(1, std::min(2 * sms * (1024 / nthreads), (n + nthreads - 1) / nthreads));
   if (env_blocks) blocks = std::max(1, std::min(env_blocks, (n + 1023) / 1024));
   // staging of a block's picks: per_block ints + per_block (index, key) pairs; blocks are added until that fits
   auto stage_of = [&](int nb) { const size_t pb = ((size_t)n + nb - 1) / nb; return ((pb + 1) & ~(size_t)1) * 4 + pb * 8 + 16; };
@@ -691,10 +693,10 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   const size_t stage_bytes = stage_of(blocks);
   if (n > 0 && !hist_ready) MSB_CUDA(launch_pdl(topk_hist_kernel, dim3(std::max(1, std::min(sms * 2, (n + 1023) / 1024))), dim3(256), 0, st, sc, n, hist));
   if (fused) {
-    MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), std::max((size_t)bm_words * 4, stage_bytes), st, sc, n, k, hist,
+    MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(nthreads), std::max((size_t)bm_words * 4, stage_bytes), st, sc, n, k, hist,
                         fine, ctl, sel, cand, out, bm_words, 1));
   } else {
-    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(1024), stage_bytes, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0));
+    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(nthreads), stage_bytes, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0));
     MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl,
                         (const int*)sel, (const uint2*)cand, out, bm_words));
   }

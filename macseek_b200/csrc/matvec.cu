@@ -16,6 +16,7 @@
 namespace msb {
 
 constexpr int kMvNW = 16;
+constexpr size_t kLightSmemLimit = 110 * 1024;   // a light block's shared memory: two fit one SM
 
 struct MvParams {
   const uint8_t* W;
@@ -49,9 +50,12 @@ struct MvSmemHead {
   float part[2][kMvNW][4];
 };
 
-template <int T, int LPR, int NR, int NC>
-__global__ void __launch_bounds__((kMvNW + 1) * 32, 1) matvec_kernel(const MvParams p) {
-  constexpr int NW = kMvNW;
+// NW consumer warps + 1 producer warp.  NW = 16: one block per SM with most of its shared memory (long streams).
+// NW = 8: a light block (at most half an SM's shared memory and registers) so that two are resident per SM -- two of
+// this launch, or the tail of this launch and the head of the next, whose producer warps then prefetch their first
+// tiles while the previous kernel is still running (programmatic dependent launch).
+template <int T, int LPR, int NR, int NC, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, NW == 8 ? 2 : 1) matvec_kernel(const MvParams p) {
   constexpr int G = 32 / LPR;
   pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t smem[];
@@ -217,11 +221,11 @@ namespace {
 // lanes per row: of 32/16/8 the one that wastes the fewest lane iterations on `items` work items per row, among
 // those whose smallest whole-row tile (16 warps x 32/lpr rows) fits `tile_cap` bytes; 32 when none does (long rows
 // are then shared by several warps or streamed in chunks)
-int pick_lpr(int items, size_t row_bytes, size_t tile_cap) {
+int pick_lpr(int items, size_t row_bytes, size_t tile_cap, int nw) {
   int best = 32;
   double best_eff = 0;
   for (int lpr : {32, 16, 8}) {
-    if (lpr < 32 && (size_t)kMvNW * (32 / lpr) * row_bytes + 192 > tile_cap) continue;
+    if (lpr < 32 && (size_t)nw * (32 / lpr) * row_bytes + 192 > tile_cap) continue;
     const int iters = (items + lpr - 1) / lpr;
     const double eff = (double)items / (iters * lpr);
     if (eff > best_eff + 1e-9) { best_eff = eff; best = lpr; }
@@ -229,10 +233,10 @@ int pick_lpr(int items, size_t row_bytes, size_t tile_cap) {
   return best;
 }
 
-template <int T, int LPR, int NR, int NC>
+template <int T, int LPR, int NR, int NC, int NW>
 int launch_cfg(MvParams& p, size_t fixed, int stages, size_t slot_bytes, cudaStream_t st, int dev) {
   const size_t smem = fixed + (size_t)stages * slot_bytes;
-  auto kern = matvec_kernel<T, LPR, NR, NC>;
+  auto kern = matvec_kernel<T, LPR, NR, NC, NW>;
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
     MSB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
@@ -240,22 +244,25 @@ int launch_cfg(MvParams& p, size_t fixed, int stages, size_t slot_bytes, cudaStr
   }
   p.stages = stages;
   p.stage_bytes = (uint32_t)slot_bytes;
-  MSB_CUDA(launch_pdl(kern, dim3(p.blocks_per_group * p.groups), dim3((kMvNW + 1) * 32), smem, st, p));
+  MSB_CUDA(launch_pdl(kern, dim3(p.blocks_per_group * p.groups), dim3((NW + 1) * 32), smem, st, p));
   MSB_LAUNCH_CHECK("matvec_kernel");
   return kOk;
 }
 
 // Tile shape: as many consecutive whole rows as fit one ring slot (one contiguous copy), bounded by what the type's
 // decode cost warrants and by the need to spread the matrix over every SM.
-template <int T, int LPR, int NC>
-int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
+template <int T, int LPR, int NC, int NW>
+int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms_real) {
+  // light blocks: two per SM, each within half of the SM's shared memory
+  const int sms = NW == 8 ? 2 * sms_real : sms_real;
+  const size_t smem_limit = NW == 8 ? kLightSmemLimit : (size_t)kSmemLimit;
   constexpr int G = 32 / LPR;
   constexpr int kMaxNR = (T == IQ1_S || T == IQ2_XXS) ? 4 : 2;
   const size_t fixed = ((sizeof(MvSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(T) +
                        (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 128;
-  if (fixed + 2 * 8192 > (size_t)kSmemLimit)
+  if (fixed + 2 * 8192 > smem_limit)
     return fail(kErrLimit, "matvec: cols %d x n %d does not fit in shared memory", p.cols, p.n);
-  const size_t avail = (size_t)kSmemLimit - fixed;
+  const size_t avail = smem_limit - fixed;
   // tuning probes: cap the slot size (KB) / the ring depth
   static const int env_slot = getenv("MSB_MV_SLOT_KB") ? atoi(getenv("MSB_MV_SLOT_KB")) : 0;
   static const int env_stages = getenv("MSB_MV_STAGES") ? std::min(kMaxStages, std::max(2, atoi(getenv("MSB_MV_STAGES")))) : 0;
@@ -274,13 +281,14 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
     // whole rows per warp (KS = 1, R = 16 * G * NR), largest first
     for (int cand : {4, 2, 1}) {
       if (cand > kMaxNR || (NC > 1 && cand > 2) || (T == Q6_K && NC > 2 && cand > 1)) continue;
-      const int r = kMvNW * G * cand;
+      const int r = NW * G * cand;
       if (r <= rows_fit && (tiles_of(r) >= want_tiles || cand == 1)) { R = r; nr = cand; break; }
     }
     // several warps per row when whole-row tiles do not fit or leave SMs idle
     if (LPR == 32 && (R == 0 || tiles_of(R) < want_tiles)) {
       for (int cand : {2, 4, 8, 16}) {
-        const int r = kMvNW / cand;
+        if (cand > NW) break;
+        const int r = NW / cand;
         if (r > rows_fit) continue;
         R = r; ks = cand; nr = 1;
         if (tiles_of(r) >= want_tiles) break;
@@ -288,7 +296,7 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
     }
     if (R == 0) {   // LPR < 32 and the smallest whole-row tile does not fit: per-row chunks instead
       nr = 1; ks = 1;
-      R = kMvNW * G;
+      R = NW * G;
       stages = 3;
       slot = std::min(slot, (avail / 3) & ~(size_t)127);
       const int chunk = chunk_units_for(T, p.units, R, LPR, slot);
@@ -299,10 +307,10 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
   } else {
     // one row does not fit a slot: all 16 warps share a row, K streamed in chunks (one large copy each)
     if (LPR != 32) return fail(kErrLimit, "matvec: row of %u bytes does not fit (type %s)", p.row_bytes, type_name(T));
-    ks = kMvNW; nr = 1; R = 1;
+    ks = NW; nr = 1; R = 1;
     stages = 3;
     slot = std::min(slot, (avail / 3) & ~(size_t)127);
-    const int chunk = chunk_units_for(T, p.units, 1, 32 * kMvNW, slot);
+    const int chunk = chunk_units_for(T, p.units, 1, 32 * NW, slot);
     if (chunk <= 0) return fail(kErrLimit, "matvec: no staging shape fits (type %s cols %d)", type_name(T), p.cols);
     p.chunk_units = chunk;
     p.pitch = piece_pitch(units_bytes(T, chunk));
@@ -318,21 +326,39 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms) {
   p.tiles_per_group = tiles_of(R);
   p.blocks_per_group = std::max(1, std::min(p.tiles_per_group, sms / p.groups));
   if (nr >= 4) {
-    if constexpr (kMaxNR >= 4 && NC == 1) return launch_cfg<T, LPR, 4, NC>(p, fixed, stages, slot, st, dev);
+    if constexpr (kMaxNR >= 4 && NC == 1) return launch_cfg<T, LPR, 4, NC, NW>(p, fixed, stages, slot, st, dev);
   }
-  if (nr >= 2) return launch_cfg<T, LPR, 2, NC>(p, fixed, stages, slot, st, dev);
-  return launch_cfg<T, LPR, 1, NC>(p, fixed, stages, slot, st, dev);
+  if (nr >= 2) return launch_cfg<T, LPR, 2, NC, NW>(p, fixed, stages, slot, st, dev);
+  return launch_cfg<T, LPR, 1, NC, NW>(p, fixed, stages, slot, st, dev);
 }
 
 template <int T, int NC>
 int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
-  // Q6_K rows are split by half super-block (4 units), the other types by unit
+  // Light blocks for matrices whose per-SM share is small next to the fixed cost of a launch (the layer's projections;
+  // not the output head): only for the table-free types and a single activation column.
+  static const int env_light = getenv("MSB_MV_LIGHT") ? atoi(getenv("MSB_MV_LIGHT")) : -1;   // tuning probe
+  bool light = false;
+  if constexpr (NC == 1 && lut_bytes_for(T) == 0) {
+    const size_t total = (size_t)p.rows_per_group * p.groups * p.row_bytes;
+    light = env_light < 0 ? total <= (size_t)96 << 20 : env_light != 0;
+    const size_t fixed_l = (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 1024;
+    if (fixed_l + 2 * 16384 > kLightSmemLimit) light = false;
+    if (light) {
+      const size_t cap = (kLightSmemLimit - fixed_l) / 2;
+      // Q6_K rows are split by half super-block (4 units), the other types by unit
+      switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, cap, 8)) {
+        case 32: return launch_rows<T, 32, NC, 8>(p, st, dev, sms);
+        case 16: return launch_rows<T, 16, NC, 8>(p, st, dev, sms);
+        default: return launch_rows<T, 8, NC, 8>(p, st, dev, sms);
+      }
+    }
+  }
   const size_t fixed = lut_bytes_for(T) + (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 1024;
   const size_t tile_cap = fixed < (size_t)kSmemLimit ? ((size_t)kSmemLimit - fixed) / 2 : 0;
-  switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, tile_cap)) {
-    case 32: return launch_rows<T, 32, NC>(p, st, dev, sms);
-    case 16: return launch_rows<T, 16, NC>(p, st, dev, sms);
-    default: return launch_rows<T, 8, NC>(p, st, dev, sms);
+  switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, tile_cap, kMvNW)) {
+    case 32: return launch_rows<T, 32, NC, kMvNW>(p, st, dev, sms);
+    case 16: return launch_rows<T, 16, NC, kMvNW>(p, st, dev, sms);
+    default: return launch_rows<T, 8, NC, kMvNW>(p, st, dev, sms);
   }
 }
 

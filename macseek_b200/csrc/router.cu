@@ -96,6 +96,16 @@ __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p)
     a[k] = (live && c < slice / 4) ? __ldg(w + c) : zero4;
   }
   pdl_wait();
+  // this unit's slice of x (and of the norm gain) is requested before the norm's reduction, not after it
+  const float4* xv = reinterpret_cast<const float4*>(p.x + (size_t)ks * slice);
+  const float4* gv = reinterpret_cast<const float4*>(p.norm_w ? p.norm_w + (size_t)ks * slice : p.x);
+  float4 b[8], g8[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const int c = lane + 32 * k;
+    b[k] = (live && c < slice / 4) ? xv[c] : zero4;
+    g8[k] = (live && p.norm_w && c < slice / 4) ? __ldg(gv + c) : zero4;
+  }
   float mul = 1.f;
   if (p.norm_w) {   // every block needs 1/rms of the whole vector: dim floats from L2, summed in a fixed order
     __shared__ float red[8];
@@ -113,19 +123,19 @@ __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p)
     mul = rsqrtf(tot / (float)p.dim + p.norm_eps);
   }
   if (live) {
-    const float4* xv = reinterpret_cast<const float4*>(p.x + (size_t)ks * slice);
-    const float4* gv = reinterpret_cast<const float4*>(p.norm_w ? p.norm_w + (size_t)ks * slice : p.x);
     float acc = 0.f;
     for (int c0 = lane; c0 < slice / 4; c0 += 32 * 8) {   // 8 independent 16-byte loads in flight per lane
-      float4 b[8];
 #pragma unroll
       for (int k = 0; k < 8; k++) {
         const int c = c0 + 32 * k;
-        if (c0 != lane) a[k] = c < slice / 4 ? __ldg(w + c) : zero4;
-        b[k] = c < slice / 4 ? xv[c] : zero4;
+        if (c0 != lane) {
+          a[k] = c < slice / 4 ? __ldg(w + c) : zero4;
+          b[k] = c < slice / 4 ? xv[c] : zero4;
+          g8[k] = (p.norm_w && c < slice / 4) ? __ldg(gv + c) : zero4;
+        }
         if (p.norm_w && c < slice / 4) {
-          const float4 g = __ldg(gv + c);
-          b[k].x = b[k].x * mul * g.x; b[k].y = b[k].y * mul * g.y; b[k].z = b[k].z * mul * g.z; b[k].w = b[k].w * mul * g.w;
+          b[k].x = b[k].x * mul * g8[k].x; b[k].y = b[k].y * mul * g8[k].y;
+          b[k].z = b[k].z * mul * g8[k].z; b[k].w = b[k].w * mul * g8[k].w;
           if (e == 0 && p.x_out) reinterpret_cast<float4*>(p.x_out + (size_t)ks * slice)[c] = b[k];
         }
       }

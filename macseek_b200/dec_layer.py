@@ -163,7 +163,7 @@ class SyntheticModel:
         q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_qb, c.index_heads * c.index_dim, c.q_lora, b.qa, w.q_norm,
                                 c.norm_eps, b.iq); n += 1
         attn.encode_kv_window(e, st, b.kv, w.kv_norm, pos); n += 1
-        attn.encode_index_decode(e, st, b.iq, b.iw, pos, c.kv_len, actq=False); n += 4
+        attn.encode_index_decode(e, st, b.iq, b.iw, pos, c.kv_len, actq=False); n += 2   # tcgen05 scoring (+ prep), selection
         attn.encode_sparse(e, st, b.qfull, w.sinks, b.attn_out, pos); n += 2
         q.encode_matvec(e, c.t_attn, w.wo_a, c.o_a_rows, c.heads * c.D // c.o_groups, b.attn_out, b.oa, False,
                         c.o_groups); n += 1
@@ -178,20 +178,19 @@ class SyntheticModel:
             ml.encode_moe_layer(e, w.moe, b.moe, b.x, b.h, c.score_fn, c.route_scale, norm_in=b.h, norm_w=w.ffn_norm,
                                 norm_eps=c.norm_eps); n += 3
             return n
-        # expert parallel: router and shared expert replicated (h += shared(x) locally), routed partial sums of the
-        # local experts combined over NVLink
+        # expert parallel: the router is replicated (every rank sees the same ids), partial sums combined over NVLink
         arch.encode_router_fused_rmsnorm(e, b.h, w.ffn_norm, c.norm_eps, b.x, w.moe.router_w, w.moe.router_bias,
                                          b.moe.ids, b.moe.w, b.moe.router_scratch, c.top_k, c.score_fn,
                                          c.route_scale); n += 1
+        # One gate/up + down launch pair per rank into a zeroed partial: the routed experts resident here, plus the
+        # (replicated) shared expert on rank 0 only, so that the sum over ranks counts it once.
         a = q.MoeDecodeArgs(c.dim, c.inter)
         a.t_gate_up, a.t_down, a.t_shared = c.t_gate_up, c.t_down, c.t_shared
-        a.n_routed, a.has_shared, a.shared = c.top_k, True, w.moe.shared
+        a.n_routed, a.has_shared, a.shared = c.top_k, self.ep_rank == 0, w.moe.shared
         a.weights, a.x, a.scratch = b.moe.w, b.x, b.moe.moe_scratch
-        a.y = b.h
-        q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.Shared); n += 2
         b.y_part.zero_()
         a.y = b.y_part
-        q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.Routed); n += 2
+        q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.All); n += 2
         ep.combine_routed(b.y_part, self.group)
         arch.encode_add(e, b.h, b.y_part, c.dim); n += 2
         return n

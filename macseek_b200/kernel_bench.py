@@ -5,6 +5,7 @@
     python -m macseek_b200.kernel_bench attn {index|scores|topk|sparse|all} [--kv-len 200000]
     python -m macseek_b200.kernel_bench gemm Q6_K 4096 4096 --n 4096
     python -m macseek_b200.kernel_bench moe_prefill [--n 4096]
+    python -m macseek_b200.kernel_bench layer            # cost added by each call of the decode layer, in context
     python -m macseek_b200.kernel_bench sweep
 
 Each case builds synthetic weights on the device (several copies, together larger than the 126 MB L2, used in
@@ -264,6 +265,71 @@ def moe_prefill_case(n: int = 4096, eager: int = 0):
           flush=True)
 
 
+def layer_stages(n_layers: int = 8, kv_len: int = 200000):
+    """The decode layer in context: CUDA graphs of n_layers layers cut after the first k calls of each layer, k = 1 ..;
+    the difference between consecutive cuts is what call k adds per layer with all overlaps as in the real step."""
+    from . import dec_layer as dl
+    cfg = dl.DecConfig(n_layers=n_layers, kv_len=kv_len)
+    model = dl.SyntheticModel(cfg, seed=1234, device=torch.device("cuda", torch.cuda.current_device()))
+    limit, count, names = [10 ** 9], [0], []
+
+    def wrap(mod, name):
+        f = getattr(mod, name)
+
+        def g(*a, **k):
+            count[0] += 1
+            if count[0] > limit[0]:
+                return None
+            if len(names) < count[0]:
+                names.append(name)
+            return f(*a, **k)
+        setattr(mod, name, g)
+        return f
+    saved = [(mod, nm, wrap(mod, nm)) for mod, nm in (
+        (q, "encode_matvec_rmsnorm"), (q, "encode_matvec"), (attn, "encode_kv_window"), (attn, "encode_index_decode"),
+        (attn, "encode_sparse"), (arch, "encode_router_fused_rmsnorm"), (q, "encode_moe_decode_ids"))]
+    stream = torch.cuda.Stream()
+
+    def encode(e):
+        for l in range(n_layers):
+            count[0] = 0
+            model.encode_dec_attn_side(e, l, cfg.kv_len - 1)
+            model.encode_dec_moe(e, l)
+
+    def run_cut(lim):
+        limit[0] = lim
+        with torch.cuda.stream(stream):
+            model.bufs.h.normal_(0, 1)
+            encode(Enc(stream))
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                encode(Enc(torch.cuda.current_stream()))
+            for _ in range(3):
+                g.replay()
+            stream.synchronize()
+            ts = []
+            for _ in range(7):
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(stream)
+                g.replay()
+                a1.record(stream)
+                stream.synchronize()
+                ts.append(a0.elapsed_time(a1) * 1e3 / n_layers)
+            ts.sort()
+            return ts[len(ts) // 2]
+    try:
+        run_cut(10 ** 9)
+        prev = 0.0
+        for lim in range(1, len(names) + 1):
+            t = run_cut(lim)
+            print(f"{lim:2d} {names[lim - 1]:28s} cumulative {t:8.2f} us/layer   +{t - prev:7.2f}", flush=True)
+            prev = t
+    finally:
+        for mod, nm, f in saved:
+            setattr(mod, nm, f)
+
+
 def sweep():
     T = q.QType
     moe_cases("every")
@@ -281,7 +347,7 @@ def sweep():
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "sweep"])
+    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "layer", "sweep"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--groups", type=int, default=1)
@@ -293,6 +359,8 @@ def main():
         matvec_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n, a.groups, a.eager)
     elif a.case == "moe":
         moe_cases(a.args[0] if a.args else "every", a.eager)
+    elif a.case == "layer":
+        layer_stages(8, a.kv_len)
     elif a.case == "moe_prefill":
         moe_prefill_case(a.n if a.n > 1 else 4096, a.eager)
     elif a.case == "gemm":

@@ -1,6 +1,7 @@
-"""Expert-parallel host logic on CPU: two gloo ranks each evaluate (with the oracle) only the routed experts they hold,
-sum their partial outputs through macseek_b200.ep.combine_routed, and must reproduce the single-rank oracle result.
-Mirrors what the GPU ranks do per layer (router + shared expert replicated, routed partials all-reduced)."""
+"""Expert-parallel host logic on CPU: two gloo ranks each evaluate (with the oracle) only the routed experts they hold
+(rank 0 also the replicated shared expert), sum their partial outputs through macseek_b200.ep.combine_routed, and must
+reproduce the single-rank oracle result.  Mirrors what the GPU ranks do per layer (router replicated, one partial per
+rank all-reduced and added to the hidden state)."""
 import os
 import socket
 
@@ -47,16 +48,17 @@ def _rank_main(rank, world, port, out):
         ids, w = orc.router(logits, np.zeros(E, np.float32), K, score_fn=1, route_scale=1.0)   # replicated
         lo, hi = ep.expert_range(E, world, rank)
         mine = ep.local_slots(ids, lo, hi)
-        # routed experts resident here, into a zero partial
-        _, part, _, _ = orc.moe_decode(D, I, ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, [G[ids[k]] for k in mine],
-                                       [U[ids[k]] for k in mine], [Dn[ids[k]] for k in mine], w[mine] if mine else None,
-                                       x, np.zeros(D), has_shared=False)
+        # routed experts resident here -- and, on rank 0 only, the replicated shared expert -- into a zero partial
+        mats = [ids[k] for k in mine]
+        gg, uu, dd = [G[m] for m in mats], [U[m] for m in mats], [Dn[m] for m in mats]
+        with_shared = rank == 0
+        if with_shared:
+            gg, uu, dd = gg + [sh[0]], uu + [sh[1]], dd + [sh[2]]
+        _, part, _, _ = orc.moe_decode(D, I, ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, gg, uu, dd, w[mine] if mine else None,
+                                       x, np.zeros(D), has_shared=with_shared)
         t = torch.from_numpy(np.asarray(part, dtype=np.float64))
         ep.combine_routed(t)
-        # shared expert replicated: every rank adds it to its copy of the hidden state
-        _, y_sh, _, _ = orc.moe_decode(D, I, ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, [sh[0]], [sh[1]], [sh[2]], None, x, y0,
-                                       has_shared=True)
-        y = y_sh + t.numpy()
+        y = np.asarray(y0, dtype=np.float64) + t.numpy()       # every rank adds the combined partial to its hidden state
         gathered = [torch.zeros(D, dtype=torch.float64) for _ in range(world)]
         dist.all_gather(gathered, torch.from_numpy(y))
         if rank == 0:
