@@ -198,6 +198,14 @@ int msb_block_max(const float* scores, int len, int bs, float* out, void* stream
 int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw, const float* w_raw, const float* cs,
                      int actq, int heads, int k, float* q_prep, float* w_prep, float* scores, int* topk_out,
                      void* topk_scratch, size_t topk_scratch_bytes, int exact_query, void* stream);
+/* The candidate-restricted form of encode_index_decode (layers that "use candidates", src/kernels/attn.mm:226-229, kernel
+ * attn_idx_score_dec2_list, attn_index.metal:1056-1112): only the keys of the key blocks in cand_list (8 keys per block,
+ * ascending block indices as msb_topk over the block maxima returns them, -1 = none) are scored; every other key counts as
+ * -inf.  scores[8 i + j] receives the score of key cand_list[i] * 8 + j; topk_out lists key indices, ascending, -1 padded.
+ * FP8 keys only. */
+int msb_index_decode_list(int key_type, const void* keys, int len, const float* q_raw, const float* w_raw, const float* cs,
+                          int actq, int heads, int k, const int* cand_list, int n_cand, float* q_prep, float* w_prep,
+                          float* scores, int* topk_out, void* topk_scratch, size_t topk_scratch_bytes, void* stream);
 
 /* ---------------------------------------------------------------- sparse attention (decode)
  * ms::attn::encode_sparse (src/kernels/attn.hpp:128-129, attn.mm:419-445); math spec tests/ref/attn_ref.cpp:204-230.

@@ -89,6 +89,7 @@ lib.msb_topk_scratch_bytes.argtypes = [_i]
 lib.msb_topk.argtypes = [_vp, _i, _i, _vp, _vp, C.c_size_t, _i, _vp]
 lib.msb_block_max.argtypes = [_vp, _i, _i, _vp, _vp]
 lib.msb_index_decode.argtypes = [_i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _vp]
+lib.msb_index_decode_list.argtypes = [_i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]
 lib.msb_sparse_scratch_bytes.restype = C.c_size_t
 lib.msb_sparse_scratch_bytes.argtypes = [_i, _i, _i]
 lib.msb_sparse_decode.argtypes = [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, C.c_size_t, _vp]

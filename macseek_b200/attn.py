@@ -100,6 +100,18 @@ def encode_index_decode(e: Enc, s: DecodeState, iq, iw, pos, length, actq=True, 
                                      s.topk_scratch.numel() * 4, 0, e.handle))
 
 
+def encode_index_decode_list(e: Enc, s: DecodeState, iq, iw, pos, length, actq=True):
+    """encode_index_decode of a layer that uses candidates (attn.mm:226-229): only the keys of the blocks in s.cand_list
+    are scored.  FP8 keys only."""
+    sh = s.shape
+    cs = s.rope[pos]
+    nb = (length + sh.cand_bs - 1) // sh.cand_bs
+    _lib.check(_lib.lib.msb_index_decode_list(sh.key_type, ptr(s.ikey), length, ptr(iq), ptr(iw), ptr(cs), int(actq),
+                                              sh.index_heads, sh.topk, ptr(s.cand_list), min(nb, sh.cand_blocks),
+                                              ptr(s.q_prep), ptr(s.w_prep), ptr(s.dec_scores), ptr(s.topk),
+                                              ptr(s.topk_scratch), s.topk_scratch.numel() * 4, e.handle))
+
+
 def encode_topk(e: Enc, scores, n, k, out, scratch):
     _lib.check(_lib.lib.msb_topk(ptr(scores), n, k, ptr(out), ptr(scratch), scratch.numel() * scratch.element_size(), 0,
                                  e.handle))

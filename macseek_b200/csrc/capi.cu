@@ -10,7 +10,8 @@ int dequant(int t, const void* src, int64_t n, float* out, cudaStream_t st);
 int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x_stride, float* Y, int64_t y_stride,
              int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st);
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
-                    int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st);
+                    int prep, const float* cs, int actq, float* q_out, float* w_out, const int* cand, int n_cand,
+                    cudaStream_t st);
 int f32_to_f16(const float* x, void* x16, size_t count, cudaStream_t st);
 size_t matmul_scratch_bytes(int t, int rows, int cols, int n, bool with_x);
 int matmul_h(int t, const void* W, int rows, int cols, const void* X16, int x_stride, float* Y, int n, bool accumulate,
@@ -43,7 +44,8 @@ int router_topk(const float* logits, const float* bias, int* ids, float* wts, in
 int route_lists(const int* ids, const float* w, int n, int k, int E, unsigned* counts, unsigned* offsets,
                 unsigned* entry, unsigned* tok, float* lw, unsigned* slot_of, cudaStream_t st);
 size_t topk_scratch_bytes(int n_max);
-int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, cudaStream_t st);
+int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, const int* pos_map,
+         cudaStream_t st);
 int index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq, int heads, float* q, float* w,
                cudaStream_t st);
 int index_scores(int key_type, const void* keys, int len, const float* q, const float* w, int heads, float* scores,
@@ -258,7 +260,7 @@ int msb_index_scores(int key_type, const void* keys, int len, const float* q, co
 size_t msb_topk_scratch_bytes(int n_max) { return topk_scratch_bytes(n_max); }
 int msb_topk(const float* scores, int n, int k, int* out, void* scratch, size_t scratch_bytes, int hist_ready,
              void* stream) {
-  return topk(scores, n, k, out, scratch, scratch_bytes, hist_ready != 0, (cudaStream_t)stream);
+  return topk(scores, n, k, out, scratch, scratch_bytes, hist_ready != 0, nullptr, (cudaStream_t)stream);
 }
 int msb_block_max(const float* scores, int len, int bs, float* out, void* stream) {
   return block_max(scores, len, bs, out, (cudaStream_t)stream);
@@ -275,7 +277,7 @@ int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw
     // tcgen05 path: the query preparation runs inside the scoring kernel (q_prep / w_prep are still written)
     if (!keys || !q_raw || !w_raw || !cs || !q_prep || !w_prep || !scores || (reinterpret_cast<uintptr_t>(keys) & 15))
       return fail(kErrArg, "index_decode: null or misaligned pointer");
-    rc = index_scores_tc(keys, len, q_raw, w_raw, heads, scores, (unsigned*)topk_scratch, 1, cs, actq, q_prep, w_prep, st);
+    rc = index_scores_tc(keys, len, q_raw, w_raw, heads, scores, (unsigned*)topk_scratch, 1, cs, actq, q_prep, w_prep, nullptr, 0, st);
   } else {
     rc = index_prep(q_raw, w_raw, cs, actq, heads, q_prep, w_prep, st);
     if (rc) return rc;
@@ -283,7 +285,26 @@ int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw
                       exact_query, st);
   }
   if (rc) return rc;
-  return topk(scores, len, k, topk_out, topk_scratch, topk_scratch_bytes_, fused, st);
+  return topk(scores, len, k, topk_out, topk_scratch, topk_scratch_bytes_, fused, nullptr, st);
+}
+int msb_index_decode_list(int key_type, const void* keys, int len, const float* q_raw, const float* w_raw, const float* cs,
+                          int actq, int heads, int k, const int* cand_list, int n_cand, float* q_prep, float* w_prep,
+                          float* scores, int* topk_out, void* topk_scratch, size_t topk_scratch_bytes_, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (key_type != MSB_KEY_FP8_E4M3) return fail(kErrType, "index_decode_list: FP8 keys only (key type %d)", key_type);
+  if (heads != 32 && heads != 64) return fail(kErrArg, "index_decode_list: heads must be 32 or 64 (got %d)", heads);
+  if (len < 0 || n_cand < 0) return fail(kErrArg, "index_decode_list: bad sizes");
+  if (!keys || !q_raw || !w_raw || !cs || !q_prep || !w_prep || !scores || !topk_out || !topk_scratch ||
+      (n_cand > 0 && !cand_list) || (reinterpret_cast<uintptr_t>(keys) & 15))
+    return fail(kErrArg, "index_decode_list: null or misaligned pointer");
+  const int nvirt = n_cand * 8;
+  if (nvirt > 0 && len > 0) {
+    int rc = index_scores_tc(keys, len, q_raw, w_raw, heads, scores, (unsigned*)topk_scratch, 1, cs, actq, q_prep, w_prep,
+                             cand_list, n_cand, st);
+    if (rc) return rc;
+    return topk(scores, nvirt, k, topk_out, topk_scratch, topk_scratch_bytes_, true, cand_list, st);
+  }
+  return topk(scores, 0, k, topk_out, topk_scratch, topk_scratch_bytes_, false, nullptr, st);
 }
 size_t msb_sparse_scratch_bytes(int total_rows_max, int heads, int D) { return sparse_scratch_bytes(total_rows_max, heads, D); }
 int msb_sparse_decode(const float* q, const float* cs, const float* sinks, int elem_type, const void* win, int n_win,

@@ -23,7 +23,8 @@ constexpr int kHistBins = 4096;
 
 // tcgen05 scoring kernel for FP8 keys (index_tc.cu)
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
-                    int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st);
+                    int prep, const float* cs, int actq, float* q_out, float* w_out, const int* cand, int n_cand,
+                    cudaStream_t st);
 
 __device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
   const uint32_t u = __float_as_uint(f);
@@ -390,13 +391,13 @@ __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024]
 
 // forward declaration: the last step, run by the compaction block that finishes last
 __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, unsigned* fine, TopkCtl* ctl,
-                                 const int* sel, const uint2* cand, int* out, int bm_words);
+                                 const int* sel, const uint2* cand, int* out, int bm_words, const int* pos_map);
 
 // Compaction over the whole grid (blocks of 1024 threads), then the exact finish in the block that takes the last
 // ticket: one launch for the whole selection after the histogram.
 __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
                                                            TopkCtl* ctl, int* sel, uint2* cand, int* out, int bm_words,
-                                                           int fused) {
+                                                           int fused, const int* pos_map) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ unsigned sh[1024];
@@ -467,21 +468,24 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words);
+  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, pos_map);
 }
 
 // the last step as its own launch (one block)
 __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
-                                                          TopkCtl* ctl, const int* sel, const uint2* cand, int* out, int bm_words) {
+                                                          TopkCtl* ctl, const int* sel, const uint2* cand, int* out, int bm_words,
+                                                          const int* pos_map) {
   pdl_launch_dependents();
   pdl_wait();
-  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words);
+  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, pos_map);
 }
 
 // The selection's last step, run by ONE block of 1024 threads (the compaction block that finishes last).
 // out[k] ascending, -1 padded.  Resets the histograms and ctl for the next call.
+// pos_map != null: the scores are indexed by virtual position 8 * i + j standing for key pos_map[i] * 8 + j (candidate
+// list, ascending); the output lists key indices (still ascending, as the list is).
 __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, unsigned* fine, TopkCtl* ctl,
-                                 const int* sel, const uint2* cand, int* out, int bm_words) {
+                                 const int* sel, const uint2* cand, int* out, int bm_words, const int* pos_map) {
   __shared__ unsigned sh[1024];
   __shared__ int buf[2048];
   __shared__ unsigned long long c2[1024];
@@ -611,7 +615,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
       while (m) {
         const int bit = __ffs(m) - 1;
         m &= m - 1;
-        if (pos < (unsigned)k) out[pos] = w * 32 + bit;
+        if (pos < (unsigned)k) { const int v = w * 32 + bit; out[pos] = pos_map ? pos_map[v >> 3] * 8 + (v & 7) : v; }
         pos++;
       }
     }
@@ -632,7 +636,10 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
         }
         __syncthreads();
       }
-    for (int i = tid; i < k; i += NT) out[i] = (i < (int)filled && buf[i] != 0x7fffffff) ? buf[i] : -1;
+    for (int i = tid; i < k; i += NT) {
+      const bool ok = i < (int)filled && buf[i] != 0x7fffffff;
+      out[i] = !ok ? -1 : (pos_map ? pos_map[buf[i] >> 3] * 8 + (buf[i] & 7) : buf[i]);
+    }
   }
   for (int b = tid; b < kHistBins; b += NT) { hist[b] = 0; fine[b] = 0; }
   if (tid == 0) { ctl->n_sel = 0; ctl->n_cand = 0; ctl->ticket = 0; }
@@ -659,7 +666,8 @@ size_t topk_scratch_bytes(int n_max) {
 
 // scratch layout: hist[4096] | fine[4096] | ctl (64 B) | sel[2048] | cand[n_max] as (index, key) pairs.  The histograms and ctl must be zero
 // on entry; the final kernel leaves them zero again.
-int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, cudaStream_t st) {
+int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_bytes, bool hist_ready, const int* pos_map,
+         cudaStream_t st) {
   if (n < 0 || k <= 0 || k > 2048) return fail(kErrArg, "topk: n %d k %d (k must be 1..2048)", n, k);
   if (!out || !scratch || (n > 0 && !sc)) return fail(kErrArg, "topk: null pointer");
   if (scratch_bytes < topk_scratch_bytes(n)) return fail(kErrScratch, "topk: scratch too small");
@@ -694,11 +702,11 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   if (n > 0 && !hist_ready) MSB_CUDA(launch_pdl(topk_hist_kernel, dim3(std::max(1, std::min(sms * 2, (n + 1023) / 1024))), dim3(256), 0, st, sc, n, hist));
   if (fused) {
     MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(nthreads), std::max((size_t)bm_words * 4, stage_bytes), st, sc, n, k, hist,
-                        fine, ctl, sel, cand, out, bm_words, 1));
+                        fine, ctl, sel, cand, out, bm_words, 1, pos_map));
   } else {
-    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(nthreads), stage_bytes, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0));
+    if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(nthreads), stage_bytes, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0, pos_map));
     MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl,
-                        (const int*)sel, (const uint2*)cand, out, bm_words));
+                        (const int*)sel, (const uint2*)cand, out, bm_words, pos_map));
   }
   MSB_LAUNCH_CHECK("topk");
   return kOk;
@@ -725,7 +733,7 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   static const int env_probe = getenv("MSB_IDX_PROBE") ? atoi(getenv("MSB_IDX_PROBE")) : 0;
   IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len, env_probe};
   static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;   // mma.sync path
-  if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, 0, nullptr, 0, nullptr, nullptr, st);
+  if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, 0, nullptr, 0, nullptr, nullptr, nullptr, 0, st);
   if (key_type == kKeyFp8 && !exact_query) {
     const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));
     if (heads == 64) MSB_CUDA(launch_pdl(idx_score_fp8_kernel<64>, dim3(grid), dim3(384), 0, st, p));

@@ -34,6 +34,9 @@ constexpr uint32_t kTcSbo = 1024;          // bytes between 8-row groups of the 
 
 struct IdxTcParams {
   CUtensorMap keys;    // [len][128] bytes, box 128 x 128, 128-byte swizzle
+  CUtensorMap keys8;   // the same matrix with a box of 128 x 8 rows (candidate-list mode: one key block per copy)
+  const int* cand;     // candidate-list mode: [n_cand] key-block indices (8 keys each), -1 = none; else null
+  int n_cand;          // entries of cand; the kernel scores n_cand * 8 virtual positions
   const float* q;      // [H][128] query: prepared, or raw when prep != 0
   const float* w;      // [H] head weights: prepared, or raw when prep != 0
   const float* cs;     // prep: [32][2] (cos, sin) of the query position
@@ -136,13 +139,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) idx_score_tc_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem = hd->tmem_base;
   volatile int* abort_flag = &hd->abort_flag;
-  const int ntiles = (p.len + kTcTile - 1) / kTcTile;
+  // candidate-list mode: virtual position v = 8 * i + j is key cand[i] * 8 + j; scores[] is indexed by v
+  const int ntiles = ((p.cand ? p.n_cand * 8 : p.len) + kTcTile - 1) / kTcTile;
   const int my_tiles = ntiles > (int)blockIdx.x ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   pdl_wait();   // the query (and possibly the newest keys) come from kernels that ran before
 
   if (warp == 5) {
-    // ------------------------------------------------------------------ TMA producer (one thread)
-    if (lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (p.cand) {
+      // candidate-list mode, whole warp: lane i < 16 owns key block i of the tile (8 rows = one 1024-byte swizzle group)
+      for (int i = 0; i < my_tiles; i++) {
+        const int s = i % kTcStages;
+        const int tile = (int)blockIdx.x + i * (int)gridDim.x;
+        const int ci = tile * 16 + lane;
+        int blk = -1;
+        if (lane < 16 && ci < p.n_cand) blk = __ldg(p.cand + ci);
+        const bool valid = blk >= 0 && (long long)blk * 8 < p.len;
+        const unsigned m = __ballot_sync(0xffffffffu, valid);
+        if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((i / kTcStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) break;
+        if (lane == 0) mbar_arrive_expect_tx(&hd->full[s], 1024u * (unsigned)__popc(m));
+        __syncwarp();
+        if (valid) tc_tma_2d(stage0 + (size_t)s * kTcTileBytes + lane * 1024, &p.keys8, 0, blk * 8, &hd->full[s]);
+      }
+    } else if (lane == 0) {
       for (int i = 0; i < my_tiles; i++) {
         const int s = i % kTcStages;
         const int tile = (int)blockIdx.x + i * (int)gridDim.x;
@@ -267,8 +286,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) idx_score_tc_kernel(const __gri
       for (int c = 0; c < H / 32; c++)
 #pragma unroll
         for (int h = 0; h < 32; h++) sc = fmaf(fmaxf(__uint_as_float(r[c][h]), 0.f), wr[32 * c + h], sc);
-      const long long key = (long long)tile * kTcTile + 32 * warp + lane;
-      const bool live = key < p.len;
+      const long long key = (long long)tile * kTcTile + 32 * warp + lane;   // key index, or virtual position
+      bool live = key < p.len;
+      if (p.cand) {
+        // rows of blocks that were not loaded hold stale bytes: their (meaningless) sums are masked here
+        const int ci = (int)(key >> 3);
+        const int blk = ci < p.n_cand ? __ldg(p.cand + ci) : -1;
+        const bool valid = blk >= 0 && (long long)blk * 8 + (key & 7) < p.len;
+        if (!valid) sc = -INFINITY;
+        live = key < (long long)p.n_cand * 8;
+      }
       if (live) p.scores[key] = sc;
       if (p.hist) {   // neighbouring scores mostly share a bin: one shared-memory atomic per distinct bin per warp
         const uint32_t bin = (live && sc > -INFINITY) ? tc_order_key(sc) >> 20 : 0xFFFFFFFFu;
@@ -316,8 +343,10 @@ EncodeTiledFn encode_tiled_fn() {
 // FP8 keys, heads 32 or 64.  Returns kOk or an error code; the caller has validated the pointers (keys 16-byte aligned).
 // prep != 0: q / w are the raw projections and the preparation of index_prep is folded in (cs, actq; the prepared
 // values are also written to q_out / w_out when those are given).
+// cand != null: candidate-list mode, scores[8 * i + j] = score of key cand[i] * 8 + j (-inf where there is no such key).
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
-                    int prep, const float* cs, int actq, float* q_out, float* w_out, cudaStream_t st) {
+                    int prep, const float* cs, int actq, float* q_out, float* w_out, const int* cand, int n_cand,
+                    cudaStream_t st) {
   Tables tb;
   int rc = get_tables(&tb);
   if (rc) return rc;
@@ -335,10 +364,16 @@ int index_scores_tc(const void* keys, int len, const float* q, const float* w, i
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fail(kErrCuda, "index_scores: tensor map encode failed (%d)", (int)cr);
+  const cuuint32_t box8[2] = {(cuuint32_t)kTcDim, 8};
+  const CUresult cr8 = encode(&p.keys8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(keys), gdim, gstride, box8, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr8 != CUDA_SUCCESS) return fail(kErrCuda, "index_scores: tensor map encode failed (%d)", (int)cr8);
+  p.cand = cand; p.n_cand = cand ? n_cand : 0;
   p.q = q; p.w = w; p.scores = scores; p.hist = hist; p.status = tb.status; p.len = len;
   p.prep = prep; p.cs = cs; p.actq = actq; p.q_out = q_out; p.w_out = w_out;
   p.wscale = (float)(pow((double)kTcDim, -0.5) * pow((double)heads, -0.5));
-  const int ntiles = (len + kTcTile - 1) / kTcTile;
+  const int ntiles = ((cand ? n_cand * 8 : len) + kTcTile - 1) / kTcTile;
   const int grid = std::max(1, std::min(sms, ntiles));
   const size_t smem = idx_score_tc_smem(heads);
   static bool configured[2][64] = {};

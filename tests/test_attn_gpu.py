@@ -140,6 +140,47 @@ def test_index_decode_benchmark_shape_200k(orc, enc, exact):
     assert np.array_equal(have, want), int((have != want).sum())      # and identical to the oracle's list
 
 
+@pytest.mark.parametrize("heads,length,k", [(64, 200000, 2048), (32, 30003, 512), (64, 900, 2048)], ids=["benchmark", "ragged", "short"])
+def test_index_decode_candidate_list(orc, enc, heads, length, k):
+    """A candidate-source pass (block maxima -> top blocks), then the restricted pass that scores only those blocks:
+    the reference masks every key outside the candidate blocks to -inf before its top-k (tests/attn_test_util.hpp:163-168)."""
+    from macseek_b200 import attn
+    sh = attn.Shape(D=576, heads=64, index_heads=heads, topk=k, key_type=attn.KEY_FP8, elem_type=attn.ELEM_BF16)
+    tab = np.zeros((1, 32, 2), np.float32); tab[:, :, 0] = 1.0
+    st = attn.DecodeState(sh, length, tab)
+    q_raw, w_raw, keys = bench_inputs(heads, length, 3, True)
+    q8 = orc.e4m3_to_f32(orc.f32_to_e4m3(q_raw))
+    k8 = torch.from_numpy(keys).cuda().to(torch.float8_e4m3fn)
+    st.ikey[:length] = k8.view(torch.uint8)
+    keys_f = k8.float().cpu().numpy()
+    q, w = orc.index_q(q8, w_raw, tab[0], False, heads, 128)
+    ref = orc.index_scores(q, w, keys_f)
+    # source pass with a DIFFERENT query, so that the candidates are not simply the restricted pass's own best blocks
+    q_src = orc.e4m3_to_f32(orc.f32_to_e4m3(bench_inputs(heads, 8, 4, True)[0]))
+    attn.encode_index_decode(enc, st, dev(q_src), dev(w_raw), 0, length, actq=False, cand_source=True)
+    enc.wait()
+    qs, ws = orc.index_q(q_src, w_raw, tab[0], False, heads, 128)
+    cand = orc.candidate_blocks(orc.index_scores(qs, ws, keys_f))
+    got_cand = st.cand_list.cpu().numpy()
+    assert np.array_equal(got_cand, cand)
+    attn.encode_index_decode_list(enc, st, dev(q8), dev(w_raw), 0, length, actq=False)
+    enc.wait()
+    masked = np.full(length, -np.inf, dtype=np.float32)
+    for b in cand[cand >= 0]:
+        masked[b * 8:min(length, b * 8 + 8)] = ref[b * 8:min(length, b * 8 + 8)]
+    want = orc.topk_sorted(masked, k)
+    have = st.topk.cpu().numpy()
+    assert np.array_equal(have, want), int((have != want).sum())
+    # the virtual score array: position 8 i + j holds the score of key cand[i] * 8 + j
+    nb = min((length + 7) // 8, sh.cand_blocks)
+    virt = st.dec_scores[:nb * 8].cpu().numpy()
+    for i in (0, nb // 2, nb - 1):
+        b = int(cand[i])
+        if b >= 0:
+            seg = ref[b * 8:min(length, b * 8 + 8)]
+            assert np.max(np.abs(virt[8 * i:8 * i + len(seg)] - seg)) <= 1e-5 * np.max(np.abs(ref))
+
+
 @pytest.mark.parametrize("cfg", [("reference", 512, 1, 700, 512, 100), ("reference-short", 512, 1, 3, 512, 2),
                                  ("benchmark", 576, 30, 200000, 2048, 199999)], ids=lambda c: c[0])
 def test_sparse_attention(orc, enc, cfg):
