@@ -34,6 +34,7 @@ struct MpTile { int slot, row0, rows, n0; };   // expert slot, first entry row, 
 
 struct MpGemmParams {
   CUtensorMap a_map;        // activations [rows_total][K] half, box 64 x 128
+  CUtensorMap b_map;        // dense source: half weights of the dense experts stacked by rows, box 64 x (64 | 128)
   const MpTile* tiles;
   const uint64_t* wptr;     // [slots][3] device addresses {gate, up, down}
   const float* wt;          // [rows_total] routing weight per entry row (mode 0)
@@ -41,6 +42,8 @@ struct MpGemmParams {
   float* z;                 // mode 1 output [rows_total][n_out]
   int* status;
   int ntiles, K, n_out;     // K = contraction length (dim / inter), n_out = output row width (inter / dim)
+                            // dense source: tile.slot = index of the expert in the stacked half matrix, whose rows
+                            // are [slot * 2 n_out, +n_out) gate, [.. + n_out, +n_out) up (mode 0) or [slot * n_out, +n_out) down
   float limit;
   Tables tb;
 };
@@ -86,8 +89,70 @@ __device__ __forceinline__ void mp_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void mp_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// One 32-element unit of an IQ1_S / IQ2_XXS row -> 32 halfs (4 chunks of 8), each value the reference's dequantised
+// float (the arithmetic of dequant8, tests/ref/dequant.cpp:72-120) rounded to half once.  The unit's raw bytes are
+// fetched one K block ahead (they come from HBM: every expert weight is read once); the scalars (block scale, 3/4-bit
+// sub-scale, delta / signs word) are combined once for the 32 elements.
+struct MpRaw { uint32_t a, b; float d; };   // IQ1_S: qs word, qh;  IQ2_XXS: grid-index word, signs + scale word;  d = block scale
+
+template <int T>
+__device__ __forceinline__ MpRaw mp_fetch_unit(const uint8_t* blk, int ib) {
+  MpRaw r;
+  r.d = ldg_half(blk);
+  if (T == IQ1_S) {
+    r.a = ldg_u16(blk + 2 + 4 * ib) | (ldg_u16(blk + 4 + 4 * ib) << 16);
+    r.b = ldg_u16(blk + 34 + 2 * ib);
+  } else {
+    const uint8_t* a8 = blk + 2 + 8 * ib;
+    r.a = ldg_u16(a8) | (ldg_u16(a8 + 2) << 16);
+    r.b = ldg_u16(a8 + 4) | (ldg_u16(a8 + 6) << 16);
+  }
+  return r;
+}
+template <int T>
+__device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const Tables& tb, uint4 (&out)[4]) {
+  if (T == IQ1_S) {
+    const uint32_t qs = r.a, qh = r.b;
+    const float dl = __fmul_rn(r.d, (float)(2 * ((qh >> 12) & 7u) + 1));
+    const float delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+      const uint32_t idx = ((qs >> (8 * l)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
+      const uint2 gv = __ldg(reinterpret_cast<const uint2*>(tb.iq1s_i8 + idx * 8));
+      __half2 h[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const uint32_t wv = j < 2 ? gv.x : gv.y;
+        const float a = (float)(int8_t)((wv >> (16 * (j & 1))) & 0xFFu), b = (float)(int8_t)((wv >> (16 * (j & 1) + 8)) & 0xFFu);
+        h[j] = __floats2half2_rn(__fmul_rn(dl, __fadd_rn(a, delta)), __fmul_rn(dl, __fadd_rn(b, delta)));
+      }
+      out[l] = *reinterpret_cast<uint4*>(h);
+    }
+  } else {
+    const uint32_t q = r.a, a1 = r.b;
+    const float db = __fmul_rn(__fmul_rn(r.d, __fadd_rn(0.5f, (float)(a1 >> 28))), 0.25f);
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+      const uint2 g = __ldg(tb.iq2xxs_grid + ((q >> (8 * l)) & 0xFFu));
+      const uint2 m = __ldg(tb.iq2_signmask + ((a1 >> (7 * l)) & 127u));
+      __half2 h[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const uint32_t gw = j < 2 ? g.x : g.y, mw = j < 2 ? m.x : m.y;
+        const int s0 = 16 * (j & 1), s1 = s0 + 8;
+        const float v0 = __fmul_rn(__fmul_rn(db, (float)((gw >> s0) & 0xFFu)), ((mw >> s0) & 1u) ? -1.f : 1.f);
+        const float v1 = __fmul_rn(__fmul_rn(db, (float)((gw >> s1) & 0xFFu)), ((mw >> s1) & 1u) ? -1.f : 1.f);
+        h[j] = __floats2half2_rn(v0, v1);
+      }
+      out[l] = *reinterpret_cast<uint4*>(h);
+    }
+  }
+}
+
 // MODE 0: gate/up + SwiGLU -> H (half);  MODE 1: down -> Z (fp32).  T = weight type of every tile of the launch.
-template <int T, int MODE>
+// DENSE: the weight tiles come by TMA from a half copy (experts with many entries are dequantised once instead of once
+// per entry tile); the producer warps idle.
+template <int T, int MODE, bool DENSE>
 __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_constant__ MpGemmParams p) {
   pdl_launch_dependents();
   extern __shared__ __align__(1024) uint8_t mp_smem_raw[];
@@ -98,7 +163,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
   constexpr uint32_t kCols = 2 * kMpBN;
 
   if (tid == 0) {
-    for (int s = 0; s < kMpStages; s++) { mbar_init(&hd->full[s], 1 + kMpProducerWarps); mbar_init(&hd->empty[s], 1); }
+    for (int s = 0; s < kMpStages; s++) { mbar_init(&hd->full[s], DENSE ? 1 : 1 + kMpProducerWarps); mbar_init(&hd->empty[s], 1); }
     for (int b = 0; b < 2; b++) { mbar_init(&hd->accfull[b], 1); mbar_init(&hd->accempty[b], 4); }
     hd->abort_flag = 0;
     mbar_fence_init();
@@ -127,8 +192,17 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         for (int k = 0; k < kb; k++, it++) {
           const int s = it % kMpStages;
           if (!mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty)) { ok = false; break; }
-          mbar_arrive_expect_tx(&hd->full[s], kMpABytes);
-          mp_tma_2d(stage0 + (size_t)s * (kMpABytes + kMpBBytes), &p.a_map, k * kMpBK, tl.row0, &hd->full[s]);
+          uint8_t* slot = stage0 + (size_t)s * (kMpABytes + kMpBBytes);
+          mbar_arrive_expect_tx(&hd->full[s], DENSE ? kMpABytes + kMpBBytes : kMpABytes);
+          mp_tma_2d(slot, &p.a_map, k * kMpBK, tl.row0, &hd->full[s]);
+          if (DENSE) {
+            if (MODE == 0) {   // 64 gate rows, then the same 64 up rows
+              mp_tma_2d(slot + kMpABytes, &p.b_map, k * kMpBK, tl.slot * 2 * p.n_out + tl.n0, &hd->full[s]);
+              mp_tma_2d(slot + kMpABytes + kMpBBytes / 2, &p.b_map, k * kMpBK, tl.slot * 2 * p.n_out + p.n_out + tl.n0, &hd->full[s]);
+            } else {
+              mp_tma_2d(slot + kMpABytes, &p.b_map, k * kMpBK, tl.slot * p.n_out + tl.n0, &hd->full[s]);
+            }
+          }
         }
       }
     }
@@ -155,6 +229,8 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         if (ok) mp_commit(&hd->accfull[buf]);
       }
     }
+  } else if (warp >= 6 && DENSE) {
+    // dense source: nothing to produce
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ weight producers: raw blocks -> half operand tile
     // chunk c = (tile row r, 8-element group j of the 64-wide K block); 8 consecutive threads share a row (one block
@@ -169,13 +245,36 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       const uint64_t* wp = p.wptr + (size_t)tl.slot * 3;
       const uint8_t* w0 = reinterpret_cast<const uint8_t*>(MODE == 0 ? wp[0] : wp[2]);   // gate | down
       const uint8_t* w1 = reinterpret_cast<const uint8_t*>(wp[1]);                        // up (mode 0)
+      // unit path (IQ1_S / IQ2_XXS): one thread per (tile row, 32-element unit); raw bytes one K block ahead
+      const int ur = pt >> 1, un = pt & 1;
+      const uint8_t* ubase = (MODE == 0 && ur >= 64) ? w1 : w0;
+      const int uwrow = tl.n0 + (MODE == 0 ? (ur & 63) : ur);
+      const bool ulive = uwrow < p.n_out;
+      auto fetch_k = [&](int k) {
+        MpRaw r{0u, 0u, 0.f};
+        if constexpr (T == IQ1_S || T == IQ2_XXS) {
+          const int u = k * 2 + un;
+          if (ulive && k < kb) r = mp_fetch_unit<T>(ubase + (size_t)uwrow * rb + (size_t)(u >> 3) * block_bytes(T), u & 7);
+        }
+        return r;
+      };
+      MpRaw cur = fetch_k(0);
       for (int k = 0; k < kb; k++, it++) {
         const int s = it % kMpStages;
+        const MpRaw nxt = fetch_k(k + 1);
         if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
           ok = false;
           break;
         }
         uint8_t* bt = stage0 + (size_t)s * (kMpABytes + kMpBBytes) + kMpABytes;
+        if constexpr (T == IQ1_S || T == IQ2_XXS) {
+          static_assert(kMpBN * 2 == kMpProducerWarps * 32, "one unit per producer thread");
+          uint4 o4[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+          if (ulive) mp_decode_unit<T>(cur, p.tb, o4);
+#pragma unroll
+          for (int l = 0; l < 4; l++) *reinterpret_cast<uint4*>(bt + ur * 128 + (((4 * un + l) ^ (ur & 7)) << 4)) = o4[l];
+          cur = nxt;
+        } else
 #pragma unroll
         for (int q = 0; q < kMpBN * 8 / (kMpProducerWarps * 32); q++) {
           const int c = pt + q * kMpProducerWarps * 32, r = c >> 3, j = c & 7;
@@ -338,12 +437,12 @@ EncodeTiledFn mp_encode_fn() {
   }
   return fn;
 }
-int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols) {
+int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols, int box_rows = kMpBM) {
   EncodeTiledFn encode = mp_encode_fn();
   if (!encode) return fail(kErrCuda, "moe_prefill: cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kMpBK, (cuuint32_t)kMpBM};
+  const cuuint32_t box[2] = {(cuuint32_t)kMpBK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult cr = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -352,11 +451,11 @@ int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols) {
   return kOk;
 }
 
-template <int T, int MODE>
+template <int T, int MODE, bool DENSE>
 int mp_launch(MpGemmParams& p, int sms, int dev, cudaStream_t st) {
   if (p.ntiles <= 0) return kOk;
   const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes);
-  auto kern = moep_gemm_kernel<T, MODE>;
+  auto kern = moep_gemm_kernel<T, MODE, DENSE>;
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
     MSB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -369,14 +468,17 @@ int mp_launch(MpGemmParams& p, int sms, int dev, cudaStream_t st) {
 template <int MODE>
 int mp_launch_type(int t, MpGemmParams& p, int sms, int dev, cudaStream_t st) {
   switch (t) {
-    case IQ1_S: return mp_launch<IQ1_S, MODE>(p, sms, dev, st);
-    case IQ2_XXS: return mp_launch<IQ2_XXS, MODE>(p, sms, dev, st);
-    case Q6_K: return mp_launch<Q6_K, MODE>(p, sms, dev, st);
-    case Q8_0: return mp_launch<Q8_0, MODE>(p, sms, dev, st);
+    case IQ1_S: return mp_launch<IQ1_S, MODE, false>(p, sms, dev, st);
+    case IQ2_XXS: return mp_launch<IQ2_XXS, MODE, false>(p, sms, dev, st);
+    case Q6_K: return mp_launch<Q6_K, MODE, false>(p, sms, dev, st);
+    case Q8_0: return mp_launch<Q8_0, MODE, false>(p, sms, dev, st);
   }
   return fail(kErrType, "moe_prefill: unsupported expert weight type %s", type_name(t));
 }
 size_t al256(size_t b) { return (b + 255) & ~(size_t)255; }
+// Experts with at least kMpDenseMin entries (at most kMpDenseMax routed ones, the largest first, plus the shared expert)
+// are dequantised to half once and read by TMA; the others are dequantised tile by tile inside the kernel.
+constexpr int kMpDenseMin = 256, kMpDenseMax = 12;
 // upper bounds of the tile counts
 size_t mp_row_tiles(int total, int n_exp, int n_tokens) {
   return (size_t)(total + kMpBM - 1) / kMpBM + (size_t)n_exp + (size_t)(n_tokens + kMpBM - 1) / kMpBM + 1;
@@ -406,8 +508,11 @@ size_t moe_prefill_scratch_bytes(int total, int n_tokens, int n_exp, int dim, in
   b += al256(rt * ((inter + 63) / 64) * sizeof(MpTile)) + al256(rt * ((dim + 127) / 128) * sizeof(MpTile));
   b += al256((size_t)(n_exp + 1) * 3 * sizeof(uint64_t)) + al256(rows * sizeof(float));
   b += al256(rows * dim * 2) + al256(rows * inter * 2) + al256(rows * dim * 4);
+  b += 2 * al256((size_t)(kMpDenseMax + 1) * 2 * inter * dim * 2) ;   // half copies of the dense experts: gate|up, down (+ slack)
   return b;
 }
+
+int weights_to_f16(int t, const void* W, int64_t count, __half* out, int part, cudaStream_t st);   // prefill_gemm.cu
 
 int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   if (a.dim <= 0 || a.inter <= 0 || a.dim % 256 || a.inter % 256) return fail(kErrArg, "moe_prefill: dim/inter must be multiples of 256");
@@ -429,8 +534,25 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int n_sh = a.has_shared ? a.n_tokens : 0;
   const size_t rows = (size_t)total + n_sh;
-  // tile tables: per expert, weight-row tiles outer, entry tiles inner (CTAs that run together share a weight tile)
-  std::vector<MpTile> t1r, t1s, t2r, t2s;
+  // dense experts: the largest routed experts with many entries, and the shared expert when there are many tokens
+  std::vector<int> dense_of(a.n_exp + 1, -1);
+  std::vector<int> dense_slots;
+  {
+    std::vector<std::pair<int, int>> bym;
+    for (int j = 0; j < a.n_exp; j++)
+      if (a.offs[j + 1] - a.offs[j] >= kMpDenseMin) bym.push_back({a.offs[j + 1] - a.offs[j], j});
+    std::sort(bym.begin(), bym.end(), [](const std::pair<int, int>& x, const std::pair<int, int>& y) {
+      return x.first != y.first ? x.first > y.first : x.second < y.second;
+    });
+    for (size_t q = 0; q < bym.size() && (int)dense_slots.size() < kMpDenseMax; q++) {
+      dense_of[bym[q].second] = (int)dense_slots.size();
+      dense_slots.push_back(bym[q].second);
+    }
+    if (n_sh >= kMpDenseMin) { dense_of[a.n_exp] = (int)dense_slots.size(); dense_slots.push_back(a.n_exp); }
+  }
+  // tile tables: per expert, weight-row tiles outer, entry tiles inner (CTAs that run together share a weight tile);
+  // t?r: routed experts decoded in the kernel, t?s: shared expert decoded in the kernel, t?d: dense (slot = dense index)
+  std::vector<MpTile> t1r, t1s, t1d, t2r, t2s, t2d;
   auto add_tiles = [&](std::vector<MpTile>& v, int slot, int row0, int m, int n_out, int step) {
     for (int n0 = 0; n0 < n_out; n0 += step)
       for (int m0 = 0; m0 < m; m0 += kMpBM) v.push_back(MpTile{slot, row0 + m0, std::min(kMpBM, m - m0), n0});
@@ -438,12 +560,22 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   for (int j = 0; j < a.n_exp; j++) {
     const int m = a.offs[j + 1] - a.offs[j];
     if (m <= 0) continue;
-    add_tiles(t1r, j, a.offs[j], m, a.inter, 64);
-    add_tiles(t2r, j, a.offs[j], m, a.dim, kMpBN);
+    if (dense_of[j] >= 0) {
+      add_tiles(t1d, dense_of[j], a.offs[j], m, a.inter, 64);
+      add_tiles(t2d, dense_of[j], a.offs[j], m, a.dim, kMpBN);
+    } else {
+      add_tiles(t1r, j, a.offs[j], m, a.inter, 64);
+      add_tiles(t2r, j, a.offs[j], m, a.dim, kMpBN);
+    }
   }
   if (n_sh) {
-    add_tiles(t1s, a.n_exp, total, n_sh, a.inter, 64);
-    add_tiles(t2s, a.n_exp, total, n_sh, a.dim, kMpBN);
+    if (dense_of[a.n_exp] >= 0) {
+      add_tiles(t1d, dense_of[a.n_exp], total, n_sh, a.inter, 64);
+      add_tiles(t2d, dense_of[a.n_exp], total, n_sh, a.dim, kMpBN);
+    } else {
+      add_tiles(t1s, a.n_exp, total, n_sh, a.inter, 64);
+      add_tiles(t2s, a.n_exp, total, n_sh, a.dim, kMpBN);
+    }
   }
   std::vector<uint64_t> wptr((size_t)(a.n_exp + 1) * 3, 0);
   for (int j = 0; j < a.n_exp; j++)
@@ -462,19 +594,35 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   float* d_wt = reinterpret_cast<float*>(cur); cur += al256(rows * sizeof(float));
   __half* d_xg = reinterpret_cast<__half*>(cur); cur += al256(rows * a.dim * 2);
   __half* d_h = reinterpret_cast<__half*>(cur); cur += al256(rows * a.inter * 2);
-  float* d_z = reinterpret_cast<float*>(cur);
+  float* d_z = reinterpret_cast<float*>(cur); cur += al256(rows * a.dim * 4);
+  __half* d_wgu = reinterpret_cast<__half*>(cur); cur += al256((size_t)(kMpDenseMax + 1) * 2 * a.inter * a.dim * 2);
+  __half* d_wd = reinterpret_cast<__half*>(cur);
   // the tables go to the device (pageable source: the runtime stages them before returning)
   auto upload = [&](void* dst, const void* src, size_t bytes) -> cudaError_t {
     return bytes ? cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st) : cudaSuccess;
   };
   MSB_CUDA(upload(d_t1, t1r.data(), t1r.size() * sizeof(MpTile)));
   MSB_CUDA(upload(d_t1 + t1r.size(), t1s.data(), t1s.size() * sizeof(MpTile)));
+  MSB_CUDA(upload(d_t1 + t1r.size() + t1s.size(), t1d.data(), t1d.size() * sizeof(MpTile)));
   MSB_CUDA(upload(d_t2, t2r.data(), t2r.size() * sizeof(MpTile)));
   MSB_CUDA(upload(d_t2 + t2r.size(), t2s.data(), t2s.size() * sizeof(MpTile)));
+  MSB_CUDA(upload(d_t2 + t2r.size() + t2s.size(), t2d.data(), t2d.size() * sizeof(MpTile)));
   MSB_CUDA(upload(d_wptr, wptr.data(), wptr.size() * sizeof(uint64_t)));
   if (rows == 0) return kOk;
   MSB_CUDA(launch_pdl(moep_gather_kernel, dim3((unsigned)rows), dim3(256), 0, st, a.X, a.tok, a.wt, d_xg, d_wt, total, n_sh,
                       a.dim));
+  // half copies of the dense experts (gate rows then up rows per expert; down rows per expert)
+  for (size_t q = 0; q < dense_slots.size(); q++) {
+    const int j = dense_slots[q];
+    const int t_gu = j == a.n_exp ? a.t_shared : a.t_gate_up, t_d = j == a.n_exp ? a.t_shared : a.t_down;
+    const size_t gu = (size_t)a.inter * a.dim;
+    rc = weights_to_f16(t_gu, reinterpret_cast<const void*>(wptr[(size_t)j * 3]), (int64_t)gu, d_wgu + (2 * q) * gu, 0, st);
+    if (rc) return rc;
+    rc = weights_to_f16(t_gu, reinterpret_cast<const void*>(wptr[(size_t)j * 3 + 1]), (int64_t)gu, d_wgu + (2 * q + 1) * gu, 0, st);
+    if (rc) return rc;
+    rc = weights_to_f16(t_d, reinterpret_cast<const void*>(wptr[(size_t)j * 3 + 2]), (int64_t)gu, d_wd + q * gu, 0, st);
+    if (rc) return rc;
+  }
   MpGemmParams p;
   p.wptr = d_wptr; p.wt = d_wt; p.h = d_h; p.z = d_z; p.status = tb.status; p.limit = a.limit > 0.f ? a.limit : 10.f; p.tb = tb;
   // gate/up + SwiGLU
@@ -487,6 +635,13 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   p.tiles = d_t1 + t1r.size(); p.ntiles = (int)t1s.size();
   rc = mp_launch_type<0>(a.t_shared, p, sms, dev, st);
   if (rc) return rc;
+  if (!t1d.empty()) {
+    rc = mp_make_map(&p.b_map, d_wgu, (int64_t)dense_slots.size() * 2 * a.inter, a.dim, 64);
+    if (rc) return rc;
+    p.tiles = d_t1 + t1r.size() + t1s.size(); p.ntiles = (int)t1d.size();
+    rc = mp_launch<F16, 0, true>(p, sms, dev, st);
+    if (rc) return rc;
+  }
   // down
   rc = mp_make_map(&p.a_map, d_h, (int64_t)rows, a.inter);
   if (rc) return rc;
@@ -497,6 +652,13 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   p.tiles = d_t2 + t2r.size(); p.ntiles = (int)t2s.size();
   rc = mp_launch_type<1>(a.t_shared, p, sms, dev, st);
   if (rc) return rc;
+  if (!t2d.empty()) {
+    rc = mp_make_map(&p.b_map, d_wd, (int64_t)dense_slots.size() * a.dim, a.inter, kMpBN);
+    if (rc) return rc;
+    p.tiles = d_t2 + t2r.size() + t2s.size(); p.ntiles = (int)t2d.size();
+    rc = mp_launch<F16, 1, true>(p, sms, dev, st);
+    if (rc) return rc;
+  }
   MSB_CUDA(launch_pdl(moep_combine_kernel, dim3((unsigned)a.n_tokens), dim3(256), 0, st, (const float*)d_z, a.slot_of, a.Y, total,
                       a.n_tokens, a.k_per_token, a.dim, a.has_shared ? 1 : 0));
   MSB_LAUNCH_CHECK("moe_prefill");

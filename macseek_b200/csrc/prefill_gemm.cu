@@ -294,7 +294,9 @@ int gemm_f16(const void* x16, int64_t x_stride, const void* w16, float* y, int n
   return kOk;
 }
 
-// W (type t) -> half [rows x cols]; part 1 = the F32 remainder term
+}  // namespace
+
+// W (type t) -> half [rows x cols]; part 1 = the F32 remainder term (also used by the MoE prefill for its dense experts)
 int weights_to_f16(int t, const void* W, int64_t count, __half* out, int part, cudaStream_t st) {
   Tables tb;
   int rc = get_tables(&tb);
@@ -320,7 +322,6 @@ int weights_to_f16(int t, const void* W, int64_t count, __half* out, int part, c
   MSB_LAUNCH_CHECK("weights_to_f16");
   return kOk;
 }
-}  // namespace
 
 int f32_to_f16(const float* x, void* x16, size_t count, cudaStream_t st) {
   if (count % 4) return fail(kErrArg, "f32_to_f16: count %zu is not a multiple of 4", count);

@@ -204,9 +204,11 @@ def gemm_case(t: q.QType, rows: int, cols: int, n: int, eager: int = 0):
             print(f"gemm {n}x{rows}x{cols} {name:34s} median {r[0]:9.2f} us   {flop / r[0] / 1e6:8.1f} TFLOP/s", flush=True)
 
 
-def moe_prefill_case(n: int = 4096, eager: int = 0):
+def moe_prefill_case(n: int = 4096, eager: int = 0, routing: str = "bias"):
     """The benchmark prefill layer: n tokens, top-8 of 384 experts (IQ1_S gate/up, IQ2_XXS down) + Q8_0 shared expert,
-    dim 4096, inter 2048; logits N(0,1) plus a log-Zipf(1.1) popularity bias over a seeded expert permutation."""
+    dim 4096, inter 2048.  routing "bias": logits N(0,1) plus a log-Zipf(1.1) popularity bias over a seeded expert
+    permutation (a few experts take most tokens); "sample": top-k drawn without replacement from Zipf(0.8)
+    popularities, as the reference's own bench does (bench/qmatmul.mm:135-152: every expert gets some tokens)."""
     gen = torch.Generator(device="cuda")
     gen.manual_seed(7)
     D, I, E, K = 4096, 2048, 384, 8
@@ -215,7 +217,12 @@ def moe_prefill_case(n: int = 4096, eager: int = 0):
     bias = torch.empty(E, device="cuda")
     bias[perm] = -1.1 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
     logits = torch.randn(n, E, device="cuda", generator=gen) + bias
-    ids = torch.topk(logits, K, dim=1).indices                                   # [n][K]
+    if routing == "sample":
+        pw = torch.empty(E, device="cuda")
+        pw[perm] = torch.arange(1, E + 1, device="cuda", dtype=torch.float32).pow(-0.8)
+        ids = torch.multinomial(pw.expand(n, E), K, replacement=False, generator=gen)
+    else:
+        ids = torch.topk(logits, K, dim=1).indices                               # [n][K]
     w = torch.softmax(torch.gather(logits, 1, ids), dim=1).float()
     flat_e = ids.reshape(-1)
     order = torch.argsort(flat_e, stable=True)                                   # entries sorted by (expert, token*K+k)
@@ -244,7 +251,7 @@ def moe_prefill_case(n: int = 4096, eager: int = 0):
     a.Y = torch.zeros(n, D, device="cuda")
     a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(offs[-1], n, len(used), D, I), dtype=torch.uint8, device="cuda")
     cs = sorted(counts)
-    print(f"moe_prefill n={n}: {len(used)} experts hit, tokens/expert min {cs[0]} median {cs[len(cs) // 2]} max {cs[-1]}", flush=True)
+    print(f"moe_prefill n={n} routing={routing}: {len(used)} experts hit, tokens/expert min {cs[0]} median {cs[len(cs) // 2]} max {cs[-1]}", flush=True)
     e = Enc()
     for _ in range(2):
         q.encode_moe_prefill(e, a)
@@ -352,6 +359,7 @@ def main():
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--groups", type=int, default=1)
     ap.add_argument("--kv-len", type=int, default=200000)
+    ap.add_argument("--routing", default="bias", choices=["bias", "sample"])
     ap.add_argument("--eager", type=int, default=0, help="issue this many plain launches and exit (no timing)")
     a = ap.parse_args()
     torch.cuda.set_device(0)
@@ -362,7 +370,7 @@ def main():
     elif a.case == "layer":
         layer_stages(8, a.kv_len)
     elif a.case == "moe_prefill":
-        moe_prefill_case(a.n if a.n > 1 else 4096, a.eager)
+        moe_prefill_case(a.n if a.n > 1 else 4096, a.eager, a.routing)
     elif a.case == "gemm":
         gemm_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n if a.n > 1 else 4096, a.eager)
     elif a.case == "attn":
