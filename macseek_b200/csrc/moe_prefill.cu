@@ -115,36 +115,31 @@ __device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const Tables& tb,
     const uint32_t qs = r.a, qh = r.b;
     const float dl = __fmul_rn(r.d, (float)(2 * ((qh >> 12) & 7u) + 1));
     const float delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+    // a unit has only three distinct values dl * (g + delta), g = -1, 0, 1: round them to half once (exactly what the
+    // per-element arithmetic gives) and let a byte permute pick two of them per table selector
+    const __half2 h01 = __floats2half2_rn(__fmul_rn(dl, __fadd_rn(-1.f, delta)), __fmul_rn(dl, __fadd_rn(0.f, delta)));
+    const __half2 h2x = __floats2half2_rn(__fmul_rn(dl, __fadd_rn(1.f, delta)), 0.f);
+    const uint32_t pool_lo = *reinterpret_cast<const uint32_t*>(&h01), pool_hi = *reinterpret_cast<const uint32_t*>(&h2x);
 #pragma unroll
     for (int l = 0; l < 4; l++) {
       const uint32_t idx = ((qs >> (8 * l)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
-      const uint2 gv = __ldg(reinterpret_cast<const uint2*>(tb.iq1s_i8 + idx * 8));
-      __half2 h[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const uint32_t wv = j < 2 ? gv.x : gv.y;
-        const float a = (float)(int8_t)((wv >> (16 * (j & 1))) & 0xFFu), b = (float)(int8_t)((wv >> (16 * (j & 1) + 8)) & 0xFFu);
-        h[j] = __floats2half2_rn(__fmul_rn(dl, __fadd_rn(a, delta)), __fmul_rn(dl, __fadd_rn(b, delta)));
-      }
-      out[l] = *reinterpret_cast<uint4*>(h);
+      const uint2 sel = __ldg(tb.iq1s_sel + idx);
+      out[l] = make_uint4(__byte_perm(pool_lo, pool_hi, sel.x & 0xFFFFu), __byte_perm(pool_lo, pool_hi, sel.x >> 16),
+                          __byte_perm(pool_lo, pool_hi, sel.y & 0xFFFFu), __byte_perm(pool_lo, pool_hi, sel.y >> 16));
     }
   } else {
     const uint32_t q = r.a, a1 = r.b;
     const float db = __fmul_rn(__fmul_rn(r.d, __fadd_rn(0.5f, (float)(a1 >> 28))), 0.25f);
+    // three magnitudes per unit (db * 8, db * 25, db * 43), rounded to half once; the sign is the half's top bit
+    const __half2 h01 = __floats2half2_rn(__fmul_rn(db, 8.f), __fmul_rn(db, 25.f));
+    const __half2 h2x = __floats2half2_rn(__fmul_rn(db, 43.f), 0.f);
+    const uint32_t pool_lo = *reinterpret_cast<const uint32_t*>(&h01), pool_hi = *reinterpret_cast<const uint32_t*>(&h2x);
 #pragma unroll
     for (int l = 0; l < 4; l++) {
-      const uint2 g = __ldg(tb.iq2xxs_grid + ((q >> (8 * l)) & 0xFFu));
-      const uint2 m = __ldg(tb.iq2_signmask + ((a1 >> (7 * l)) & 127u));
-      __half2 h[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const uint32_t gw = j < 2 ? g.x : g.y, mw = j < 2 ? m.x : m.y;
-        const int s0 = 16 * (j & 1), s1 = s0 + 8;
-        const float v0 = __fmul_rn(__fmul_rn(db, (float)((gw >> s0) & 0xFFu)), ((mw >> s0) & 1u) ? -1.f : 1.f);
-        const float v1 = __fmul_rn(__fmul_rn(db, (float)((gw >> s1) & 0xFFu)), ((mw >> s1) & 1u) ? -1.f : 1.f);
-        h[j] = __floats2half2_rn(v0, v1);
-      }
-      out[l] = *reinterpret_cast<uint4*>(h);
+      const uint2 sel = __ldg(tb.iq2_sel + ((q >> (8 * l)) & 0xFFu));
+      const uint4 sg = __ldg(tb.iq2_sign16 + ((a1 >> (7 * l)) & 127u));
+      out[l] = make_uint4(__byte_perm(pool_lo, pool_hi, sel.x & 0xFFFFu) ^ sg.x, __byte_perm(pool_lo, pool_hi, sel.x >> 16) ^ sg.y,
+                          __byte_perm(pool_lo, pool_hi, sel.y & 0xFFFFu) ^ sg.z, __byte_perm(pool_lo, pool_hi, sel.y >> 16) ^ sg.w);
     }
   }
 }
@@ -258,10 +253,17 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         }
         return r;
       };
-      MpRaw cur = fetch_k(0);
-      for (int k = 0; k < kb; k++, it++) {
+      // raw bytes of four K blocks in flight per thread (they come from HBM, a microsecond away); K is a multiple of
+      // 256, so the number of K blocks is a multiple of 4 and the ring index is a compile-time constant
+      MpRaw ring[4] = {fetch_k(0), fetch_k(1), fetch_k(2), fetch_k(3)};
+      for (int k0 = 0; ok && k0 < kb; k0 += 4)
+#pragma unroll
+      for (int kk = 0; kk < 4; kk++) {
+        if (!ok) break;
+        const int k = k0 + kk;
         const int s = it % kMpStages;
-        const MpRaw nxt = fetch_k(k + 1);
+        const MpRaw cur = ring[kk];
+        ring[kk] = fetch_k(k + 4);
         if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
           ok = false;
           break;
@@ -273,7 +275,6 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
           if (ulive) mp_decode_unit<T>(cur, p.tb, o4);
 #pragma unroll
           for (int l = 0; l < 4; l++) *reinterpret_cast<uint4*>(bt + ur * 128 + (((4 * un + l) ^ (ur & 7)) << 4)) = o4[l];
-          cur = nxt;
         } else
 #pragma unroll
         for (int q = 0; q < kMpBN * 8 / (kMpProducerWarps * 32); q++) {
@@ -301,6 +302,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&hd->full[s]);
+        it++;
       }
     }
   } else {

@@ -159,6 +159,10 @@ struct Tables {
   const uint2* iq2_signmask;   // [128]
   const uint16_t* iq4nl_pair;  // [256]
   const int8_t* iq1s_i8;       // [2048][8]
+  const uint2* iq2_sel;        // [256] the same selectors for the IQ2_XXS grid (codes 0..2 = magnitudes 8, 25, 43)
+  const uint4* iq2_sign16;     // [128] sign words for 8 halfs (0x8000 in the half of a negative element)
+  const uint2* iq1s_sel;       // [2048] four 16-bit byte-permute selectors per entry: pair j of the entry's 8 codes picks
+                               // two halfs out of the pool {h(code 0), h(code 1), h(code 2)} (MoE prefill weight producers)
   const uint8_t* img_iq1s;
   const uint8_t* img_iq2g;
   const uint8_t* img_iq2s;

@@ -50,8 +50,11 @@ struct HostImage {
   std::vector<uint32_t> iq2_sign;   // 2 words per entry
   std::vector<uint16_t> iq4_pair;
   std::vector<int8_t> iq1s_i8;
+  std::vector<uint32_t> iq1s_sel;   // 2 words per entry
+  std::vector<uint32_t> iq2_sel;    // 2 words per entry
+  std::vector<uint32_t> iq2_sign16; // 4 words per entry
   std::vector<uint32_t> img_iq1s, img_iq2g, img_iq2s, img_iq4;
-  HostImage() : iq2_grid(512), iq2_sign(256), iq4_pair(256), iq1s_i8(2048 * 8) {
+  HostImage() : iq2_grid(512), iq2_sign(256), iq4_pair(256), iq1s_i8(2048 * 8), iq1s_sel(2048 * 2, 0), iq2_sel(256 * 2, 0), iq2_sign16(128 * 4, 0) {
     img_iq1s.assign(2048 * 4 * 2, 0);
     for (int i = 0; i < 2048; i++) {
       uint32_t w[2] = {0, 0};
@@ -61,14 +64,29 @@ struct HostImage {
         w[j / 4] |= f << (8 * (j % 4));
       }
       for (int c = 0; c < 4; c++) { img_iq1s[(i * 4 + c) * 2] = w[0]; img_iq1s[(i * 4 + c) * 2 + 1] = w[1]; }
+      // selectors: code c (0..2) of an element picks bytes (2c, 2c+1) of the 8-byte pool of three halfs
+      for (int j = 0; j < 4; j++) {
+        const uint32_t ca = (kMsbIq1sPacked[i] >> (4 * j)) & 3, cb = (kMsbIq1sPacked[i] >> (4 * j + 2)) & 3;
+        const uint32_t sel = (2 * ca) | ((2 * ca + 1) << 4) | ((2 * cb) << 8) | ((2 * cb + 1) << 12);
+        iq1s_sel[2 * i + j / 2] |= sel << (16 * (j % 2));
+      }
     }
     static const uint32_t lv[4] = {8, 25, 43, 0};
     for (int i = 0; i < 256; i++)
       for (int j = 0; j < 8; j++) iq2_grid[2 * i + j / 4] |= lv[(kMsbIq2xxsPacked[i] >> (2 * j)) & 3] << (8 * (j % 4));
+    for (int i = 0; i < 256; i++)
+      for (int j = 0; j < 4; j++) {
+        const uint32_t ca = (kMsbIq2xxsPacked[i] >> (4 * j)) & 3, cb = (kMsbIq2xxsPacked[i] >> (4 * j + 2)) & 3;
+        const uint32_t sel = (2 * ca) | ((2 * ca + 1) << 4) | ((2 * cb) << 8) | ((2 * cb + 1) << 12);
+        iq2_sel[2 * i + j / 2] |= sel << (16 * (j % 2));
+      }
     for (int i = 0; i < 128; i++) {
       const int bits = i | ((__builtin_popcount((unsigned)i) & 1) << 7);
       for (int j = 0; j < 8; j++)
-        if ((bits >> j) & 1) iq2_sign[2 * i + j / 4] |= 0xFFu << (8 * (j % 4));
+        if ((bits >> j) & 1) {
+          iq2_sign[2 * i + j / 4] |= 0xFFu << (8 * (j % 4));
+          iq2_sign16[4 * i + j / 2] |= 0x8000u << (16 * (j % 2));
+        }
     }
     for (int b = 0; b < 256; b++)
       iq4_pair[b] = (uint16_t)((uint8_t)kIq4nl[b & 15] | ((uint16_t)(uint8_t)kIq4nl[b >> 4] << 8));
@@ -111,6 +129,9 @@ int get_tables(Tables* out) {
     MSB_CUDA(upload(img.iq2_sign, (const void**)&d.t.iq2_signmask));
     MSB_CUDA(upload(img.iq4_pair, (const void**)&d.t.iq4nl_pair));
     MSB_CUDA(upload(img.iq1s_i8, (const void**)&d.t.iq1s_i8));
+    MSB_CUDA(upload(img.iq1s_sel, (const void**)&d.t.iq1s_sel));
+    MSB_CUDA(upload(img.iq2_sel, (const void**)&d.t.iq2_sel));
+    MSB_CUDA(upload(img.iq2_sign16, (const void**)&d.t.iq2_sign16));
     MSB_CUDA(cudaMalloc((void**)&d.t.status, 2048));     // status word, scheduling counters, argmax partials
     MSB_CUDA(cudaMemset(d.t.status, 0, 2048));
     d.ready = true;
