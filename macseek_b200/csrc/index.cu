@@ -54,7 +54,6 @@ struct IdxParams {
   float* scores;       // [len]
   unsigned* hist;      // [4096] or null
   int len;
-  int probe;           // tuning probe: 1 = fetch the keys but skip the tensor-core work
 };
 
 __device__ __forceinline__ void hist_flush(unsigned* sh, unsigned* gh, int tid, int nthreads) {
@@ -141,10 +140,6 @@ __global__ void __launch_bounds__(384, 1) idx_score_fp8_kernel(const IdxParams p
     const uint32_t A0[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
     const uint32_t A1[8] = {cur[2].x, cur[2].y, cur[2].z, cur[2].w, cur[3].x, cur[3].y, cur[3].z, cur[3].w};
     float s0 = 0.f, s1 = 0.f;
-    if (p.probe == 1) {
-      s0 = __uint_as_float((A0[0] ^ A0[1] ^ A0[2] ^ A0[3] ^ A0[4] ^ A0[5] ^ A0[6] ^ A0[7]) & 0x3FFFFFFFu);
-      s1 = __uint_as_float((A1[0] ^ A1[1] ^ A1[2] ^ A1[3] ^ A1[4] ^ A1[5] ^ A1[6] ^ A1[7]) & 0x3FFFFFFFu);
-    } else
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
       float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -730,8 +725,7 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   int dev = 0, sms = 0;
   MSB_CUDA(cudaGetDevice(&dev));
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  static const int env_probe = getenv("MSB_IDX_PROBE") ? atoi(getenv("MSB_IDX_PROBE")) : 0;
-  IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len, env_probe};
+  IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len};
   static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;   // mma.sync path
   if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, 0, nullptr, 0, nullptr, nullptr, nullptr, 0, st);
   if (key_type == kKeyFp8 && !exact_query) {

@@ -29,7 +29,6 @@ struct MvParams {
   int64_t x_stride, y_stride;   // elements between activation columns / output columns
   uint32_t row_bytes;
   int accumulate;
-  int probe_skip_compute;       // tuning probe: stream the tiles, skip the arithmetic
   int units;                    // cols / 32
   int ks;                       // warps sharing one row (1 = each warp owns whole rows)
   int tile_rows;                // R
@@ -178,7 +177,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 8 ? 2 : 1) matvec_kernel(
         rowp[i] = slot_s + (uint32_t)(lr0 + i) * p.pitch + mis + (uint32_t)units_bytes(T, ua);
       }
       if (!consumer_wait(ring, n)) return;
-      if (ub > ua && !p.probe_skip_compute) consume_rows<T, LPR, NR, NC>(rowp, li, xq, u0 + ua, ub - ua, L, acc);
+      if (ub > ua) consume_rows<T, LPR, NR, NC>(rowp, li, xq, u0 + ua, ub - ua, L, acc);
       consumer_release(ring, n, lane);
     }
     if (KS > 1) {
@@ -405,8 +404,6 @@ int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x
   p.x_stride = x_stride; p.y_stride = y_stride;
   p.row_bytes = (uint32_t)row_bytes(t, cols);
   p.accumulate = accumulate;
-  static const int env_skip = getenv("MSB_MV_SKIP") ? atoi(getenv("MSB_MV_SKIP")) : 0;
-  p.probe_skip_compute = env_skip;
   p.units = cols / 32;
   for (int c0 = 0; c0 < n;) {
     const int left = n - c0;
