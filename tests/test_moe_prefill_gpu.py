@@ -173,3 +173,70 @@ def test_moe_prefill_reference_cases(orc, c):
     assert err_f <= 5e-3, (err_h, err_f)
     # tokens the reference check did not look at must at least have moved from Y0 when they have any expert
     assert not np.array_equal(outs[0], Y0)
+
+
+def test_moe_prefill_edge_cases(orc):
+    """Shared expert only (no routed experts); routed only with tokens that have no expert at all (slot_of = -1 keeps
+    their rows of Y untouched); zero tokens."""
+    from macseek_b200 import quant as q
+    from macseek_b200.core import Enc
+    D, I, n = 512, 256, 37
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    mats = [synth.random_weights(t, r, c, 800 + i) for i, (t, r, c) in enumerate(
+        [(ol.Q8_0, I, D), (ol.Q8_0, I, D), (ol.Q8_0, D, I), (ol.IQ1_S, I, D), (ol.IQ1_S, I, D), (ol.IQ2_XXS, D, I)])]
+    X = synth.randn(n * D, 3).reshape(n, D)
+    Y0 = synth.randn(n * D, 4).reshape(n, D)
+
+    def ref_expert(g, u, d, tg, td, toks, ws):
+        wg = r16(orc.dequant(tg, g, I * D).reshape(I, D).astype(np.float64))
+        wu = r16(orc.dequant(tg, u, I * D).reshape(I, D).astype(np.float64))
+        wd = r16(orc.dequant(td, d, I * D).reshape(D, I).astype(np.float64))
+        xin = r16(X[toks].astype(np.float64))
+        gg, uu = np.minimum(xin @ wg.T, 10.0), np.clip(xin @ wu.T, -10.0, 10.0)
+        h = r16((gg / (1 + np.exp(-gg)) * uu * ws[:, None]).astype(np.float32).astype(np.float64))
+        return h @ wd.T, np.abs(h) @ np.abs(wd).T
+
+    def slot(i0):
+        s = q.ExpertSlot()
+        s.gate, s.up, s.down = dev(mats[i0]), dev(mats[i0 + 1]), dev(mats[i0 + 2])
+        return s
+    e = Enc()
+    # (1) shared expert only
+    a = q.MoePrefillArgs(D, I)
+    a.t_gate_up, a.t_down, a.t_shared = ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0
+    a.n_tokens, a.k_per_token, a.has_shared = n, 2, True
+    a.shared = slot(0)
+    a.offs = [0]
+    a.slot_of = dev(-np.ones(n * 2, np.int32))
+    a.tok, a.wt = dev(np.zeros(1, np.int32)), dev(np.zeros(1, np.float32))
+    a.X, a.Y = dev(X), dev(Y0)
+    a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(0, n, 0, D, I), dtype=torch.uint8, device="cuda")
+    q.encode_moe_prefill(e, a)
+    e.wait()
+    o, om = ref_expert(mats[0], mats[1], mats[2], ol.Q8_0, ol.Q8_0, np.arange(n), np.ones(n))
+    got = a.Y.cpu().numpy().astype(np.float64)
+    assert np.max(np.abs(got - (Y0 + o)) / (np.abs(Y0) + om + 1e-9)) <= 1e-3
+    # (2) one routed expert for the even tokens only, no shared expert
+    toks = np.arange(0, n, 2).astype(np.int32)
+    ws = np.full(len(toks), 0.25, np.float32)
+    so = -np.ones(n * 2, np.int32)
+    so[toks * 2 + 1] = np.arange(len(toks))
+    b = q.MoePrefillArgs(D, I)
+    b.t_gate_up, b.t_down, b.t_shared = ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0
+    b.n_tokens, b.k_per_token, b.has_shared = n, 2, False
+    b.slots = [slot(3)]
+    b.offs = [0, len(toks)]
+    b.tok, b.wt, b.slot_of = dev(toks), dev(ws), dev(so)
+    b.X, b.Y = dev(X), dev(Y0)
+    b.scratch = torch.zeros(q.moe_prefill_scratch_bytes(len(toks), n, 1, D, I), dtype=torch.uint8, device="cuda")
+    q.encode_moe_prefill(e, b)
+    e.wait()
+    got = b.Y.cpu().numpy()
+    odd = np.arange(1, n, 2)
+    assert np.array_equal(got[odd].view(np.uint32), Y0[odd].view(np.uint32))          # untouched rows
+    o, om = ref_expert(mats[3], mats[4], mats[5], ol.IQ1_S, ol.IQ2_XXS, toks, ws.astype(np.float64))
+    assert np.max(np.abs(got[toks].astype(np.float64) - (Y0[toks] + o)) / (np.abs(Y0[toks]) + om + 1e-9)) <= 1e-3
+    # (3) zero tokens: nothing happens
+    b.n_tokens = 0
+    q.encode_moe_prefill(e, b)
+    e.wait()
