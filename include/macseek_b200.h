@@ -122,6 +122,15 @@ int msb_moe_decode_table_part(const msb_moe_decode_args* a, const uint64_t* tabl
  * parallelism) are computed, the others contribute nothing to y. */
 int msb_moe_decode_ids(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
                        int expert_hi, int part, void* stream);
+/* NO COUNTERPART IN THE REFERENCE.  msb_moe_decode_ids whose activation is RMSNorm(norm_in) * norm_w, computed inside
+ * the gate/up launch (a.x is ignored; same association as msb_router_fused_rmsnorm, so both see identical bits).  The
+ * launch builds the activation and runs the shared expert's gate/up rows BEFORE the previous kernel of the stream has
+ * finished, and waits for it only when it needs ids / weights.  Contract: the previous kernel of the stream is
+ * msb_router_fused_rmsnorm over the same norm_in (it releases its dependents only after everything before it has
+ * completed), and nothing between that launch and this one writes norm_in.  norm_in == NULL: plain msb_moe_decode_ids. */
+int msb_moe_decode_ids_normed(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
+                              int expert_hi, int part, const float* norm_in, const float* norm_w, float norm_eps,
+                              void* stream);
 
 /* ---------------------------------------------------------------- router
  * ms::arch::encode_router_fused / encode_router_topk / RouteLists / encode_route_lists (src/kernels/arch.hpp:79-97,

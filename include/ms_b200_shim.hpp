@@ -124,6 +124,16 @@ inline void encode_moe_decode_ids(Enc& e, const MoeDecodeArgs& a, const Buffer& 
   check(msb_moe_decode_ids(&c, (const uint64_t*)expert_table.ptr(), (const int*)ids.ptr(), expert_lo, expert_hi,
                            (int)part, e.stream), "encode_moe_decode_ids");
 }
+// Not in the reference: the same on x = RMSNorm(norm_in) * norm_w built inside the gate/up launch (a.x ignored); the
+// launch directly before in the stream must be encode_router_fused_rmsnorm over the same norm_in.
+inline void encode_moe_decode_ids_normed(Enc& e, const MoeDecodeArgs& a, const Buffer& expert_table, const Buffer& ids,
+                                         int expert_lo, int expert_hi, const Buffer& norm_in, const Buffer& norm_w,
+                                         float norm_eps, MoePart part = MoePart::All) {
+  const msb_moe_decode_args c = to_c(a);
+  check(msb_moe_decode_ids_normed(&c, (const uint64_t*)expert_table.ptr(), (const int*)ids.ptr(), expert_lo, expert_hi,
+                                  (int)part, (const float*)norm_in.ptr(), (const float*)norm_w.ptr(), norm_eps, e.stream),
+        "encode_moe_decode_ids_normed");
+}
 // prefill MoE (quant.hpp:87-118), with dim / inter as fields
 struct MoePrefillArgs {
   int dim = 5120, inter = 2304;

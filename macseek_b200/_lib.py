@@ -75,6 +75,7 @@ lib.msb_moe_decode.argtypes = [C.POINTER(MoeDecodeArgsC), _vp]
 lib.msb_moe_decode_noalloc.argtypes = [C.POINTER(MoeDecodeArgsC), _vp]
 lib.msb_moe_decode_table_part.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _i, _vp]
 lib.msb_moe_decode_ids.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _vp, _i, _i, _i, _vp]
+lib.msb_moe_decode_ids_normed.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _vp, _i, _i, _i, _vp, _vp, C.c_float, _vp]
 lib.msb_router_scratch_bytes.restype = C.c_size_t
 lib.msb_router_scratch_bytes.argtypes = [_i]
 lib.msb_router_fused.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _i, _f, _vp]

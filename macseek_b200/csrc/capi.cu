@@ -174,6 +174,21 @@ int msb_moe_decode_ids(const msb_moe_decode_args* a, const uint64_t* expert_tabl
   return moe_decode(p, a->t_gate_up, a->t_down, a->t_shared, part, a->scratch_bytes, (cudaStream_t)stream);
 }
 
+int msb_moe_decode_ids_normed(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
+                              int expert_hi, int part, const float* norm_in, const float* norm_w, float norm_eps,
+                              void* stream) {
+  if (!a) return fail(kErrArg, "moe_decode_ids_normed: null args");
+  msb_moe_decode_args b = *a;
+  if (norm_in) b.x = norm_in;     // only for the shared argument checks: the launch reads norm_in, never a.x
+  MoeParams p;
+  int rc = moe_fill(&b, &p);
+  if (rc) return rc;
+  if (!expert_table || !ids) return fail(kErrArg, "moe_decode_ids_normed: null table or ids");
+  p.table = expert_table; p.ids = ids; p.expert_lo = expert_lo; p.expert_hi = expert_hi;
+  if (norm_in) { p.x = nullptr; p.norm_in = norm_in; p.norm_w = norm_w; p.norm_eps = norm_eps; }
+  return moe_decode(p, a->t_gate_up, a->t_down, a->t_shared, part, a->scratch_bytes, (cudaStream_t)stream);
+}
+
 // ---- msb_moe_decode with library-resident scratch: no allocation of any kind on this path.
 // The scratch (the h rows of every routed slot + the shared expert) lives in a file-scope device array; its address is
 // looked up once per device with cudaGetSymbolAddress and handed to the kernels like a caller's buffer.

@@ -205,19 +205,31 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
       const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
       const int k = hd->local_slot[i];
       tl.G = hd->p0[i]; tl.U = hd->p1[i]; tl.r0 = rt * R_R; tl.R = R_R; tl.KS = 1; tl.rb = rb_r; tl.pitch = p.gu_r_pitch;
-      tl.hrow = p.h + (size_t)k * p.inter; tl.w = __ldg(p.weights + k);
+      tl.hrow = p.h + (size_t)k * p.inter; tl.w = __ldcg(p.weights + k);
     }
     return tl;
   };
   uint32_t n = 0;
   if (warp == kMoeNW) {
     int t = blockIdx.x;
-    const bool early = t < tiles_s;
-    if (early && !gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
-    __syncthreads();
-    pdl_wait();
+    if (p.norm_in) {
+      // every shared-expert tile is constant data and the consumers build the activation themselves: stream them
+      // all before the router's result is needed
+      while (t < tiles_s) {
+        if (!gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
+        t = next_tile(p.sched, lane);
+      }
+      pdl_wait();
+      if (lane == 0) resolve_local(p, hd, p.gu_r != 0, false);   // published to the consumers by the tiles' barriers
+      __syncwarp();
+    } else {
+      const bool early = t < tiles_s;
+      if (early && !gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
+      __syncthreads();
+      pdl_wait();
+      if (early) t = next_tile(p.sched, lane);
+    }
     const int ntiles = tiles_s + hd->n_local * tiles_r1;
-    if (early) t = next_tile(p.sched, lane);
     while (t < ntiles) {
       if (!gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
       t = next_tile(p.sched, lane);
@@ -227,10 +239,33 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
   }
   LaneLuts L;
   const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
-  pdl_wait();     // the router's ids / weights and x come from the previous kernels
-  if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
-  quantize_x(p.x, xq[0], tid, kMoeNW * 32);
-  __syncthreads();
+  bool resolved = true;
+  if (p.norm_in) {
+    // 1 / rms in the association of the router's fused norm (256 threads strided over the vector, eight warp sums
+    // added in order), so that both kernels see bit-identical activations
+    if (tid < 256) {
+      float ss = 0.f;
+      for (int i = tid; i < p.dim / 4; i += 256) {
+        const float4 v = reinterpret_cast<const float4*>(p.norm_in)[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) hd->part[0][warp][0] = ss;   // free until the first tile
+    }
+    bar_sync_named(1, kMoeNW * 32);
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += hd->part[0][i][0];
+    const float mul = rsqrtf(tot / (float)p.dim + p.norm_eps);
+    quantize_x(p.norm_in, xq[0], tid, kMoeNW * 32, mul, p.norm_w);
+    bar_sync_named(1, kMoeNW * 32);
+    resolved = false;
+  } else {
+    pdl_wait();     // the router's ids / weights and x come from the previous kernels
+    if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
+    quantize_x(p.x, xq[0], tid, kMoeNW * 32);
+    __syncthreads();
+  }
   if (!luts_ok) return;
   const bool two_pairs = R_R == kMoeNW * (32 / LPR) * 2;   // row pairs per lane group of a routed tile: 2 or 1
   uint32_t tile_count = 0;
@@ -238,6 +273,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
     if (!consumer_wait(ring, n)) return;
     const int t = *reinterpret_cast<volatile int*>(&hd->meta[n % ring.stages]);
     if (t < 0) return;
+    if (!resolved && t >= tiles_s) { pdl_wait(); resolved = true; }   // first routed tile: the router has finished
     const GuTile tl = tile_of(t);
     bool ok;
     if (t < tiles_s) ok = gu_tile_consume<TS, LPR, 1>(p, ring, n, tl, U, warp, lane, xq, L, hd, tile_count);
@@ -515,7 +551,9 @@ int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, s
   p.d_s = p.has_shared && (part == 0 || part == 2 || part == 3 || part == 5 || part == 7);
   if (p.n_routed == 0) p.gu_r = p.d_r = 0;
   if (!p.gu_r && !p.gu_s && !p.d_r && !p.d_s) return kOk;
-  if (!p.x || !p.y || !p.h || (p.gu_r && !p.weights)) return fail(kErrArg, "moe_decode: null pointer");
+  if ((!p.x && !p.norm_in) || !p.y || !p.h || (p.gu_r && !p.weights)) return fail(kErrArg, "moe_decode: null pointer");
+  if (p.norm_in && (!p.norm_w || ((reinterpret_cast<uintptr_t>(p.norm_in) | reinterpret_cast<uintptr_t>(p.norm_w)) & 15)))
+    return fail(kErrArg, "moe_decode: norm_in needs a gain vector, both 16-byte aligned");
   int rc = get_tables(&p.tb);
   if (rc) return rc;
   int dev = 0, sms = 0;

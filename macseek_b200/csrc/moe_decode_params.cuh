@@ -20,6 +20,12 @@ struct MoeParams {
   int expert_lo, expert_hi;               // experts resident on this GPU (with table)
   const float* weights;                   // device [n_routed]
   const float* x;
+  // not null: the gate/up launch ignores x and computes RMSNorm(norm_in) * norm_w itself, before the grid dependency
+  // resolves.  norm_in must have been complete before the PREVIOUS kernel of the stream started (the fused-norm router
+  // over the same vector is that kernel: it releases its dependents only after its own dependency resolved).
+  const float* norm_in;
+  const float* norm_w;
+  float norm_eps;
   float* y;
   float* h;                               // [n_routed + 1][inter]
   unsigned* sched;                        // [2] counter of tiles handed out after each block's first (tile = its

@@ -80,7 +80,6 @@ __device__ __forceinline__ void router_topk_warp(const float* logits, const floa
 // Fused decode router: every warp computes one (expert, K-slice) partial dot; the block that finishes last sums the
 // slices in a fixed order, writes the logits and selects.
 __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p) {
-  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit = blockIdx.x * 8 + warp;
   const int slice = p.dim / kRouterKSplit;   // floats per slice, a multiple of 4
@@ -96,6 +95,9 @@ __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p)
     a[k] = (live && c < slice / 4) ? __ldg(w + c) : zero4;
   }
   pdl_wait();
+  // Dependents are released only now: a dependent that starts may rely on everything before this launch being complete
+  // (the MoE gate/up launch reads the un-normalised vector before its own dependency resolves).
+  pdl_launch_dependents();
   // this unit's slice of x (and of the norm gain) is requested before the norm's reduction, not after it
   const float4* xv = reinterpret_cast<const float4*>(p.x + (size_t)ks * slice);
   const float4* gv = reinterpret_cast<const float4*>(p.norm_w ? p.norm_w + (size_t)ks * slice : p.x);

@@ -179,6 +179,7 @@ class SyntheticModel:
                                 norm_eps=c.norm_eps); n += 3
             return n
         # expert parallel: the router is replicated (every rank sees the same ids), partial sums combined over NVLink
+        b.y_part.zero_()     # before the router, which must be the launch directly ahead of the MoE pair
         arch.encode_router_fused_rmsnorm(e, b.h, w.ffn_norm, c.norm_eps, b.x, w.moe.router_w, w.moe.router_bias,
                                          b.moe.ids, b.moe.w, b.moe.router_scratch, c.top_k, c.score_fn,
                                          c.route_scale); n += 1
@@ -188,9 +189,9 @@ class SyntheticModel:
         a.t_gate_up, a.t_down, a.t_shared = c.t_gate_up, c.t_down, c.t_shared
         a.n_routed, a.has_shared, a.shared = c.top_k, self.ep_rank == 0, w.moe.shared
         a.weights, a.x, a.scratch = b.moe.w, b.x, b.moe.moe_scratch
-        b.y_part.zero_()
         a.y = b.y_part
-        q.encode_moe_decode_ids(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, q.MoePart.All); n += 2
+        q.encode_moe_decode_ids_normed(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, b.h, w.ffn_norm,
+                                       c.norm_eps, q.MoePart.All); n += 2
         ep.combine_routed(b.y_part, self.group)
         arch.encode_add(e, b.h, b.y_part, c.dim); n += 2
         return n

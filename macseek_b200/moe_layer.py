@@ -102,4 +102,8 @@ def encode_moe_layer(e: Enc, lw: MoeLayerWeights, b: MoeLayerBufs, x, y, score_f
     a.n_routed, a.has_shared = b.k, add_shared
     a.shared = lw.shared
     a.weights, a.x, a.y, a.scratch = b.w, x, y, b.moe_scratch
-    q.encode_moe_decode_ids(e, a, lw.table, b.ids, lw.expert_lo, lw.expert_hi)
+    if norm_in is not None:
+        # the router above is the launch directly before: the gate/up kernel may build x from norm_in on its own
+        q.encode_moe_decode_ids_normed(e, a, lw.table, b.ids, lw.expert_lo, lw.expert_hi, norm_in, norm_w, norm_eps)
+    else:
+        q.encode_moe_decode_ids(e, a, lw.table, b.ids, lw.expert_lo, lw.expert_hi)

@@ -166,6 +166,16 @@ def encode_moe_decode_ids(e: Enc, a: MoeDecodeArgs, expert_table, ids, expert_lo
     _lib.check(_lib.lib.msb_moe_decode_ids(c, ptr(expert_table), ptr(ids), expert_lo, expert_hi, int(part), e.handle))
 
 
+def encode_moe_decode_ids_normed(e: Enc, a: MoeDecodeArgs, expert_table, ids, expert_lo, expert_hi, norm_in, norm_w,
+                                 norm_eps, part=MoePart.All):
+    """encode_moe_decode_ids on x = RMSNorm(norm_in) * norm_w built inside the gate/up launch (a.x is ignored), which
+    then starts on the shared expert while the previous kernel -- the fused-norm router over the same norm_in, by
+    contract -- is still selecting.  No reference counterpart."""
+    c = a._c()
+    _lib.check(_lib.lib.msb_moe_decode_ids_normed(c, ptr(expert_table), ptr(ids), expert_lo, expert_hi, int(part),
+                                                  ptr(norm_in), ptr(norm_w), norm_eps, e.handle))
+
+
 def encode_matvec_rmsnorm(e: Enc, t, W, rows, cols, x, norm_w, eps, y):
     """y = W . (x * rsqrt(mean(x^2) + eps) * norm_w): input RMSNorm fused into the x load (quant.hpp:19-26)."""
     _lib.check(_lib.lib.msb_matvec_rmsnorm(int(t), ptr(W), rows, cols, ptr(x), ptr(norm_w), eps, ptr(y), e.handle))

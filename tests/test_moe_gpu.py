@@ -297,3 +297,58 @@ def test_router_fused_rmsnorm(orc, enc):
         rid, rw = orc.router(got_logits, np.zeros(E, np.float32), k, 1, 1.0)
         assert np.array_equal(ids.cpu().numpy(), rid)
         assert np.max(np.abs(w.cpu().numpy() - rw) / rw) <= 1e-5
+
+
+@pytest.mark.parametrize("types", ((ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, True), (ol.IQ2_XXS, ol.IQ2_XXS, ol.Q6_K, True),
+                                   (ol.IQ1_S, ol.IQ1_S, ol.Q8_0, False)),
+                         ids=lambda t: "%s-%s-%s%s" % (ol.TYPE_NAMES[t[0]], ol.TYPE_NAMES[t[1]], ol.TYPE_NAMES[t[2]],
+                                                      "-s" if t[3] else ""))
+def test_moe_decode_ids_normed_matches_two_step(orc, enc, types):
+    """The MoE launch that builds RMSNorm(h) * gain itself (and starts before the router ahead of it has finished) gives
+    the bits of: fused-norm router -> x, then the plain launch on x.  Repeated back to back, as in a decode step."""
+    from macseek_b200 import arch
+    gu, dn, sh, shared = types
+    n_exp, k, E = 16, 8, 16
+    case = MoeCase(4096, 2048, gu, dn, sh, k, shared, n_experts=n_exp, seed=5)
+    q = case.q
+    table = torch.tensor([[s.gate.data_ptr(), s.up.data_ptr(), s.down.data_ptr()] for s in case.slots[:n_exp]],
+                         dtype=torch.int64, device="cuda")
+    rng = np.random.default_rng(3)
+    W = dev((rng.standard_normal((E, case.D)) * 0.02).astype(np.float32))
+    gain = dev((1.0 + 0.1 * rng.standard_normal(case.D)).astype(np.float32))
+    s = arch.Scratch.create(E)
+    ids = torch.zeros(k, dtype=torch.int32, device="cuda")
+    w = torch.zeros(k, dtype=torch.float32, device="cuda")
+    xo = torch.zeros(case.D, dtype=torch.float32, device="cuda")
+    for trial in range(4):
+        h = dev(synth.randn(case.D, 300 + trial, 1.0 + trial))
+        outs = []
+        for normed in (False, True):
+            a = case.args()
+            a.weights, a.x = w, xo
+            a.y = dev(case.y0)
+            arch.encode_router_fused_rmsnorm(enc, h, gain, 1e-6, xo, W, None, ids, w, s, k, 1, 1.0)
+            if normed:
+                a.x = None
+                q.encode_moe_decode_ids_normed(enc, a, table, ids, 0, n_exp, h, gain, 1e-6)
+            else:
+                q.encode_moe_decode_ids(enc, a, table, ids, 0, n_exp)
+            enc.wait()
+            outs.append((a.y.cpu().numpy(), a.scratch.cpu().numpy()))
+        assert np.array_equal(bits(outs[0][0]), bits(outs[1][0])), trial
+        assert np.array_equal(bits(outs[0][1]), bits(outs[1][1])), trial
+    # expert-parallel style: no shared expert, only half of the experts resident
+    a = case.args()
+    a.weights, a.x, a.has_shared = w, None, False
+    a.y = torch.zeros(case.D, device="cuda")
+    b2 = case.args()
+    b2.weights, b2.x, b2.has_shared = w, xo, False
+    b2.y = torch.zeros(case.D, device="cuda")
+    arch.encode_router_fused_rmsnorm(enc, h, gain, 1e-6, xo, W, None, ids, w, s, k, 1, 1.0)
+    q.encode_moe_decode_ids_normed(enc, a, table, ids, 8, 16, h, gain, 1e-6)
+    arch.encode_router_fused_rmsnorm(enc, h, gain, 1e-6, xo, W, None, ids, w, s, k, 1, 1.0)
+    q.encode_moe_decode_ids(enc, b2, table, ids, 8, 16)
+    enc.wait()
+    assert np.array_equal(bits(a.y.cpu().numpy()), bits(b2.y.cpu().numpy()))
+    from macseek_b200 import _lib
+    assert _lib.device_status() == 0
