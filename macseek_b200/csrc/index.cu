@@ -386,7 +386,8 @@ __device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024]
 
 // forward declaration: the last step, run by the compaction block that finishes last
 __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, unsigned* fine, TopkCtl* ctl,
-                                 const int* sel, const uint2* cand, int* out, int bm_words, const int* pos_map);
+                                 const int* sel, const uint2* cand, int* out, int bm_words, const int* pos_map,
+                                 bool have_bin, int bin_known, unsigned above_known);
 
 // Compaction over the whole grid (blocks of 1024 threads), then the exact finish in the block that takes the last
 // ticket: one launch for the whole selection after the histogram.
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, pos_map);
+  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, pos_map, true, bstar, above);
 }
 
 // the last step as its own launch (one block)
@@ -472,15 +473,17 @@ __global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n
                                                           const int* pos_map) {
   pdl_launch_dependents();
   pdl_wait();
-  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, pos_map);
+  topk_final_block(sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, pos_map, false, 0, 0u);
 }
 
 // The selection's last step, run by ONE block of 1024 threads (the compaction block that finishes last).
 // out[k] ascending, -1 padded.  Resets the histograms and ctl for the next call.
 // pos_map != null: the scores are indexed by virtual position 8 * i + j standing for key pos_map[i] * 8 + j (candidate
 // list, ascending); the output lists key indices (still ascending, as the list is).
+// have_bin: the caller already holds the coarse threshold bin and the count above it (the compaction computed them).
 __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, unsigned* fine, TopkCtl* ctl,
-                                 const int* sel, const uint2* cand, int* out, int bm_words, const int* pos_map) {
+                                 const int* sel, const uint2* cand, int* out, int bm_words, const int* pos_map,
+                                 bool have_bin, int bin_known, unsigned above_known) {
   __shared__ unsigned sh[1024];
   __shared__ int buf[2048];
   __shared__ unsigned long long c2[1024];
@@ -494,8 +497,8 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
     else { const unsigned pos = atomicAdd(&s_cnt, 1u); if (pos < 2048u) buf[pos] = (int)idx; }
   };
   for (int i = tid; i < bm_words; i += NT) bitmap[i] = 0;
-  unsigned above;
-  const int bstar = threshold_bin(hist, k, sh, &above);
+  unsigned above = above_known;
+  const int bstar = have_bin ? bin_known : threshold_bin(hist, k, sh, &above);
   const unsigned n_sel = *reinterpret_cast<volatile unsigned*>(&ctl->n_sel);
   const unsigned n_cand = *reinterpret_cast<volatile unsigned*>(&ctl->n_cand);
   for (int i = tid; i < 2048; i += NT) buf[i] = 0x7fffffff;
