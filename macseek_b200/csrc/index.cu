@@ -353,35 +353,44 @@ __device__ __forceinline__ unsigned block_scan_incl(unsigned v, unsigned* wsum, 
   return x + (warp ? wsum[warp - 1] : 0u);
 }
 
-__device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024] */, unsigned* above_out) {
-  const int tid = threadIdx.x;   // blockDim.x == 1024 or 256; each thread owns a contiguous run of bins from the top
-  const int per = kHistBins / blockDim.x;
-  unsigned c[kHistBins / 256];
+// The thread's run of bins, from the top (blocks of kTopkThreads): issued early, consumed by threshold_from().
+constexpr int kTopkThreads = 1024;                 // block size of the selection kernels
+constexpr int kBinsPerThread = kHistBins / kTopkThreads;
+struct BinRun { unsigned c[kBinsPerThread]; };
+__device__ __forceinline__ void threshold_load(const unsigned* hist, BinRun& r) {
+#pragma unroll
+  for (int j = 0; j < kBinsPerThread; j++) r.c[j] = __ldcg(hist + (kHistBins - 1 - (threadIdx.x * kBinsPerThread + j)));
+}
+// count_out (may be null): the population of the threshold bin itself
+__device__ __forceinline__ int threshold_from(const BinRun& r, int k, unsigned* sh /* [1024] */, unsigned* above_out, unsigned* count_out) {
+  const int tid = threadIdx.x;
+  constexpr int per = kBinsPerThread;
   unsigned mine = 0;
 #pragma unroll
-  for (int j = 0; j < kHistBins / 256; j++) {
-    c[j] = j < per ? __ldcg(hist + (kHistBins - 1 - (tid * per + j))) : 0u;
-    mine += c[j];
-  }
+  for (int j = 0; j < kBinsPerThread; j++) mine += r.c[j];
   unsigned total;
   const unsigned incl = block_scan_incl(mine, sh, &total), excl = incl - mine;
   __shared__ int res_bin;
-  __shared__ unsigned res_above;
-  if (tid == 0) { res_bin = -1; res_above = total; }
+  __shared__ unsigned res_above, res_count;
+  if (tid == 0) { res_bin = -1; res_above = total; res_count = 0; }
   __syncthreads();
   if (excl < (unsigned)k && incl >= (unsigned)k) {   // the threshold lies in this thread's run
     unsigned run = excl;
 #pragma unroll
-    for (int j = 0; j < kHistBins / 256; j++) {
-      if (j < per) {
-        if (run + c[j] >= (unsigned)k) { res_bin = kHistBins - 1 - (tid * per + j); res_above = run; break; }
-        run += c[j];
-      }
+    for (int j = 0; j < kBinsPerThread; j++) {
+      if (run + r.c[j] >= (unsigned)k) { res_bin = kHistBins - 1 - (tid * per + j); res_above = run; res_count = r.c[j]; break; }
+      run += r.c[j];
     }
   }
   __syncthreads();
   *above_out = res_above;
+  if (count_out) *count_out = res_count;
   return res_bin;
+}
+__device__ int threshold_bin(const unsigned* hist, int k, unsigned* sh /* [1024] */, unsigned* above_out) {
+  BinRun r;
+  threshold_load(hist, r);
+  return threshold_from(r, k, sh, above_out, nullptr);
 }
 
 // forward declaration: the last step, run by the compaction block that finishes last
@@ -391,7 +400,7 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
 
 // Compaction over the whole grid (blocks of 1024 threads), then the exact finish in the block that takes the last
 // ticket: one launch for the whole selection after the histogram.
-__global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
+__global__ void __launch_bounds__(kTopkThreads, 2) topk_select_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
                                                            TopkCtl* ctl, int* sel, uint2* cand, int* out, int bm_words,
                                                            int fused, const int* pos_map) {
   pdl_launch_dependents();
@@ -399,13 +408,20 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
   __shared__ unsigned sh[1024];
   __shared__ unsigned sh_fine[kHistBins];
   __shared__ int is_last;
+  const int lane = threadIdx.x & 31;
+  const int per_block = (n + gridDim.x - 1) / gridDim.x;
+  const int i0 = blockIdx.x * per_block, i1 = min(n, i0 + per_block);
+  // the first trip's scores (usually the only trip) are requested together with the histogram, ahead of the scan
+  float f0[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = i0 + j * (int)blockDim.x + (int)threadIdx.x;
+    f0[j] = i < i1 ? sc[i] : -INFINITY;
+  }
   unsigned above;
   const int bstar = threshold_bin(hist, k, sh, &above);
   for (int b = threadIdx.x; b < kHistBins; b += blockDim.x) sh_fine[b] = 0;
   __syncthreads();
-  const int lane = threadIdx.x & 31;
-  const int per_block = (n + gridDim.x - 1) / gridDim.x;
-  const int i0 = blockIdx.x * per_block, i1 = min(n, i0 + per_block);
   // The block's picks are collected in shared memory first (dynamic region: per_block ints for the outright selections,
   // per_block (index, key) pairs for the threshold bin's members) and appended to the global lists with ONE atomic per
   // kind and block: thousands of same-address atomics from individual warps were the bulk of this kernel's time.
@@ -421,7 +437,7 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int i = base + j * (int)blockDim.x + (int)threadIdx.x;
-      f[j] = i < i1 ? sc[i] : -INFINITY;
+      f[j] = base == i0 ? f0[j] : (i < i1 ? sc[i] : -INFINITY);
     }
 #pragma unroll
     for (int j = 0; j < 4; j++) {
@@ -468,7 +484,7 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* sc, int 
 }
 
 // the last step as its own launch (one block)
-__global__ void __launch_bounds__(1024) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
+__global__ void __launch_bounds__(kTopkThreads) topk_final_kernel(const float* sc, int n, int k, unsigned* hist, unsigned* fine,
                                                           TopkCtl* ctl, const int* sel, const uint2* cand, int* out, int bm_words,
                                                           const int* pos_map) {
   pdl_launch_dependents();
@@ -489,32 +505,39 @@ __device__ void topk_final_block(const float* sc, int n, int k, unsigned* hist, 
   __shared__ unsigned long long c2[1024];
   __shared__ unsigned s_cnt, s_c2, s_need, s_digit;
   extern __shared__ unsigned bitmap[];          // bm_words words when the bitmap path is used (n <= 32 * bm_words)
-  const int tid = threadIdx.x, NT = blockDim.x;   // any multiple of 32 from 256 to 1024
+  const int tid = threadIdx.x, NT = blockDim.x;   // kTopkThreads
   // chosen indices go into a bitmap of the n positions (read back in ascending order: no sort), or, for very long
   // inputs that do not fit shared memory, into buf[] which is then sorted
   auto emit = [&](unsigned idx) {
     if (bm_words) atomicOr(&bitmap[idx >> 5], 1u << (idx & 31));
     else { const unsigned pos = atomicAdd(&s_cnt, 1u); if (pos < 2048u) buf[pos] = (int)idx; }
   };
+  // Every global read of the finish that does not depend on another one is requested here, together: the counters,
+  // the fine histogram, the first 2 NT outright selections and the first NT threshold-bin candidates.  One memory
+  // latency instead of four in a row on what is the serial tail of the selection.
+  const unsigned n_sel = *reinterpret_cast<volatile unsigned*>(&ctl->n_sel);
+  const unsigned n_cand = *reinterpret_cast<volatile unsigned*>(&ctl->n_cand);
+  BinRun fr;
+  threshold_load(fine, fr);
+  const int sel0 = __ldcg(sel + min(tid, 2047)), sel1 = __ldcg(sel + min(tid + NT, 2047));
+  const uint2 cand0 = __ldcg(cand + min(tid, max(n, 1) - 1));
   for (int i = tid; i < bm_words; i += NT) bitmap[i] = 0;
   unsigned above = above_known;
   const int bstar = have_bin ? bin_known : threshold_bin(hist, k, sh, &above);
-  const unsigned n_sel = *reinterpret_cast<volatile unsigned*>(&ctl->n_sel);
-  const unsigned n_cand = *reinterpret_cast<volatile unsigned*>(&ctl->n_cand);
   for (int i = tid; i < 2048; i += NT) buf[i] = 0x7fffffff;
   if (tid == 0) { s_cnt = 0; s_c2 = 0; }
   __syncthreads();
-  for (unsigned i = tid; i < n_sel && i < 2048u; i += NT) emit((unsigned)__ldcg(sel + i));
+  for (unsigned i = tid, j = 0; i < n_sel && i < 2048u; i += NT, j++)
+    emit((unsigned)(j == 0 ? sel0 : j == 1 ? sel1 : __ldcg(sel + i)));
   if (bstar >= 0 && n_cand > 0) {
     const unsigned need = (unsigned)k - above;   // how many of the threshold bin's members are taken
-    unsigned above2;
-    const int fstar = threshold_bin(fine, (int)need, sh, &above2);
-    const unsigned m2 = fstar >= 0 ? __ldcg(fine + fstar) : 0;
+    unsigned above2, m2;
+    const int fstar = threshold_from(fr, (int)need, sh, &above2, &m2);
     if (fstar >= 0 && m2 <= 1024u) {
       const unsigned need2 = need - above2;
 #pragma unroll 4
       for (unsigned i = tid; i < n_cand; i += NT) {
-        const uint2 cd = __ldcg(cand + i);
+        const uint2 cd = i == (unsigned)tid ? cand0 : __ldcg(cand + i);
         const unsigned idx = cd.x;
         const uint32_t key = cd.y;
         const int fb = (int)((key >> 8) & 0xFFFu);
@@ -687,8 +710,7 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
   }
   static const int fused = getenv("MSB_TOPK_FUSED") ? atoi(getenv("MSB_TOPK_FUSED")) : 1;   // tuning probe
   static const int env_blocks = getenv("MSB_TOPK_BLOCKS") ? atoi(getenv("MSB_TOPK_BLOCKS")) : 0;
-  static const int env_threads = getenv("MSB_TOPK_THREADS") ? atoi(getenv("MSB_TOPK_THREADS")) : 0;
-  const int nthreads = (env_threads == 256 || env_threads == 512) ? env_threads : 1024;
+  const int nthreads = kTopkThreads;
   // one element per thread and up to two blocks per SM: the per-block fixed work (threshold, fine histogram) is small
   // next to the latency of a longer per-thread loop
   int blocks = std::max(1, std::min(2 * sms * (1024 / nthreads), (n + nthreads - 1) / nthreads));
@@ -703,7 +725,7 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
                         fine, ctl, sel, cand, out, bm_words, 1, pos_map));
   } else {
     if (n > 0) MSB_CUDA(launch_pdl(topk_select_kernel, dim3(blocks), dim3(nthreads), stage_bytes, st, sc, n, k, hist, fine, ctl, sel, cand, out, bm_words, 0, pos_map));
-    MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(1024), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl,
+    MSB_CUDA(launch_pdl(topk_final_kernel, dim3(1), dim3(kTopkThreads), (size_t)bm_words * 4, st, sc, n, k, hist, fine, ctl,
                         (const int*)sel, (const uint2*)cand, out, bm_words, pos_map));
   }
   MSB_LAUNCH_CHECK("topk");
