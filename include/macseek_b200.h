@@ -136,7 +136,8 @@ int msb_moe_decode_ids_normed(const msb_moe_decode_args* a, const uint64_t* expe
  * ms::arch::encode_router_fused / encode_router_topk / RouteLists / encode_route_lists (src/kernels/arch.hpp:79-97,
  * arch.mm:173-239).  E experts (<= 512), top-k (<= 16); score_fn 0 = sqrt(softplus(logit)) (arch_router.metal:16-24),
  * 1 = sigmoid (reference/inference/model.py:816-817); key = score + bias (bias may be NULL); ties -> lowest id;
- * w = score / (sum + 1e-20) * route_scale; ids / w in descending key order. */
+ * w = score / (sum + 1e-20) * route_scale; ids / w in descending key order.  scratch (fused forms): at least
+ * msb_router_scratch_bytes(E) bytes, 16-byte aligned; afterwards its first E floats are the logits. */
 /* ---- MoE prefill: ms::q::MoePrefillArgs / moe_prefill_scratch_bytes / encode_moe_prefill (src/kernels/quant.hpp:87-118).
  * Grouped expert GEMMs on the tensor cores (tcgen05) with half operands and fp32 accumulation, as the reference's tensor
  * path.  Routing is expert-sorted: routed expert j owns entries [offs[j], offs[j+1]) of tok[] (token row in X) and wt[];

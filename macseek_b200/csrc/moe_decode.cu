@@ -32,25 +32,35 @@ __device__ __forceinline__ float swiglu(float g, float u, float w, float limit) 
   return g / (1.f + expf(-g)) * u * w;
 }
 
-// Resolve which routed slots are handled by this GPU and their matrix addresses.  Thread 0 only.
-__device__ __forceinline__ void resolve_local(const MoeParams& p, MoeSmemHead* hd, bool want_routed, bool down) {
-  int nl = 0;
-  if (want_routed) {
-    for (int k = 0; k < p.n_routed; k++) {
-      if (p.table) {
-        const int id = p.ids ? p.ids[k] : k;          // no ids: the table holds one entry per routed slot
-        if (p.ids && (id < p.expert_lo || id >= p.expert_hi)) continue;
+// Resolve which routed slots are handled by this GPU and their matrix addresses.  Called by ONE WHOLE WARP: lane k looks
+// slot k up (its id, then its table row: two dependent reads, all slots at once rather than one after the other) and
+// the resident ones are compacted in slot order.
+__device__ __forceinline__ void resolve_local(const MoeParams& p, MoeSmemHead* hd, bool want_routed, bool down, int lane) {
+  static_assert(kMaxRouted <= 32, "one lane per routed slot");
+  bool mine = want_routed && lane < p.n_routed;
+  const uint8_t* a0 = nullptr;
+  const uint8_t* a1 = nullptr;
+  if (mine) {
+    if (p.table) {
+      const int id = p.ids ? p.ids[lane] : lane;       // no ids: the table holds one entry per routed slot
+      if (p.ids && (id < p.expert_lo || id >= p.expert_hi)) mine = false;
+      if (mine) {
         const uint64_t* row = p.table + (size_t)id * 3;
-        hd->p0[nl] = reinterpret_cast<const uint8_t*>(down ? row[2] : row[0]);
-        hd->p1[nl] = reinterpret_cast<const uint8_t*>(row[1]);
-      } else {
-        hd->p0[nl] = down ? p.down[k] : p.gate[k];
-        hd->p1[nl] = p.up[k];
+        a0 = reinterpret_cast<const uint8_t*>(down ? row[2] : row[0]);
+        a1 = reinterpret_cast<const uint8_t*>(row[1]);
       }
-      hd->local_slot[nl++] = k;
+    } else {
+      a0 = down ? p.down[lane] : p.gate[lane];
+      a1 = p.up[lane];
     }
   }
-  hd->n_local = nl;
+  const unsigned m = __ballot_sync(0xffffffffu, mine);
+  if (mine) {
+    const int pos = __popc(m & ((1u << lane) - 1u));
+    hd->p0[pos] = a0; hd->p1[pos] = a1; hd->local_slot[pos] = lane;
+  }
+  if (lane == 0) hd->n_local = __popc(m);
+  __syncwarp();
 }
 
 __device__ __forceinline__ void finish_block(unsigned* sched) {
@@ -220,8 +230,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
         t = next_tile(p.sched, lane);
       }
       pdl_wait();
-      if (lane == 0) resolve_local(p, hd, p.gu_r != 0, false);   // published to the consumers by the tiles' barriers
-      __syncwarp();
+      resolve_local(p, hd, p.gu_r != 0, false, lane);   // published to the consumers by the tiles' barriers
     } else {
       const bool early = t < tiles_s;
       if (early && !gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
@@ -262,7 +271,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
     resolved = false;
   } else {
     pdl_wait();     // the router's ids / weights and x come from the previous kernels
-    if (tid == 0) resolve_local(p, hd, p.gu_r != 0, false);
+    if (warp == 0) resolve_local(p, hd, p.gu_r != 0, false, lane);
     quantize_x(p.x, xq[0], tid, kMoeNW * 32);
     __syncthreads();
   }
@@ -364,7 +373,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   LaneLuts L;
   const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
   pdl_wait();     // h comes from the gate/up kernel
-  if (tid == 0) resolve_local(p, hd, p.d_r != 0, true);
+  if (warp == 0) resolve_local(p, hd, p.d_r != 0, true, lane);
   quantize_x(p.h, xq[0], tid, kMoeNW * 32);
   __syncthreads();
   if (!luts_ok) return;

@@ -35,16 +35,31 @@ __device__ __forceinline__ float router_score(float x, int score_fn) {
 }
 
 // One warp selects the top-k experts of one token (descending key; ties -> lowest id) and writes ids / weights.
-__device__ __forceinline__ void router_topk_warp(const float* logits, const float* bias, int E, int k, int score_fn,
-                                                 float route_scale, int lane, int* ids, float* wts) {
-  constexpr int EPL = kRouterMaxE / 32;
+// The bias values of the lane's experts (e = lane + 32 i) are passed in registers so that a caller can request them
+// ahead of the logits.
+constexpr int kRouterEPL = kRouterMaxE / 32;
+__device__ __forceinline__ void router_load_bias(const float* bias, int E, int lane, float (&bz)[kRouterEPL]) {
+#pragma unroll
+  for (int i = 0; i < kRouterEPL; i++) {
+    const int e = lane + 32 * i;
+    bz[i] = (bias && e < E) ? __ldg(bias + e) : 0.f;
+  }
+}
+// order-preserving map of a float onto an unsigned (NaN -> 0, below everything)
+__device__ __forceinline__ unsigned router_ord(float f) {
+  const unsigned u = __float_as_uint(f);
+  return f == f ? (u ^ ((unsigned)((int)u >> 31) | 0x80000000u)) : 0u;
+}
+__device__ __forceinline__ void router_topk_warp(const float* logits, const float (&bz)[kRouterEPL], int E, int k,
+                                                 int score_fn, float route_scale, int lane, int* ids, float* wts) {
+  constexpr int EPL = kRouterEPL;
   float sc[EPL], key[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; i++) {
     const int e = lane + 32 * i;
     if (e < E) {
       sc[i] = router_score(logits[e], score_fn);
-      key[i] = sc[i] + (bias ? bias[e] : 0.f);
+      key[i] = sc[i] + bz[i];
     } else {
       sc[i] = 0.f;
       key[i] = -INFINITY;
@@ -53,23 +68,27 @@ __device__ __forceinline__ void router_topk_warp(const float* logits, const floa
   float sum = 0.f, my_w = 0.f;
   int my_e = 0;
   unsigned taken = 0;
+  bool rescan = true;
+  float bk = -INFINITY, bs = 0.f;
+  int be = 0x7fffffff;
   for (int j = 0; j < k; j++) {
-    // this lane's best remaining candidate: ascending expert id with a strict compare keeps the lowest id on ties
-    float bk = -INFINITY, bs = 0.f;
-    int be = 0x7fffffff;
+    // this lane's best remaining candidate: ascending expert id with a strict compare keeps the lowest id on ties;
+    // only the lane that lost its candidate in the previous round looks again
+    if (rescan) {
+      bk = -INFINITY; bs = 0.f; be = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < EPL; i++) {
-      const int e = lane + 32 * i;
-      if (e < E && !((taken >> i) & 1u) && (be == 0x7fffffff || key[i] > bk)) { bk = key[i]; bs = sc[i]; be = e; }
+      for (int i = 0; i < EPL; i++) {
+        const int e = lane + 32 * i;
+        if (e < E && !((taken >> i) & 1u) && (be == 0x7fffffff || key[i] > bk)) { bk = key[i]; bs = sc[i]; be = e; }
+      }
+      rescan = false;
     }
-    float m = bk;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    int win = (bk == m) ? be : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) win = min(win, __shfl_xor_sync(0xffffffffu, win, o));
+    // warp-wide: the largest key, then the lowest expert id that holds it (one reduction instruction each)
+    const unsigned uk = be == 0x7fffffff ? 0u : router_ord(bk);
+    const unsigned m = __reduce_max_sync(0xffffffffu, uk);
+    const int win = (int)__reduce_min_sync(0xffffffffu, (uk == m) ? (unsigned)be : 0x7fffffffu);
     const float wscore = __shfl_sync(0xffffffffu, bs, win & 31);   // the owner's best candidate is the winner
-    if (lane == (win & 31)) taken |= 1u << (win >> 5);
+    if (lane == (win & 31)) { taken |= 1u << (win >> 5); rescan = true; }
     sum += wscore;
     if (lane == j) { my_e = win; my_w = wscore; }
   }
@@ -160,15 +179,19 @@ __global__ void __launch_bounds__(256) router_fused_kernel(const RouterParams p)
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // the finishing block: the serial tail of the launch.  Bias (constant) and partial sums are requested together; the
+  // logits reach the selecting warp through shared memory (the copy in global memory is a diagnostic).
+  __shared__ float s_logits[kRouterMaxE];
+  float bz[kRouterEPL];
+  if (warp == 0) router_load_bias(p.bias, p.E, lane, bz);
   for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-    const volatile float* q = p.partial + (size_t)e * kRouterKSplit;
-    float s = q[0];
-#pragma unroll
-    for (int i = 1; i < kRouterKSplit; i++) s += q[i];
+    const float4 q = __ldcg(reinterpret_cast<const float4*>(p.partial) + e);
+    const float s = ((q.x + q.y) + q.z) + q.w;
     p.logits[e] = s;
+    s_logits[e] = s;
   }
   __syncthreads();
-  if (warp == 0) router_topk_warp(p.logits, p.bias, p.E, p.k, p.score_fn, p.route_scale, lane, p.ids, p.wts);
+  if (warp == 0) router_topk_warp(s_logits, bz, p.E, p.k, p.score_fn, p.route_scale, lane, p.ids, p.wts);
   if (threadIdx.x == 0) *p.ticket = 0;
 }
 
@@ -179,7 +202,9 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* logits, c
   pdl_wait();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= n) return;
-  router_topk_warp(logits + (size_t)t * E, bias, E, k, score_fn, route_scale, threadIdx.x & 31, ids + (size_t)t * k,
+  float bz[kRouterEPL];
+  router_load_bias(bias, E, threadIdx.x & 31, bz);
+  router_topk_warp(logits + (size_t)t * E, bz, E, k, score_fn, route_scale, threadIdx.x & 31, ids + (size_t)t * k,
                    wts + (size_t)t * k);
 }
 
@@ -241,7 +266,8 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int* ids, cons
 }
 
 // ---------------------------------------------------------------- host side
-size_t router_scratch_bytes(int E) { return sizeof(float) * (size_t)E * (1 + kRouterKSplit); }
+// logits [E], padded to a multiple of 4 floats so that the partials [E][4] behind them are 16-byte aligned
+size_t router_scratch_bytes(int E) { return sizeof(float) * ((size_t)((E + 3) & ~3) + (size_t)E * kRouterKSplit); }
 
 int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_out, const float* W, const float* bias,
                  int* ids, float* wts, void* scratch, size_t scratch_bytes, int E, int dim, int k, int score_fn,
@@ -250,6 +276,8 @@ int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_o
     return fail(kErrArg, "router: bad shape (E %d dim %d k %d)", E, dim, k);
   if (!x || !W || !ids || !wts || !scratch) return fail(kErrArg, "router: null pointer");
   if (scratch_bytes < router_scratch_bytes(E)) return fail(kErrScratch, "router: scratch too small");
+  if (reinterpret_cast<uintptr_t>(scratch) & 15) return fail(kErrArg, "router: scratch must be 16-byte aligned");
+  static_assert(kRouterKSplit == 4, "the finishing block reads one float4 of partials per expert");
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return fail(kErrArg, "router: x and W must be 16-byte aligned");
   Tables tb;
@@ -261,7 +289,7 @@ int router_fused(const float* x, const float* norm_w, float norm_eps, float* x_o
   p.x = x; p.norm_w = norm_w; p.norm_eps = norm_eps; p.x_out = norm_w ? x_out : nullptr;
   p.W = W; p.bias = bias; p.ids = ids; p.wts = wts;
   p.logits = reinterpret_cast<float*>(scratch);
-  p.partial = p.logits + E;
+  p.partial = p.logits + ((E + 3) & ~3);
   p.ticket = reinterpret_cast<unsigned*>(tb.status) + 16;
   p.E = E; p.dim = dim; p.k = k; p.score_fn = score_fn; p.route_scale = route_scale;
   const int units = E * kRouterKSplit;
