@@ -56,6 +56,13 @@ int msb_matvec(int qtype, const void* W, int rows, int cols, const float* x, flo
  * excludes the IQ types). */
 int msb_matvec_rmsnorm(int qtype, const void* W, int rows, int cols, const float* x, const float* norm_w, float eps,
                        float* y, void* stream);
+/* NO COUNTERPART IN THE REFERENCE.  msb_matvec_rmsnorm as a launch that shares the GPU: one small block per SM (96 KB of
+ * shared memory, 288 threads) instead of filling every SM, so that kernels of ANOTHER stream (or graph branch) that
+ * do not depend on it run beside it.  Slower alone, meant to hide under a latency-bound chain.  Same result as
+ * msb_matvec_rmsnorm up to the fp32 summation order.  Types with a shared-memory codebook (IQ1_S, IQ2_XXS, IQ4_NL) and
+ * rows too long for the small block fall back to the ordinary launch. */
+int msb_matvec_rmsnorm_shared(int qtype, const void* W, int rows, int cols, const float* x, const float* norm_w, float eps,
+                              float* y, void* stream);
 /* Y[n x rows] (+)= X[n x cols*groups] . W^T, 1 <= n <= 16 -- ms::q::encode_matvec_n (quant.hpp:32-35, quant.mm:129-156).
  * Row stride of X = cols*groups, of Y = rows. */
 int msb_matvec_n(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate,

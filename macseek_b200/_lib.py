@@ -100,3 +100,4 @@ lib.msb_kv_window.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]
 lib.msb_argmax.argtypes = [_vp, _i, _vp, _vp, _vp]
 lib.msb_add.argtypes = [_vp, _vp, _i, _vp]
 lib.msb_matvec_rmsnorm.argtypes = [_i, _vp, _i, _i, _vp, _vp, _f, _vp, _vp]
+lib.msb_matvec_rmsnorm_shared.argtypes = [_i, _vp, _i, _i, _vp, _vp, _f, _vp, _vp]

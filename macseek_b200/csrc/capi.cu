@@ -8,7 +8,7 @@ namespace msb {
 const char* last_error_text();
 int dequant(int t, const void* src, int64_t n, float* out, cudaStream_t st);
 int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x_stride, float* Y, int64_t y_stride,
-             int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st);
+             int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st, bool share = false);
 int index_scores_tc(const void* keys, int len, const float* q, const float* w, int heads, float* scores, unsigned* hist,
                     int prep, const float* cs, int actq, float* q_out, float* w_out, const int* cand, int n_cand,
                     cudaStream_t st);
@@ -105,6 +105,12 @@ int msb_matvec_rmsnorm(int qtype, const void* W, int rows, int cols, const float
                        float* y, void* stream) {
   if (!norm_w) return fail(kErrArg, "matvec_rmsnorm: null norm_w");
   return matvec_n(qtype, W, rows, cols, x, cols, y, rows, 1, 0, 1, norm_w, eps, (cudaStream_t)stream);
+}
+
+int msb_matvec_rmsnorm_shared(int qtype, const void* W, int rows, int cols, const float* x, const float* norm_w, float eps,
+                              float* y, void* stream) {
+  if (!norm_w) return fail(kErrArg, "matvec_rmsnorm_shared: null norm_w");
+  return matvec_n(qtype, W, rows, cols, x, cols, y, rows, 1, 0, 1, norm_w, eps, (cudaStream_t)stream, true);
 }
 
 int msb_matvec_n(int qtype, const void* W, int rows, int cols, const float* X, float* Y, int n, int accumulate,

@@ -27,7 +27,7 @@ namespace msb {
 constexpr int kTcDim = 128;               // key bytes = contraction length
 constexpr int kTcTile = 128;              // keys per tile = MMA M
 constexpr int kTcTileBytes = kTcTile * kTcDim;
-constexpr int kTcStages = 8;
+constexpr int kTcStages = 6;
 constexpr int kTcThreads = 6 * 32;
 constexpr int kTcHistBins = 4096;
 constexpr uint32_t kTcSbo = 1024;          // bytes between 8-row groups of the swizzled K-major layout (8 x 128)

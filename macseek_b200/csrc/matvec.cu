@@ -17,6 +17,8 @@ namespace msb {
 
 constexpr int kMvNW = 16;
 constexpr size_t kLightSmemLimit = 110 * 1024;   // a light block's shared memory: two fit one SM
+constexpr size_t kShareSmemLimit = 96 * 1024;    // a sharing launch: ONE light block per SM, the rest of the SM left free
+thread_local bool g_share_launch = false;        // set around a launch by matvec_n(..., share = true)
 
 struct MvParams {
   const uint8_t* W;
@@ -253,8 +255,9 @@ int launch_cfg(MvParams& p, size_t fixed, int stages, size_t slot_bytes, cudaStr
 template <int T, int LPR, int NC, int NW>
 int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms_real) {
   // light blocks: two per SM, each within half of the SM's shared memory
-  const int sms = NW == 8 ? 2 * sms_real : sms_real;
-  const size_t smem_limit = NW == 8 ? kLightSmemLimit : (size_t)kSmemLimit;
+  const bool share = NW == 8 && g_share_launch;
+  const int sms = (NW == 8 && !share) ? 2 * sms_real : sms_real;
+  const size_t smem_limit = share ? kShareSmemLimit : NW == 8 ? kLightSmemLimit : (size_t)kSmemLimit;
   constexpr int G = 32 / LPR;
   constexpr int kMaxNR = (T == IQ1_S || T == IQ2_XXS) ? 4 : 2;
   const size_t fixed = ((sizeof(MvSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(T) +
@@ -342,8 +345,11 @@ int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
     light = env_light < 0 ? total <= (size_t)96 << 20 : env_light != 0;
     const size_t fixed_l = (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 1024;
     if (fixed_l + 2 * 16384 > kLightSmemLimit) light = false;
+    const size_t light_limit = (g_share_launch && fixed_l + 2 * 16384 <= kShareSmemLimit) ? kShareSmemLimit : kLightSmemLimit;
+    if (light_limit == kLightSmemLimit) g_share_launch = false;    // does not fit the sharing form: an ordinary launch
+    else light = true;
     if (light) {
-      const size_t cap = (kLightSmemLimit - fixed_l) / 2;
+      const size_t cap = (light_limit - fixed_l) / 2;
       // Q6_K rows are split by half super-block (4 units), the other types by unit
       switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, cap, 8)) {
         case 32: return launch_rows<T, 32, NC, 8>(p, st, dev, sms);
@@ -381,7 +387,8 @@ int launch_cols(int t, MvParams& p, cudaStream_t st, int dev, int sms) {
 // Y[n x rows] (+)= X[n x cols*groups] . W^T.  n columns are processed four (then two, then one) at a time; each pass
 // streams W once.  norm_w != null fuses the input RMSNorm (groups must be 1).
 int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x_stride, float* Y, int64_t y_stride,
-             int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st) {
+             int n, int accumulate, int groups, const float* norm_w, float norm_eps, cudaStream_t st, bool share) {
+  struct ShareScope { ShareScope(bool s) { g_share_launch = s; } ~ShareScope() { g_share_launch = false; } } scope(share);
   if (!type_known(t)) return fail(kErrType, "matvec: unsupported weight type %d", t);
   const int qk = block_elems(t) == 1 ? 32 : block_elems(t);
   if (rows <= 0 || cols <= 0 || n <= 0 || groups < 1 || rows % groups != 0 || cols % qk != 0 || cols % 32 != 0)

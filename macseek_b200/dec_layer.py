@@ -150,6 +150,7 @@ class SyntheticModel:
         self.out_norm = torch.ones(c.dim, dtype=torch.float32, device=device)
         self.w_head = synthetic.random_weights(c.t_head, c.vocab, c.dim, gen)
         self.bufs = DecBufs(c, device)
+        self.side_stream = torch.cuda.Stream(device=device)
         self.launches_per_token = 0
 
     # ------------------------------------------------------------------ one layer
@@ -159,11 +160,18 @@ class SyntheticModel:
         # the input RMSNorms are fused into the activation load of the matvecs that consume them
         q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_a_kv, c.q_lora + c.D, c.dim, b.h, w.attn_norm, c.norm_eps, b.qa_kv); n += 1
         q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_proj, c.index_heads, c.dim, b.h, w.attn_norm, c.norm_eps, b.iw); n += 1
-        q.encode_matvec_rmsnorm(e, c.t_attn, w.wq_b, c.heads * c.D, c.q_lora, b.qa, w.q_norm, c.norm_eps, b.qfull); n += 1
         q.encode_matvec_rmsnorm(e, c.t_index, w.w_idx_qb, c.index_heads * c.index_dim, c.q_lora, b.qa, w.q_norm,
                                 c.norm_eps, b.iq); n += 1
+        # The query projection (bandwidth) and the index decode (a latency chain) depend on nothing of each other:
+        # q_b runs on a second stream as one small block per SM, under the index decode, and joins before the
+        # attention that needs both.
+        side = self.side_stream
+        side.wait_stream(e.stream)
+        q.encode_matvec_rmsnorm_shared(Enc(side), c.t_attn, w.wq_b, c.heads * c.D, c.q_lora, b.qa, w.q_norm, c.norm_eps,
+                                       b.qfull); n += 1
         attn.encode_kv_window(e, st, b.kv, w.kv_norm, pos); n += 1
         attn.encode_index_decode(e, st, b.iq, b.iw, pos, c.kv_len, actq=False); n += 2   # tcgen05 scoring (+ prep), selection
+        e.stream.wait_stream(side)
         attn.encode_sparse(e, st, b.qfull, w.sinks, b.attn_out, pos); n += 2
         q.encode_matvec(e, c.t_attn, w.wo_a, c.o_a_rows, c.heads * c.D // c.o_groups, b.attn_out, b.oa, False,
                         c.o_groups); n += 1

@@ -293,8 +293,9 @@ def layer_stages(n_layers: int = 8, kv_len: int = 200000):
         setattr(mod, name, g)
         return f
     saved = [(mod, nm, wrap(mod, nm)) for mod, nm in (
-        (q, "encode_matvec_rmsnorm"), (q, "encode_matvec"), (attn, "encode_kv_window"), (attn, "encode_index_decode"),
-        (attn, "encode_sparse"), (arch, "encode_router_fused_rmsnorm"), (q, "encode_moe_decode_ids"))]
+        (q, "encode_matvec_rmsnorm"), (q, "encode_matvec_rmsnorm_shared"), (q, "encode_matvec"), (attn, "encode_kv_window"), (attn, "encode_index_decode"),
+        (attn, "encode_sparse"), (arch, "encode_router_fused_rmsnorm"), (q, "encode_moe_decode_ids"),
+        (q, "encode_moe_decode_ids_normed"))]
     stream = torch.cuda.Stream()
 
     def encode(e):

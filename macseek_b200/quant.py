@@ -181,6 +181,12 @@ def encode_matvec_rmsnorm(e: Enc, t, W, rows, cols, x, norm_w, eps, y):
     _lib.check(_lib.lib.msb_matvec_rmsnorm(int(t), ptr(W), rows, cols, ptr(x), ptr(norm_w), eps, ptr(y), e.handle))
 
 
+def encode_matvec_rmsnorm_shared(e: Enc, t, W, rows, cols, x, norm_w, eps, y):
+    """encode_matvec_rmsnorm as a launch of one small block per SM, leaving room for another stream's kernels beside
+    it (no reference counterpart)."""
+    _lib.check(_lib.lib.msb_matvec_rmsnorm_shared(int(t), ptr(W), rows, cols, ptr(x), ptr(norm_w), eps, ptr(y), e.handle))
+
+
 def moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim=5120, inter=2304):
     return _lib.lib.msb_moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim, inter)
 

@@ -185,3 +185,31 @@ def test_matvec_rmsnorm_fused(orc, q, enc, t):
     enc.wait()
     ry, mag = orc.matvec(t, W, rows, cols, orc.rmsnorm(x, nw, 1e-6))
     assert orc.max_norm_err(y.cpu().numpy(), ry, mag) <= TOL
+
+
+@pytest.mark.parametrize("t,rows,cols", ((ol.Q6_K, 16384, 1024), (ol.Q6_K, 1280, 4096), (ol.Q8_0, 4096, 4096),
+                                         (ol.BF16, 512, 2048), (ol.IQ1_S, 1280, 4096), (ol.Q6_K, 96, 16384)))
+def test_matvec_rmsnorm_shared_launch(orc, q, enc, t, rows, cols):
+    """The launch form that leaves room on every SM for another stream (one small block per SM): same values as the
+    oracle; table types and rows too long for the small block take the ordinary launch.  Also run beside work on a
+    second stream."""
+    W = synth.random_weights(t, rows, cols, 31)
+    x = synth.randn(cols, 32, 2.0)
+    nw = (1 + 0.1 * synth.randn(cols, 33)).astype(np.float32)
+    Wd, xd, nd = dev(W), dev(x), dev(nw)
+    y = torch.zeros(rows, device="cuda")
+    q.encode_matvec_rmsnorm_shared(enc, t, Wd, rows, cols, xd, nd, 1e-6, y)
+    enc.wait()
+    ry, mag = orc.matvec(t, W, rows, cols, orc.rmsnorm(x, nw, 1e-6))
+    assert orc.max_norm_err(y.cpu().numpy(), ry, mag) <= TOL
+    # beside an ordinary launch on another stream
+    from macseek_b200.core import Enc
+    side = torch.cuda.Stream()
+    y2, y3 = torch.zeros(rows, device="cuda"), torch.zeros(rows, device="cuda")
+    side.wait_stream(enc.stream)
+    q.encode_matvec_rmsnorm_shared(Enc(side), t, Wd, rows, cols, xd, nd, 1e-6, y2)
+    q.encode_matvec_rmsnorm(enc, t, Wd, rows, cols, xd, nd, 1e-6, y3)
+    enc.stream.wait_stream(side)
+    enc.wait()
+    assert np.array_equal(y2.cpu().numpy().view(np.uint32), y.cpu().numpy().view(np.uint32))
+    assert orc.max_norm_err(y3.cpu().numpy(), ry, mag) <= TOL
