@@ -55,6 +55,12 @@ inline void encode_matvec_rmsnorm(Enc& e, QType t, const Buffer& W, int rows, in
   check(msb_matvec_rmsnorm((int)t, W.ptr(), rows, cols, (const float*)x.ptr(), (const float*)norm_w.ptr(), eps,
                            (float*)y.ptr(), e.stream), "encode_matvec_rmsnorm");
 }
+// Not in the reference: the same as a launch of one small block per SM, for a second stream that runs beside another.
+inline void encode_matvec_rmsnorm_shared(Enc& e, QType t, const Buffer& W, int rows, int cols, const Buffer& x,
+                                         const Buffer& norm_w, float eps, const Buffer& y) {
+  check(msb_matvec_rmsnorm_shared((int)t, W.ptr(), rows, cols, (const float*)x.ptr(), (const float*)norm_w.ptr(), eps,
+                                  (float*)y.ptr(), e.stream), "encode_matvec_rmsnorm_shared");
+}
 inline void encode_matvec_n(Enc& e, QType t, const Buffer& W, int rows, int cols, const Buffer& X, const Buffer& Y, int n,
                             bool accumulate = false, int groups = 1) {
   check(msb_matvec_n((int)t, W.ptr(), rows, cols, (const float*)X.ptr(), (float*)Y.ptr(), n, accumulate, groups, e.stream),
