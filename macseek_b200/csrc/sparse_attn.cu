@@ -282,6 +282,14 @@ __global__ void __launch_bounds__(D / 4) sparse_combine_kernel(const SparseParam
   __shared__ float fs[1024];      // per-split rescale factors exp(m_s - M)
   __shared__ float ls[1024];
   const int h = blockIdx.x, t = threadIdx.x, d = blockIdx.y * DQ + t;
+  // this thread's partial outputs of the first kPre splits are requested before anything else: one memory latency for
+  // all of them, under the staging of (m, l) below, instead of a batch of loads per 16 splits afterwards
+  constexpr int kPre = 72;
+  const float* po = p.part_o + (size_t)h * D + d;
+  const size_t stride = (size_t)p.H * D;
+  float pv[kPre];
+#pragma unroll
+  for (int s = 0; s < kPre; s++) pv[s] = s < p.splits ? __ldcg(po + (size_t)s * stride) : 0.f;
   const float sink = p.sinks[h];
   // every thread needs M and the denominator: stage (m, l) of all splits once, then every thread reduces them from
   // shared memory in the same order
@@ -298,10 +306,11 @@ __global__ void __launch_bounds__(D / 4) sparse_combine_kernel(const SparseParam
   float den = expf(sink - M);
   for (int s = 0; s < p.splits; s++) den += ls[s] * fs[s];
   float acc = 0.f;
-  const float* po = p.part_o + (size_t)h * D + d;
-  const size_t stride = (size_t)p.H * D;
+#pragma unroll
+  for (int s = 0; s < kPre; s++)
+    if (s < p.splits) acc += pv[s] * fs[s];
 #pragma unroll 16
-  for (int s = 0; s < p.splits; s++) acc += po[(size_t)s * stride] * fs[s];
+  for (int s = kPre; s < p.splits; s++) acc += po[(size_t)s * stride] * fs[s];
   xs[t] = acc / den;
   __syncthreads();
   float v = xs[t];
