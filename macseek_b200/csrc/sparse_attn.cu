@@ -120,20 +120,33 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
     cp_async_commit();
   };
 
-  // the first tile's rows are requested before anything else: the round trip overlaps the query prologue
-  if (nit > 0) gather(0, 0);
   // ---- query fragments for this warp's contraction range, roped, as hi + lo terms.  The 16 heads' queries pass
-  // through the (still unused) second row buffer with coalesced 16-byte loads.
+  // through the (still unused) second row buffer with coalesced 16-byte loads.  Every independent global read of the
+  // prologue is requested before the first dependent one: the queries and the rope factors first, then the first
+  // tile's rows (whose addresses wait for the selected indices), so that one round trip covers them all.
+  constexpr int kQ4 = kSaHeadsPerBlock * D / 4 / 128;   // 16-byte pieces per thread (16 or 18)
+  static_assert(kSaHeadsPerBlock * D / 4 % 128 == 0, "query staging assumes a whole number of pieces per thread");
+  float4 qv[kQ4];
+  {
+    const float4* src = reinterpret_cast<const float4*>(p.q + (size_t)hg * kSaHeadsPerBlock * D);
+#pragma unroll
+    for (int i = 0; i < kQ4; i++) qv[i] = src[tid + 128 * i];
+  }
+  float rc[KS][2], rs[KS][2];     // cos / sin of the rope pair this lane holds at (k-step s, half j); (1, 0) outside
+#pragma unroll
+  for (int s = 0; s < KS; s++)
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const int d = kbase + 16 * s + 8 * j + 2 * t;
+      const bool roped = d >= D - 64;
+      rc[s][j] = roped ? p.cs[d - (D - 64)] : 1.f;
+      rs[s][j] = roped ? p.cs[d - (D - 64) + 1] : 0.f;
+    }
+  if (nit > 0) gather(0, 0);
   {
     float4* qs4 = reinterpret_cast<float4*>(rows[1]);
-    const float4* src = reinterpret_cast<const float4*>(p.q + (size_t)hg * kSaHeadsPerBlock * D);
-    constexpr int kQ4 = kSaHeadsPerBlock * D / 4 / 128;   // 16-byte pieces per thread (16 or 18)
-    static_assert(kSaHeadsPerBlock * D / 4 % 128 == 0, "query staging assumes a whole number of pieces per thread");
-    float4 v[kQ4];
 #pragma unroll
-    for (int i = 0; i < kQ4; i++) v[i] = src[tid + 128 * i];       // all loads in flight before the first store
-#pragma unroll
-    for (int i = 0; i < kQ4; i++) qs4[tid + 128 * i] = v[i];
+    for (int i = 0; i < kQ4; i++) qs4[tid + 128 * i] = qv[i];
   }
   __syncthreads();
   uint32_t qh[KS][4], ql[KS][4];
@@ -149,8 +162,7 @@ __global__ void __launch_bounds__(128, 1) sparse_partial_kernel(const SparsePara
           const float2 v = *reinterpret_cast<const float2*>(qs + (g + 8 * r) * D + d);
           float a = v.x, b = v.y;
           if (d >= D - 64) {
-            const int i = (d - (D - 64)) >> 1;
-            const float c = p.cs[2 * i], sn = p.cs[2 * i + 1];
+            const float c = rc[s][j], sn = rs[s][j];
             const float ra = a * c - b * sn, rb = a * sn + b * c;
             a = ra; b = rb;
           }
