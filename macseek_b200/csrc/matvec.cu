@@ -350,8 +350,8 @@ int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
     else light = true;
     if (light) {
       const size_t cap = (light_limit - fixed_l) / 2;
-      // Q6_K rows are split by half super-block (4 units), the other types by unit
-      switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, cap, 8)) {
+      // Q6_K and IQ1_S rows are split by half super-block (4 units), the other types by unit
+      switch (pick_lpr((T == Q6_K || T == IQ1_S) ? p.units / 4 : p.units, p.row_bytes, cap, 8)) {
         case 32: return launch_rows<T, 32, NC, 8>(p, st, dev, sms);
         case 16: return launch_rows<T, 16, NC, 8>(p, st, dev, sms);
         default: return launch_rows<T, 8, NC, 8>(p, st, dev, sms);
@@ -360,7 +360,7 @@ int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
   }
   const size_t fixed = lut_bytes_for(T) + (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 1024;
   const size_t tile_cap = fixed < (size_t)kSmemLimit ? ((size_t)kSmemLimit - fixed) / 2 : 0;
-  switch (pick_lpr(T == Q6_K ? p.units / 4 : p.units, p.row_bytes, tile_cap, kMvNW)) {
+  switch (pick_lpr((T == Q6_K || T == IQ1_S) ? p.units / 4 : p.units, p.row_bytes, tile_cap, kMvNW)) {
     case 32: return launch_rows<T, 32, NC, kMvNW>(p, st, dev, sms);
     case 16: return launch_rows<T, 16, NC, kMvNW>(p, st, dev, sms);
     default: return launch_rows<T, 8, NC, kMvNW>(p, st, dev, sms);

@@ -24,6 +24,7 @@ struct MoeSmemHead {
   const uint8_t* p1[kMaxRouted];   // up
   const uint8_t* srcs[kMaxStages][kMaxRouted];   // per ring slot: source addresses of the staged piece
   float part[2][kMoeNW][2];        // per-warp partial sums of a tile (double-buffered): down: [0]; gate/up: (g, u)
+  float rpart[2][kMoeNW][kMoeNW / 2];   // down: per-warp partial sums of the routed experts for the tile's rows
 };
 
 __device__ __forceinline__ float swiglu(float g, float u, float w, float limit) {
@@ -293,6 +294,38 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
 }
 
 // ---------------------------------------------------------------------------------------------------- down
+// Routed part of a down tile.  A work item is (resident expert, run of PU consecutive units of its rows); warps take
+// items round robin.  Inside an item LP lanes split the run and each lane applies the activation registers it loaded
+// to NRT of the tile's 8 rows (32 / LP row groups x NRT rows = 8), so the expert's h is read from shared memory once
+// per 8 rows instead of once per row.  Every warp leaves its 8 row sums (zero without items) in rpart.
+template <int TR, int LP, int NRT>
+__device__ __forceinline__ void down_routed(const MoeParams& p, MoeSmemHead* hd, saddr_t slot, uint32_t rb_r, int r0, int Ui,
+                                            int n_local, int warp, int lane, const XqSmem (&xq)[1], const LaneLuts& L,
+                                            int pb) {
+  static_assert(NRT * (32 / LP) == kMoeNW / 2, "row groups x rows per lane = rows of a tile");
+  constexpr int PU = TR == IQ1_S ? 4 * LP : LP;      // IQ1_S lanes work on half super-blocks (4 units)
+  const int rg = lane / LP, li = lane % LP;
+  const int parts = (Ui + PU - 1) / PU;
+  float acc[NRT][1];
+#pragma unroll
+  for (int i = 0; i < NRT; i++) acc[i][0] = 0.f;
+  for (int it = warp; it < n_local * parts; it += kMoeNW) {
+    const int e = it / parts, ua = (it - e * parts) * PU, nu = min(PU, Ui - ua);
+    const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)r0 * rb_r;
+    saddr_t rowp[NRT];
+#pragma unroll
+    for (int i = 0; i < NRT; i++)
+      rowp[i] = slot + (uint32_t)e * p.d_src_pitch + (uint32_t)(a & 15u) + (uint32_t)(rg * NRT + i) * rb_r +
+                (uint32_t)units_bytes(TR, ua);
+    consume_rows<TR, LP, NRT, 1>(rowp, li, xq, hd->local_slot[e] * Ui + ua, nu, L, acc);
+  }
+#pragma unroll
+  for (int i = 0; i < NRT; i++) {
+    const float v = group_sum<LP>(acc[i][0]);
+    if (li == 0) hd->rpart[pb][warp][rg * NRT + i] = v;
+  }
+}
+
 // Tile = 8 output rows.  The first piece stages those 8 rows of every resident routed expert's down matrix (one
 // contiguous copy per expert, side by side), the second the shared expert's rows.  Two warps share a row: the even
 // warp takes the even sources (and the first half of the shared expert's units), the odd warp the rest; the two
@@ -403,27 +436,32 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
       consumer_release(ring, n, lane);
       n++;
     }
+    const int pb = tile_count & 1;
     if (n_local > 0) {
       if (!consumer_wait(ring, n)) return;
       const saddr_t slot = smem_u32(ring.slot(n));
-      for (int e = half * Gn + grp; e < n_local; e += 2 * Gn) {
-        const uintptr_t a = reinterpret_cast<uintptr_t>(hd->p0[e]) + (size_t)r0 * rb_r;
-        const saddr_t rowp[1] = {slot + (uint32_t)e * p.d_src_pitch + (uint32_t)(a & 15u) + (uint32_t)row * rb_r};
-        consume_rows<TR, LPR, 1, 1>(rowp, li, xq, hd->local_slot[e] * Ui, Ui, L, acc);
-      }
+      if constexpr (TR == IQ1_S) down_routed<TR, 8, 2>(p, hd, slot, rb_r, r0, Ui, n_local, warp, lane, xq, L, pb);
+      else if (n_local >= 5) down_routed<TR, 32, 8>(p, hd, slot, rb_r, r0, Ui, n_local, warp, lane, xq, L, pb);
+      else if (n_local >= 3) down_routed<TR, 16, 4>(p, hd, slot, rb_r, r0, Ui, n_local, warp, lane, xq, L, pb);
+      else down_routed<TR, 8, 2>(p, hd, slot, rb_r, r0, Ui, n_local, warp, lane, xq, L, pb);
       consumer_release(ring, n, lane);
       n++;
     }
-    // combine: lane groups inside the warp (fixed order), then the two warps of the row
+    // combine: the shared expert's lane groups inside the warp (fixed order); then, per row, the two warps that split the
+    // shared expert's units and every warp's routed sum, in warp order
     float v = group_sum<LPR>(acc[0][0]);
 #pragma unroll
     for (int o = LPR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    const int pb = tile_count & 1;
     if (lane == 0) hd->part[pb][warp][0] = v;
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->tilebar);
     if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return;
-    if (half == 0 && lane == 0 && r0 + row < p.dim) p.y[r0 + row] += hd->part[pb][warp][0] + hd->part[pb][warp + 1][0];
+    if (warp == 0 && lane < R && r0 + lane < p.dim) {
+      float s = hd->part[pb][2 * lane][0] + hd->part[pb][2 * lane + 1][0];
+      if (n_local > 0)
+        for (int w = 0; w < kMoeNW; w++) s += hd->rpart[pb][w][lane];
+      p.y[r0 + lane] += s;
+    }
     tile_count++;
   }
 }

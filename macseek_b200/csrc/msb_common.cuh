@@ -150,9 +150,10 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 //   IQ2_XXS: 256 x uint2 (8 unsigned bytes 8/25/43);  signs: 128 x uint2 (byte 0xFF where the element is negative).
 //   IQ4_NL : 256 x u16: low byte = value of the low nibble, high byte = value of the high nibble.
 //   IQ1_S  : 2048 x 8 int8 values.
-// Shared-memory images (dot kernels), already replicated per bank group so that one bulk copy fills the block's LUT:
-//   img_iq1s  [2048][4 copies] uint2: 8 bytes (value + 1) of the entry        (64 KB)
-//   img_iq2g  [256][16 copies] uint2, img_iq2s [128][16 copies] uint2          (32 KB + 16 KB)
+// Shared-memory images (dot kernels), already replicated per bank group so that one bulk copy fills the block's LUT
+// (4-bit codes, eight per word; layouts in quant_blocks.cuh):
+//   img_iq1s  [2048][8 copies] u32                                               (64 KB)
+//   img_iq2g  [256][32 copies] u32, img_iq2s [128][32 copies] u32                (32 KB + 16 KB)
 //   img_iq4   [256][8 copies]  u32 (byte pair in the low 16 bits)               (8 KB)
 struct Tables {
   const uint2* iq2xxs_grid;    // [256]

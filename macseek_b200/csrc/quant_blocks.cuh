@@ -13,14 +13,20 @@
 
 namespace msb {
 
-// Shared-memory lookup tables are replicated so that lanes of a warp hit disjoint banks: copy c of entry i lives at
-// i * (entry_bytes * copies) + c * entry_bytes.
-constexpr int kIq1sCopies = 4;    // 2048 x 8 B x 4  = 64 KB
-constexpr int kIq2Copies = 16;    // 256 x 8 B x 16 = 32 KB (grid) + 128 x 8 B x 16 = 16 KB (signs)
+// Shared-memory lookup tables hold 4-bit codes, eight per 32-bit entry (element k of an entry's 8 in the low nibble of
+// byte k for k < 4, element k + 4 in the high nibble), and are replicated so that lanes of a warp hit disjoint banks:
+// copy c of entry i is the word at i * copies + c.
+//   IQ1_S  : nibble = grid value + 1 (0..2).  (entry & 0x0F0F0F0F) is a dp4a operand for elements 0..3 and
+//            (entry & 0xF0F0F0F0) one for elements 4..7 scaled by 16, which an exact shift removes from the integer sum.
+//   IQ2_XXS: grid nibble = magnitude code 0..2 (8, 25, 43), sign nibble = 3 for a negative element; their sum selects a
+//            byte of the pool {8, 25, 43, -8, -25, -43} with one byte-permute per four elements.  Here the nibbles are in
+//            element order (nibble k = element k), the order the permute's selector wants.
+constexpr int kIq1sCopies = 8;    // 2048 x 4 B x 8  = 64 KB: four lanes share a copy
+constexpr int kIq2Copies = 32;    // 256 x 4 B x 32 = 32 KB (grid) + 128 x 4 B x 32 = 16 KB (signs): one copy per lane
 constexpr int kIq4Copies = 8;     // 256 x 4 B x 8  = 8 KB
-constexpr size_t kIq1sLutBytes = 2048 * 8 * kIq1sCopies;
-constexpr size_t kIq2GridLutBytes = 256 * 8 * kIq2Copies;
-constexpr size_t kIq2SignLutBytes = 128 * 8 * kIq2Copies;
+constexpr size_t kIq1sLutBytes = 2048 * 4 * kIq1sCopies;
+constexpr size_t kIq2GridLutBytes = 256 * 4 * kIq2Copies;
+constexpr size_t kIq2SignLutBytes = 128 * 4 * kIq2Copies;
 constexpr size_t kIq4LutBytes = 256 * 4 * kIq4Copies;
 
 __host__ __device__ constexpr size_t lut_bytes_for(int t) {
@@ -56,7 +62,7 @@ struct LaneLuts {      // per-lane shared-space base addresses (already offset t
 // Quantised activation in shared memory: U units of 32 elements.  x ~= scale * (256 * hi + lo), hi signed bytes,
 // lo unsigned bytes.  plane[0][.] / plane[1][.] = hi bytes of elements 0..15 / 16..31, plane[2..3] = lo bytes.
 // meta[.] = {scale, scale * sum of the fixed-point values, (int) sum over elements 0..15, (int) sum over 16..31}.
-// In the padded form (used when a Q6_K matrix reads it) unit u sits at slot u + u/8 of each array: one 16-byte slot
+// In the padded form (used when a Q6_K or IQ1_S matrix reads it) unit u sits at slot u + u/8 of each array: one 16-byte slot
 // of padding per 8 units, so that lanes that each walk their own half super-block (unit stride 4) reach distinct banks,
 // as lanes on consecutive units do in either form.
 struct XqSmem {
@@ -67,7 +73,7 @@ struct XqSmem {
   int U, S;
   uint32_t padmask;   // all ones in the padded form, else 0
 };
-__host__ __device__ constexpr bool xq_padded(int t) { return t == Q6_K; }
+__host__ __device__ constexpr bool xq_padded(int t) { return t == Q6_K || t == IQ1_S; }
 __host__ __device__ inline int xq_pos_padded(int u) { return u + (u >> 3); }
 __host__ __device__ inline int xq_slots(int U, bool padded) { return padded ? U + ((U + 7) >> 3) : U; }
 __host__ __device__ inline size_t xq_bytes(int U, bool dense, bool padded) {
@@ -182,48 +188,88 @@ __device__ __forceinline__ void decode_unit(saddr_t rowp, int u, const LaneLuts&
 template <int T>
 __device__ __forceinline__ float dot_unit(const Dec<T>& d, const XRegs& x);
 
-// ---- IQ1_S: codes + 1 (0,1,2) unsigned; sum (code + delta) x = sum (code + 1) x + (delta - 1) sum x
-template <>
-__device__ __forceinline__ void decode_unit<IQ1_S>(saddr_t rowp, int u, const LaneLuts& L, Dec<IQ1_S>& d) {
-  const saddr_t blk = rowp + (uint32_t)(u >> 3) * 50u;
-  const int ib = u & 7;
-  const uint32_t qs = lds_u32_a2(blk + 2 + 4 * ib);
-  const uint32_t qh = lds_u16(blk + 34 + 2 * ib);
-  // entry address = lut + 32 * (8-bit code) + 8192 * (3 high bits): the lane's copy is folded into L.iq1s
-#pragma unroll
-  for (int l = 0; l < 4; l++) {
-    const uint32_t lo = (l == 0 ? (qs << 5) : (qs >> (8 * l - 5))) & 0x1FE0u;
-    const uint32_t hi = (qh << (13 - 3 * l)) & 0xE000u;
-    const uint2 v = lds_u64(L.iq1s + lo + hi);
-    d.w[2 * l] = v.x;
-    d.w[2 * l + 1] = v.y;
-  }
-  d.a = lds_half(blk) * (float)(2 * ((qh >> 12) & 7u) + 1);
-  d.b = (qh & 0x8000u) ? -1.125f : -0.875f;
+// ---- IQ1_S, one half super-block (4 units = 128 elements) of NRT rows against NC activation columns.
+// weight = d (2 s_u + 1) (g + delta_u), g in {-1, 0, 1}, delta_u = +-1/8 per unit.  With the table's codes c = g + 1 and
+// the unit's fixed-point activation x = xs_u * xi:
+//   row . x = d * sum_u xs_u/8 * [ 8 (2 s_u + 1) sum_k c_k xi_k  +  (2 s_u + 1) (8 delta_u - 8) sum_k xi_k ]
+// the bracket is an exact integer (8 delta - 8 = -7 or -9), converted to float once per unit and row.  A look-up returns
+// 8 codes as nibbles; e = w & 0x0F0F0F0F multiplies elements 0..3, w - e (elements 4..7 scaled by 16) the other four,
+// and an exact shift takes the 16 out of that partial sum.
+// `blk[i]` = shared address of row i's block (2-byte aligned), `u0` = the half block's first unit in the activation.
+__device__ __forceinline__ uint32_t sub_fma_pipe(uint32_t w, uint32_t e) {   // w - e as a multiply-add
+  uint32_t o;
+  asm("mad.lo.u32 %0, %1, 0xFFFFFFFF, %2;" : "=r"(o) : "r"(e), "r"(w));
+  return o;
 }
-template <>
-__device__ __forceinline__ float dot_unit<IQ1_S>(const Dec<IQ1_S>& d, const XRegs& x) {
-  int sh = 0, sl = 0, th = 0, tl = 0;      // two independent chains per limb
+template <int NRT, int NC>
+__device__ __forceinline__ void iq1s_half_block(const saddr_t (&blk)[NRT], int half, const XqSmem (&xq)[NC], int u0,
+                                                const LaneLuts& L, float (&acc)[NRT][NC]) {
+  uint32_t q[NRT][4], hw[NRT][2];
+  float part[NRT][NC];
 #pragma unroll
-  for (int i = 0; i < 8; i += 2) {
-    sh = dp4a_us(d.w[i], x.h[i], sh); sl = dp4a_uu(d.w[i], x.l[i], sl);
-    th = dp4a_us(d.w[i + 1], x.h[i + 1], th); tl = dp4a_uu(d.w[i + 1], x.l[i + 1], tl);
+  for (int i = 0; i < NRT; i++) {
+    load_words<4>(blk[i] + 2 + 16 * half, q[i]);
+    load_words<2>(blk[i] + 34 + 8 * half, hw[i]);
+#pragma unroll
+    for (int c = 0; c < NC; c++) part[i][c] = 0.f;
   }
-  return d.a * (x.s * (float)((sh + th) * 256 + (sl + tl)) + d.b * x.sx);
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    XRegs x[NC];
+    float xs8[NC];
+    int xi[NC];
+#pragma unroll
+    for (int c = 0; c < NC; c++) { load_xq(xq[c], u0 + u, x[c]); xs8[c] = 0.125f * x[c].s; xi[c] = x[c].sa + x[c].sb; }
+#pragma unroll
+    for (int i = 0; i < NRT; i++) {
+      // qh of the unit in the low 16 bits (for even u the next unit's word rides along above them; every use masks)
+      const uint32_t h = (u & 1) ? (hw[i][u >> 1] >> 16) : hw[i][u >> 1];
+      uint32_t w[4];
+#pragma unroll
+      for (int l = 0; l < 4; l++) {
+        // entry address = lut + 32 * (8-bit code) + 8192 * (3 high bits); the lane's copy is folded into L.iq1s
+        const uint32_t hi = (h & (7u << (3 * l))) * (8192u >> (3 * l)) + L.iq1s;
+        w[l] = lds_u32(__byte_perm(q[i][u], 0, 0x4440 | l) * 32u + hi);
+      }
+      const int sc = (int)(((h >> 11) & 14u) | 1u);
+      const int sg = (h & 0x8000u) ? -9 * sc : -7 * sc;
+#pragma unroll
+      for (int c = 0; c < NC; c++) {
+        int he = 0, le = 0, ho = 0, lo = 0;
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+          const uint32_t e = w[l] & 0x0F0F0F0Fu, o = sub_fma_pipe(w[l], e);
+          he = dp4a_us(e, x[c].h[2 * l], he); le = dp4a_uu(e, x[c].l[2 * l], le);
+          ho = dp4a_us(o, x[c].h[2 * l + 1], ho); lo = dp4a_uu(o, x[c].l[2 * l + 1], lo);
+        }
+        const int S = (he * 256 + le) + ((ho * 256 + lo) >> 4);
+        part[i][c] = fmaf(xs8[c], (float)(8 * sc * S + sg * xi[c]), part[i][c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NRT; i++) {
+    const float d = lds_half(blk[i]);
+#pragma unroll
+    for (int c = 0; c < NC; c++) acc[i][c] = fmaf(d, part[i][c], acc[i][c]);
+  }
 }
 
-// ---- IQ2_XXS: signed bytes (+-8, +-25, +-43): negative elements are negated bytewise, (g ^ m) + (m & 1)
+// ---- IQ2_XXS: the grid entry's magnitude codes (0..2) plus 3 for a negative element select a byte of the pool
+// {8, 25, 43, -8, -25, -43}: one addition and two byte-permutes per 8 elements
 template <>
 __device__ __forceinline__ void decode_unit<IQ2_XXS>(saddr_t rowp, int u, const LaneLuts& L, Dec<IQ2_XXS>& d) {
+  constexpr uint32_t kPoolA = 0xF82B1908u, kPoolB = 0x0000D5E7u;   // bytes 8, 25, 43, -8 | -25, -43
   const saddr_t blk = rowp + (uint32_t)(u >> 3) * 66u;
   const saddr_t a8 = blk + 2 + 8 * (u & 7);
   const uint32_t q = lds_u32_a2(a8), a1 = lds_u32_a2(a8 + 4);
 #pragma unroll
   for (int l = 0; l < 4; l++) {
-    const uint2 g = lds_u64(L.iq2g + ((q >> (8 * l)) & 0xFFu) * (8 * kIq2Copies));
-    const uint2 m = lds_u64(L.iq2s + ((a1 >> (7 * l)) & 127u) * (8 * kIq2Copies));
-    d.w[2 * l] = (g.x ^ m.x) + (m.x & 0x01010101u);
-    d.w[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
+    const uint32_t g = lds_u32(L.iq2g + __byte_perm(q, 0, 0x4440 | l) * (4 * kIq2Copies));
+    const uint32_t m = lds_u32(L.iq2s + ((a1 >> (7 * l)) & 127u) * (4 * kIq2Copies));
+    const uint32_t sel = g + m;
+    d.w[2 * l] = __byte_perm(kPoolA, kPoolB, sel);
+    d.w[2 * l + 1] = __byte_perm(kPoolA, kPoolB, sel >> 16);
   }
   d.a = lds_half(blk) * (0.5f + (float)(a1 >> 28)) * 0.25f;
   d.b = 0.f;

@@ -111,10 +111,10 @@ __device__ __forceinline__ bool load_luts(uint8_t* lut, bool iq1s, bool iq2, boo
   saddr_t p = smem_u32(lut);
   L.iq1s = L.iq2g = L.iq2s = L.iq4 = p;
   uint32_t total = 0;
-  if (iq1s) { L.iq1s = p + 8 * (lane % kIq1sCopies); p += kIq1sLutBytes; total += kIq1sLutBytes; }
+  if (iq1s) { L.iq1s = p + 4 * (lane % kIq1sCopies); p += kIq1sLutBytes; total += kIq1sLutBytes; }
   if (iq2) {
-    L.iq2g = p + 8 * (lane % kIq2Copies); p += kIq2GridLutBytes;
-    L.iq2s = p + 8 * (lane % kIq2Copies); p += kIq2SignLutBytes;
+    L.iq2g = p + 4 * (lane % kIq2Copies); p += kIq2GridLutBytes;
+    L.iq2s = p + 4 * (lane % kIq2Copies); p += kIq2SignLutBytes;
     total += kIq2GridLutBytes + kIq2SignLutBytes;
   }
   if (iq4) { L.iq4 = p + 4 * (lane % kIq4Copies); p += kIq4LutBytes; total += kIq4LutBytes; }
@@ -146,6 +146,16 @@ __device__ __forceinline__ void consume_rows(const saddr_t (&rowp)[NRT], int li,
 #pragma unroll
       for (int i = 0; i < NRT; i++) blk[i] = rowp[i] + (uint32_t)(it >> 1) * 210u;
       q6k_half_block<NRT, NC>(blk, it & 1, xq, unit0 + 4 * it, acc);
+    }
+    return;
+  }
+  if constexpr (T == IQ1_S) {
+    // lanes split the row's half super-blocks, as above
+    for (int it = li; it < nunits / 4; it += LPR) {
+      saddr_t blk[NRT];
+#pragma unroll
+      for (int i = 0; i < NRT; i++) blk[i] = rowp[i] + (uint32_t)(it >> 1) * 50u;
+      iq1s_half_block<NRT, NC>(blk, it & 1, xq, unit0 + 4 * it, L, acc);
     }
     return;
   }
@@ -194,6 +204,7 @@ __device__ __forceinline__ void consume_rows(const saddr_t (&rowp)[NRT], int li,
     }
     return;
   }
+  if constexpr (T != IQ1_S && T != Q6_K && !is_dense(T))
   for (int uu = li; uu < nunits; uu += LPR) {
     XRegs xr[NC];
 #pragma unroll
