@@ -8,6 +8,7 @@
 // first), so the split adapts to how many of the routed experts are resident on this GPU (expert parallelism) without
 // a host round trip.  A row's partial sums are always formed in the same order, whichever block computes it.
 #include <algorithm>
+#include <cstdlib>
 #include "stream_pipe.cuh"
 #include "moe_decode_params.cuh"
 

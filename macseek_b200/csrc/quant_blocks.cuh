@@ -43,17 +43,21 @@ __host__ __device__ constexpr int units_bytes(int t, int units) {
 // Every hot-path shared-memory read goes through explicit ld.shared with 32-bit shared-space addresses: pointers that
 // travel through structs lose their address space and would otherwise compile to generic loads.
 typedef uint32_t saddr_t;
-// Plain loads through a pointer rebuilt from the shared-space address: the compiler sees the address space (ld.shared),
-// folds constant offsets into the instruction and is free to schedule the loads; it will not move them across the
-// mbarrier waits, which are volatile asm with a memory clobber.
-template <typename V>
-__device__ __forceinline__ V lds_as(saddr_t a) { return *reinterpret_cast<const V*>(__cvta_shared_to_generic((size_t)a)); }
-__device__ __forceinline__ uint32_t lds_u8(saddr_t a) { return lds_as<uint8_t>(a); }
-__device__ __forceinline__ uint32_t lds_u16(saddr_t a) { return lds_as<uint16_t>(a); }
-__device__ __forceinline__ uint32_t lds_u32(saddr_t a) { return lds_as<uint32_t>(a); }
-__device__ __forceinline__ uint2 lds_u64(saddr_t a) { return lds_as<uint2>(a); }
-__device__ __forceinline__ uint4 lds_u128(saddr_t a) { return lds_as<uint4>(a); }
-__device__ __forceinline__ float4 lds_f128(saddr_t a) { return lds_as<float4>(a); }
+// Loads are explicit ld.shared instructions on 32-bit shared-space addresses (no generic-address arithmetic).  They are
+// volatile asm statements: the compiler keeps them in program order relative to the mbarrier waits and named barriers
+// (also volatile asm), and the assembler schedules them freely among the arithmetic.
+__device__ __forceinline__ uint32_t lds_u8(saddr_t a) { uint32_t v; asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u16(saddr_t a) { uint32_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u32(saddr_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds_u64(saddr_t a) {
+  uint2 v; asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint4 lds_u128(saddr_t a) {
+  uint4 v; asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
+}
+__device__ __forceinline__ float4 lds_f128(saddr_t a) {
+  float4 v; asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v;
+}
 
 struct LaneLuts {      // per-lane shared-space base addresses (already offset to the lane's copy)
   saddr_t iq1s, iq2g, iq2s, iq4;
@@ -227,9 +231,9 @@ __device__ __forceinline__ void iq1s_half_block(const saddr_t (&blk)[NRT], int h
       uint32_t w[4];
 #pragma unroll
       for (int l = 0; l < 4; l++) {
-        // entry address = lut + 32 * (8-bit code) + 8192 * (3 high bits); the lane's copy is folded into L.iq1s
-        const uint32_t hi = (h & (7u << (3 * l))) * (8192u >> (3 * l)) + L.iq1s;
-        w[l] = lds_u32(__byte_perm(q[i][u], 0, 0x4440 | l) * 32u + hi);
+        // entry address = lut + 4 copies * ((8-bit code) + 256 * (3 high bits)); the lane's copy is folded into L.iq1s
+        const uint32_t hi = (h & (7u << (3 * l))) * ((1024u * kIq1sCopies) >> (3 * l)) + L.iq1s;
+        w[l] = lds_u32(__byte_perm(q[i][u], 0, 0x4440 | l) * (4u * kIq1sCopies) + hi);
       }
       const int sc = (int)(((h >> 11) & 14u) | 1u);
       const int sg = (h & 0x8000u) ? -9 * sc : -7 * sc;

@@ -4,7 +4,7 @@
 #include <cstring>
 #include <mutex>
 #include <vector>
-#include "msb_common.cuh"
+#include "quant_blocks.cuh"
 #include "iq_grids_packed.h"
 
 namespace msb {
@@ -55,7 +55,7 @@ struct HostImage {
   std::vector<uint32_t> iq2_sign16; // 4 words per entry
   std::vector<uint32_t> img_iq1s, img_iq2g, img_iq2s, img_iq4;
   HostImage() : iq2_grid(512), iq2_sign(256), iq4_pair(256), iq1s_i8(2048 * 8), iq1s_sel(2048 * 2, 0), iq2_sel(256 * 2, 0), iq2_sign16(128 * 4, 0) {
-    img_iq1s.assign(2048 * 8, 0);
+    img_iq1s.assign(2048 * kIq1sCopies, 0);
     for (int i = 0; i < 2048; i++) {
       uint32_t w = 0;
       for (int j = 0; j < 8; j++) {
@@ -63,7 +63,7 @@ struct HostImage {
         iq1s_i8[i * 8 + j] = (int8_t)((int)f - 1);
         w |= f << (8 * (j % 4) + 4 * (j / 4));                    // element j: byte j % 4, high nibble for j >= 4
       }
-      for (int c = 0; c < 8; c++) img_iq1s[i * 8 + c] = w;
+      for (int c = 0; c < kIq1sCopies; c++) img_iq1s[i * kIq1sCopies + c] = w;
       // selectors: code c (0..2) of an element picks bytes (2c, 2c+1) of the 8-byte pool of three halfs
       for (int j = 0; j < 4; j++) {
         const uint32_t ca = (kMsbIq1sPacked[i] >> (4 * j)) & 3, cb = (kMsbIq1sPacked[i] >> (4 * j + 2)) & 3;
@@ -90,20 +90,20 @@ struct HostImage {
     }
     for (int b = 0; b < 256; b++)
       iq4_pair[b] = (uint16_t)((uint8_t)kIq4nl[b & 15] | ((uint16_t)(uint8_t)kIq4nl[b >> 4] << 8));
-    img_iq2g.assign(256 * 32, 0);
-    img_iq2s.assign(128 * 32, 0);
+    img_iq2g.assign(256 * kIq2Copies, 0);
+    img_iq2s.assign(128 * kIq2Copies, 0);
     img_iq4.assign(256 * 8, 0);
     for (int i = 0; i < 256; i++) {
       uint32_t w = 0;                                             // nibble j = magnitude code of element j
       for (int j = 0; j < 8; j++) w |= ((kMsbIq2xxsPacked[i] >> (2 * j)) & 3u) << (4 * j);
-      for (int c = 0; c < 32; c++) img_iq2g[i * 32 + c] = w;
+      for (int c = 0; c < kIq2Copies; c++) img_iq2g[i * kIq2Copies + c] = w;
     }
     for (int i = 0; i < 128; i++) {
       const int bits = i | ((__builtin_popcount((unsigned)i) & 1) << 7);
       uint32_t w = 0;                                             // nibble j = 3 where element j is negative
       for (int j = 0; j < 8; j++)
         if ((bits >> j) & 1) w |= 3u << (4 * j);
-      for (int c = 0; c < 32; c++) img_iq2s[i * 32 + c] = w;
+      for (int c = 0; c < kIq2Copies; c++) img_iq2s[i * kIq2Copies + c] = w;
     }
     for (int i = 0; i < 256; i++)
       for (int c = 0; c < 8; c++) img_iq4[i * 8 + c] = iq4_pair[i];
