@@ -33,7 +33,9 @@ const char* msb_version(void);
 /* Prepares the current device (codebook tables, status word).  Optional: every entry point does it on first use. */
 int msb_init(void);
 /* Synchronises the current device and returns the device-side failure word: 0, or 1/2 when a kernel abandoned a
- * bounded wait on its shared-memory ring, 3 for an abandoned peer wait.  The word is cleared by the call. */
+ * bounded wait on its shared-memory ring, 3 for an abandoned peer wait.  A non-zero word means the launch that set it
+ * (and anything queued behind it) returned early with incomplete outputs; the call then also resets the library's
+ * device-side scheduling counters, so that later launches start from a clean state.  The word is cleared by the call. */
 int msb_device_status(void);
 
 /* Block geometry: ms::q::block_elems / block_bytes / row_bytes (src/kernels/quant_types.hpp:15-36). */
@@ -138,6 +140,39 @@ int msb_moe_decode_ids(const msb_moe_decode_args* a, const uint64_t* expert_tabl
 int msb_moe_decode_ids_normed(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
                               int expert_hi, int part, const float* norm_in, const float* norm_w, float norm_eps,
                               void* stream);
+
+/* ---------------------------------------------------------------- expert-parallel MoE decode over NVLink peer memory
+ * NO COUNTERPART IN THE REFERENCE (one GPU, experts streamed from SSD).  The semantics follow the reference model's
+ * expert-parallel MoE (reference/inference/model.py:869-904): contiguous expert ranges per rank, replicated router, the
+ * ranks' outputs summed.  One process per GPU; rank r holds experts [r E/N, (r+1) E/N) and computes rows
+ * [shared_lo, shared_hi) of the shared expert's gate/up and the same K range of its down matrix (multiples of 256).
+ *
+ * msb_moe_decode_ep = msb_moe_decode_ids_normed (norm_in may be NULL) restricted to that shared-expert slice.  With
+ * comm == NULL the partial output is accumulated into a.y as usual (combine it yourself, e.g. ncclAllReduce).  With a
+ * comm, a.y is ignored: the down launch stores its partial into slot `rank` of every rank's exchange buffer (plain
+ * stores to peer-mapped memory) and raises flag `rank` there.  msb_ep_combine then waits -- bounded, about one second of
+ * SM clock, after which device status 3 is recorded and h is left unchanged -- for all `world` flags and adds the
+ * partials to h in rank order (bit-identical on every rank).  Every rank must issue the same sequence of
+ * msb_moe_decode_ep / msb_ep_combine pairs; the buffers are double-buffered by a device-side epoch, so the pair can be
+ * captured in a CUDA graph and replayed.
+ * Exchange buffers: msb_ep_exchange_bytes(dim, world) bytes from msb_ep_alloc (cudaMalloc + zero fill; not for use
+ * inside a stream capture), exported with msb_ipc_export and mapped by the peers with msb_ipc_import (CUDA IPC, peer
+ * access enabled on first use); base[r] is rank r's buffer as seen from this process (base[rank] = the local one). */
+#define MSB_MAX_EP_WORLD 8
+typedef struct { int world, rank; void* base[MSB_MAX_EP_WORLD]; } msb_ep_comm;
+int msb_moe_decode_ep(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
+                      int expert_hi, const float* norm_in, const float* norm_w, float norm_eps, int shared_lo,
+                      int shared_hi, const msb_ep_comm* comm, void* stream);
+size_t msb_ep_exchange_bytes(int dim, int world);
+int msb_ep_combine(const msb_ep_comm* comm, float* h, int dim, void* stream);
+/* Limit of msb_ep_combine's flag wait in SM clock cycles (default 2e9; <= 0 restores it).  Host-side setting, read at
+ * launch. */
+void msb_set_peer_wait_cycles(long long cycles);
+int msb_ep_alloc(size_t bytes, void** out);
+int msb_ep_free(void* p);
+int msb_ipc_export(void* p, unsigned char* handle64);           /* handle64: 64 bytes of host memory */
+int msb_ipc_import(const unsigned char* handle64, void** out);
+int msb_ipc_release(void* p);
 
 /* ---------------------------------------------------------------- router
  * ms::arch::encode_router_fused / encode_router_topk / RouteLists / encode_route_lists (src/kernels/arch.hpp:79-97,

@@ -101,3 +101,21 @@ lib.msb_argmax.argtypes = [_vp, _i, _vp, _vp, _vp]
 lib.msb_add.argtypes = [_vp, _vp, _i, _vp]
 lib.msb_matvec_rmsnorm.argtypes = [_i, _vp, _i, _i, _vp, _vp, _f, _vp, _vp]
 lib.msb_matvec_rmsnorm_shared.argtypes = [_i, _vp, _i, _i, _vp, _vp, _f, _vp, _vp]
+
+
+class EpCommC(C.Structure):
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("base", C.c_void_p * 8)]
+
+
+lib.msb_moe_decode_ep.argtypes = [C.POINTER(MoeDecodeArgsC), _vp, _vp, _i, _i, _vp, _vp, C.c_float, _i, _i,
+                                  C.POINTER(EpCommC), _vp]
+lib.msb_ep_exchange_bytes.restype = C.c_size_t
+lib.msb_ep_exchange_bytes.argtypes = [_i, _i]
+lib.msb_ep_combine.argtypes = [C.POINTER(EpCommC), _vp, _i, _vp]
+lib.msb_set_peer_wait_cycles.restype = None
+lib.msb_set_peer_wait_cycles.argtypes = [C.c_longlong]
+lib.msb_ep_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+lib.msb_ep_free.argtypes = [_vp]
+lib.msb_ipc_export.argtypes = [_vp, C.c_char_p]
+lib.msb_ipc_import.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+lib.msb_ipc_release.argtypes = [_vp]

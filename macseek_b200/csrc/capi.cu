@@ -61,6 +61,13 @@ int kv_window(const float* kv, const float* norm_w, const float* cs, int actq, i
               cudaStream_t st);
 int argmax(const float* x, int n, int* out_idx, float* out_val, cudaStream_t st);
 int vec_add(float* y, const float* a, int n, cudaStream_t st);
+int ep_combine(uint8_t* const* base, int world, int rank, float* h, int dim, cudaStream_t st);
+void set_peer_wait_cycles(long long c);
+int ep_alloc(size_t bytes, void** out);
+int ep_free(void* p);
+int ipc_export(void* p, unsigned char* handle64);
+int ipc_import(const unsigned char* handle64, void** out);
+int ipc_release(void* p);
 }  // namespace msb
 #include "moe_decode_params.cuh"
 
@@ -83,7 +90,9 @@ int msb_device_status(void) {
   MSB_CUDA(cudaDeviceSynchronize());
   int v = 0;
   MSB_CUDA(cudaMemcpy(&v, t.status, sizeof v, cudaMemcpyDeviceToHost));
-  if (v) MSB_CUDA(cudaMemset(t.status, 0, sizeof v));
+  // A kernel that gave up a wait returned early: the library's scheduling counters and tickets that follow the status
+  // word may be left non-zero.  Nothing is in flight after the synchronise above, so the whole buffer is reset.
+  if (v) MSB_CUDA(cudaMemset(t.status, 0, 2048));
   return v;
 }
 
@@ -225,6 +234,46 @@ int msb_moe_decode_noalloc(const msb_moe_decode_args* a, void* stream) {
   b.scratch_bytes = sizeof(float) * (size_t)(kMaxRouted + 1) * kNoAllocMaxInter;
   return msb_moe_decode(&b, stream);
 }
+
+static int ep_fill(const msb_ep_comm* comm, MoeParams* p) {
+  if (!comm) return kOk;
+  if (comm->world < 1 || comm->world > kMaxEpWorld || comm->rank < 0 || comm->rank >= comm->world)
+    return fail(kErrArg, "moe_decode_ep: bad world %d / rank %d", comm->world, comm->rank);
+  p->ep_world = comm->world; p->ep_rank = comm->rank;
+  for (int r = 0; r < comm->world; r++) p->ep_base[r] = (uint8_t*)comm->base[r];
+  return kOk;
+}
+
+int msb_moe_decode_ep(const msb_moe_decode_args* a, const uint64_t* expert_table, const int* ids, int expert_lo,
+                      int expert_hi, const float* norm_in, const float* norm_w, float norm_eps, int shared_lo,
+                      int shared_hi, const msb_ep_comm* comm, void* stream) {
+  if (!a) return fail(kErrArg, "moe_decode_ep: null args");
+  msb_moe_decode_args b = *a;
+  if (norm_in) b.x = norm_in;
+  MoeParams p;
+  int rc = moe_fill(&b, &p);
+  if (rc) return rc;
+  if (!expert_table || !ids) return fail(kErrArg, "moe_decode_ep: null table or ids");
+  p.table = expert_table; p.ids = ids; p.expert_lo = expert_lo; p.expert_hi = expert_hi;
+  if (norm_in) { p.x = nullptr; p.norm_in = norm_in; p.norm_w = norm_w; p.norm_eps = norm_eps; }
+  p.s_lo = shared_lo; p.s_hi = shared_hi;
+  if (a->has_shared && shared_lo == shared_hi) p.has_shared = 0;      // an empty slice
+  rc = ep_fill(comm, &p);
+  if (rc) return rc;
+  return moe_decode(p, a->t_gate_up, a->t_down, a->t_shared, MSB_MOE_ALL, a->scratch_bytes, (cudaStream_t)stream);
+}
+
+size_t msb_ep_exchange_bytes(int dim, int world) { return ep_exchange_bytes(dim, world); }
+int msb_ep_combine(const msb_ep_comm* comm, float* h, int dim, void* stream) {
+  if (!comm) return fail(kErrArg, "ep_combine: null comm");
+  return ep_combine((uint8_t* const*)comm->base, comm->world, comm->rank, h, dim, (cudaStream_t)stream);
+}
+void msb_set_peer_wait_cycles(long long cycles) { set_peer_wait_cycles(cycles); }
+int msb_ep_alloc(size_t bytes, void** out) { return ep_alloc(bytes, out); }
+int msb_ep_free(void* p) { return ep_free(p); }
+int msb_ipc_export(void* p, unsigned char* handle64) { return ipc_export(p, handle64); }
+int msb_ipc_import(const unsigned char* handle64, void** out) { return ipc_import(handle64, out); }
+int msb_ipc_release(void* p) { return ipc_release(p); }
 
 size_t msb_moe_prefill_scratch_bytes(int total_entries, int n_tokens, int n_exp, int dim, int inter) {
   return moe_prefill_scratch_bytes(total_entries, n_tokens, n_exp, dim, inter);

@@ -95,7 +95,7 @@ __device__ __forceinline__ void end_of_tiles(const Ring& ring, uint32_t n, MoeSm
 // registers loaded once.  Routed experts (cheap bytes, expensive decode): each warp owns NR whole row pairs.  Shared
 // expert (long rows): KS warps share a row pair, each a contiguous run of units; the (gate, up) partial sums meet in
 // shared memory.
-struct GuTile { const uint8_t* G; const uint8_t* U; int r0, R, KS; uint32_t rb, pitch; float* hrow; float w; };
+struct GuTile { const uint8_t* G; const uint8_t* U; int r0, R, KS, rlim; uint32_t rb, pitch; float* hrow; float w; };
 
 __device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& ring, uint32_t& n, const GuTile& tl,
                                                 int lane, int tile, MoeSmemHead* hd) {
@@ -108,7 +108,7 @@ __device__ __forceinline__ bool gu_tile_produce(const MoeParams& p, const Ring& 
   __syncwarp();
   Piece pc;
   pc.src = hd->srcs[s]; pc.nsrc = 2; pc.rows_per_src = 1; pc.nrows = 1; pc.row_stride = tl.rb;
-  pc.bytes = (uint32_t)min(tl.R, p.inter - tl.r0) * tl.rb;
+  pc.bytes = (uint32_t)min(tl.R, tl.rlim - tl.r0) * tl.rb;
   if (!produce_piece(ring, n, pc, tl.pitch, lane)) return false;
   n++;
   return true;
@@ -154,7 +154,7 @@ __device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& 
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->tilebar);
     if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return false;
-    if (kpart == 0 && lane == 0 && tl.r0 + lr0 < p.inter) {
+    if (kpart == 0 && lane == 0 && tl.r0 + lr0 < tl.rlim) {
       float gs = 0.f, us = 0.f;
       for (int k = 0; k < KS; k++) { gs += hd->part[pb][warp + k][0]; us += hd->part[pb][warp + k][1]; }
       tl.hrow[tl.r0 + lr0] = swiglu(gs, us, tl.w, p.limit);
@@ -164,7 +164,7 @@ __device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& 
 #pragma unroll
     for (int i = 0; i < NR; i++) {
       const float g = group_sum<LPR>(acc[i][0]), u = group_sum<LPR>(acc[NR + i][0]);
-      if (li == 0 && tl.r0 + lr0 + i < p.inter) tl.hrow[tl.r0 + lr0 + i] = swiglu(g, u, tl.w, p.limit);
+      if (li == 0 && tl.r0 + lr0 + i < tl.rlim) tl.hrow[tl.r0 + lr0 + i] = swiglu(g, u, tl.w, p.limit);
     }
   }
   return true;
@@ -204,19 +204,21 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
   __syncthreads();
 
   const int R_R = p.gu_r_rows, R_S = p.gu_s_rows;
-  const int tiles_s = p.gu_s ? (p.inter + R_S - 1) / R_S : 0;
+  const int tiles_s = p.gu_s ? (p.s_hi - p.s_lo + R_S - 1) / R_S : 0;
   const int tiles_r1 = (p.inter + R_R - 1) / R_R;
   const uint32_t rb_r = (uint32_t)row_bytes(TR, p.dim), rb_s = (uint32_t)row_bytes(TS, p.dim);
   // tile id -> what to stream: shared-expert tiles first (they are the largest), then the resident routed experts
   auto tile_of = [&](int t) {
     GuTile tl;
     if (t < tiles_s) {
-      tl.G = p.sgate; tl.U = p.sup; tl.r0 = t * R_S; tl.R = R_S; tl.KS = p.gu_s_ks; tl.rb = rb_s; tl.pitch = p.gu_s_pitch;
+      tl.G = p.sgate; tl.U = p.sup; tl.r0 = p.s_lo + t * R_S; tl.R = R_S; tl.KS = p.gu_s_ks; tl.rb = rb_s; tl.pitch = p.gu_s_pitch;
+      tl.rlim = p.s_hi;
       tl.hrow = p.h + (size_t)p.n_routed * p.inter; tl.w = 1.0f;
     } else {
       const int i = (t - tiles_s) / tiles_r1, rt = (t - tiles_s) % tiles_r1;
       const int k = hd->local_slot[i];
       tl.G = hd->p0[i]; tl.U = hd->p1[i]; tl.r0 = rt * R_R; tl.R = R_R; tl.KS = 1; tl.rb = rb_r; tl.pitch = p.gu_r_pitch;
+      tl.rlim = p.inter;
       tl.hrow = p.h + (size_t)k * p.inter; tl.w = __ldcg(p.weights + k);
     }
     return tl;
@@ -358,6 +360,10 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   __syncthreads();
   const int ntiles = (p.dim + R - 1) / R;
   const uint32_t rb_r = (uint32_t)row_bytes(TR, p.inter), rb_s = (uint32_t)row_bytes(TS, p.inter);
+  // the shared expert's K range handled here: units [s_u0, s_u0 + Us) of each of its rows
+  const int s_u0 = p.s_lo / 32, Us = (p.s_hi - p.s_lo) / 32;
+  const bool s_whole = Us == Ui;
+  const uint32_t s_off = (uint32_t)units_bytes(TS, s_u0), s_bytes = (uint32_t)units_bytes(TS, Us);
   uint32_t n = 0;
   if (warp == kMoeNW) {
     // Per tile: the shared expert's rows first (constant data: the first tile's are staged before the grid
@@ -372,10 +378,13 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
       if (announce ? !announce_tile(ring, n, hd, t, lane)
                    : !mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty))
         return false;
-      if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s;
+      if (lane == 0) hd->srcs[s][0] = p.sdown + (size_t)r0 * rb_s + s_off;
       __syncwarp();
-      pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s; pc.bytes = (uint32_t)nrows * rb_s;
-      if (!produce_piece(ring, n, pc, 0, lane)) return false;
+      pc.src = hd->srcs[s]; pc.nsrc = 1; pc.row_stride = rb_s;
+      if (s_whole) { pc.rows_per_src = 1; pc.nrows = 1; pc.bytes = (uint32_t)nrows * rb_s; }      // one contiguous copy
+      else { pc.rows_per_src = R; pc.nrows = nrows; pc.bytes = s_bytes; }                        // a K range of each row
+      if (!produce_piece(ring, n, pc, s_whole ? 0 : p.d_s_pitch, lane)) return false;
+      pc.rows_per_src = 1; pc.nrows = 1;
       n++;
       return true;
     };
@@ -407,6 +416,10 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   LaneLuts L;
   const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
   pdl_wait();     // h comes from the gate/up kernel
+  // expert-parallel exchange: the epoch (completed combines on this rank) picks the slot / flag parity
+  unsigned ep_epoch = 0;
+  if (p.ep_world > 0) ep_epoch = *reinterpret_cast<volatile unsigned*>(p.ep_base[p.ep_rank]);
+  const int ep_par = (int)(ep_epoch & 1u);
   if (warp == 0) resolve_local(p, hd, p.d_r != 0, true, lane);
   quantize_x(p.h, xq[0], tid, kMoeNW * 32);
   __syncthreads();
@@ -415,24 +428,34 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   const int row = warp >> 1, half = warp & 1;
   const int grp = lane / LPR, li = lane % LPR;   // LPR < 32: lane groups take alternate sources / unit runs
   uint32_t tile_count = 0;
+  if (p.ep_world > 0 && n_local == 0 && !p.d_s && warp == 0 && lane < R) {
+    // nothing of this token's MoE lives here: the exchange still needs this rank's (zero) partial
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const size_t at = ((size_t)(ep_par * p.ep_world + p.ep_rank)) * p.dim + (size_t)t * R + lane;
+      if (t * R + lane < p.dim)
+        for (int r = 0; r < p.ep_world; r++) reinterpret_cast<float*>(p.ep_base[r] + kEpSlotsOff)[at] = 0.f;
+    }
+  }
   for (;;) {
     if (!consumer_wait(ring, n)) return;
     const int t = *reinterpret_cast<volatile int*>(&hd->meta[n % ring.stages]);
-    if (t < 0) return;
+    if (t < 0) break;
     const int r0 = t * R;
     float acc[1][1] = {{0.f}};
     if (p.d_s) {
       if (!consumer_wait(ring, n)) return;
       const saddr_t slot = smem_u32(ring.slot(n));
-      const uintptr_t a = reinterpret_cast<uintptr_t>(p.sdown) + (size_t)r0 * rb_s;
+      // staged: the tile's rows back to back (whole rows), or one K range per row at pitch d_s_pitch
+      const uintptr_t a = reinterpret_cast<uintptr_t>(p.sdown) + (size_t)r0 * rb_s + s_off + (s_whole ? 0 : (size_t)row * rb_s);
+      const saddr_t row_s = slot + (uint32_t)(a & 15u) + (uint32_t)row * (s_whole ? rb_s : p.d_s_pitch);
       // the 2 * Gn lane groups that share this row split its units into equal runs of whole super-blocks
       const int parts = 2 * Gn, me = half * Gn + grp;
       constexpr int step = block_elems(TS) == 256 ? 8 : 1;
-      const int per = ((Ui + parts * step - 1) / (parts * step)) * step;
-      const int ua = min(Ui, me * per), ub = min(Ui, ua + per);
+      const int per = ((Us + parts * step - 1) / (parts * step)) * step;
+      const int ua = min(Us, me * per), ub = min(Us, ua + per);
       if (ub > ua) {
-        const saddr_t rowp[1] = {slot + (uint32_t)(a & 15u) + (uint32_t)row * rb_s + (uint32_t)units_bytes(TS, ua)};
-        consume_rows<TS, LPR, 1, 1>(rowp, li, xq, p.n_routed * Ui + ua, ub - ua, L, acc);
+        const saddr_t rowp[1] = {row_s + (uint32_t)units_bytes(TS, ua)};
+        consume_rows<TS, LPR, 1, 1>(rowp, li, xq, p.n_routed * Ui + s_u0 + ua, ub - ua, L, acc);
       }
       consumer_release(ring, n, lane);
       n++;
@@ -461,9 +484,35 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
       float s = hd->part[pb][2 * lane][0] + hd->part[pb][2 * lane + 1][0];
       if (n_local > 0)
         for (int w = 0; w < kMoeNW; w++) s += hd->rpart[pb][w][lane];
-      p.y[r0 + lane] += s;
+      if (p.ep_world > 0) {
+        // this rank's partial sum of the row goes to every rank's exchange buffer (plain peer stores)
+        const size_t at = ((size_t)(ep_par * p.ep_world + p.ep_rank)) * p.dim + r0 + lane;
+        for (int r = 0; r < p.ep_world; r++) reinterpret_cast<float*>(p.ep_base[r] + kEpSlotsOff)[at] = s;
+      } else {
+        p.y[r0 + lane] += s;
+      }
     }
     tile_count++;
+  }
+  if (p.ep_world > 0 && warp == 0) {
+    // Every row of this block is stored.  The last block of the launch to get here publishes the partial: after a
+    // system-wide fence it writes E + 1 into flag ep_rank of every rank (release), which the combine kernels poll.
+    __threadfence_system();
+    __syncwarp();
+    unsigned last = 0;
+    if (lane == 0) {
+      unsigned* done = p.sched + 2;
+      last = atomicAdd(done, 1u) == gridDim.x - 1;
+      if (last) *done = 0;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence_system();
+      if (lane < p.ep_world) {
+        unsigned* flag = reinterpret_cast<unsigned*>(p.ep_base[lane] + kEpFlagsOff) + ep_par * kMaxEpWorld + p.ep_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(ep_epoch + 1u) : "memory");
+      }
+    }
   }
 }
 
@@ -525,7 +574,7 @@ int launch_gu(MoeParams& p, int sms, int dev, cudaStream_t st) {
   static bool done[64] = {};
   int rc = set_smem(kern, dev, done);
   if (rc) return rc;
-  const int tiles = (p.gu_s ? (p.inter + p.gu_s_rows - 1) / p.gu_s_rows : 0) +
+  const int tiles = (p.gu_s ? (p.s_hi - p.s_lo + p.gu_s_rows - 1) / p.gu_s_rows : 0) +
                     (p.gu_r ? p.n_routed : 0) * ((p.inter + p.gu_r_rows - 1) / p.gu_r_rows);
   MSB_CUDA(launch_pdl(kern, dim3(std::max(1, std::min(sms, tiles))), dim3((kMoeNW + 1) * 32), fixed + (size_t)stages * slot, st, p));
   MSB_LAUNCH_CHECK("moe_gu_kernel");
@@ -540,6 +589,7 @@ int launch_down(MoeParams& p, int sms, int dev, cudaStream_t st) {
   const size_t rb_r = row_bytes(TR, p.inter), rb_s = row_bytes(TS, p.inter);
   p.d_rows = R;
   p.d_src_pitch = (uint32_t)((R * rb_r + 15 + 16 + 15) & ~(size_t)15);
+  p.d_s_pitch = piece_pitch((uint32_t)units_bytes(TS, (p.s_hi - p.s_lo) / 32));
   const size_t need = std::max((size_t)std::max(1, p.n_routed) * p.d_src_pitch, R * rb_s + 64);
   for (int stages = kMaxStages; stages >= 2; stages--) {
     if (fixed + (size_t)stages * need > (size_t)kSmemLimit) continue;
@@ -598,8 +648,21 @@ int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, s
   p.d_r = part == 0 || part == 2 || part == 4 || part == 7;
   p.d_s = p.has_shared && (part == 0 || part == 2 || part == 3 || part == 5 || part == 7);
   if (p.n_routed == 0) p.gu_r = p.d_r = 0;
+  if (p.s_lo == 0 && p.s_hi == 0) p.s_hi = p.inter;      // default: the whole shared expert
+  if (p.s_lo < 0 || p.s_hi > p.inter || p.s_lo > p.s_hi || p.s_lo % 256 || p.s_hi % 256)
+    return fail(kErrArg, "moe_decode: shared-expert range [%d, %d) must be multiples of 256 inside 0..%d", p.s_lo, p.s_hi, p.inter);
+  if (p.s_lo == p.s_hi) p.gu_s = p.d_s = 0;              // an empty slice: no shared-expert work on this rank
+  if (p.ep_world < 0 || p.ep_world > kMaxEpWorld || (p.ep_world > 0 && (p.ep_rank < 0 || p.ep_rank >= p.ep_world)))
+    return fail(kErrArg, "moe_decode: bad expert-parallel world %d / rank %d", p.ep_world, p.ep_rank);
+  for (int r = 0; r < p.ep_world; r++)
+    if (!p.ep_base[r] || (reinterpret_cast<uintptr_t>(p.ep_base[r]) & 255))
+      return fail(kErrArg, "moe_decode: exchange buffer of rank %d missing or not 256-byte aligned", r);
+  if (p.ep_world > 0 && !(p.d_r || p.d_s)) {
+    // the exchange needs a down launch on every rank, even one without work: it publishes zeros
+    p.d_r = 1;
+  }
   if (!p.gu_r && !p.gu_s && !p.d_r && !p.d_s) return kOk;
-  if ((!p.x && !p.norm_in) || !p.y || !p.h || (p.gu_r && !p.weights)) return fail(kErrArg, "moe_decode: null pointer");
+  if ((!p.x && !p.norm_in) || (!p.y && p.ep_world == 0) || !p.h || (p.gu_r && !p.weights)) return fail(kErrArg, "moe_decode: null pointer");
   if (p.norm_in && (!p.norm_w || ((reinterpret_cast<uintptr_t>(p.norm_in) | reinterpret_cast<uintptr_t>(p.norm_w)) & 15)))
     return fail(kErrArg, "moe_decode: norm_in needs a gain vector, both 16-byte aligned");
   int rc = get_tables(&p.tb);

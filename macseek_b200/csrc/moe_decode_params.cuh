@@ -6,6 +6,7 @@ namespace msb {
 
 constexpr int kMaxRouted = 16;
 constexpr int kMoeNW = 16;
+constexpr int kMaxEpWorld = 8;
 
 
 struct MoeParams {
@@ -37,10 +38,26 @@ struct MoeParams {
   int gu_s_rows, gu_s_ks;                 // shared gate/up tile rows, warps sharing a row
   int d_rows;                             // down tile rows (two warps share a row)
   uint32_t d_src_pitch;                   // shared-memory distance between the experts' row blocks of a down piece
+  uint32_t d_s_pitch;                     // distance between the shared expert's staged row pieces when only a K range is read
   uint32_t stage_bytes;
   int stages;
+  // Rows [s_lo, s_hi) of the shared expert's gate / up matrices, and the same range of the K dimension of its down
+  // matrix, are computed by this launch (multiples of 256; 0 .. inter = all of it).  Under expert parallelism rank r
+  // takes the r-th slice, so the ranks' partial outputs add up to the whole shared expert.
+  int s_lo, s_hi;
+  // Expert-parallel exchange (ep_world > 0): the down launch does not touch y; it stores its row sums into slot ep_rank
+  // of every rank's exchange buffer (peer-mapped memory, plain stores) and its last block then raises flag ep_rank there.
+  int ep_world, ep_rank;
+  uint8_t* ep_base[kMaxEpWorld];
   Tables tb;
 };
+
+// Exchange buffer of one rank (zero-filled at creation):
+//   +0    u32 epoch E: combines completed on this rank; slot / flag parity of the current exchange = E & 1
+//   +64   u32 flags[2][kMaxEpWorld]: flags[parity][r] == E + 1 once rank r's partial for this exchange is in place
+//   +256  f32 slots[2][world][dim]
+constexpr size_t kEpFlagsOff = 64, kEpSlotsOff = 256;
+inline size_t ep_exchange_bytes(int dim, int world) { return kEpSlotsOff + sizeof(float) * 2 * (size_t)world * dim; }
 
 size_t moe_decode_scratch_bytes(int inter, int max_routed);
 // part: 0 All, 1 SharedGu, 2 AfterSharedGu, 3 Shared, 4 Routed, 5 SharedDown

@@ -81,7 +81,7 @@ class DecConfig:
 class LayerW:
     """Weights of one layer (the reference's ds41::LayerW, dec_layer.hpp:18-50), all device tensors."""
 
-    def __init__(self, cfg: DecConfig, gen, ep_lo, ep_hi, moe_gen):
+    def __init__(self, cfg: DecConfig, gen, ep_lo, ep_hi, expert_seed):
         dev = gen.device
         c = cfg
         rw = lambda t, rows, cols: synthetic.random_weights(t, rows, cols, gen)
@@ -98,7 +98,7 @@ class LayerW:
         self.wo_b = rw(c.t_attn, c.dim, c.o_a_rows)
         self.sinks = torch.zeros(c.heads, dtype=torch.float32, device=dev).normal_(0, 1, generator=gen)
         self.moe = ml.MoeLayerWeights(c.dim, c.inter, c.n_experts, c.t_gate_up, c.t_down, c.t_shared, ep_lo, ep_hi, dev)
-        self.moe.randomize(moe_gen, router_gen=gen)
+        self.moe.randomize(gen, router_gen=gen, expert_seed=expert_seed)
 
 
 class DecBufs:
@@ -122,20 +122,28 @@ class DecBufs:
 class SyntheticModel:
     """All layers resident in HBM: attention/dense weights replicated, experts [ep_rank * E / ep_world, ...) local."""
 
-    def __init__(self, cfg: DecConfig, seed=1234, device="cuda", ep_rank=0, ep_world=1, group=None):
+    def __init__(self, cfg: DecConfig, seed=1234, device="cuda", ep_rank=0, ep_world=1, group=None, combine="peer",
+                 comm=None):
+        """combine: how the ranks' partial MoE outputs meet when ep_world > 1 -- "peer" (the down kernel stores into
+        every rank's exchange buffer over NVLink, ep.EpComm) or "nccl" (one all-reduce per layer).  comm: an existing
+        ep.EpComm (tests that run the ranks one after the other on one GPU); otherwise one is built over `group`."""
         self.cfg, self.device, self.ep_rank, self.ep_world, self.group = cfg, device, ep_rank, ep_world, group
         c = cfg
         self.ep_lo, self.ep_hi = ep.expert_range(c.n_experts, ep_world, ep_rank)
+        self.s_lo, self.s_hi = ep.shared_range(c.inter, ep_world, ep_rank)
+        self.combine = combine if ep_world > 1 else "none"
+        self.comm = comm
+        if self.combine == "peer" and self.comm is None:
+            self.comm = ep.EpComm(c.dim, group)
         gen = torch.Generator(device=device)
         gen.manual_seed(seed)                      # replicated tensors: the same stream on every rank
-        moe_gen = torch.Generator(device=device)
-        moe_gen.manual_seed(seed * 1000 + 17 + ep_rank)
         rope = attn.make_rope_table(c.kv_len + 1, True)
         self.rope = torch.from_numpy(rope).to(device)
         self.layers, self.state = [], []
         sh = c.attn_shape()
-        for _ in range(c.n_layers):
-            self.layers.append(LayerW(c, gen, self.ep_lo, self.ep_hi, moe_gen))
+        for l in range(c.n_layers):
+            # experts are seeded by (model seed, layer, global expert id): every world size holds the same model
+            self.layers.append(LayerW(c, gen, self.ep_lo, self.ep_hi, seed * 64 + l))
             st = attn.DecodeState(sh, c.kv_len, self.rope, device)
             # synthetic caches ~ N(0,1), as the reference fills them for its 200K benches (bench/attn200k.mm:60-66)
             st.ckv.normal_(0, 1, generator=gen)
@@ -179,6 +187,12 @@ class SyntheticModel:
         return n
 
     def encode_dec_moe(self, e: Enc, l):
+        n = self.encode_dec_moe_partial(e, l)
+        return n + self.encode_dec_moe_combine(e, l)
+
+    def encode_dec_moe_partial(self, e: Enc, l):
+        """Router + the two MoE kernels on what is resident here.  Single GPU: the result is accumulated into h and
+        nothing is left for encode_dec_moe_combine."""
         c, w, b = self.cfg, self.layers[l], self.bufs
         n = 0
         # the FFN RMSNorm (h -> x) runs inside the router launch
@@ -186,23 +200,34 @@ class SyntheticModel:
             ml.encode_moe_layer(e, w.moe, b.moe, b.x, b.h, c.score_fn, c.route_scale, norm_in=b.h, norm_w=w.ffn_norm,
                                 norm_eps=c.norm_eps); n += 3
             return n
-        # expert parallel: the router is replicated (every rank sees the same ids), partial sums combined over NVLink
-        b.y_part.zero_()     # before the router, which must be the launch directly ahead of the MoE pair
+        # expert parallel: the router is replicated (every rank sees the same ids); each rank runs ONE gate/up + down
+        # launch pair over the routed experts resident here and its slice of the shared expert
+        a = q.MoeDecodeArgs(c.dim, c.inter)
+        a.t_gate_up, a.t_down, a.t_shared = c.t_gate_up, c.t_down, c.t_shared
+        a.n_routed, a.has_shared, a.shared = c.top_k, True, w.moe.shared
+        a.weights, a.x, a.scratch = b.moe.w, b.x, b.moe.moe_scratch
+        a.y = b.y_part
+        if self.combine == "nccl":
+            b.y_part.zero_()     # before the router, which must be the launch directly ahead of the MoE pair
         arch.encode_router_fused_rmsnorm(e, b.h, w.ffn_norm, c.norm_eps, b.x, w.moe.router_w, w.moe.router_bias,
                                          b.moe.ids, b.moe.w, b.moe.router_scratch, c.top_k, c.score_fn,
                                          c.route_scale); n += 1
-        # One gate/up + down launch pair per rank into a zeroed partial: the routed experts resident here, plus the
-        # (replicated) shared expert on rank 0 only, so that the sum over ranks counts it once.
-        a = q.MoeDecodeArgs(c.dim, c.inter)
-        a.t_gate_up, a.t_down, a.t_shared = c.t_gate_up, c.t_down, c.t_shared
-        a.n_routed, a.has_shared, a.shared = c.top_k, self.ep_rank == 0, w.moe.shared
-        a.weights, a.x, a.scratch = b.moe.w, b.x, b.moe.moe_scratch
-        a.y = b.y_part
-        q.encode_moe_decode_ids_normed(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, b.h, w.ffn_norm,
-                                       c.norm_eps, q.MoePart.All); n += 2
-        ep.combine_routed(b.y_part, self.group)
-        arch.encode_add(e, b.h, b.y_part, c.dim); n += 2
+        # "peer": the down launch stores its partial into every rank's exchange buffer; "nccl": into y_part
+        q.encode_moe_decode_ep(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, self.s_lo, self.s_hi,
+                               self.comm if self.combine == "peer" else None, b.h, w.ffn_norm, c.norm_eps); n += 2
         return n
+
+    def encode_dec_moe_combine(self, e: Enc, l):
+        """h += the sum of the ranks' partial MoE outputs."""
+        c, b = self.cfg, self.bufs
+        if self.ep_world == 1:
+            return 0
+        if self.combine == "peer":
+            ep.encode_combine(e, self.comm, b.h)
+            return 1
+        ep.combine_routed(b.y_part, self.group)
+        arch.encode_add(e, b.h, b.y_part, c.dim)
+        return 2
 
     def encode_head(self, e: Enc):
         c, b = self.cfg, self.bufs

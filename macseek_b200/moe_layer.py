@@ -25,9 +25,11 @@ class MoeLayerWeights:
         self.table = None         # int64 [E][3] device addresses (0 for experts not resident here)
         self.shared = q.ExpertSlot()
 
-    def randomize(self, gen, router_gen=None):
-        """Fill with seeded synthetic weights.  The router (replicated on every rank) draws from router_gen so that
-        all ranks of an expert-parallel group hold the same router and shared expert."""
+    def randomize(self, gen, router_gen=None, expert_seed=None):
+        """Fill with seeded synthetic weights.  The router and the shared expert (replicated on every rank) draw from
+        router_gen.  With expert_seed every expert draws from its own stream, seeded by its GLOBAL id, so that a rank
+        holding experts [lo, hi) holds exactly the bytes the single-GPU model has for them; without it the whole local
+        arena comes from gen in one pass (faster, for single-GPU benches)."""
         rg = router_gen if router_gen is not None else gen
         dev = self.device
         E, dim, inter = self.n_experts, self.dim, self.inter
@@ -44,8 +46,16 @@ class MoeLayerWeights:
         # gate|up of every local expert first, then the down matrices: two uniform regions, filled in place
         gu_all = self.arena[:n_local * 2 * self.gu_bytes]
         d_all = self.arena[n_local * 2 * self.gu_bytes:]
-        synthetic.random_weights(self.t_gate_up, n_local * 2 * inter, dim, gen, out=gu_all)
-        synthetic.random_weights(self.t_down, n_local * dim, inter, gen, out=d_all)
+        if expert_seed is None:
+            synthetic.random_weights(self.t_gate_up, n_local * 2 * inter, dim, gen, out=gu_all)
+            synthetic.random_weights(self.t_down, n_local * dim, inter, gen, out=d_all)
+        else:
+            eg = torch.Generator(device=dev)
+            for i in range(n_local):
+                eg.manual_seed(int(expert_seed) * 4096 + self.expert_lo + i)
+                synthetic.random_weights(self.t_gate_up, 2 * inter, dim, eg,
+                                         out=gu_all[i * 2 * self.gu_bytes:(i + 1) * 2 * self.gu_bytes])
+                synthetic.random_weights(self.t_down, dim, inter, eg, out=d_all[i * self.d_bytes:(i + 1) * self.d_bytes])
         self.build_table()
         return self
 

@@ -176,6 +176,18 @@ def encode_moe_decode_ids_normed(e: Enc, a: MoeDecodeArgs, expert_table, ids, ex
                                                   ptr(norm_in), ptr(norm_w), norm_eps, e.handle))
 
 
+def encode_moe_decode_ep(e: Enc, a: MoeDecodeArgs, expert_table, ids, expert_lo, expert_hi, shared_lo, shared_hi,
+                         comm=None, norm_in=None, norm_w=None, norm_eps=0.0):
+    """Expert-parallel form: the experts in [expert_lo, expert_hi) plus rows [shared_lo, shared_hi) of the shared
+    expert.  comm (an ep.EpComm) given: the partial output goes to every rank's exchange buffer for ep.encode_combine;
+    comm None: it is accumulated into a.y.  No reference counterpart (model.py:869-904 gives the semantics)."""
+    import ctypes as C
+    c = a._c()
+    _lib.check(_lib.lib.msb_moe_decode_ep(c, ptr(expert_table), ptr(ids), expert_lo, expert_hi, ptr(norm_in), ptr(norm_w),
+                                          norm_eps, shared_lo, shared_hi, C.byref(comm.c) if comm is not None else None,
+                                          e.handle))
+
+
 def encode_matvec_rmsnorm(e: Enc, t, W, rows, cols, x, norm_w, eps, y):
     """y = W . (x * rsqrt(mean(x^2) + eps) * norm_w): input RMSNorm fused into the x load (quant.hpp:19-26)."""
     _lib.check(_lib.lib.msb_matvec_rmsnorm(int(t), ptr(W), rows, cols, ptr(x), ptr(norm_w), eps, ptr(y), e.handle))

@@ -123,3 +123,49 @@ def test_step_repeatable_and_graph_equals_eager():
         g.replay()
         s.synchronize()
     assert torch.equal(b.logits, outs[0][0])
+
+
+@pytest.mark.parametrize("world,inter", [(2, 256), (2, 512), (4, 1024)])
+def test_expert_parallel_step_equals_single_gpu(world, inter):
+    """The whole step under expert parallelism, the ranks' models built side by side on one GPU and encoded layer by
+    layer in rank order (so that every partial is stored before a combine is launched): every rank ends with the same
+    bits, and with the single-GPU model's token and logits within the MoE tolerance."""
+    from macseek_b200 import ep
+    from macseek_b200.core import Enc
+    from macseek_b200.dec_layer import SyntheticModel
+    cfg = small_cfg()
+    cfg.inter = inter
+    cfg.n_experts = 16
+    h0 = torch.randn(cfg.dim, device="cuda")
+    ref = SyntheticModel(cfg, seed=11)
+    e = Enc()
+    ref.bufs.h.copy_(h0)
+    ref.forward_token(e)
+    e.wait()
+    comms = ep.EpComm.local(cfg.dim, world)
+    try:
+        ranks = [SyntheticModel(cfg, seed=11, ep_rank=r, ep_world=world, combine="peer", comm=comms[r]) for r in range(world)]
+        # rank r holds exactly the single-GPU model's bytes for its experts
+        lo, hi = ranks[1].ep_lo, ranks[1].ep_hi
+        g_ref = ref.layers[0].moe.expert_views(lo)[0]
+        assert torch.equal(ranks[1].layers[0].moe.expert_views(lo)[0], g_ref)
+        pos = cfg.kv_len - 1
+        for m in ranks:
+            m.bufs.h.copy_(h0)
+        for l in range(cfg.n_layers):
+            for m in ranks:
+                m.encode_dec_attn_side(e, l, pos)
+                m.encode_dec_moe_partial(e, l)
+            for m in ranks:
+                m.encode_dec_moe_combine(e, l)
+        for m in ranks:
+            m.encode_head(e)
+        e.wait()
+        for m in ranks[1:]:
+            assert torch.equal(m.bufs.logits, ranks[0].bufs.logits)
+        a, b = ranks[0].bufs.logits.cpu().numpy(), ref.bufs.logits.cpu().numpy()
+        assert np.max(np.abs(a - b)) <= 1e-3 * np.max(np.abs(b))
+        assert int(ranks[0].bufs.next_id.item()) == int(ref.bufs.next_id.item())
+    finally:
+        for c in comms:
+            c.close()
