@@ -39,6 +39,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=43)
     ap.add_argument("--kv-len", type=int, default=200000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--combine", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the ranks' partial MoE outputs are summed (peer-memory exchange, or an NCCL all-reduce)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel roofline sweeps (cfg1/cfg2/cfg4)")
     return ap.parse_args()
 
 
@@ -52,13 +55,14 @@ def workload_config(a, world):
 
 
 # ------------------------------------------------------------------------------------------------ CPU sample
-def cpu_token_seconds(a, use_ref=True, threads=None, reps=1):
-    """Time the CPU routines on a bounded sample of one token's work and scale to the whole token.
-    Returns (seconds per token, dict describing the sample)."""
+def cpu_token_seconds(a, use_ref=True, threads=None, row_div=1):
+    """Time the CPU routines on a bounded sample of one token's work and scale to the whole token.  row_div > 1 times
+    1 / row_div of every matrix's rows (and of the keys) and scales linearly: the single-thread run uses it to stay
+    bounded.  Returns (seconds per token, dict describing the sample).  Imports nothing that loads the CUDA library."""
     import numpy as np
     import oracle_lib as ol
     import synth
-    from macseek_b200.dec_layer import DecConfig
+    from macseek_b200.shapes import DecConfig
     c = DecConfig(n_layers=a.layers, kv_len=a.kv_len)
     orc = ol.Oracle()
     ref = ol.Ref.load(build=False) if use_ref else None
@@ -66,22 +70,23 @@ def cpu_token_seconds(a, use_ref=True, threads=None, reps=1):
     rng = np.random.default_rng(0)
 
     def mv(t, rows, cols, groups=1):
-        W = synth.random_weights(int(t), rows, cols, rows + cols)
+        r = max(groups, (rows // row_div) // groups * groups)
+        W = synth.random_weights(int(t), r, cols, rows + cols)
         x = synth.randn(cols * groups, 3)
         t0 = time.perf_counter()
         if ref is not None:
-            ref.matvec(int(t), W, rows, cols, x, groups, threads=T)
+            ref.matvec(int(t), W, r, cols, x, groups, threads=T)
         else:
-            orc.matvec(int(t), W, rows, cols, x, groups, threads=T)
-        return time.perf_counter() - t0
+            orc.matvec(int(t), W, r, cols, x, groups, threads=T)
+        return (time.perf_counter() - t0) * (rows / r)
 
     hD = c.heads * c.D
     layer = 0.0
-    # attention projections (full)
+    # attention projections
     layer += mv(c.t_attn, c.q_lora, c.dim) + mv(c.t_attn, c.D, c.dim) + mv(c.t_attn, hD, c.q_lora)
     layer += mv(c.t_index, c.index_heads, c.dim) + mv(c.t_index, c.index_heads * c.index_dim, c.q_lora)
     layer += mv(c.t_attn, c.o_a_rows, hD // c.o_groups, c.o_groups) + mv(c.t_attn, c.dim, c.o_a_rows)
-    # MoE: router + 8 routed + shared (full layer)
+    # MoE: router + 8 routed + shared
     Wr = (rng.standard_normal((c.n_experts, c.dim)) * 0.02).astype(np.float32)
     x = synth.randn(c.dim, 5)
     t0 = time.perf_counter()
@@ -92,7 +97,7 @@ def cpu_token_seconds(a, use_ref=True, threads=None, reps=1):
                                (c.t_shared, c.inter, c.dim, 2), (c.t_shared, c.dim, c.inter, 1)):
         layer += mv(t, rows, cols) * cnt
     # indexer on a sample of the keys, exact top-k on full-length scores, sparse attention (full)
-    n_keys = min(c.kv_len, 20000)
+    n_keys = max(1000, min(c.kv_len, 20000) // row_div)
     keys = rng.standard_normal((n_keys, c.index_dim)).astype(np.float32)
     qi = rng.standard_normal((c.index_heads, c.index_dim)).astype(np.float32)
     wi = rng.standard_normal(c.index_heads).astype(np.float32)
@@ -113,14 +118,24 @@ def cpu_token_seconds(a, use_ref=True, threads=None, reps=1):
     n_head = 8192
     head = mv(c.t_head, n_head, c.dim) * (c.vocab / n_head)
     total = layer * c.n_layers + head
+    frac = "" if row_div == 1 else " (1/%d of every matrix's rows and of the key sample, scaled)" % row_div
     return total, {"kind": "reference" if ref is not None else "port", "cores": T,
-                   "sample": "one layer in full (projections, router, 8 routed + shared expert, sparse attention, top-k) "
+                   "sample": "one layer (projections, router, 8 routed + shared expert, sparse attention, top-k)%s "
                              "with the indexer on %d of %d keys and the head on %d of %d rows, scaled to %d layers + head; "
-                             "%s" % (n_keys, c.kv_len, n_head, c.vocab, c.n_layers,
+                             "%s" % (frac, n_keys, c.kv_len, max(1, n_head // row_div), c.vocab, c.n_layers,
                                      "matvec-shaped parts through the reference's own ref::dequant_row + double dot "
                                      "(oracle/_ref), router / indexer / attention at the benchmark's shapes through the C "
                                      "port because the reference fixes those shapes at compile time"
                                      if ref is not None else "C port of the reference routines (oracle/msb_oracle.c)")}
+
+
+def cpu_baseline_dict(a):
+    """The threaded figure (all host cores) with the single-thread-as-written figure beside it."""
+    sec, info = cpu_token_seconds(a, use_ref=True)
+    sec1, info1 = cpu_token_seconds(a, use_ref=True, threads=1, row_div=16)
+    d = dict(info, value=1.0 / sec, unit=UNIT)
+    d["single_thread"] = {"value": 1.0 / sec1, "unit": UNIT, "cores": 1, "sample": info1["sample"]}
+    return d
 
 
 def run_reference(a):
@@ -137,6 +152,8 @@ def run_reference(a):
             times.append(t)
     sec = sum(times) / len(times)
     val = 1.0 / sec
+    sec1, info1 = cpu_token_seconds(a, use_ref=True, threads=1, row_div=16)
+    info = dict(info, single_thread={"value": 1.0 / sec1, "unit": UNIT, "cores": 1, "sample": info1["sample"]})
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f64 accumulate over f32 dequantised weights", "data": "synthetic",
@@ -214,7 +231,7 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     cfg = DecConfig(n_layers=a.layers, kv_len=a.kv_len)
-    model = SyntheticModel(cfg, seed=1234, device=dev, ep_rank=rank, ep_world=world, group=group)
+    model = SyntheticModel(cfg, seed=1234, device=dev, ep_rank=rank, ep_world=world, group=group, combine=a.combine)
     b = model.bufs
     gen = torch.Generator(device=dev)
     gen.manual_seed(99)
@@ -267,34 +284,60 @@ def run_ours(a):
         ms_e2e = ev2.elapsed_time(ev3)
         clocks = sampler.stop()
 
-        # ---- roofline of the dominant kernel (MoE gate/up of all experts), timed alone, one launch per layer
+        # ---- roofline of the dominant kernel (MoE gate/up of all experts), timed alone, one launch per layer.  Each
+        # layer's launch uses the ids its own router produced for this token (logged in one eager pass), so that the
+        # byte count is the sum over layers of the experts actually resident here.
+        ids_log = torch.zeros(cfg.n_layers, cfg.top_k, dtype=torch.int32, device=dev)
+        model.ids_log = ids_log
+        b.h.copy_(h_in)
+        model.forward_token(e)
+        e.wait()
+        model.ids_log = None
+        ids_host = ids_log.cpu().tolist()
         lw0 = model.layers[0].moe
-        gu_bytes = 0
+        s_lo, s_hi = model.s_lo, model.s_hi
+        shared_gu = 2 * q.row_bytes(cfg.t_shared, cfg.dim) * (s_hi - s_lo)
+        shared_d = q.row_bytes(cfg.t_shared, s_hi - s_lo) * cfg.dim
+        n_local_layers = [sum(1 for i in ids_host[l] if lw0.expert_lo <= i < lw0.expert_hi) for l in range(cfg.n_layers)]
         reps = max(1, 40 // cfg.n_layers)
         n_gu = reps * cfg.n_layers
-        torch.cuda.synchronize()
-        ggraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(ggraph, stream=stream):
-            for _ in range(reps):
-                for l in range(cfg.n_layers):
-                    w = model.layers[l].moe
-                    args = q.MoeDecodeArgs(cfg.dim, cfg.inter)
-                    args.t_gate_up, args.t_down, args.t_shared = cfg.t_gate_up, cfg.t_down, cfg.t_shared
-                    args.n_routed, args.has_shared, args.shared = cfg.top_k, True, w.shared
-                    args.weights, args.x, args.y, args.scratch = b.moe.w, b.x, b.y_part, b.moe.moe_scratch
-                    q.encode_moe_decode_ids(Enc(torch.cuda.current_stream()), args, w.table, b.moe.ids, w.expert_lo,
-                                            w.expert_hi, q.MoePart.GuAll)
-        ggraph.replay()
-        stream.synchronize()
-        ev4, ev5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev4.record(stream)
-        ggraph.replay()
-        ev5.record(stream)
-        stream.synchronize()
-        gu_us = ev4.elapsed_time(ev5) * 1e3 / n_gu
-        ids_now = b.moe.ids.cpu().tolist()
-        n_local = sum(1 for i in ids_now if lw0.expert_lo <= i < lw0.expert_hi)
-        gu_bytes = n_local * 2 * lw0.gu_bytes + (lw0.shared.gate.numel() + lw0.shared.up.numel())
+        gu_bytes = sum(n * 2 * lw0.gu_bytes + shared_gu for n in n_local_layers) / cfg.n_layers
+        d_bytes = sum(n * lw0.d_bytes + shared_d for n in n_local_layers) / cfg.n_layers
+
+        def moe_graph(part):
+            g = torch.cuda.CUDAGraph()
+            y_tmp = torch.zeros(cfg.dim, dtype=torch.float32, device=dev)
+            with torch.cuda.graph(g, stream=stream):
+                for _ in range(reps):
+                    for l in range(cfg.n_layers):
+                        w = model.layers[l].moe
+                        args = q.MoeDecodeArgs(cfg.dim, cfg.inter)
+                        args.t_gate_up, args.t_down, args.t_shared = cfg.t_gate_up, cfg.t_down, cfg.t_shared
+                        args.n_routed, args.has_shared, args.shared = cfg.top_k, True, w.shared
+                        args.weights, args.x, args.y, args.scratch = b.moe.w, b.x, y_tmp, b.moe.moe_scratch
+                        ec = Enc(torch.cuda.current_stream())
+                        if world == 1:
+                            q.encode_moe_decode_ids(ec, args, w.table, ids_log[l], w.expert_lo, w.expert_hi, part)
+                        else:
+                            # the expert-parallel form has no "part" argument: time both launches, gate/up = pair - down
+                            q.encode_moe_decode_ep(ec, args, w.table, ids_log[l], w.expert_lo, w.expert_hi, s_lo, s_hi, None)
+            g.replay()
+            stream.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            g.replay()
+            t1.record(stream)
+            stream.synchronize()
+            return g, t0.elapsed_time(t1) * 1e3 / n_gu
+
+        if world == 1:
+            ggraph, gu_us = moe_graph(q.MoePart.GuAll)
+            dgraph, d_us = moe_graph(q.MoePart.DownAll)
+            pair_us = gu_us + d_us
+        else:
+            ggraph, pair_us = moe_graph(q.MoePart.All)
+            dgraph = None
+            gu_us = d_us = None
         # the output head (Q6_K 129280 x dim) alone: the one launch of the step that is purely a weight stream
         hgraph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(hgraph, stream=stream):
@@ -309,6 +352,43 @@ def run_ours(a):
         ev7.record(stream)
         stream.synchronize()
         head_us = ev6.elapsed_time(ev7) * 1e3 / 4
+        # ---- expert parallel: the N-rank step must compute what one GPU computes.  A 2-layer model with ALL experts
+        # and the same model split over the ranks (experts are seeded by global id) decode the same token.
+        ep_check = None
+        if world > 1:
+            ccfg = DecConfig(n_layers=2, kv_len=8192)
+            full = SyntheticModel(ccfg, seed=77, device=dev)
+            part = SyntheticModel(ccfg, seed=77, device=dev, ep_rank=rank, ep_world=world, group=group, combine=a.combine,
+                                  comm=model.comm)
+            gen2 = torch.Generator(device=dev)
+            gen2.manual_seed(5)
+            hc = torch.empty(cfg.dim, dtype=torch.float32, device=dev).normal_(0, 1, generator=gen2)
+            full.bufs.h.copy_(hc)
+            full.forward_token(e)
+            part.bufs.h.copy_(hc)
+            part.forward_token(e)
+            e.wait()
+            ref_l, got_l = full.bufs.logits, part.bufs.logits
+            rel = float((got_l - ref_l).abs().max() / ref_l.abs().max())
+            same_id = int(full.bufs.next_id.item()) == int(part.bufs.next_id.item())
+            chk = torch.stack([got_l.view(torch.int32).to(torch.int64).sum(), part.bufs.next_id.to(torch.int64)[0]])
+            allchk = [torch.zeros_like(chk) for _ in range(world)]
+            dist.all_gather(allchk, chk)
+            ranks_identical = all(torch.equal(c, allchk[0]) for c in allchk)
+            ep_check = {"ep_matches_n1": bool(same_id and rel <= 1e-3), "next_id_equal": same_id, "max_rel_logit_diff": rel,
+                        "ranks_bit_identical": bool(ranks_identical), "model": "2 layers, all experts vs split over ranks"}
+            del full, part
+        extras = {}
+        if world == 1 and not a.no_extras:
+            import kernel_bench as kb
+            T = q.QType
+            sweep = [kb.matvec_case(T.IQ1_S, 4096, 4096, 1, quiet=True)]                         # cfg1
+            for t in (T.Q8_0, T.Q6_K, T.Q5_K, T.IQ4_NL, T.IQ2_XXS):                               # cfg2
+                for rows, cols in ((4096, 4096), (16384, 4096), (4096, 16384)):
+                    for n in (1, 4):
+                        sweep.append(kb.matvec_case(t, rows, cols, n, quiet=True))
+            extras["matvec"] = sweep
+            extras["prefill"] = kb.moe_prefill_case(4096, quiet=True)
         st = __import__("macseek_b200._lib", fromlist=["x"]).device_status()
         if st:
             raise RuntimeError("device-side failure word %d" % st)
@@ -326,20 +406,29 @@ def run_ours(a):
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-        achieved = gu_bytes / gu_us / 1e3
+        tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+        if world == 1:
+            r_kernel = "moe_gu_kernel (gate/up + SwiGLU of the 8 routed experts + shared expert)"
+            r_us, r_bytes = gu_us, gu_bytes
+        else:
+            r_kernel = "moe_gu_kernel + moe_down_kernel pair on the experts resident on rank 0 and its slice of the shared expert"
+            r_us, r_bytes = pair_us, gu_bytes + d_bytes
+        achieved = r_bytes / r_us / 1e3
         lb = cfg.layer_bytes(1.0 / world)
         token_bytes = lb["total"] * cfg.n_layers + cfg.head_bytes()
         line = {"metric": METRIC, "value": a.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": a.steps,
                 "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "u8 codes x int16 fixed-point activations (dp4a), f32 accumulate; fp8 tcgen05 (indexer) and bf16 mma (attention)",
-                "data": "synthetic", "config": workload_config(a, world),
+                "data": "synthetic", "config": dict(workload_config(a, world), combine=(a.combine if world > 1 else "none")),
                 "e2e": {"value": a.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": cfg.dim * 4,
                         "d2h_bytes_per_step": 4},
                 "gpu_launches": launches * a.steps,
                 "clocks": clocks,
-                "roofline": {"bound": "hbm", "kernel": "moe_gu_kernel (gate/up + SwiGLU of the routed experts resident here + shared expert)",
+                "roofline": {"bound": "hbm", "kernel": r_kernel,
                              "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "peak_source": peak_src, "us_per_launch": gu_us, "bytes_per_launch": gu_bytes,
+                             "peak_source": peak_src, "us_per_launch": r_us, "bytes_per_launch": r_bytes,
+                             "local_experts_per_layer": {"min": min(n_local_layers), "mean": sum(n_local_layers) / len(n_local_layers),
+                                                         "max": max(n_local_layers)},
                              # dram__bytes_read.sum + dram__bytes_write.sum of one launch with all 8 routed
                              # experts resident, from the ncu capture summarised under profiles/
                              "traffic": NCU_GU_TRAFFIC_BYTES if world == 1 else None},
@@ -347,11 +436,29 @@ def run_ours(a):
                                   "achieved": cfg.head_bytes() / head_us / 1e3, "peak": peak, "unit": "GB/s",
                                   "frac": cfg.head_bytes() / head_us / 1e3 / peak, "us_per_launch": head_us,
                                   "bytes_per_launch": cfg.head_bytes()},
-                "step_bytes": {"per_token_this_rank": token_bytes, "gbs_whole_step": token_bytes / (ms / a.steps) / 1e6}}
+                "step_bytes": {"per_token_this_rank": token_bytes, "gbs_whole_step": token_bytes / (ms / a.steps) / 1e6,
+                               "moe_this_rank": lb["moe"], "replicated": lb["total"] - lb["moe"]}}
+        if world == 1:
+            line["roofline_moe_down"] = {"bound": "hbm", "kernel": "moe_down_kernel (8 routed IQ2_XXS + shared Q8_0, accumulated into y)",
+                                         "achieved": d_bytes / d_us / 1e3, "peak": peak, "unit": "GB/s",
+                                         "frac": d_bytes / d_us / 1e3 / peak, "us_per_launch": d_us, "bytes_per_launch": d_bytes}
+        if ep_check is not None:
+            line["ep_check"] = ep_check
+            line["ep_matches_n1"] = ep_check["ep_matches_n1"]
+        if "matvec" in extras:
+            # cfg1 and the cfg2 sweep: CUDA-graph replays of 20 launches rotating over a pool of weight copies >= 512 MB
+            line["roofline_matvec"] = [dict(m, frac=m["gbs"] / peak, unit="GB/s") for m in extras["matvec"]]
+        if "prefill" in extras:
+            pf = extras["prefill"]
+            line["roofline_prefill"] = {"bound": "tensor", "kernel": "msb_moe_prefill (moep_gemm_kernel x4 + gather + combine), cfg4: "
+                                        "4096 tokens, top-8 of 384, N(0,1) logits + log-Zipf(1.1) bias", "achieved": pf["tflops"],
+                                        "peak": tf_peak, "unit": "TFLOP/s", "frac": pf["tflops"] / tf_peak,
+                                        "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst); half operands",
+                                        "ms_per_layer": pf["ms"], "flop": pf["flop"], "experts_hit": pf["experts_hit"],
+                                        "tokens_per_expert": pf["tokens_per_expert"]}
         if world == 1 and not a.no_cpu_baseline:
             try:
-                sec, info = cpu_token_seconds(a, use_ref=True)
-                line["cpu_baseline"] = dict(info, value=1.0 / sec, unit=UNIT)
+                line["cpu_baseline"] = cpu_baseline_dict(a)
             except Exception as ex:      # the oracle is test infrastructure: never let it break the GPU number
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "error": str(ex)[:200]}
         print(json.dumps(line), flush=True)
@@ -361,7 +468,7 @@ def run_ours(a):
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        del graph, ggraph, hgraph
+        del graph, ggraph, hgraph, dgraph
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()

@@ -1,12 +1,12 @@
 """Per-kernel timing of the decode path's kernels, outside the full decode step.
 
-    python -m macseek_b200.kernel_bench matvec Q6_K 129280 4096 [--n 1] [--groups 1]
-    python -m macseek_b200.kernel_bench moe {router|gu|down|all}
-    python -m macseek_b200.kernel_bench attn {index|scores|topk|sparse|all} [--kv-len 200000]
-    python -m macseek_b200.kernel_bench gemm Q6_K 4096 4096 --n 4096
-    python -m macseek_b200.kernel_bench moe_prefill [--n 4096]
-    python -m macseek_b200.kernel_bench layer            # cost added by each call of the decode layer, in context
-    python -m macseek_b200.kernel_bench sweep
+    python kernel_bench.py matvec Q6_K 129280 4096 [--n 1] [--groups 1]
+    python kernel_bench.py moe {router|gu|down|all}
+    python kernel_bench.py attn {index|scores|topk|sparse|all} [--kv-len 200000]
+    python kernel_bench.py gemm Q6_K 4096 4096 --n 4096
+    python kernel_bench.py moe_prefill [--n 4096]
+    python kernel_bench.py layer            # cost added by each call of the decode layer, in context
+    python kernel_bench.py sweep
 
 Each case builds synthetic weights on the device (several copies, together larger than the 126 MB L2, used in
 rotation), records 20 launches into one CUDA graph and times graph replays with CUDA events on the replaying
@@ -19,9 +19,8 @@ import argparse
 
 import torch
 
-from . import _lib, arch, attn, moe_layer as ml, quant as q, synthetic
-from .core import ptr
-from .core import Enc
+from macseek_b200 import _lib, arch, attn, moe_layer as ml, quant as q, synthetic
+from macseek_b200.core import Enc, ptr
 
 
 def graph_time(fn, n_in_graph: int = 20, reps: int = 10):
@@ -59,7 +58,7 @@ def run(fn, eager: int):
     return graph_time(fn)
 
 
-def matvec_case(t: q.QType, rows: int, cols: int, n: int = 1, groups: int = 1, eager: int = 0):
+def matvec_case(t: q.QType, rows: int, cols: int, n: int = 1, groups: int = 1, eager: int = 0, quiet: bool = False):
     gen = torch.Generator(device="cuda")
     gen.manual_seed(2)
     nbytes = synthetic.row_bytes(t, cols) * rows
@@ -76,12 +75,15 @@ def matvec_case(t: q.QType, rows: int, cols: int, n: int = 1, groups: int = 1, e
             q.encode_matvec_n(e, t, Ws[i % copies], rows, cols, x, y, n, False, groups)
 
     r = run(f, eager)
-    if r:
+    if r and not quiet:
         print(f"matvec {t.name:8s} {rows:6d}x{cols:6d} n={n} g={groups} median {r[0]:8.2f} us min {r[1]:8.2f}"
               f"  {nbytes / r[0] / 1e3:8.1f} GB/s  ({nbytes / 1e6:.1f} MB x{copies})", flush=True)
+    if r:
+        return {"type": t.name, "rows": rows, "cols": cols, "batch": n, "us": r[0], "bytes": nbytes,
+                "gbs": nbytes / r[0] / 1e3, "weight_copies": copies}
 
 
-def moe_cases(which: str, eager: int = 0):
+def moe_cases(which: str, eager: int = 0, quiet: bool = False):
     """The benchmark MoE layer: 8 of 384 routed experts (IQ1_S gate/up, IQ2_XXS down) + Q8_0 shared expert."""
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
@@ -119,12 +121,16 @@ def moe_cases(which: str, eager: int = 0):
     d_bytes = 8 * iq2 + q8b
     cases = {"router": (router, 384 * 4096 * 4), "gu": (mk(q.MoePart.GuAll), gu_bytes),
              "down": (mk(q.MoePart.DownAll), d_bytes), "all": (mk(q.MoePart.All), gu_bytes + d_bytes)}
+    out = {}
     for name in (cases if which == "every" else [which]):
         fn, nbytes = cases[name]
         r = run(fn, eager)
         if r:
-            print(f"moe {name:8s} median {r[0]:8.2f} us  min {r[1]:8.2f} us   {nbytes / r[0] / 1e3:8.1f} GB/s",
-                  flush=True)
+            out[name] = {"us": r[0], "bytes": nbytes, "gbs": nbytes / r[0] / 1e3}
+            if not quiet:
+                print(f"moe {name:8s} median {r[0]:8.2f} us  min {r[1]:8.2f} us   {nbytes / r[0] / 1e3:8.1f} GB/s",
+                      flush=True)
+    return out
 
 
 def attn_cases(which: str, kv_len: int = 200000, eager: int = 0):
@@ -204,7 +210,7 @@ def gemm_case(t: q.QType, rows: int, cols: int, n: int, eager: int = 0):
             print(f"gemm {n}x{rows}x{cols} {name:34s} median {r[0]:9.2f} us   {flop / r[0] / 1e6:8.1f} TFLOP/s", flush=True)
 
 
-def moe_prefill_case(n: int = 4096, eager: int = 0, routing: str = "bias"):
+def moe_prefill_case(n: int = 4096, eager: int = 0, routing: str = "bias", quiet: bool = False):
     """The benchmark prefill layer: n tokens, top-8 of 384 experts (IQ1_S gate/up, IQ2_XXS down) + Q8_0 shared expert,
     dim 4096, inter 2048.  routing "bias": logits N(0,1) plus a log-Zipf(1.1) popularity bias over a seeded expert
     permutation (a few experts take most tokens); "sample": top-k drawn without replacement from Zipf(0.8)
@@ -251,7 +257,8 @@ def moe_prefill_case(n: int = 4096, eager: int = 0, routing: str = "bias"):
     a.Y = torch.zeros(n, D, device="cuda")
     a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(offs[-1], n, len(used), D, I), dtype=torch.uint8, device="cuda")
     cs = sorted(counts)
-    print(f"moe_prefill n={n} routing={routing}: {len(used)} experts hit, tokens/expert min {cs[0]} median {cs[len(cs) // 2]} max {cs[-1]}", flush=True)
+    if not quiet:
+        print(f"moe_prefill n={n} routing={routing}: {len(used)} experts hit, tokens/expert min {cs[0]} median {cs[len(cs) // 2]} max {cs[-1]}", flush=True)
     e = Enc()
     for _ in range(2):
         q.encode_moe_prefill(e, a)
@@ -268,14 +275,17 @@ def moe_prefill_case(n: int = 4096, eager: int = 0, routing: str = "bias"):
         ts.append(t0.elapsed_time(t1))
     ts.sort()
     flop = 2.0 * 3 * D * I * (n * K + n)
-    print(f"moe_prefill n={n} median {ts[2]:8.3f} ms   {flop / ts[2] / 1e9:8.1f} TFLOP/s (algorithmic 2*3*D*I*(entries+tokens))",
-          flush=True)
+    if not quiet:
+        print(f"moe_prefill n={n} median {ts[2]:8.3f} ms   {flop / ts[2] / 1e9:8.1f} TFLOP/s (algorithmic 2*3*D*I*(entries+tokens))",
+              flush=True)
+    return {"tokens": n, "routing": routing, "ms": ts[2], "flop": flop, "tflops": flop / ts[2] / 1e9,
+            "experts_hit": len(used), "tokens_per_expert": {"min": cs[0], "median": cs[len(cs) // 2], "max": cs[-1]}}
 
 
 def layer_stages(n_layers: int = 8, kv_len: int = 200000):
     """The decode layer in context: CUDA graphs of n_layers layers cut after the first k calls of each layer, k = 1 ..;
     the difference between consecutive cuts is what call k adds per layer with all overlaps as in the real step."""
-    from . import dec_layer as dl
+    from macseek_b200 import dec_layer as dl
     cfg = dl.DecConfig(n_layers=n_layers, kv_len=kv_len)
     model = dl.SyntheticModel(cfg, seed=1234, device=torch.device("cuda", torch.cuda.current_device()))
     limit, count, names = [10 ** 9], [0], []

@@ -5,7 +5,7 @@ from . import _lib
 from .core import Enc, ptr
 
 kExperts, kTopK, kRouteScale = 384, 6, 1.5      # the reference's compile-time shape (arch.hpp:13,16)
-SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
+from .shapes import SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID  # noqa: E402,F401
 
 
 class Scratch:

@@ -11,8 +11,7 @@ import torch
 from . import _lib
 from .core import Enc, ptr
 
-KEY_F16, KEY_FP8 = 1, 101
-ELEM_F16, ELEM_BF16 = 1, 30
+from .shapes import KEY_F16, KEY_FP8, ELEM_F16, ELEM_BF16  # noqa: E402,F401
 
 
 class Shape:

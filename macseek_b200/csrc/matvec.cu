@@ -412,12 +412,15 @@ int matvec_n(int t, const void* W, int rows, int cols, const float* X, int64_t x
   p.row_bytes = (uint32_t)row_bytes(t, cols);
   p.accumulate = accumulate;
   p.units = cols / 32;
+  // activation columns per pass: as many as leave at least half of the shared memory to the weight ring
+  int max_nc = 4;
+  while (max_nc > 1 && lut_bytes_for(t) + (size_t)max_nc * xq_bytes(p.units, is_dense(t), xq_padded(t)) > (size_t)kSmemLimit / 2) max_nc >>= 1;
   for (int c0 = 0; c0 < n;) {
     const int left = n - c0;
     p.x = X + (size_t)c0 * x_stride;
     p.y = Y + (size_t)c0 * y_stride;
-    if (left >= 4) { p.n = 4; rc = launch_cols<4>(t, p, st, dev, sms); c0 += 4; }
-    else if (left >= 2) { p.n = 2; rc = launch_cols<2>(t, p, st, dev, sms); c0 += 2; }
+    if (left >= 4 && max_nc >= 4) { p.n = 4; rc = launch_cols<4>(t, p, st, dev, sms); c0 += 4; }
+    else if (left >= 2 && max_nc >= 2) { p.n = 2; rc = launch_cols<2>(t, p, st, dev, sms); c0 += 2; }
     else { p.n = 1; rc = launch_cols<1>(t, p, st, dev, sms); c0 += 1; }
     if (rc) return rc;
   }

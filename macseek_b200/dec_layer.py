@@ -13,69 +13,12 @@ import torch
 
 from . import arch, attn, ep, moe_layer as ml, quant as q, synthetic
 from .core import Enc
+from .shapes import DecConfig  # noqa: F401  (re-exported)
 
 
-class DecConfig:
-    """Shapes of the synthetic decode step (benchmark configuration: hidden 4096, 43 layers, 64 heads, KV rows of
-    512 + 64 rope dims in bf16, 64 x 128 FP8 index heads with top-k 2048 over a 200K KV, 384 experts top-8 + 1 shared,
-    expert inter 2048, vocab 129280 with a Q6_K head).  Projection shapes follow the reference's structure
-    (tests/dec_synth.hpp:113-132) scaled to this hidden size."""
-
-    def __init__(self, **kw):
-        self.dim = 4096
-        self.n_layers = 43
-        self.heads = 64
-        self.D = 576
-        self.q_lora = 1280
-        self.o_groups = 8
-        self.o_a_rows = 8192
-        self.window = 128
-        self.index_heads = 64
-        self.index_dim = 128
-        self.topk = 2048
-        self.kv_len = 200000
-        self.n_experts = 384
-        self.top_k = 8
-        self.inter = 2048
-        self.vocab = 129280
-        self.score_fn = arch.SCORE_SIGMOID
-        self.route_scale = 1.0
-        self.t_attn = q.QType.Q6_K
-        self.t_index = q.QType.BF16
-        self.t_gate_up = q.QType.IQ1_S
-        self.t_down = q.QType.IQ2_XXS
-        self.t_shared = q.QType.Q8_0
-        self.t_head = q.QType.Q6_K
-        self.key_type = attn.KEY_FP8
-        self.elem_type = attn.ELEM_BF16
-        self.norm_eps = 1e-6
-        for k, v in kw.items():
-            if not hasattr(self, k):
-                raise AttributeError(k)
-            setattr(self, k, v)
-
-    def attn_shape(self):
-        return attn.Shape(D=self.D, heads=self.heads, window=self.window, index_heads=self.index_heads, topk=self.topk,
-                          key_type=self.key_type, elem_type=self.elem_type)
-
-    # ---- byte model: what one token must read, per layer and for the head
-    def layer_bytes(self, local_expert_fraction=1.0):
-        rb = synthetic.row_bytes
-        hD = self.heads * self.D
-        attn_w = (rb(self.t_attn, self.dim) * (self.q_lora + self.D) + rb(self.t_attn, self.q_lora) * hD
-                  + rb(self.t_attn, hD // self.o_groups) * self.o_a_rows + rb(self.t_attn, self.o_a_rows) * self.dim)
-        idx_w = rb(self.t_index, self.dim) * self.index_heads + rb(self.t_index, self.q_lora) * self.index_heads * self.index_dim
-        keys = self.kv_len * self.index_dim * (1 if self.key_type == attn.KEY_FP8 else 2)
-        rows = (self.window + self.topk) * self.D * 2
-        expert = 2 * rb(self.t_gate_up, self.dim) * self.inter + rb(self.t_down, self.inter) * self.dim
-        shared = 2 * rb(self.t_shared, self.dim) * self.inter + rb(self.t_shared, self.inter) * self.dim
-        router = self.n_experts * self.dim * 4
-        moe = int(self.top_k * expert * local_expert_fraction) + shared + router
-        return {"attn_weights": attn_w, "index_weights": idx_w, "index_keys": keys, "kv_rows": rows, "moe": moe,
-                "total": attn_w + idx_w + keys + rows + moe}
-
-    def head_bytes(self):
-        return synthetic.row_bytes(self.t_head, self.dim) * self.vocab
+def attn_shape(c: DecConfig):
+    return attn.Shape(D=c.D, heads=c.heads, window=c.window, index_heads=c.index_heads, topk=c.topk,
+                      key_type=c.key_type, elem_type=c.elem_type)
 
 
 class LayerW:
@@ -140,7 +83,7 @@ class SyntheticModel:
         rope = attn.make_rope_table(c.kv_len + 1, True)
         self.rope = torch.from_numpy(rope).to(device)
         self.layers, self.state = [], []
-        sh = c.attn_shape()
+        sh = attn_shape(c)
         for l in range(c.n_layers):
             # experts are seeded by (model seed, layer, global expert id): every world size holds the same model
             self.layers.append(LayerW(c, gen, self.ep_lo, self.ep_hi, seed * 64 + l))
@@ -160,6 +103,7 @@ class SyntheticModel:
         self.bufs = DecBufs(c, device)
         self.side_stream = torch.cuda.Stream(device=device)
         self.launches_per_token = 0
+        self.ids_log = None      # optional int32 [n_layers][top_k]: every layer's router ids are copied there
 
     # ------------------------------------------------------------------ one layer
     def encode_dec_attn_side(self, e: Enc, l, pos):
@@ -199,6 +143,8 @@ class SyntheticModel:
         if self.ep_world == 1:
             ml.encode_moe_layer(e, w.moe, b.moe, b.x, b.h, c.score_fn, c.route_scale, norm_in=b.h, norm_w=w.ffn_norm,
                                 norm_eps=c.norm_eps); n += 3
+            if self.ids_log is not None:
+                self.ids_log[l].copy_(b.moe.ids)
             return n
         # expert parallel: the router is replicated (every rank sees the same ids); each rank runs ONE gate/up + down
         # launch pair over the routed experts resident here and its slice of the shared expert
@@ -215,6 +161,8 @@ class SyntheticModel:
         # "peer": the down launch stores its partial into every rank's exchange buffer; "nccl": into y_part
         q.encode_moe_decode_ep(e, a, w.moe.table, b.moe.ids, w.moe.expert_lo, w.moe.expert_hi, self.s_lo, self.s_hi,
                                self.comm if self.combine == "peer" else None, b.h, w.ffn_norm, c.norm_eps); n += 2
+        if self.ids_log is not None:
+            self.ids_log[l].copy_(b.moe.ids)
         return n
 
     def encode_dec_moe_combine(self, e: Enc, l):

@@ -6,19 +6,7 @@ import torch
 
 from . import _lib
 from .core import Enc, ptr
-
-
-class QType(enum.IntEnum):
-    """ggml type ids (src/kernels/quant_types.hpp:10-12)."""
-    F32 = 0
-    F16 = 1
-    Q8_0 = 8
-    Q5_K = 13
-    Q6_K = 14
-    IQ2_XXS = 16
-    IQ1_S = 19
-    IQ4_NL = 20
-    BF16 = 30
+from .shapes import QType  # noqa: F401
 
 
 def block_elems(t):

@@ -3,21 +3,7 @@ block scales ~ U(0.01, 0.05) (divided per type so that dequantised magnitudes ar
 configurations specify.  Used by bench.py and the decode-step driver; parity tests build their inputs on the host."""
 import torch
 
-from .quant import QType
-
-_BLOCK = {QType.Q8_0: (32, 34), QType.Q5_K: (256, 176), QType.Q6_K: (256, 210), QType.IQ2_XXS: (256, 66),
-          QType.IQ1_S: (256, 50), QType.IQ4_NL: (32, 18)}
-
-
-def row_bytes(t, cols):
-    t = QType(t)
-    if t == QType.F32:
-        return cols * 4
-    if t in (QType.F16, QType.BF16):
-        return cols * 2
-    be, bb = _BLOCK[t]
-    return cols // be * bb
-
+from .shapes import BLOCK as _BLOCK, QType, row_bytes  # noqa: F401
 
 def random_weights(t, rows, cols, gen, lo=0.01, hi=0.05, out=None):
     """uint8 tensor of rows * row_bytes(t, cols) bytes on gen.device."""
