@@ -4,9 +4,9 @@
 // Replaces the reference's q_moe_gu[_t] / q_moe_down[_t] Metal kernels (src/kernels/quant_moe.metal:50-147,175-259)
 // behind ms::q::encode_moe_decode / encode_moe_decode_table[_part] (src/kernels/quant.hpp:49-85, quant.mm:264-369).
 //
-// Work distribution: persistent blocks pull row tiles from a device-side tile counter (big shared-expert tiles
-// first), so the split adapts to how many of the routed experts are resident on this GPU (expert parallelism) without
-// a host round trip.  A row's partial sums are always formed in the same order, whichever block computes it.
+// Work distribution: persistent blocks walk the launch's row tiles with a fixed stride (big shared-expert tiles first);
+// the tile list is formed on the device from the experts resident on this GPU (expert parallelism), so the split adapts
+// without a host round trip.  A row's partial sums are always formed in the same order, whichever block computes it.
 #include <algorithm>
 #include <cstdlib>
 #include "stream_pipe.cuh"
@@ -65,12 +65,6 @@ __device__ __forceinline__ void resolve_local(const MoeParams& p, MoeSmemHead* h
   __syncwarp();
 }
 
-__device__ __forceinline__ void finish_block(unsigned* sched) {
-  __threadfence();
-  const unsigned old = atomicAdd(&sched[1], 1u);
-  if (old == gridDim.x - 1) { sched[0] = 0; sched[1] = 0; __threadfence(); }
-}
-
 // Producer side of "first piece of a tile": wait for the slot, publish the tile id, then the piece.
 __device__ __forceinline__ bool announce_tile(const Ring& ring, uint32_t n, MoeSmemHead* hd, int tile, int lane) {
   const int s = n % ring.stages;
@@ -79,13 +73,12 @@ __device__ __forceinline__ bool announce_tile(const Ring& ring, uint32_t n, MoeS
   __syncwarp();
   return true;
 }
-__device__ __forceinline__ void end_of_tiles(const Ring& ring, uint32_t n, MoeSmemHead* hd, unsigned* sched, int lane) {
+__device__ __forceinline__ void end_of_tiles(const Ring& ring, uint32_t n, MoeSmemHead* hd, int lane) {
   const int s = n % ring.stages;
   if (!mbar_wait(&ring.empty[s], ((n / ring.stages) & 1u) ^ 1u, ring.abort_flag, ring.status, kDevWaitEmpty)) return;
   if (lane == 0) {
     *reinterpret_cast<volatile int*>(&hd->meta[s]) = -1;
     mbar_arrive(&ring.full[s]);
-    finish_block(sched);
   }
 }
 
@@ -170,15 +163,12 @@ __device__ __forceinline__ bool gu_tile_consume(const MoeParams& p, const Ring& 
   return true;
 }
 
-// Tile order: a block's first tile is its block index, later ones come from the launch's atomic counter (offset by the
-// grid size).  The producer warp stages that first tile before the grid dependency is resolved when it is a
-// shared-expert tile (constant data); everything that depends on the router's output waits for the consumers, which
-// resolve the dependency, the resident experts and the activation, at the block barrier.
-__device__ __forceinline__ int next_tile(unsigned* sched, int lane) {
-  int t = 0;
-  if (lane == 0) t = (int)(gridDim.x + atomicAdd(&sched[0], 1u));
-  return __shfl_sync(0xffffffffu, t, 0);
-}
+// Tile order: block b takes tiles b, b + grid, b + 2 grid, ... (tiles of one kind cost the same, so a fixed stride
+// balances as well as a shared counter would, without a global atomic round trip per tile).  The producer warp stages
+// its first tile before the grid dependency is resolved when it is a shared-expert tile (constant data); everything
+// that depends on the router's output waits for the consumers, which resolve the dependency, the resident experts and
+// the activation, at the block barrier.
+__device__ __forceinline__ int next_tile(int t) { return t + (int)gridDim.x; }
 
 template <int TR, int TS, int LPR>
 __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeParams p) {
@@ -231,7 +221,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
       // all before the router's result is needed
       while (t < tiles_s) {
         if (!gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
-        t = next_tile(p.sched, lane);
+        t = next_tile(t);
       }
       pdl_wait();
       resolve_local(p, hd, p.gu_r != 0, false, lane);   // published to the consumers by the tiles' barriers
@@ -240,14 +230,14 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_gu_kernel(const MoeP
       if (early && !gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
       __syncthreads();
       pdl_wait();
-      if (early) t = next_tile(p.sched, lane);
+      if (early) t = next_tile(t);
     }
     const int ntiles = tiles_s + hd->n_local * tiles_r1;
     while (t < ntiles) {
       if (!gu_tile_produce(p, ring, n, tile_of(t), lane, t, hd)) return;
-      t = next_tile(p.sched, lane);
+      t = next_tile(t);
     }
-    end_of_tiles(ring, n, hd, p.sched, lane);
+    end_of_tiles(ring, n, hd, lane);
     return;
   }
   LaneLuts L;
@@ -408,9 +398,9 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
         if (!produce_piece(ring, n, pc, p.d_src_pitch, lane)) return;
         n++;
       }
-      t = next_tile(p.sched, lane);
+      t = next_tile(t);
     }
-    end_of_tiles(ring, n, hd, p.sched, lane);
+    end_of_tiles(ring, n, hd, lane);
     return;
   }
   LaneLuts L;
@@ -501,7 +491,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
     __syncwarp();
     unsigned last = 0;
     if (lane == 0) {
-      unsigned* done = p.sched + 2;
+      unsigned* done = p.sched;
       last = atomicAdd(done, 1u) == gridDim.x - 1;
       if (last) *done = 0;
     }
@@ -672,7 +662,7 @@ int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, s
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int lpr_gu = lpr_for(p.dim / 32), lpr_d = lpr_for(p.inter / 32);
   if (!lpr_gu || !lpr_d) return fail(kErrArg, "moe_decode: dim/inter not supported");
-  unsigned* sched_base = reinterpret_cast<unsigned*>(p.tb.status) + 8;
+  unsigned* sched_base = reinterpret_cast<unsigned*>(p.tb.status) + 8;   // [0]: blocks of a down launch that stored their partial
   if (p.gu_r || p.gu_s) {
     p.sched = sched_base;
 #define MSB_GU(TR, TS) rc = launch_gu_lpr<TR, TS>(p, lpr_gu, sms, dev, st)
@@ -684,7 +674,7 @@ int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, s
     if (rc) return rc;
   }
   if (p.d_r || p.d_s) {
-    p.sched = sched_base + 2;
+    p.sched = sched_base;
 #define MSB_DN(TR, TS) rc = launch_down_lpr<TR, TS>(p, lpr_d, sms, dev, st)
     if (t_down == IQ1_S && t_shared == Q8_0) MSB_DN(IQ1_S, Q8_0);
     else if (t_down == IQ1_S) MSB_DN(IQ1_S, Q6_K);

@@ -29,8 +29,8 @@ struct MoeParams {
   float norm_eps;
   float* y;
   float* h;                               // [n_routed + 1][inter]
-  unsigned* sched;                        // [2] counter of tiles handed out after each block's first (tile = its
-                                          // block index), finished-block counter; both zero between launches
+  unsigned* sched;                        // [1] expert-parallel exchange: blocks of the down launch that have stored their
+                                          // partial; zero between launches
   float limit;
   // tile shapes (whole rows, every piece one contiguous bulk copy per source)
   int gu_r_rows;                          // routed gate/up tile rows (each warp owns whole rows)

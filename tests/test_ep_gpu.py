@@ -123,3 +123,4 @@ def test_ep_combine_wait_expires_with_status_3(enc):
         assert np.isfinite(h0.cpu().numpy()).all() and not np.array_equal(bits(h0.cpu().numpy()), bits(case.y0))
     finally:
         comms[0].close()
+
