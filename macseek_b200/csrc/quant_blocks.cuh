@@ -139,15 +139,24 @@ __device__ __forceinline__ void quantize_x(const float* __restrict__ x, const Xq
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const float inv = amax > 0.f ? 32767.f / amax : 0.f;
-    int sum = 0;
-    uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
+    // round to the nearest integer in [-32767, 32767] by adding 1.5 * 2^23: the sum's low 16 mantissa bits are the
+    // two's-complement value (high byte signed, low byte unsigned), picked out with byte permutes; no clamp is needed,
+    // |v * inv| <= 32767 (1 + 2^-22) rounds to at most 32767
+    constexpr float kMagic = 12582912.f;
+    uint32_t f[8];
+    float fsum = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      int qv = __float2int_rn(v[i] * inv);
-      qv = max(-32767, min(32767, qv));
-      sum += qv;
-      hw[i >> 2] |= (uint32_t)((qv >> 8) & 0xFF) << (8 * (i & 3));
-      lw[i >> 2] |= (uint32_t)(qv & 0xFF) << (8 * (i & 3));
+      const float r = fmaf(v[i], inv, kMagic);
+      f[i] = __float_as_uint(r);
+      fsum += r - kMagic;                  // exact small integers
+    }
+    const int sum = (int)fsum;
+    uint32_t hw[2], lw[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      hw[j] = __byte_perm(__byte_perm(f[4 * j], f[4 * j + 1], 0x0051), __byte_perm(f[4 * j + 2], f[4 * j + 3], 0x0051), 0x5410);
+      lw[j] = __byte_perm(__byte_perm(f[4 * j], f[4 * j + 1], 0x0040), __byte_perm(f[4 * j + 2], f[4 * j + 3], 0x0040), 0x5410);
     }
     const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);   // lanes (0,1): elements 0..15, (2,3): 16..31
     const int other = __shfl_xor_sync(0xffffffffu, pair, 2);
