@@ -240,3 +240,111 @@ def test_moe_prefill_edge_cases(orc):
     b.n_tokens = 0
     q.encode_moe_prefill(e, b)
     e.wait()
+
+
+def test_moe_prefill_benchmark_layer_full_size(orc, capsys):
+    """The benchmark's prefill configuration at its stated size: 4096 tokens, top-8 of 384 experts (IQ1_S gate/up,
+    IQ2_XXS down) + Q8_0 shared expert, dim 4096 / inter 2048, router logits N(0,1) + log-Zipf(1.1) bias over a seeded
+    expert permutation (a few experts take thousands of tokens -- the pre-dequantised TMA-fed path -- while most hit
+    experts take a handful -- the in-kernel dequantisation path).  Checked as the reference checks its own large case
+    (tests/test_quant_moe_prefill.mm:165-177,223): the tokens of experts with at most two entries, tile-boundary tokens
+    and a random sample, against the half-emulating (<= 1e-3) and the F32 (<= 5e-3) references; two runs bit-identical."""
+    from macseek_b200 import moe_layer as ml, quant as q
+    from macseek_b200.core import Enc
+    n, D, I, E, K = 4096, 4096, 2048, 384, 8
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    lw = ml.MoeLayerWeights(D, I, E, q.QType.IQ1_S, q.QType.IQ2_XXS, q.QType.Q8_0).randomize(gen)
+    perm = torch.randperm(E, device="cuda", generator=gen)
+    bias = torch.empty(E, device="cuda")
+    bias[perm] = -1.1 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
+    logits = torch.randn(n, E, device="cuda", generator=gen) + bias
+    ids = torch.topk(logits, K, dim=1).indices
+    w = torch.softmax(torch.gather(logits, 1, ids), dim=1).float()
+    flat_e = ids.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)              # entries sorted by (expert, token * K + k)
+    tok = (order // K).int().contiguous()
+    wt = w.reshape(-1)[order].contiguous()
+    slot_of = torch.empty(n * K, dtype=torch.int32, device="cuda")
+    slot_of[order] = torch.arange(n * K, dtype=torch.int32, device="cuda")
+    counts = torch.bincount(flat_e, minlength=E).cpu().numpy()
+    used = [e for e in range(E) if counts[e] > 0]
+    offs = [0]
+    for e in used:
+        offs.append(offs[-1] + int(counts[e]))
+    cs = np.sort(counts[counts > 0])
+    with capsys.disabled():
+        print("\n  cfg4 routing: %d experts hit, tokens/expert min %d median %d max %d, %d experts with >= 256 entries"
+              % (len(used), cs[0], cs[len(cs) // 2], cs[-1], int((cs >= 256).sum())))
+    assert cs[-1] >= 256 and cs[0] < 64            # both weight paths are exercised
+    a = q.MoePrefillArgs(D, I)
+    a.t_gate_up, a.t_down, a.t_shared = lw.t_gate_up, lw.t_down, lw.t_shared
+    a.n_tokens, a.k_per_token, a.has_shared = n, K, True
+    for e in used:
+        s = q.ExpertSlot()
+        s.gate, s.up, s.down = lw.expert_views(e)
+        a.slots.append(s)
+    a.shared = lw.shared
+    a.offs = offs
+    a.tok, a.wt, a.slot_of = tok, wt, slot_of
+    a.X = torch.randn(n, D, device="cuda", generator=gen)
+    Y0 = torch.randn(n, D, device="cuda", generator=gen)
+    a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(offs[-1], n, len(used), D, I), dtype=torch.uint8, device="cuda")
+    e_ = Enc()
+    outs = []
+    for _ in range(2):
+        a.Y = Y0.clone()
+        q.encode_moe_prefill(e_, a)
+        e_.wait()
+        outs.append(a.Y.cpu().numpy())
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32)), "repeat differs"
+    got = outs[0].astype(np.float64)
+    assert np.all(np.isfinite(got))
+    # tokens to check
+    tok_h, ids_h, w_h = tok.cpu().numpy(), ids.cpu().numpy(), w.cpu().numpy().astype(np.float64)
+    chk = set()
+    rare = [e for e in used if counts[e] <= 2][:6]
+    pos = {e: j for j, e in enumerate(used)}
+    for e in rare:
+        chk.update(int(t) for t in tok_h[offs[pos[e]]:offs[pos[e] + 1]])
+    chk.update((0, 127, 128, n - 1))
+    chk.update(int(t) for t in np.random.default_rng(1).integers(0, n, 6))
+    chk = sorted(chk)
+    X = a.X[chk].cpu().numpy().astype(np.float64)
+    yh = Y0[chk].cpu().numpy().astype(np.float64)
+    yf = yh.copy()
+    ym = np.abs(yh)
+    need = sorted({int(e) for t in chk for e in ids_h[t]})
+    raw = lambda t: t.cpu().numpy()
+
+    def add_expert(g, u, d, tg, td, rows, ws):
+        wg = orc.dequant(tg, raw(g), I * D).reshape(I, D).astype(np.float64)
+        wu = orc.dequant(tg, raw(u), I * D).reshape(I, D).astype(np.float64)
+        wd = orc.dequant(td, raw(d), I * D).reshape(D, I).astype(np.float64)
+        for hv in (0, 1):
+            xin = r16(X[rows]) if hv else X[rows]
+            g_ = xin @ (r16(wg) if hv else wg).T
+            u_ = xin @ (r16(wu) if hv else wu).T
+            gg, uu = np.minimum(g_, 10.0), np.clip(u_, -10.0, 10.0)
+            h = (gg / (1 + np.exp(-gg)) * uu * ws[:, None]).astype(np.float32).astype(np.float64)
+            wdd = r16(wd) if hv else wd
+            if hv:
+                h = r16(h)
+                yh[rows] += h @ wdd.T
+                ym[rows] += np.abs(h) @ np.abs(wdd).T
+            else:
+                yf[rows] += h @ wdd.T
+    # the kernel adds the shared expert first, then the routed slots in k order; the reference sums in float64, where the
+    # order does not matter at these tolerances
+    add_expert(lw.shared.gate, lw.shared.up, lw.shared.down, ol.Q8_0, ol.Q8_0, np.arange(len(chk)), np.ones(len(chk)))
+    for e in need:
+        rows = np.array([i for i, t in enumerate(chk) if e in ids_h[t]])
+        ws = np.array([w_h[chk[i]][list(ids_h[chk[i]]).index(e)] for i in rows])
+        g, u, d = lw.expert_views(e)
+        add_expert(g, u, d, ol.IQ1_S, ol.IQ2_XXS, rows, ws)
+    err_h = float(np.max(np.abs(got[chk] - yh) / (ym + 1e-9)))
+    err_f = float(np.max(np.abs(got[chk] - yf) / (ym + 1e-9)))
+    with capsys.disabled():
+        print("  cfg4 parity on %d tokens / %d experts: half-emulating %.2e (<= 1e-3), F32 %.2e (<= 5e-3)"
+              % (len(chk), len(need), err_h, err_f))
+    assert err_h <= 1e-3 and err_f <= 5e-3, (err_h, err_f)
