@@ -11,7 +11,11 @@ import synth
 pytestmark = pytest.mark.gpu
 
 QUANT_TYPES = (ol.Q8_0, ol.Q5_K, ol.Q6_K, ol.IQ2_XXS, ol.IQ1_S, ol.IQ4_NL)
-TOL = 2e-5
+TOL = 2e-5          # the reference's own bound on |got - ref| / sum_k |w_k x_k| (tests/test_quant_matvec.mm:42)
+# The relative bound asked of this path, |got - ref| / |ref| <= 1e-3: taken over the whole output vector (L2 norms) and
+# per row for every row whose terms do not cancel (see run_matvec); for cancelling rows the normalised bound above is
+# the meaningful one.
+REL_TOL = 1e-3
 
 
 @pytest.fixture(scope="module")
@@ -75,13 +79,18 @@ def run_matvec(orc, q, enc, t, rows, cols, groups=1, acc=False, n=1, seed=0):
     enc.wait()
     got = yd.cpu().numpy()
     err = orc.max_norm_err(got, ry, mag)
-    rel = np.max(np.abs(got - ry) / (np.abs(ry) + 1e-3 * mag.mean()))
+    # relative error: over the whole output (L2), and row by row where the row's terms do not cancel (|ref| at least 5 %
+    # of the summed magnitudes); a row whose terms cancel to ~0 has no meaningful relative error in any arithmetic
+    solid = np.abs(ry) >= 0.05 * mag
+    rel_rows = float(np.max(np.abs(got - ry)[solid] / np.abs(ry)[solid])) if solid.any() else 0.0
+    rel = max(rel_rows, float(np.linalg.norm(got - ry) / (np.linalg.norm(ry) + 1e-30)))
     return err, rel, (Wd, xd, yd)
 
 
 def test_cfg1_iq1s_4096(orc, q, enc):
     err, rel, _ = run_matvec(orc, q, enc, ol.IQ1_S, 4096, 4096)
     assert err <= TOL, err
+    assert rel <= REL_TOL, rel
 
 
 @pytest.mark.parametrize("t", (ol.Q8_0, ol.Q6_K, ol.Q5_K, ol.IQ4_NL, ol.IQ2_XXS))
@@ -90,6 +99,7 @@ def test_cfg1_iq1s_4096(orc, q, enc):
 def test_cfg2_sweep(orc, q, enc, t, shape, n):
     err, rel, _ = run_matvec(orc, q, enc, t, shape[0], shape[1], n=n)
     assert err <= TOL, (ol.TYPE_NAMES[t], shape, n, err)
+    assert rel <= REL_TOL, (ol.TYPE_NAMES[t], shape, n, rel)
 
 
 # the reference's own shape list (tests/test_quant_matvec.mm:14-28): type, rows, cols, groups, accumulate
@@ -112,6 +122,7 @@ def test_reference_shapes(orc, q, enc, case):
     t, rows, cols, groups, acc = case
     err, rel, _ = run_matvec(orc, q, enc, t, rows, cols, groups, acc)
     assert err <= TOL, err
+    assert rel <= REL_TOL, rel
 
 
 @pytest.mark.parametrize("n", (2, 3, 5, 8, 16))
@@ -147,7 +158,9 @@ def test_unaligned_weight_base_and_repeatability(orc, q, enc):
 
 
 def test_large_activation_outlier(orc, q, enc):
-    # one huge activation in a 32-element block must not wreck the fixed-point copy of its neighbours
+    # One huge activation in a 32-element unit coarsens the fixed-point step of its 31 neighbours (the unit's step is
+    # amax / 32767).  The scheme's worst-case error is sum_units (amax_u / 65534) * sum_{k in u} |w_k|: the result must
+    # stay inside that bound row by row, and inside 5e-5 of the summed magnitudes overall.
     rows, cols, t = 512, 4096, ol.Q6_K
     W = synth.random_weights(t, rows, cols, 8)
     x = synth.randn(cols, 9)
@@ -157,7 +170,12 @@ def test_large_activation_outlier(orc, q, enc):
     q.encode_matvec(enc, t, dev(W), rows, cols, dev(x), y)
     enc.wait()
     ry, mag = orc.matvec(t, W, rows, cols, x)
-    assert orc.max_norm_err(y.cpu().numpy(), ry, mag) <= 1e-4
+    got = y.cpu().numpy()
+    wabs = np.abs(orc.dequant(t, W, rows * cols).reshape(rows, cols // 32, 32)).sum(axis=2)      # [rows][units]
+    step = np.abs(x.reshape(-1, 32)).max(axis=1) / 65534.0                                     # half a step per unit
+    bound = wabs @ step + 4e-6 * mag                                                           # + fp32 accumulation
+    assert np.all(np.abs(got - ry) <= bound)
+    assert orc.max_norm_err(got, ry, mag) <= 5e-5
 
 
 def test_bad_arguments_fail_loudly(q, enc):
@@ -213,3 +231,31 @@ def test_matvec_rmsnorm_shared_launch(orc, q, enc, t, rows, cols):
     enc.wait()
     assert np.array_equal(y2.cpu().numpy().view(np.uint32), y.cpu().numpy().view(np.uint32))
     assert orc.max_norm_err(y3.cpu().numpy(), ry, mag) <= TOL
+
+
+# ---- the 16-bit fixed-point activation at its weak spots: heavy tails and a wide dynamic range inside one unit
+@pytest.mark.parametrize("t", (ol.IQ1_S, ol.IQ2_XXS, ol.Q8_0, ol.Q6_K, ol.Q5_K, ol.IQ4_NL))
+def test_heavy_tailed_activation(orc, q, enc, t):
+    # Student-t with 3 degrees of freedom: what a residual stream with outlier channels looks like
+    rows, cols = 1024, 4096
+    W = synth.random_weights(t, rows, cols, 41)
+    x = np.random.default_rng(42).standard_t(3, cols).astype(np.float32)
+    y = torch.zeros(rows, device="cuda")
+    q.encode_matvec(enc, t, dev(W), rows, cols, dev(x), y)
+    enc.wait()
+    ry, mag = orc.matvec(t, W, rows, cols, x)
+    assert orc.max_norm_err(y.cpu().numpy(), ry, mag) <= TOL
+
+
+@pytest.mark.parametrize("t", (ol.IQ2_XXS, ol.IQ1_S, ol.Q8_0))
+def test_activation_spanning_decades_inside_a_unit(orc, q, enc, t):
+    # |x| log-uniform over 1e-4 .. 10 within every 32-element unit, as the SwiGLU outputs read by the MoE down projection
+    rows, cols = 1024, 2048
+    rng = np.random.default_rng(43)
+    x = (10.0 ** rng.uniform(-4, 1, cols) * rng.choice([-1.0, 1.0], cols)).astype(np.float32)
+    W = synth.random_weights(t, rows, cols, 44)
+    y = torch.zeros(rows, device="cuda")
+    q.encode_matvec(enc, t, dev(W), rows, cols, dev(x), y)
+    enc.wait()
+    ry, mag = orc.matvec(t, W, rows, cols, x)
+    assert orc.max_norm_err(y.cpu().numpy(), ry, mag) <= TOL
