@@ -708,13 +708,12 @@ int topk(const float* sc, int n, int k, int* out, void* scratch, size_t scratch_
     MSB_CUDA(cudaFuncSetAttribute(topk_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
     configured[dev & 63] = true;
   }
-  static const int fused = getenv("MSB_TOPK_FUSED") ? atoi(getenv("MSB_TOPK_FUSED")) : 1;   // tuning probe
-  static const int env_blocks = getenv("MSB_TOPK_BLOCKS") ? atoi(getenv("MSB_TOPK_BLOCKS")) : 0;
+  // MSB_TOPK_FUSED=0: selection and read-out as two launches (topk_select_kernel + topk_final_kernel) instead of one
+  static const int fused = getenv("MSB_TOPK_FUSED") ? atoi(getenv("MSB_TOPK_FUSED")) : 1;
   const int nthreads = kTopkThreads;
   // one element per thread and up to two blocks per SM: the per-block fixed work (threshold, fine histogram) is small
   // next to the latency of a longer per-thread loop
   int blocks = std::max(1, std::min(2 * sms * (1024 / nthreads), (n + nthreads - 1) / nthreads));
-  if (env_blocks) blocks = std::max(1, std::min(env_blocks, (n + 1023) / 1024));
   // staging of a block's picks: per_block ints + per_block (index, key) pairs; blocks are added until that fits
   auto stage_of = [&](int nb) { const size_t pb = ((size_t)n + nb - 1) / nb; return ((pb + 1) & ~(size_t)1) * 4 + pb * 8 + 16; };
   while (stage_of(blocks) > 100 * 1024) blocks *= 2;
@@ -751,7 +750,8 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   MSB_CUDA(cudaGetDevice(&dev));
   MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   IdxParams p{(const uint8_t*)keys, q, w, scores, hist, len};
-  static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;   // mma.sync path
+  // MSB_IDX_LEGACY=1: FP8 scoring on mma.sync (idx_score_fp8_kernel) instead of the tcgen05 kernel
+  static const bool legacy = getenv("MSB_IDX_LEGACY") && atoi(getenv("MSB_IDX_LEGACY")) != 0;
   if (key_type == kKeyFp8 && !exact_query && !legacy) return index_scores_tc(keys, len, q, w, heads, scores, hist, 0, nullptr, 0, nullptr, nullptr, nullptr, 0, st);
   if (key_type == kKeyFp8 && !exact_query) {
     const int grid = std::max(1, std::min(sms, (len + 16 * 12 - 1) / (16 * 12)));

@@ -265,13 +265,9 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms_real) {
   if (fixed + 2 * 8192 > smem_limit)
     return fail(kErrLimit, "matvec: cols %d x n %d does not fit in shared memory", p.cols, p.n);
   const size_t avail = smem_limit - fixed;
-  // tuning probes: cap the slot size (KB) / the ring depth
-  static const int env_slot = getenv("MSB_MV_SLOT_KB") ? atoi(getenv("MSB_MV_SLOT_KB")) : 0;
-  static const int env_stages = getenv("MSB_MV_STAGES") ? std::min(kMaxStages, std::max(2, atoi(getenv("MSB_MV_STAGES")))) : 0;
   // A tile may take up to half of the free shared memory (a two-slot ring): rows that share a lane's activation
   // registers cut the shared-memory traffic per weight, which matters more than ring depth once a slot holds tens of KB.
   size_t slot = (avail / 2) & ~(size_t)127;
-  if (env_slot) slot = std::min<size_t>(slot, (size_t)env_slot * 1024);
   int stages = 2;
   const long rows_fit = ((long)slot - 64) / (long)p.row_bytes;
   const int want_tiles = std::max(1, sms / p.groups);
@@ -322,7 +318,6 @@ int launch_rows(MvParams& p, cudaStream_t st, int dev, int sms_real) {
     slot = ((size_t)R * p.row_bytes + 64 + 127) & ~(size_t)127;
     stages = (int)std::min<size_t>(kMaxStages, avail / slot);
   }
-  if (env_stages) stages = std::min(stages, env_stages);
   p.tile_rows = R;
   p.ks = ks;
   p.tiles_per_group = tiles_of(R);
@@ -338,11 +333,10 @@ template <int T, int NC>
 int launch_type(MvParams& p, cudaStream_t st, int dev, int sms) {
   // Light blocks for matrices whose per-SM share is small next to the fixed cost of a launch (the layer's projections;
   // not the output head): only for the table-free types and a single activation column.
-  static const int env_light = getenv("MSB_MV_LIGHT") ? atoi(getenv("MSB_MV_LIGHT")) : -1;   // tuning probe
   bool light = false;
   if constexpr (NC == 1 && lut_bytes_for(T) == 0) {
     const size_t total = (size_t)p.rows_per_group * p.groups * p.row_bytes;
-    light = env_light < 0 ? total <= (size_t)96 << 20 : env_light != 0;
+    light = total <= (size_t)96 << 20;
     const size_t fixed_l = (size_t)NC * xq_bytes(p.units, is_dense(T), xq_padded(T)) + 1024;
     if (fixed_l + 2 * 16384 > kLightSmemLimit) light = false;
     const size_t light_limit = (g_share_launch && fixed_l + 2 * 16384 <= kShareSmemLimit) ? kShareSmemLimit : kLightSmemLimit;

@@ -519,3 +519,119 @@ void orc_sparse_attn(const float* q_raw, const float* cs, const float* rows, int
   sa_ctx c = {q_raw, cs, rows, sinks, n_rows, D, out};
   orc_parallel(sa_heads, &c, H, threads);
 }
+
+/* ---------------------------------------------------------------- hyper-connections (tests/ref/arch_ref.cpp:22-95)
+ * D = width of one residual stream, 4 streams; mix[24] = pre[4], post[4], comb[4][4] (comb[j][k] at 8 + 4 j + k). */
+static double sigmoid_d(double x) { return 1.0 / (1.0 + exp(-x)); }
+
+void orc_hc_split(const double* m, const float* scale, const float* base, float* mix, int iters, double eps) { /* :22-50 */
+  double c[4][4];
+  for (int j = 0; j < 4; j++) mix[j] = (float)(sigmoid_d(m[j] * scale[0] + base[j]) + eps);
+  for (int j = 0; j < 4; j++) mix[4 + j] = (float)(2.0 * sigmoid_d(m[4 + j] * scale[1] + base[4 + j]));
+  for (int j = 0; j < 4; j++)
+    for (int k = 0; k < 4; k++) c[j][k] = m[8 + 4 * j + k] * scale[2] + base[8 + 4 * j + k];
+  for (int j = 0; j < 4; j++) { /* row softmax + eps */
+    double mx = c[j][0], s = 0;
+    for (int k = 1; k < 4; k++) if (c[j][k] > mx) mx = c[j][k];
+    for (int k = 0; k < 4; k++) { c[j][k] = exp(c[j][k] - mx); s += c[j][k]; }
+    for (int k = 0; k < 4; k++) c[j][k] = c[j][k] / s + eps;
+  }
+  for (int it = 0; it < iters; it++) {
+    if (it > 0)
+      for (int j = 0; j < 4; j++) { /* row normalisation */
+        double s = c[j][0] + c[j][1] + c[j][2] + c[j][3];
+        for (int k = 0; k < 4; k++) c[j][k] /= (s + eps);
+      }
+    for (int k = 0; k < 4; k++) { /* column normalisation */
+      double s = c[0][k] + c[1][k] + c[2][k] + c[3][k];
+      for (int j = 0; j < 4; j++) c[j][k] /= (s + eps);
+    }
+  }
+  for (int j = 0; j < 4; j++)
+    for (int k = 0; k < 4; k++) mix[8 + 4 * j + k] = (float)c[j][k];
+}
+
+void orc_hc_mixes(const float* h, const float* fn, const float* scale, const float* base, int D, float* mix, int iters,
+                  double norm_eps, double hc_eps) { /* :52-66 */
+  const int HCD = 4 * D;
+  double ss = 0, m[24];
+  for (int i = 0; i < HCD; i++) ss += (double)h[i] * h[i];
+  const double rstd = 1.0 / sqrt(ss / HCD + norm_eps);
+  for (int r = 0; r < 24; r++) {
+    double a = 0;
+    const float* f = fn + (size_t)r * HCD;
+    for (int i = 0; i < HCD; i++) a += (double)f[i] * h[i];
+    m[r] = a * rstd;
+  }
+  orc_hc_split(m, scale, base, mix, iters, hc_eps);
+}
+
+/* One sublayer boundary (:75-95).  x_sub / fn / x_out may be NULL as in the reference; h_out is written only with x_sub. */
+void orc_hc_step(const float* h_in, const float* x_sub, const float* mix_prev, const float* fn, const float* scale,
+                 const float* base, const float* norm_w, int D, float* h_out, float* mix_out, float* x_out) {
+  const int HCD = 4 * D;
+  float* hn = (float*)malloc(sizeof(float) * HCD);
+  memcpy(hn, h_in, sizeof(float) * HCD);
+  if (x_sub) {
+    for (int d = 0; d < D; d++)
+      for (int i = 0; i < 4; i++) {
+        double a = (double)mix_prev[4 + i] * x_sub[d];
+        for (int j = 0; j < 4; j++) a += (double)mix_prev[8 + 4 * j + i] * h_in[j * D + d];
+        hn[i * D + d] = (float)a;
+      }
+    memcpy(h_out, hn, sizeof(float) * HCD);
+  }
+  if (fn) orc_hc_mixes(hn, fn, scale, base, D, mix_out, 20, 1e-20, 1e-6);
+  if (x_out) {
+    float* xp = (float*)malloc(sizeof(float) * D);
+    for (int d = 0; d < D; d++) {
+      double a = 0;
+      for (int j = 0; j < 4; j++) a += (double)mix_prev[j] * hn[j * D + d];
+      xp[d] = (float)a;
+    }
+    orc_rmsnorm(xp, norm_w, x_out, D, 1e-20);
+    free(xp);
+  }
+  free(hn);
+}
+
+/* ---------------------------------------------------------------- compressor + index key (tests/ref/attn_ref.cpp:116-161)
+ * One token at position p for a KV source of ratio r (1 or 2): st_kv / st_sc are the source's partial group
+ * [r][D] (st_sc starts at -inf).  Returns 1 when a row was emitted: ckv_row[D] (roped, fp4 e4m3/16 when actq) and
+ * ikey_row[ID] (roped, fp4 e8m0/32 when actq); cs_tab is the YaRN rope table [max_pos][32][2].  The rope dims are the
+ * last 64 of each vector. */
+int orc_compress_token(int ratio, int p, const float* ckv_in, const float* cgate_in, const float* cnorm_w,
+                       const uint16_t* wk_bf16, const float* knorm_w, const float* cs_tab, int actq, int D, int ID,
+                       float* st_kv, float* st_sc, float* ckv_row, float* ikey_row) {
+  const int r = ratio;
+  float* lat = ckv_row;
+  if (r == 1) {
+    memcpy(lat, ckv_in, sizeof(float) * D);
+  } else {
+    const int slot = p % r;
+    memcpy(st_kv + (size_t)slot * D, ckv_in, sizeof(float) * D);
+    memcpy(st_sc + (size_t)slot * D, cgate_in, sizeof(float) * D);
+    if ((p + 1) % r != 0) return 0;
+    for (int c = 0; c < D; c++) {
+      float m = -INFINITY, e[8], sum = 0, v = 0;
+      for (int j = 0; j < r; j++) m = fmaxf(m, st_sc[(size_t)j * D + c]);
+      for (int j = 0; j < r; j++) { e[j] = expf(st_sc[(size_t)j * D + c] - m); sum += e[j]; }
+      for (int j = 0; j < r; j++) v += st_kv[(size_t)j * D + c] * (e[j] / sum);
+      lat[c] = v;
+    }
+  }
+  rmsnorm_f(lat, cnorm_w, D, 1e-20f);
+  const int row = p / r;
+  const float* cs = cs_tab + (size_t)row * r * 64;
+  for (int o = 0; o < ID; o++) { /* index key from the pre-rope latent */
+    double acc = 0;
+    for (int d = 0; d < D; d++) acc += (double)orc_bf16_to_f32(wk_bf16[(size_t)o * D + d]) * lat[d];
+    ikey_row[o] = (float)acc;
+  }
+  rmsnorm_f(ikey_row, knorm_w, ID, 1e-20f);
+  orc_rope(ikey_row + ID - 64, cs, 0);
+  if (actq) orc_fp4_sim_e8m0(ikey_row, ID);
+  orc_rope(lat + D - 64, cs, 0);
+  if (actq) orc_fp4_sim_e4m3(lat, D);
+  return 1;
+}

@@ -101,6 +101,17 @@ void orc_sparse_attn(const float* q_raw, const float* cs, const float* rows, int
 /* tests/ref/attn_ref.cpp:109-114 */
 void orc_window_row(const float* kv_raw, const float* norm_w, const float* cs, int actq, int D, float* out);
 
+/* hyper-connections: tests/ref/arch_ref.cpp:22-95 with the stream width D as a parameter (the reference: 5120) */
+void orc_hc_split(const double* m, const float* scale, const float* base, float* mix, int iters, double eps);
+void orc_hc_mixes(const float* h, const float* fn, const float* scale, const float* base, int D, float* mix, int iters,
+                  double norm_eps, double hc_eps);
+void orc_hc_step(const float* h_in, const float* x_sub, const float* mix_prev, const float* fn, const float* scale,
+                 const float* base, const float* norm_w, int D, float* h_out, float* mix_out, float* x_out);
+/* compressor + index key of one token: tests/ref/attn_ref.cpp:116-161 with the state passed explicitly */
+int orc_compress_token(int ratio, int p, const float* ckv_in, const float* cgate_in, const float* cnorm_w,
+                       const uint16_t* wk_bf16, const float* knorm_w, const float* cs_tab, int actq, int D, int ID,
+                       float* st_kv, float* st_sc, float* ckv_row, float* ikey_row);
+
 int orc_hardware_threads(void);
 
 #ifdef __cplusplus

@@ -129,6 +129,24 @@ void msref_window_row(const float* kv_raw, const float* norm_w, const float* cs,
   attnref::window_row(kv_raw, norm_w, cs, actq != 0, out);
 }
 
+// hyper-connection step and compressor of the reference (fixed shapes: 4 x 5120 streams; 512-wide latent, 128-wide keys)
+void msref_hc_step(const float* h_in, const float* x_sub, const float* mix_prev, const float* fn, const float* scale,
+                   const float* base, const float* norm_w, float* h_out, float* mix_out, float* x_out) {
+  ref_arch::hc_step(h_in, x_sub, mix_prev, fn, scale, base, norm_w, h_out, mix_out, x_out);
+}
+// feeds tokens 0 .. n-1 to a fresh source; returns the number of rows emitted into ckv [rows][512] / ikey [rows][128]
+int msref_compress_tokens(int ratio, int n, const float* ckv_in, const float* cgate_in, const float* cnorm_w,
+                          const uint16_t* wk, const float* knorm_w, int actq, float* ckv, float* ikey) {
+  attnref::Source s;
+  attnref::source_init(s, ratio);
+  std::vector<float> tab = attnref::rope_table(n + 1, true);
+  for (int p = 0; p < n; p++)
+    attnref::compress_token(s, p, ckv_in + (size_t)p * 512, cgate_in ? cgate_in + (size_t)p * 512 : nullptr, cnorm_w, wk,
+                            knorm_w, tab, actq != 0);
+  std::copy(s.ckv.begin(), s.ckv.end(), ckv);
+  std::copy(s.ikey.begin(), s.ikey.end(), ikey);
+  return s.rows();
+}
 int msref_hardware_threads() { return (int)std::thread::hardware_concurrency(); }
 
 }  // extern "C"

@@ -86,6 +86,25 @@ def main():
     g["win_kv"], g["win_nw"] = kv, nw
     for actq in (0, 1):
         g["win_out_%d" % actq] = ref.window_row(kv, nw, cs, actq)
+    # --- hyper-connection step (4 x 5120 streams): inputs are integer-hashed patterns (synth.hashed), only outputs stored
+    import synth
+    D = 5120
+    h_in, x_sub = synth.hashed(4 * D, 1, 4.0), synth.hashed(D, 2, 2.0)
+    fn, scale, base = synth.hashed(24 * 4 * D, 3, 0.05), np.array([0.7, 1.3, 0.9], np.float32), synth.hashed(24, 4, 1.0)
+    norm_w = 1 + synth.hashed(D, 5, 0.2)
+    mix_prev = np.abs(synth.hashed(24, 6, 2.0)) + 0.05
+    h_out, mix_out, x_out = ref.hc_step(h_in, x_sub, mix_prev, fn, scale, base, norm_w)
+    g["hc_h_out"], g["hc_mix_out"], g["hc_x_out"] = h_out, mix_out, x_out
+    _, mix0, x0 = ref.hc_step(h_in, None, mix_prev, fn, scale, base, norm_w)          # layer-0 form: no sublayer output
+    g["hc0_mix_out"], g["hc0_x_out"] = mix0, x0
+    # --- compressor + index key, ratio 2 and ratio 1, 6 tokens
+    cn, kn = 1 + synth.hashed(512, 7, 0.2), 1 + synth.hashed(128, 8, 0.2)
+    wk = synth.hashed_bf16(128 * 512, 9, 0.2)
+    ckv_in, cg_in = synth.hashed(6 * 512, 10, 3.0), synth.hashed(6 * 512, 11, 4.0)
+    for ratio in (1, 2):
+        for actq in (0, 1):
+            ck, ik = ref.compress_tokens(ratio, ckv_in, cg_in if ratio > 1 else None, cn, wk, kn, actq)
+            g["cmp_ckv_r%d_q%d" % (ratio, actq)], g["cmp_ikey_r%d_q%d" % (ratio, actq)] = ck, ik
     out = os.path.join(HERE, "golden_ref.npz")
     np.savez_compressed(out, **g)
     print("wrote", out, os.path.getsize(out), "bytes,", len(g), "arrays")

@@ -231,6 +231,47 @@ class Oracle:
         return out
 
 
+def _opt(a):
+    return _p(a) if a is not None else None
+
+
+def _oracle_hc_step(self, h_in, x_sub, mix_prev, fn, scale, base, norm_w, D, want_x=True):
+    """hc_step of one token (arch_ref.cpp:75-95): returns (h_out, mix_out, x_out); parts not asked for are None."""
+    h_in = _f32(h_in)
+    h_out = np.array(h_in, copy=True)
+    mix_out = np.zeros(24, np.float32) if fn is not None else None
+    x_out = np.zeros(D, np.float32) if want_x else None
+    keep = [_f32(v) if v is not None else None for v in (x_sub, mix_prev, fn, scale, base, norm_w)]
+    self.lib.orc_hc_step(_p(h_in), _opt(keep[0]), _p(keep[1]), _opt(keep[2]), _opt(keep[3]), _opt(keep[4]), _opt(keep[5]),
+                         D, _p(h_out), _opt(mix_out), _opt(x_out))
+    return h_out, mix_out, x_out
+
+
+def _oracle_compress_tokens(self, ratio, ckv_in, cgate_in, cnorm_w, wk_bf16, knorm_w, actq, D=512, ID=128):
+    """Feeds tokens 0 .. n-1 to a fresh source (attn_ref.cpp:116-161): returns (ckv rows [rows][D], ikey rows [rows][ID])."""
+    ckv_in = _f32(ckv_in).reshape(-1, D)
+    n = ckv_in.shape[0]
+    cg = _f32(cgate_in).reshape(-1, D) if cgate_in is not None else None
+    tab = self.rope_table(n + 1, True)
+    st_kv = np.zeros((ratio, D), np.float32)
+    st_sc = np.full((ratio, D), -np.inf, np.float32)
+    wk = np.ascontiguousarray(wk_bf16, dtype=np.uint16)
+    cn, kn = _f32(cnorm_w), _f32(knorm_w)
+    ck, ik = [], []
+    row_c, row_k = np.zeros(D, np.float32), np.zeros(ID, np.float32)
+    for p in range(n):
+        g = np.ascontiguousarray(cg[p]) if cg is not None else None
+        x = np.ascontiguousarray(ckv_in[p])
+        if self.lib.orc_compress_token(ratio, p, _p(x), _opt(g), _p(cn), wk.ctypes.data_as(C.c_void_p), _p(kn), _p(tab),
+                                       int(actq), D, ID, _p(st_kv), _p(st_sc), _p(row_c), _p(row_k)):
+            ck.append(row_c.copy()); ik.append(row_k.copy())
+    return np.array(ck, np.float32).reshape(-1, D), np.array(ik, np.float32).reshape(-1, ID)
+
+
+Oracle.hc_step = _oracle_hc_step
+Oracle.compress_tokens = _oracle_compress_tokens
+
+
 class Ref:
     """The reference project's own routines (oracle/_ref/libmsref.so); None-safe: use Ref.load()."""
 
@@ -349,3 +390,24 @@ class Ref:
         x = _f32(x); y = np.empty_like(x)
         self.lib.msref_rmsnorm(_p(x), _p(_f32(w)), _p(y), x.size, eps)
         return y
+
+    def hc_step(self, h_in, x_sub, mix_prev, fn, scale, base, norm_w, want_x=True):
+        h_in = _f32(h_in)
+        h_out = np.array(h_in, copy=True)
+        mix_out = np.zeros(24, np.float32) if fn is not None else None
+        x_out = np.zeros(5120, np.float32) if want_x else None
+        keep = [_f32(v) if v is not None else None for v in (x_sub, mix_prev, fn, scale, base, norm_w)]
+        self.lib.msref_hc_step(_p(h_in), _opt(keep[0]), _p(keep[1]), _opt(keep[2]), _opt(keep[3]), _opt(keep[4]),
+                               _opt(keep[5]), _p(h_out), _opt(mix_out), _opt(x_out))
+        return h_out, mix_out, x_out
+
+    def compress_tokens(self, ratio, ckv_in, cgate_in, cnorm_w, wk_bf16, knorm_w, actq):
+        ckv_in = _f32(ckv_in).reshape(-1, 512)
+        n = ckv_in.shape[0]
+        cg = _f32(cgate_in).reshape(-1, 512) if cgate_in is not None else None
+        ck = np.zeros((n, 512), np.float32); ik = np.zeros((n, 128), np.float32)
+        wk = np.ascontiguousarray(wk_bf16, dtype=np.uint16)
+        self.lib.msref_compress_tokens.restype = C.c_int
+        rows = self.lib.msref_compress_tokens(ratio, n, _p(ckv_in), _opt(cg), _p(_f32(cnorm_w)),
+                                              wk.ctypes.data_as(C.c_void_p), _p(_f32(knorm_w)), int(actq), _p(ck), _p(ik))
+        return ck[:rows], ik[:rows]

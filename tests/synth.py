@@ -41,3 +41,19 @@ def random_weights(t, rows, cols, seed, lo=0.01, hi=0.05):
 
 def randn(n, seed, scale=1.0):
     return (np.random.default_rng(seed).standard_normal(n) * scale).astype(np.float32)
+
+
+def hashed(n, salt, scale=1.0):
+    """n float32 values in scale * [-0.5, 0.5) from integer arithmetic only (no library generator): the same bits on
+    every platform and numpy version, so large golden-vector inputs need not be stored."""
+    i = np.arange(n, dtype=np.uint64)
+    v = (i * np.uint64(2654435761) + np.uint64(salt) * np.uint64(40503) + (i >> np.uint64(7)) * np.uint64(97)) & np.uint64(0xFFFF)
+    return ((v.astype(np.float64) / 65536.0 - 0.5) * scale).astype(np.float32)
+
+
+def hashed_bf16(n, salt, scale=1.0):
+    """The same values rounded to bf16 bit patterns (uint16)."""
+    f = hashed(n, salt, scale)
+    u = f.view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return u.astype(np.uint16)

@@ -112,6 +112,37 @@ def test_sparse_attn_and_window_golden(orc):
                               bits(G["win_out_%d" % actq]))
 
 
+def _hc_inputs():
+    import synth
+    D = 5120
+    return (synth.hashed(4 * D, 1, 4.0), synth.hashed(D, 2, 2.0), np.abs(synth.hashed(24, 6, 2.0)) + 0.05,
+            synth.hashed(24 * 4 * D, 3, 0.05), np.array([0.7, 1.3, 0.9], np.float32), synth.hashed(24, 4, 1.0),
+            1 + synth.hashed(D, 5, 0.2))
+
+
+def test_hc_step_golden(orc):
+    h_in, x_sub, mix_prev, fn, scale, base, norm_w = _hc_inputs()
+    h_out, mix_out, x_out = orc.hc_step(h_in, x_sub, mix_prev, fn, scale, base, norm_w, 5120)
+    assert np.array_equal(bits(h_out), bits(G["hc_h_out"]))
+    assert np.array_equal(bits(mix_out), bits(G["hc_mix_out"]))
+    assert np.array_equal(bits(x_out), bits(G["hc_x_out"]))
+    _, mix0, x0 = orc.hc_step(h_in, None, mix_prev, fn, scale, base, norm_w, 5120)
+    assert np.array_equal(bits(mix0), bits(G["hc0_mix_out"])) and np.array_equal(bits(x0), bits(G["hc0_x_out"]))
+
+
+def test_compressor_golden(orc):
+    import synth
+    cn, kn = 1 + synth.hashed(512, 7, 0.2), 1 + synth.hashed(128, 8, 0.2)
+    wk = synth.hashed_bf16(128 * 512, 9, 0.2)
+    ckv_in, cg_in = synth.hashed(6 * 512, 10, 3.0), synth.hashed(6 * 512, 11, 4.0)
+    for ratio in (1, 2):
+        for actq in (0, 1):
+            ck, ik = orc.compress_tokens(ratio, ckv_in, cg_in if ratio > 1 else None, cn, wk, kn, actq)
+            assert ck.shape[0] == 6 // ratio
+            assert np.array_equal(bits(ck), bits(G["cmp_ckv_r%d_q%d" % (ratio, actq)]))
+            assert np.array_equal(bits(ik), bits(G["cmp_ikey_r%d_q%d" % (ratio, actq)]))
+
+
 # ---------------------------------------------------------------- against the reference code itself (when present)
 @pytest.mark.parametrize("t", ALL_TYPES)
 def test_dequant_vs_reference_1m(orc, ref, t):
