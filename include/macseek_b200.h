@@ -254,7 +254,7 @@ int msb_index_decode(int key_type, const void* keys, int len, const float* q_raw
  * attn_idx_score_dec2_list, attn_index.metal:1056-1112): only the keys of the key blocks in cand_list (8 keys per block,
  * ascending block indices as msb_topk over the block maxima returns them, -1 = none) are scored; every other key counts as
  * -inf.  scores[8 i + j] receives the score of key cand_list[i] * 8 + j; topk_out lists key indices, ascending, -1 padded.
- * FP8 keys only. */
+ * F16 keys (the reference's layout: one warp per candidate key) or FP8 keys (tcgen05 kernel). */
 int msb_index_decode_list(int key_type, const void* keys, int len, const float* q_raw, const float* w_raw, const float* cs,
                           int actq, int heads, int k, const int* cand_list, int n_cand, float* q_prep, float* w_prep,
                           float* scores, int* topk_out, void* topk_scratch, size_t topk_scratch_bytes, void* stream);
@@ -284,6 +284,29 @@ int msb_kv_window(const float* kv, const float* norm_w, const float* cs, int act
 int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream);
 /* y[i] += a[i] */
 int msb_add(float* y, const float* a, int n, void* stream);
+
+/* ---------------------------------------------------------------- hyper-connection step and KV compressor
+ * One sublayer boundary of the 4-stream residual -- ms::arch::encode_hc_step / HcStep (src/kernels/arch.hpp:44-77);
+ * math tests/ref/arch_ref.cpp:22-95.  All F32; h [n][4][dim]; mix [n][24] = pre[4], post[4], comb[4][4].
+ *   h_new  = x_sub ? post[i] * x_sub + sum_j comb[j][i] * h_in[j] : h_in     (h_out written only with x_sub; may alias h_in)
+ *   mix_out = fn ? Sinkhorn split of fn . h_new * rsqrt(mean(h_new^2) + 1e-20) : -    (fn [24][4 dim], scale[3], base[24])
+ *   x_out  = rmsnorm(sum_j mix_prev.pre[j] * h_new[j]) * norm_w                       (x_out NULL: skipped)
+ * x_sub, fn, x_out may be NULL as in the reference; mix_out must not alias mix_prev.  scratch: msb_hc_scratch_bytes(n)
+ * bytes, ZERO-FILLED before its first use (every call leaves its counters zeroed again). */
+size_t msb_hc_scratch_bytes(int n_tokens);
+int msb_hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn,
+                const float* scale, const float* base, float* mix_out, const float* norm_w, float* x_out, int dim,
+                int n_tokens, void* scratch, size_t scratch_bytes, void* stream);
+/* Compressor + index key of ONE decode token at position pos for a KV source of compression ratio `ratio` -- the n == 1
+ * case of ms::attn::encode_compress (src/kernels/attn.hpp:118); math tests/ref/attn_ref.cpp:116-161.  c_kv / c_gate: the
+ * layer's compressor projections F32[D] (c_gate only for ratio > 1); state: F32 [2][ratio][D] partial group of the source
+ * (kv values, then gate scores; start it at 0 / -inf).  When position pos completes a group a row is written at index
+ * pos / ratio: ckv_rows (D elements of elem_type MSB_F16 / MSB_BF16) and ikey_rows (index_dim elements, MSB_F16 or
+ * MSB_KEY_FP8_E4M3); otherwise only the state is updated.  cs = (cos, sin)[32] of position (pos / ratio) * ratio; rope on
+ * the last 64 dims of both vectors; actq: the fp4 quant-dequant simulations of the reference. */
+int msb_compress(const float* c_kv, const float* c_gate, const float* c_norm, const void* wk_bf16, const float* k_norm,
+                 const float* cs, float* state, int ratio, int pos, int actq, int D, int index_dim, int elem_type,
+                 void* ckv_rows, int key_type, void* ikey_rows, void* stream);
 
 #ifdef __cplusplus
 }

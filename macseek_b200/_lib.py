@@ -119,3 +119,7 @@ lib.msb_ep_free.argtypes = [_vp]
 lib.msb_ipc_export.argtypes = [_vp, C.c_char_p]
 lib.msb_ipc_import.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
 lib.msb_ipc_release.argtypes = [_vp]
+lib.msb_hc_scratch_bytes.restype = C.c_size_t
+lib.msb_hc_scratch_bytes.argtypes = [_i]
+lib.msb_hc_step.argtypes = [_vp] * 10 + [_i, _i, _vp, C.c_size_t, _vp]
+lib.msb_compress.argtypes = [_vp] * 7 + [_i] * 6 + [_vp, _i, _vp, _vp]

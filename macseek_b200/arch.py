@@ -86,3 +86,14 @@ def encode_argmax(e: Enc, logits, rows, V, out_idx, out_val=None):
 
 def encode_add(e: Enc, y, a, n):
     _lib.check(_lib.lib.msb_add(ptr(y), ptr(a), n, e.handle))
+
+
+def hc_scratch(n_tokens=1, device="cuda"):
+    return torch.zeros(_lib.lib.msb_hc_scratch_bytes(n_tokens) // 4 + 1, dtype=torch.int32, device=device)
+
+
+def encode_hc_step(e: Enc, h_in, h_out, x_sub, mix_prev, fn, scale, base, mix_out, norm_w, x_out, dim, scratch, n=1):
+    """One hyper-connection boundary (arch.hpp:44-77): x_sub / fn / x_out may be None."""
+    _lib.check(_lib.lib.msb_hc_step(ptr(h_in), ptr(h_out), ptr(x_sub), ptr(mix_prev), ptr(fn), ptr(scale), ptr(base),
+                                    ptr(mix_out), ptr(norm_w), ptr(x_out), dim, n, ptr(scratch),
+                                    scratch.numel() * scratch.element_size(), e.handle))

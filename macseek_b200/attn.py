@@ -101,7 +101,7 @@ def encode_index_decode(e: Enc, s: DecodeState, iq, iw, pos, length, actq=True, 
 
 def encode_index_decode_list(e: Enc, s: DecodeState, iq, iw, pos, length, actq=True):
     """encode_index_decode of a layer that uses candidates (attn.mm:226-229): only the keys of the blocks in s.cand_list
-    are scored.  FP8 keys only."""
+    are scored (F16 or FP8 keys)."""
     sh = s.shape
     cs = s.rope[pos]
     nb = (length + sh.cand_bs - 1) // sh.cand_bs
@@ -132,3 +132,13 @@ def encode_kv_window(e: Enc, s: DecodeState, kv, norm_w, pos, actq=False):
     slot = pos % sh.window
     _lib.check(_lib.lib.msb_kv_window(ptr(kv), ptr(norm_w), ptr(s.rope[pos]), int(actq), sh.D, sh.elem_type,
                                       ptr(s.win[slot]), e.handle))
+
+
+def encode_compress(e: Enc, s: DecodeState, c_kv, c_gate, c_norm, wk_bf16, k_norm, state, ratio, pos, actq=True):
+    """Compressor + index key of the token at pos for this KV source (attn.hpp:118, n == 1): updates `state`
+    (f32 [2][ratio][D]) and, when pos completes a group, writes row pos // ratio of s.ckv and s.ikey."""
+    sh = s.shape
+    cs = s.rope[(pos // ratio) * ratio]
+    _lib.check(_lib.lib.msb_compress(ptr(c_kv), ptr(c_gate), ptr(c_norm), ptr(wk_bf16), ptr(k_norm), ptr(cs), ptr(state),
+                                     ratio, pos, int(actq), sh.D, sh.index_dim, sh.elem_type, ptr(s.ckv), sh.key_type,
+                                     ptr(s.ikey), e.handle))

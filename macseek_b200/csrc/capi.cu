@@ -51,6 +51,15 @@ int index_prep(const float* q_raw, const float* w_raw, const float* cs, int actq
 int index_scores(int key_type, const void* keys, int len, const float* q, const float* w, int heads, float* scores,
                  unsigned* hist, int exact_query, cudaStream_t st);
 int block_max(const float* sc, int len, int bs, float* out, cudaStream_t st);
+int index_scores_list_f16(const void* keys, int len, const float* q, const float* w, int heads, const int* cand, int n_cand,
+                          float* scores, cudaStream_t st);
+size_t hc_scratch_bytes(int n);
+int hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn, const float* scale,
+            const float* base, float* mix_out, const float* norm_w, float* x_out, int D, int n, void* scratch,
+            size_t scratch_bytes, cudaStream_t st);
+int compress_token(const float* c_kv, const float* c_gate, const float* c_norm, const void* wk_bf16, const float* k_norm,
+                   const float* cs, float* state, int ratio, int pos, int actq, int D, int ID, int elem_type, void* ckv_rows,
+                   int key_type, void* ikey_rows, cudaStream_t st);
 size_t sparse_scratch_bytes(int total_rows_max, int H, int D);
 int sparse_decode(const float* q, const float* cs, const float* sinks, int elem_type, const void* win, int n_win,
                   const void* cache, const int* topk, int k, int H, int D, float* out, void* scratch,
@@ -361,13 +370,21 @@ int msb_index_decode_list(int key_type, const void* keys, int len, const float* 
                           int actq, int heads, int k, const int* cand_list, int n_cand, float* q_prep, float* w_prep,
                           float* scores, int* topk_out, void* topk_scratch, size_t topk_scratch_bytes_, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  if (key_type != MSB_KEY_FP8_E4M3) return fail(kErrType, "index_decode_list: FP8 keys only (key type %d)", key_type);
+  if (key_type != MSB_KEY_FP8_E4M3 && key_type != MSB_F16) return fail(kErrType, "index_decode_list: F16 or FP8 keys (key type %d)", key_type);
   if (heads != 32 && heads != 64) return fail(kErrArg, "index_decode_list: heads must be 32 or 64 (got %d)", heads);
   if (len < 0 || n_cand < 0) return fail(kErrArg, "index_decode_list: bad sizes");
   if (!keys || !q_raw || !w_raw || !cs || !q_prep || !w_prep || !scores || !topk_out || !topk_scratch ||
       (n_cand > 0 && !cand_list) || (reinterpret_cast<uintptr_t>(keys) & 15))
     return fail(kErrArg, "index_decode_list: null or misaligned pointer");
   const int nvirt = n_cand * 8;
+  if (nvirt > 0 && len > 0 && key_type == MSB_F16) {
+    // F16 keys (the reference's cache layout): prepared query, one warp per candidate key, then the exact top-k
+    int rc = index_prep(q_raw, w_raw, cs, actq, heads, q_prep, w_prep, st);
+    if (rc) return rc;
+    rc = index_scores_list_f16(keys, len, q_prep, w_prep, heads, cand_list, n_cand, scores, st);
+    if (rc) return rc;
+    return topk(scores, nvirt, k, topk_out, topk_scratch, topk_scratch_bytes_, false, cand_list, st);
+  }
   if (nvirt > 0 && len > 0) {
     int rc = index_scores_tc(keys, len, q_raw, w_raw, heads, scores, (unsigned*)topk_scratch, 1, cs, actq, q_prep, w_prep,
                              cand_list, n_cand, st);
@@ -396,5 +413,19 @@ int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream
   return argmax(x, n, out_idx, out_val, (cudaStream_t)stream);
 }
 int msb_add(float* y, const float* a, int n, void* stream) { return vec_add(y, a, n, (cudaStream_t)stream); }
+
+size_t msb_hc_scratch_bytes(int n_tokens) { return hc_scratch_bytes(n_tokens); }
+int msb_hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn,
+                const float* scale, const float* base, float* mix_out, const float* norm_w, float* x_out, int dim,
+                int n_tokens, void* scratch, size_t scratch_bytes, void* stream) {
+  return hc_step(h_in, h_out, x_sub, mix_prev, fn, scale, base, mix_out, norm_w, x_out, dim, n_tokens, scratch, scratch_bytes,
+                 (cudaStream_t)stream);
+}
+int msb_compress(const float* c_kv, const float* c_gate, const float* c_norm, const void* wk_bf16, const float* k_norm,
+                 const float* cs, float* state, int ratio, int pos, int actq, int D, int index_dim, int elem_type,
+                 void* ckv_rows, int key_type, void* ikey_rows, void* stream) {
+  return compress_token(c_kv, c_gate, c_norm, wk_bf16, k_norm, cs, state, ratio, pos, actq, D, index_dim, elem_type, ckv_rows,
+                        key_type, ikey_rows, (cudaStream_t)stream);
+}
 
 }  // extern "C"

@@ -771,6 +771,68 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
   return kOk;
 }
 
+// Candidate-restricted scoring for F16 keys (the reference's attn_idx_score_dec2_list, attn_index.metal:1056-1112):
+// scores[8 i + j] = score of key cand[i] * 8 + j, -inf when cand[i] < 0 or the key is beyond len.  One warp per key:
+// the key's 128 values sit in shared memory, lane l accumulates heads l and l + 32 over all 128 dims against the
+// prepared fp32 query held in shared memory with a padded row stride (conflict-free), then the warp adds
+// relu(q_h . k) * w_h over the heads in a fixed order.
+template <int H>
+__global__ void __launch_bounds__(256) idx_score_list_f16_kernel(const __half* keys, int len, const float* q, const float* w,
+                                                                 const int* cand, int n_cand, float* scores) {
+  pdl_launch_dependents();
+  extern __shared__ float sm[];
+  float* qs = sm;                         // [H][129]
+  float* ks = sm + H * 129;               // [8][128]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_wait();
+  for (int i = tid; i < H * 128; i += 256) qs[(i >> 7) * 129 + (i & 127)] = q[i];
+  __syncthreads();
+  for (int b = blockIdx.x; b < n_cand; b += gridDim.x) {
+    const int blk = cand[b];
+    const long key = (long)blk * 8 + warp;
+    const bool live = blk >= 0 && key < len;
+    float sc = -INFINITY;
+    if (live) {
+      const __half2* kp = reinterpret_cast<const __half2*>(keys + (size_t)key * 128);
+      const float2 a = __half22float2(kp[lane * 2]), c = __half22float2(kp[lane * 2 + 1]);
+      float* kr = ks + warp * 128 + lane * 4;
+      kr[0] = a.x; kr[1] = a.y; kr[2] = c.x; kr[3] = c.y;
+      __syncwarp();
+      float acc[H / 32];
+#pragma unroll
+      for (int g = 0; g < H / 32; g++) acc[g] = 0.f;
+      const float* kk = ks + warp * 128;
+#pragma unroll 8
+      for (int d = 0; d < 128; d++) {
+        const float kv = kk[d];
+#pragma unroll
+        for (int g = 0; g < H / 32; g++) acc[g] = fmaf(qs[(lane + 32 * g) * 129 + d], kv, acc[g]);
+      }
+      float v = 0.f;
+#pragma unroll
+      for (int g = 0; g < H / 32; g++) v += fmaxf(acc[g], 0.f) * w[lane + 32 * g];
+      sc = warp_sum(v);
+      __syncwarp();
+    }
+    if (lane == 0) scores[(size_t)b * 8 + warp] = sc;
+  }
+}
+
+int index_scores_list_f16(const void* keys, int len, const float* q, const float* w, int heads, const int* cand, int n_cand,
+                          float* scores, cudaStream_t st) {
+  if (heads != 32 && heads != 64) return fail(kErrArg, "index_scores_list: heads must be 32 or 64");
+  if (!keys || !q || !w || !cand || !scores || n_cand <= 0) return fail(kErrArg, "index_scores_list: bad arguments");
+  int dev = 0, sms = 0;
+  MSB_CUDA(cudaGetDevice(&dev));
+  MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const size_t smem = ((size_t)heads * 129 + 8 * 128) * sizeof(float);
+  const int grid = std::max(1, std::min(n_cand, sms * 4));
+  if (heads == 64) MSB_CUDA(launch_pdl(idx_score_list_f16_kernel<64>, dim3(grid), dim3(256), smem, st, (const __half*)keys, len, q, w, cand, n_cand, scores));
+  else MSB_CUDA(launch_pdl(idx_score_list_f16_kernel<32>, dim3(grid), dim3(256), smem, st, (const __half*)keys, len, q, w, cand, n_cand, scores));
+  MSB_LAUNCH_CHECK("idx_score_list_f16_kernel");
+  return kOk;
+}
+
 int block_max(const float* sc, int len, int bs, float* out, cudaStream_t st) {
   if (len <= 0 || bs <= 0 || !sc || !out) return fail(kErrArg, "block_max: bad arguments");
   const int nb = (len + bs - 1) / bs;
