@@ -285,6 +285,16 @@ int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream
 /* y[i] += a[i] */
 int msb_add(float* y, const float* a, int n, void* stream);
 
+/* ---------------------------------------------------------------- device memory for hosts without CUDA headers
+ * What the reference's Device::alloc (zero-filled) and Buffer::cpu() (shared storage) become with separate device memory
+ * (src/core/metal.hpp:11-40): allocation, blocking copies on a stream, and the fill dispatch of the layer code
+ * (src/model/dec_layer.mm, fill0).  Not for use inside a stream capture (except msb_fill_f32). */
+int msb_device_alloc(size_t bytes, void** out);
+int msb_device_free(void* p);
+int msb_copy_to_device(void* dst, const void* src, size_t bytes, void* stream);
+int msb_copy_to_host(void* dst, const void* src, size_t bytes, void* stream);
+int msb_fill_f32(float* p, float value, size_t n, void* stream);
+
 /* ---------------------------------------------------------------- hyper-connection step and KV compressor
  * One sublayer boundary of the 4-stream residual -- ms::arch::encode_hc_step / HcStep (src/kernels/arch.hpp:44-77);
  * math tests/ref/arch_ref.cpp:22-95.  All F32; h [n][4][dim]; mix [n][24] = pre[4], post[4], comb[4][4].

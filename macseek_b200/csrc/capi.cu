@@ -53,6 +53,11 @@ int index_scores(int key_type, const void* keys, int len, const float* q, const 
 int block_max(const float* sc, int len, int bs, float* out, cudaStream_t st);
 int index_scores_list_f16(const void* keys, int len, const float* q, const float* w, int heads, const int* cand, int n_cand,
                           float* scores, cudaStream_t st);
+int device_alloc(size_t bytes, void** out);
+int device_free(void* p);
+int copy_to_device(void* dst, const void* src, size_t bytes, cudaStream_t st);
+int copy_to_host(void* dst, const void* src, size_t bytes, cudaStream_t st);
+int fill_f32(float* p, float v, size_t n, cudaStream_t st);
 size_t hc_scratch_bytes(int n);
 int hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn, const float* scale,
             const float* base, float* mix_out, const float* norm_w, float* x_out, int D, int n, void* scratch,
@@ -413,6 +418,12 @@ int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream
   return argmax(x, n, out_idx, out_val, (cudaStream_t)stream);
 }
 int msb_add(float* y, const float* a, int n, void* stream) { return vec_add(y, a, n, (cudaStream_t)stream); }
+
+int msb_device_alloc(size_t bytes, void** out) { return device_alloc(bytes, out); }
+int msb_device_free(void* p) { return device_free(p); }
+int msb_copy_to_device(void* dst, const void* src, size_t bytes, void* stream) { return copy_to_device(dst, src, bytes, (cudaStream_t)stream); }
+int msb_copy_to_host(void* dst, const void* src, size_t bytes, void* stream) { return copy_to_host(dst, src, bytes, (cudaStream_t)stream); }
+int msb_fill_f32(float* p, float value, size_t n, void* stream) { return fill_f32(p, value, n, (cudaStream_t)stream); }
 
 size_t msb_hc_scratch_bytes(int n_tokens) { return hc_scratch_bytes(n_tokens); }
 int msb_hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn,

@@ -59,3 +59,26 @@ def test_argmax_ties_take_the_lowest_index():
     arch.encode_argmax(e, dev(x), 1, x.size, out)
     e.wait()
     assert int(out.item()) == 313
+
+
+@pytest.mark.parametrize("D,elem", [(512, "f16"), (576, "bf16")])
+def test_kv_window_row_with_fp8_simulation(D, elem):
+    # rmsnorm -> rope -> fp8 (e4m3, power-of-two scale per 32) simulation: on the e4m3 lattice every value equals the
+    # oracle's except where the fp32 rounding of the normalised value falls on the other side of a lattice midpoint
+    from macseek_b200 import _lib, attn
+    from macseek_b200.core import Enc
+    orc = ol.Oracle()
+    kv = synth.randn(D, 7, 3.0)
+    nw = (1 + 0.1 * synth.randn(D, 8)).astype(np.float32)
+    cs = attn.make_rope_table(300, True)[257]
+    out = torch.zeros(D, dtype=torch.float16 if elem == "f16" else torch.bfloat16, device="cuda")
+    e = Enc()
+    kd, nd, cd = dev(kv), dev(nw), dev(cs)
+    _lib.check(_lib.lib.msb_kv_window(kd.data_ptr(), nd.data_ptr(), cd.data_ptr(), 1, D,
+                                      attn.ELEM_F16 if elem == "f16" else attn.ELEM_BF16, out.data_ptr(), e.handle))
+    e.wait()
+    want = orc.window_row(kv, nw, cs, True)
+    got = out.float().cpu().numpy()
+    if elem == "bf16":
+        want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+    assert np.mean(got == want) >= 0.99 and np.max(np.abs(got - want)) <= 0.13 * np.max(np.abs(want))

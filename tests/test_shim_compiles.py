@@ -7,7 +7,7 @@ import tempfile
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 SRC = r'''
-#include "ms_b200_shim.hpp"
+#include "ms_b200_dec_layer.hpp"
 int main(int argc, char**) {
   ms::Enc e;
   ms::Buffer W, x, y;
@@ -21,6 +21,19 @@ int main(int argc, char**) {
     ms::attn::DecodeCaches c;
     ms::attn::encode_index_decode(e, c, x, x, 10, 5);
     ms::attn::encode_sparse(e, c, x, x, y, 10);
+    // the reference's own signatures over attn::State (src/kernels/attn.hpp:116-129)
+    ms::attn::State st;
+    ms::attn::init(st, ms::attn::Options{});
+    ms::attn::encode_kv_window(e, st, 3, x, x, 10, 1);
+    ms::attn::encode_index_decode(e, st, 2, x, x, 10);
+    ms::attn::encode_sparse(e, st, 3, x, x, y, 10, 1, true);
+    ms::attn::LayerIO io;
+    ms::attn::encode_layer(e, st, io, 10, 1);
+    // the layer-forward surface (src/model/dec_layer.hpp:107-118)
+    ms::ds41::DecCtx ctx;
+    ms::ds41::encode_dec_prologue(e, ctx, x);
+    ms::ds41::encode_dec_attn_side(e, ctx, 0, 10);
+    ms::ds41::encode_dec_moe_table(e, ctx, 0, ms::q::QType::IQ1_S, ms::q::QType::IQ2_XXS, x);
     e.wait();
   }
   return ms::q::row_bytes(ms::q::QType::IQ1_S, 4096) == 800 ? 0 : 1;
