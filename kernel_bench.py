@@ -282,6 +282,95 @@ def moe_prefill_case(n: int = 4096, eager: int = 0, routing: str = "bias", quiet
             "experts_hit": len(used), "tokens_per_expert": {"min": cs[0], "median": cs[len(cs) // 2], "max": cs[-1]}}
 
 
+def moe_prefill_ep_case(n: int = 4096, check: bool = True, quiet: bool = False):
+    """The benchmark prefill layer expert-parallel (run under torchrun, one rank per GPU): tokens sharded n / N per rank,
+    experts 384 / N per rank, all-to-all dispatch of bf16 rows and all-to-all combine of f32 expert outputs.  With
+    check, every rank also holds the whole layer and computes the single-GPU result for ITS tokens to compare with."""
+    import torch.distributed as dist
+    from macseek_b200 import ep, ep_prefill
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    D, I, E, K = 4096, 2048, 384, 8
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)                                     # the same routing, inputs and replicated weights on every rank
+    lo, hi = ep.expert_range(E, world, rank)
+    lw = ml.MoeLayerWeights(D, I, E, q.QType.IQ1_S, q.QType.IQ2_XXS, q.QType.Q8_0, lo, hi, dev).randomize(gen, expert_seed=99)
+    perm = torch.randperm(E, device=dev, generator=gen)
+    bias = torch.empty(E, device=dev)
+    bias[perm] = -1.1 * torch.log(torch.arange(1, E + 1, device=dev, dtype=torch.float32))
+    logits = torch.randn(n, E, device=dev, generator=gen) + bias
+    ids = torch.topk(logits, K, dim=1).indices
+    w = torch.softmax(torch.gather(logits, 1, ids), dim=1).float()
+    X = torch.randn(n, D, device=dev, generator=gen).to(torch.bfloat16).float()
+    per = n // world
+    sl = slice(rank * per, (rank + 1) * per)
+    e = Enc()
+    run_local, run_shared = ep_prefill.cuda_local_experts(lw, e), ep_prefill.cuda_shared_expert(lw, e)
+    stats = {}
+
+    def step():
+        Y = torch.zeros(per, D, device=dev)
+        ep_prefill.moe_prefill_ep(X[sl], ids[sl], w[sl], E, run_local, run_shared, Y, stats=stats)
+        return Y
+    Y = step()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(3):
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        Y = step()
+        t1.record()
+        torch.cuda.synchronize()
+        ts.append(t0.elapsed_time(t1))
+    t = torch.tensor([sorted(ts)[1]], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    rows = [None] * world
+    dist.all_gather_object(rows, stats["rows_received"])
+    out = {"tokens": n, "world": world, "ms": float(t.item()), "rows_received_per_rank": rows,
+           "flop": 2.0 * 3 * D * I * (n * K + n)}
+    out["tflops"] = out["flop"] / out["ms"] / 1e9
+    if check:
+        # the whole layer on this rank (experts seeded by global id: the same bytes), this rank's tokens, one GPU
+        full = ml.MoeLayerWeights(D, I, E, q.QType.IQ1_S, q.QType.IQ2_XXS, q.QType.Q8_0, 0, E, dev)
+        g2 = torch.Generator(device=dev)
+        g2.manual_seed(7)
+        full.randomize(g2, expert_seed=99)
+        Xl, il, wl = X[sl].contiguous(), ids[sl], w[sl]
+        flat_e = il.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        counts = torch.bincount(flat_e, minlength=E).cpu().tolist()
+        used = [x for x in range(E) if counts[x] > 0]
+        a = q.MoePrefillArgs(D, I)
+        a.t_gate_up, a.t_down, a.t_shared = full.t_gate_up, full.t_down, full.t_shared
+        a.n_tokens, a.k_per_token, a.has_shared, a.shared = per, K, True, full.shared
+        offs = [0]
+        for ex in used:
+            sl_ = q.ExpertSlot()
+            sl_.gate, sl_.up, sl_.down = full.expert_views(ex)
+            a.slots.append(sl_)
+            offs.append(offs[-1] + counts[ex])
+        a.offs = offs
+        a.tok = (order // K).int().contiguous()
+        a.wt = wl.reshape(-1)[order].contiguous()
+        a.slot_of = torch.empty(per * K, dtype=torch.int32, device=dev)
+        a.slot_of[order] = torch.arange(per * K, dtype=torch.int32, device=dev)
+        a.X, a.Y = Xl, torch.zeros(per, D, device=dev)
+        a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(offs[-1], per, len(used), D, I), dtype=torch.uint8, device=dev)
+        q.encode_moe_prefill(e, a)
+        e.wait()
+        rel = float((Y - a.Y).abs().max() / a.Y.abs().max())
+        r = torch.tensor([rel], dtype=torch.float64, device=dev)
+        dist.all_reduce(r, op=dist.ReduceOp.MAX)
+        out["max_rel_diff_vs_single_gpu"] = float(r.item())
+        out["matches_single_gpu"] = bool(r.item() <= 1e-3)
+        del full
+    if rank == 0 and not quiet:
+        print("moe_prefill_ep", out, flush=True)
+    return out
+
+
 def layer_stages(n_layers: int = 8, kv_len: int = 200000):
     """The decode layer in context: CUDA graphs of n_layers layers cut after the first k calls of each layer, k = 1 ..;
     the difference between consecutive cuts is what call k adds per layer with all overlaps as in the real step."""
@@ -365,7 +454,7 @@ def sweep():
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "layer", "sweep"])
+    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "moe_prefill_ep", "layer", "sweep"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--groups", type=int, default=1)
@@ -373,6 +462,15 @@ def main():
     ap.add_argument("--routing", default="bias", choices=["bias", "sample"])
     ap.add_argument("--eager", type=int, default=0, help="issue this many plain launches and exit (no timing)")
     a = ap.parse_args()
+    if a.case == "moe_prefill_ep":                      # under torchrun: one rank per GPU
+        import os
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        moe_prefill_ep_case(a.n if a.n > 1 else 4096)
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)
     torch.cuda.set_device(0)
     if a.case == "matvec":
         matvec_case(q.QType[a.args[0]], int(a.args[1]), int(a.args[2]), a.n, a.groups, a.eager)
