@@ -389,6 +389,14 @@ def run_ours(a):
                         sweep.append(kb.matvec_case(t, rows, cols, n, quiet=True))
             extras["matvec"] = sweep
             extras["prefill"] = kb.moe_prefill_case(4096, quiet=True)
+        if world > 1 and not a.no_extras:
+            # cfg4's prefill layer expert-parallel: tokens and experts sharded over the ranks, all-to-all dispatch and
+            # combine, every rank's result checked against the single-GPU kernels on the same tokens
+            import kernel_bench as kb
+            try:
+                extras["prefill_ep"] = kb.moe_prefill_ep_case(4096, check=True, quiet=True)
+            except Exception as ex:
+                extras["prefill_ep"] = {"error": str(ex)[:200]}
         st = __import__("macseek_b200._lib", fromlist=["x"]).device_status()
         if st:
             raise RuntimeError("device-side failure word %d" % st)
@@ -456,6 +464,8 @@ def run_ours(a):
                                         "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst); half operands",
                                         "ms_per_layer": pf["ms"], "flop": pf["flop"], "experts_hit": pf["experts_hit"],
                                         "tokens_per_expert": pf["tokens_per_expert"]}
+        if "prefill_ep" in extras:
+            line["prefill_ep"] = extras["prefill_ep"]
         if world == 1 and not a.no_cpu_baseline:
             try:
                 line["cpu_baseline"] = cpu_baseline_dict(a)
