@@ -116,11 +116,15 @@ size_t msb_moe_decode_scratch_bytes(int inter, int max_routed);
 int msb_moe_decode(const msb_moe_decode_args* a, void* stream);
 /* NO COUNTERPART IN THE REFERENCE.  msb_moe_decode for callers that cannot allocate device memory: a.scratch and
  * a.scratch_bytes are ignored, the h rows go to an array inside the library (static device memory, one instance per
- * device).  Nothing is allocated on this path, now or on first use: msb_init() must have run on the device before
- * (else MSB_E_DEVICE), and the first call per device only looks the array's address up (cudaGetSymbolAddress) -- make
- * that first call before any stream capture.  Limits: inter <= 4096 and n_routed <= 16, beyond them MSB_E_LIMIT.
- * Nothing in the array has to start at zero (the gate/up launch writes every h row the down launch reads).  Calls
- * that overlap in time on one device (two streams) share the array and race: serialise them. */
+ * device).  Nothing is allocated or looked up on this path: msb_init() must have run on the device before (else
+ * MSB_E_DEVICE) -- it is msb_init() that resolves the array's address (cudaGetSymbolAddress, which loads the module
+ * that holds it) and caches it under the library's lock; this call only reads that, so it is safe inside a stream
+ * capture and from several host threads.  Limits: inter <= 4096 and n_routed <= 16 for the scratch, AND what
+ * msb_moe_decode itself can stage -- the down launch keeps the quantised h of all n_routed + 1 experts (2.5 bytes per
+ * element), its code tables and two ring slots in 227 KB of shared memory, so inter x (n_routed + 1) is bounded: e.g.
+ * inter 2048 with 8 routed fits, inter 4096 with 8 routed does not.  Beyond either limit: MSB_E_LIMIT, nothing
+ * enqueued, y untouched.  Nothing in the array has to start at zero (the gate/up launch writes every h row the down
+ * launch reads).  Calls that overlap in time on one device (two streams) share the array and race: serialise them. */
 int msb_moe_decode_noalloc(const msb_moe_decode_args* a, void* stream);
 /* Routed matrices come from `table`: n_routed entries of 3 device addresses {gate, up, down} (uint64), a.slot[] is
  * ignored -- encode_moe_decode_table_part (quant.hpp:75-85). */
@@ -205,6 +209,12 @@ typedef struct {
   float swiglu_limit;                 /* 0 selects the reference's 10 */
 } msb_moe_prefill_args;
 size_t msb_moe_prefill_scratch_bytes(int total_entries, int n_tokens, int n_exp, int dim, int inter);
+/* Unlike the decode entry points this one is NOT enqueue-only: it reads offs[] and slots[] on the host, builds its tile
+ * tables there and uploads them with stream-ordered copies from pageable host memory, which block the calling thread
+ * until the copy engine has taken them.  It therefore cannot be captured into a CUDA graph, and a caller that overlaps
+ * it with other host work should give it a thread of its own.  (The reference's encode_moe_prefill builds the same
+ * per-expert dispatch list on the CPU, quant.mm:385-487.)  Like every entry point it creates the library's tables on
+ * first use on a device: call msb_init() before any stream capture. */
 int msb_moe_prefill(const msb_moe_prefill_args* a, void* stream);
 
 size_t msb_router_scratch_bytes(int n_experts);

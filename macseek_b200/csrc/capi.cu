@@ -221,31 +221,19 @@ int msb_moe_decode_ids_normed(const msb_moe_decode_args* a, const uint64_t* expe
 // ---- msb_moe_decode with library-resident scratch: no allocation of any kind on this path.
 // The scratch (the h rows of every routed slot + the shared expert) lives in a file-scope device array; its address is
 // looked up once per device with cudaGetSymbolAddress and handed to the kernels like a caller's buffer.
-namespace {
-constexpr int kNoAllocMaxInter = 4096;     // largest expert intermediate width served
-constexpr int kNoAllocMaxDev = 64;
-__device__ __align__(256) float g_noalloc_moe_scratch[(size_t)(kMaxRouted + 1) * kNoAllocMaxInter];   // 272 KB
-float* g_noalloc_addr[kNoAllocMaxDev] = {};
-}  // namespace
-
 int msb_moe_decode_noalloc(const msb_moe_decode_args* a, void* stream) {
   if (!a) return fail(kErrArg, "moe_decode_noalloc: null args");
+  static_assert(kNoAllocFloats == (kMaxRouted + 1) * kNoAllocMaxInter, "scratch sized for kMaxRouted routed + the shared expert");
   if (a->inter > kNoAllocMaxInter || a->n_routed > kMaxRouted)
     return fail(kErrLimit, "moe_decode_noalloc: inter %d / n_routed %d beyond the built-in scratch (inter <= %d, n_routed <= %d)",
                 a->inter, a->n_routed, kNoAllocMaxInter, kMaxRouted);
-  int dev = 0;
-  MSB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kNoAllocMaxDev) return fail(kErrArg, "moe_decode_noalloc: device index %d out of range", dev);
-  if (!tables_ready())
-    return fail(kErrDevice, "moe_decode_noalloc: msb_init() has not run on device %d (this entry point creates nothing)", dev);
-  if (!g_noalloc_addr[dev]) {
-    void* ptr = nullptr;
-    MSB_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_moe_scratch));   // the current device's instance of the array
-    g_noalloc_addr[dev] = static_cast<float*>(ptr);
-  }
+  size_t bytes = 0;
+  float* scratch = noalloc_scratch(&bytes);      // cached by msb_init(); nothing is looked up or created here
+  if (!scratch)
+    return fail(kErrDevice, "moe_decode_noalloc: msb_init() has not run on this device (this entry point creates nothing)");
   msb_moe_decode_args b = *a;
-  b.scratch = g_noalloc_addr[dev];
-  b.scratch_bytes = sizeof(float) * (size_t)(kMaxRouted + 1) * kNoAllocMaxInter;
+  b.scratch = scratch;
+  b.scratch_bytes = bytes;
   return msb_moe_decode(&b, stream);
 }
 

@@ -663,6 +663,20 @@ int moe_decode(MoeParams p, int t_gate_up, int t_down, int t_shared, int part, s
   const int lpr_gu = lpr_for(p.dim / 32), lpr_d = lpr_for(p.inter / 32);
   if (!lpr_gu || !lpr_d) return fail(kErrArg, "moe_decode: dim/inter not supported");
   unsigned* sched_base = reinterpret_cast<unsigned*>(p.tb.status) + 8;   // [0]: blocks of a down launch that stored their partial
+  if (p.d_r || p.d_s) {
+    // The down launch keeps the quantised h of every routed expert and of the shared expert in shared memory beside its
+    // tables and a two-slot ring: checked here, before the gate/up launch, so that a size that does not fit leaves
+    // nothing enqueued (the same arithmetic as launch_down).
+    const size_t U = (size_t)(p.n_routed + 1) * (p.inter / 32);
+    const size_t fixed = ((sizeof(MoeSmemHead) + 127) & ~(size_t)127) + lut_bytes_for(t_down) +
+                         xq_bytes((int)U, false, xq_padded(t_down) || xq_padded(t_shared)) + 128;
+    const size_t R = kMoeNW / 2;
+    const size_t pitch = (R * row_bytes(t_down, p.inter) + 15 + 16 + 15) & ~(size_t)15;
+    const size_t need = std::max((size_t)std::max(1, p.n_routed) * pitch, R * row_bytes(t_shared, p.inter) + 64);
+    if (fixed + 2 * need > (size_t)kSmemLimit)
+      return fail(kErrLimit, "moe_decode: down staging does not fit (inter %d, %d routed): inter x (routed + 1) x 2.5 bytes of "
+                  "quantised h, the tables and two ring slots must fit %d bytes of shared memory", p.inter, p.n_routed, (int)kSmemLimit);
+  }
   if (p.gu_r || p.gu_s) {
     p.sched = sched_base;
 #define MSB_GU(TR, TS) rc = launch_gu_lpr<TR, TS>(p, lpr_gu, sms, dev, st)

@@ -173,5 +173,8 @@ struct Tables {
 // Builds the tables on the current device the first time it is called for that device.
 int get_tables(Tables* out);
 bool tables_ready();
+constexpr int kNoAllocMaxInter = 4096;                       // msb_moe_decode_noalloc: widest expert its scratch serves
+constexpr int kNoAllocFloats = (16 + 1) * kNoAllocMaxInter;  // (max routed + shared) h rows
+float* noalloc_scratch(size_t* bytes);
 
 }  // namespace msb

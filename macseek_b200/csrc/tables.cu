@@ -41,7 +41,9 @@ static const int8_t kIq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 1
 
 namespace {
 constexpr int kMaxDev = 64;
-struct DevTables { bool ready = false; Tables t{}; };
+struct DevTables { bool ready = false; Tables t{}; float* noalloc = nullptr; };
+// scratch of msb_moe_decode_noalloc: static device memory, (kMaxRouted + 1) x 4096 floats = 272 KB per device
+__device__ __align__(256) float g_noalloc_moe_scratch[(size_t)kNoAllocFloats];
 DevTables g_tables[kMaxDev];
 std::mutex g_mu;
 
@@ -129,19 +131,27 @@ int get_tables(Tables* out) {
   DevTables& d = g_tables[dev];
   if (!d.ready) {
     static const HostImage img;
-    MSB_CUDA(upload(img.img_iq1s, (const void**)&d.t.img_iq1s));
-    MSB_CUDA(upload(img.img_iq2g, (const void**)&d.t.img_iq2g));
-    MSB_CUDA(upload(img.img_iq2s, (const void**)&d.t.img_iq2s));
-    MSB_CUDA(upload(img.img_iq4, (const void**)&d.t.img_iq4));
-    MSB_CUDA(upload(img.iq2_grid, (const void**)&d.t.iq2xxs_grid));
-    MSB_CUDA(upload(img.iq2_sign, (const void**)&d.t.iq2_signmask));
-    MSB_CUDA(upload(img.iq4_pair, (const void**)&d.t.iq4nl_pair));
-    MSB_CUDA(upload(img.iq1s_i8, (const void**)&d.t.iq1s_i8));
-    MSB_CUDA(upload(img.iq1s_sel, (const void**)&d.t.iq1s_sel));
-    MSB_CUDA(upload(img.iq2_sel, (const void**)&d.t.iq2_sel));
-    MSB_CUDA(upload(img.iq2_sign16, (const void**)&d.t.iq2_sign16));
-    MSB_CUDA(cudaMalloc((void**)&d.t.status, 2048));     // status word, scheduling counters, argmax partials
-    MSB_CUDA(cudaMemset(d.t.status, 0, 2048));
+    Tables t{};
+    const void** slots[] = {(const void**)&t.img_iq1s, (const void**)&t.img_iq2g, (const void**)&t.img_iq2s, (const void**)&t.img_iq4,
+                            (const void**)&t.iq2xxs_grid, (const void**)&t.iq2_signmask, (const void**)&t.iq4nl_pair,
+                            (const void**)&t.iq1s_i8, (const void**)&t.iq1s_sel, (const void**)&t.iq2_sel, (const void**)&t.iq2_sign16};
+    cudaError_t e = cudaSuccess;
+    auto up = [&](auto& v, int k) { if (e == cudaSuccess) e = upload(v, slots[k]); };
+    up(img.img_iq1s, 0); up(img.img_iq2g, 1); up(img.img_iq2s, 2); up(img.img_iq4, 3); up(img.iq2_grid, 4); up(img.iq2_sign, 5);
+    up(img.iq4_pair, 6); up(img.iq1s_i8, 7); up(img.iq1s_sel, 8); up(img.iq2_sel, 9); up(img.iq2_sign16, 10);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&t.status, 2048);     // status word, scheduling counters, argmax partials
+    if (e == cudaSuccess) e = cudaMemset(t.status, 0, 2048);
+    void* na = nullptr;
+    // the first symbol look-up loads the module that holds the array: done here, never on the allocation-free path
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&na, g_noalloc_moe_scratch);
+    if (e != cudaSuccess) {
+      // nothing half-built survives: a later call starts over instead of leaking what was uploaded so far
+      for (const void** sl : slots) if (*sl) cudaFree(const_cast<void*>(*sl));
+      if (t.status) cudaFree(t.status);
+      return cuda_fail(e, "get_tables");
+    }
+    d.t = t;
+    d.noalloc = static_cast<float*>(na);
     d.ready = true;
   }
   *out = d.t;
@@ -154,6 +164,17 @@ bool tables_ready() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return false;
   std::lock_guard<std::mutex> lk(g_mu);
   return g_tables[dev].ready;
+}
+
+// The allocation-free MoE entry point's scratch on the current device, or nullptr when msb_init() has not run there.
+// A pure read of what get_tables() cached: no CUDA call that could create anything, safe during a stream capture.
+float* noalloc_scratch(size_t* bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_tables[dev].ready) return nullptr;
+  if (bytes) *bytes = sizeof(float) * (size_t)kNoAllocFloats;
+  return g_tables[dev].noalloc;
 }
 
 }  // namespace msb
