@@ -121,3 +121,56 @@ class EpComm:
 def encode_combine(e, comm: EpComm, h: torch.Tensor):
     """h += sum over ranks of the partial outputs that the ranks' MoE down launches stored for this exchange."""
     comm._lib.check(comm._lib.lib.msb_ep_combine(C.byref(comm.c), h.data_ptr(), h.numel(), e.handle))
+
+
+class HostExchange:
+    """The exchange protocol of the peer combine, on the host: what `moe_down_kernel`'s epilogue and `ep_combine_kernel`
+    do with peer stores and flags, restated over a torch.distributed key-value store so that the protocol (epochs,
+    double-buffered slots, rank-ordered sum, BOUNDED wait with a status instead of a hang) can be exercised by CPU ranks.
+
+    publish(partial): this rank's partial of the current epoch becomes visible to every rank (slot write + flag).
+    combine(h, timeout_s): wait -- at most timeout_s -- for every rank's flag of the current epoch, add the partials to h in
+    rank order and advance the epoch.  Returns 0, or STATUS_PEER_WAIT (3, the device status word's value for the same
+    event) with h untouched when a rank's contribution did not arrive in time; the epoch does not advance then."""
+
+    STATUS_PEER_WAIT = 3
+
+    def __init__(self, store, world: int, rank: int, prefix: str = "msb_ep"):
+        self.store, self.world, self.rank, self.prefix = store, world, rank, prefix
+        self.epoch = 0
+
+    def _key(self, epoch, rank):
+        # two buffers, by epoch parity: a rank may publish epoch e + 1 while a slower rank still reads epoch e
+        return "%s/%d/%d" % (self.prefix, epoch & 1, rank)
+
+    def publish(self, partial: torch.Tensor):
+        import io
+        buf = io.BytesIO()
+        torch.save((self.epoch + 1, partial.detach().cpu().to(torch.float32)), buf)
+        self.store.set(self._key(self.epoch, self.rank), buf.getvalue())
+
+    def combine(self, h: torch.Tensor, timeout_s: float = 1.0) -> int:
+        import io
+        import time
+        deadline = time.monotonic() + timeout_s
+        parts = []
+        for r in range(self.world):                       # fixed rank order, as the kernel sums
+            while True:
+                got = None
+                try:
+                    if self.store.check([self._key(self.epoch, r)]):
+                        flag, part = torch.load(io.BytesIO(self.store.get(self._key(self.epoch, r))))
+                        if flag == self.epoch + 1:        # the flag carries the epoch: a stale slot does not count
+                            got = part
+                except Exception:
+                    got = None
+                if got is not None:
+                    parts.append(got)
+                    break
+                if time.monotonic() >= deadline:
+                    return self.STATUS_PEER_WAIT
+                time.sleep(0.002)
+        for part in parts:
+            h += part.to(h.dtype)
+        self.epoch += 1
+        return 0

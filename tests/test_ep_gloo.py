@@ -100,3 +100,56 @@ def test_two_rank_combine_matches_single_rank():
     assert covered, "every routed slot must be owned by exactly one rank"
     assert same, "ranks disagree on the combined output"
     assert err < 1e-12, err
+
+
+def _exchange_main(rank, world, port, out, skip_rank, skip_epoch):
+    """Three epochs of the host exchange; rank `skip_rank` does not publish in epoch `skip_epoch` (None: every rank
+    always publishes)."""
+    from macseek_b200 import ep
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=60))
+    ex = ep.HostExchange(store, world, rank)
+    h = torch.zeros(8, dtype=torch.float64)
+    statuses = []
+    for epoch in range(3):
+        part = torch.full((8,), float((rank + 1) * 10 ** epoch), dtype=torch.float32)
+        if not (rank == skip_rank and epoch == skip_epoch):
+            ex.publish(part)
+        st = ex.combine(h, timeout_s=1.0 if skip_rank is not None else 20.0)
+        statuses.append(st)
+        if st:
+            break
+    out.put((rank, statuses, h.tolist()))
+    # leave only after every rank has reported: the store's master must outlive the others' last reads
+    store.add("done", 1)
+    while int(store.add("done", 0)) < world:
+        __import__("time").sleep(0.01)
+
+
+def _run_exchange(world, skip_rank, skip_epoch):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_exchange_main, args=(r, world, port, out, skip_rank, skip_epoch)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(out.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return res
+
+
+def test_host_exchange_sums_in_rank_order_over_epochs():
+    res = _run_exchange(2, None, None)
+    for rank, statuses, h in res:
+        assert statuses == [0, 0, 0]
+        assert h == [3.0 + 30.0 + 300.0] * 8              # (1 + 2) * (1 + 10 + 100), identical on every rank
+
+
+def test_host_exchange_missing_contribution_sets_status_3_and_returns():
+    """Rank 1 skips its contribution in the second epoch: every rank's bounded wait runs out, reports status 3 (the
+    device status word's value for an expired peer wait), leaves h as the first epoch made it, and returns."""
+    res = _run_exchange(2, 1, 1)
+    for rank, statuses, h in res:
+        assert statuses == [0, 3]
+        assert h == [3.0] * 8
