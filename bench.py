@@ -166,24 +166,62 @@ def run_reference(a):
 
 # ------------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
+    """SM clock and slowdown reasons of one GPU while the timed regions run: a thread that reads NVML every 10 ms
+    (reading only; nothing is set), or -- without the NVML binding -- an `nvidia-smi -lms` child process."""
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
-    def __init__(self, index):
-        self.index, self.proc, self.path = index, None, None
+    def __init__(self, index, pci_bus_id=None):
+        self.index, self.pci, self.proc, self.path = index, pci_bus_id, None, None
+        self.thread, self.stop_flag, self.samples, self.max_mhz, self.how = None, False, [], None, None
+
+    def _nvml_loop(self, nv, h):
+        import time
+        bits = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap))
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.samples.append((float(mhz), [n for n, b in bits if mask & b]))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByPciBusId(self.pci.encode()) if self.pci else nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            self.how = "nvml thread, 10 ms"
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            self.how = "nvidia-smi -lms 100"
         except Exception:
             self.proc = None
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            sm = sorted(v for v, _ in self.samples)
+            if sm:
+                reasons = sorted({r for _, rs in self.samples for r in rs})
+                out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(sm),
+                       "how": self.how}
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -209,7 +247,8 @@ class ClockSampler:
             pass
         if sm:
             sm.sort()
-            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                   "how": self.how}
         return out
 
 
@@ -260,7 +299,12 @@ def run_ours(a):
             torch.cuda.synchronize()
 
         # ---- value: device-resident input, K graph replays
-        sampler = ClockSampler(local)
+        try:
+            pr = torch.cuda.get_device_properties(dev)
+            pci = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        except Exception:
+            pci = None
+        sampler = ClockSampler(local, pci)
         barrier()
         sampler.start()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
