@@ -27,7 +27,7 @@ METRIC = "decode_tok_per_s_200k_ctx"
 UNIT = "tok/s"
 # DRAM bytes (read + write) of one moe_gu_kernel launch of the benchmark layer, all 8 routed experts resident:
 # measured once with ncu (profiles/moe_gu_kernel_cfg3_ncu_full.txt); the algorithmic bytes are 44,040,192
-NCU_GU_TRAFFIC_BYTES = 44_283_648
+NCU_GU_TRAFFIC_BYTES = 44_191_488     # dram__bytes_read.sum 44,190,976 + dram__bytes_write.sum 512
 
 
 def parse():
