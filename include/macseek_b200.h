@@ -295,6 +295,28 @@ int msb_argmax(const float* x, int n, int* out_idx, float* out_val, void* stream
 /* y[i] += a[i] */
 int msb_add(float* y, const float* a, int n, void* stream);
 
+/* ---------------------------------------------------------------- sampling head (src/kernels/arch.hpp:109-126)
+ * Scratch for the three calls below: msb_sample_scratch_bytes(rows) bytes, 16-byte aligned, zeroed once after
+ * allocation (the kernels leave it ready for the next call).  One scratch serves one stream at a time. */
+size_t msb_sample_scratch_bytes(int rows);
+/* Argmax of each of `rows` rows of V logits, ties -> lowest index, one launch -- ms::arch::encode_argmax
+ * (arch.hpp:111-115, arch_sample.metal:46-83).  temperature > 0: Gumbel-max sampling of softmax(logits / temperature)
+ * (exact multinomial sampling over the whole row; counter-based noise keyed by (seed, row, index), the reference's
+ * mixer arch_sample.metal:15-26); out_val (may be NULL) receives the winning (noisy) value. */
+int msb_argmax_rows(const float* logits, int rows, int V, int* out_idx, float* out_val, float temperature,
+                    unsigned long long seed, void* scratch, size_t scratch_bytes, void* stream);
+/* Top-k (1 <= k <= 64) of each row: raw logits descending (ties -> lower index) in out_v [rows][64] and their ids in
+ * out_i [rows][64], plus out_lse[row] = logsumexp(logits / temperature) over the WHOLE row (temperature <= 0 counts as
+ * 1) -- ms::arch::encode_topk (arch.hpp:116-119, arch_sample.metal:124-181).  V <= 262144. */
+int msb_sample_topk(const float* logits, int rows, int V, int k, float temperature, float* out_v, int* out_i,
+                    float* out_lse, void* scratch, size_t scratch_bytes, void* stream);
+/* out = in - logsumexp(in) per row; out may alias in -- ms::arch::encode_log_softmax (arch.hpp:120-121). */
+int msb_log_softmax(const float* in, float* out, int rows, int V, void* stream);
+/* HOST function, as in the reference (arch.hpp:122-126, arch.mm:322-342): temperature + top-p sampling from
+ * msb_sample_topk's output copied to the host.  p_i = exp(v_i / T - lse); keeps the smallest prefix whose cumulative
+ * mass reaches top_p, renormalised; u in [0, 1).  Returns the token id (ids[0] when temperature <= 0 or k <= 1). */
+int msb_sample_top_p(const float* vals, const int* ids, int k, float lse, float temperature, float top_p, double u);
+
 /* ---------------------------------------------------------------- device memory for hosts without CUDA headers
  * What the reference's Device::alloc (zero-filled) and Buffer::cpu() (shared storage) become with separate device memory
  * (src/core/metal.hpp:11-40): allocation, blocking copies on a stream, and the fill dispatch of the layer code

@@ -39,6 +39,7 @@ struct Enc {              // src/core/metal.hpp:43-71
 inline void check(int rc, const char* what) {   // the reference's die() (src/kernels/quant.mm:34-37)
   if (rc != 0) { std::fprintf(stderr, "macseek_b200: %s failed: %s\n", what, msb_last_error()); std::abort(); }
 }
+[[noreturn]] inline void die(const char* msg) { std::fprintf(stderr, "macseek_b200: %s\n", msg); std::abort(); }
 
 namespace q {             // src/kernels/quant.hpp
 enum class QType : int { F32 = 0, F16 = 1, Q8_0 = 8, Q5_K = 13, Q6_K = 14, IQ2_XXS = 16, IQ1_S = 19, IQ4_NL = 20, BF16 = 30 };
@@ -173,7 +174,9 @@ inline void encode_moe_prefill(Enc& e, const MoePrefillArgs& a) {
 }  // namespace q
 
 namespace arch {          // src/kernels/arch.hpp:79-130 (router, rmsnorm, argmax)
-struct Scratch { Buffer router; int n_experts = 384; };   // router: msb_router_scratch_bytes(n_experts) bytes
+// router: msb_router_scratch_bytes(n_experts) bytes; sample (optional): msb_sample_scratch_bytes(max_rows) zeroed bytes
+// for the sampling calls (the reference's Scratch::sample_part / counters, arch.hpp:30-33)
+struct Scratch { Buffer router; int n_experts = 384; Buffer sample; int max_rows = 0; };
 inline void encode_router_fused(Enc& e, Buffer x, Buffer W, Buffer bias, Buffer ids, Buffer w, const Scratch& s,
                                 int dim = 5120, int k = 6, int score_fn = 0, float route_scale = 1.5f) {
   check(msb_router_fused((const float*)x.ptr(), (const float*)W.ptr(), (const float*)bias.ptr(), (int*)ids.ptr(),
@@ -209,6 +212,29 @@ inline void encode_argmax(Enc& e, Buffer logits, int rows, int V, Buffer out_idx
   for (int r = 0; r < rows; r++)
     check(msb_argmax((const float*)logits.ptr() + (size_t)r * V, V, (int*)out_idx.ptr() + r,
                      out_val.buf ? (float*)out_val.ptr() + r : nullptr, e.stream), "encode_argmax");
+}
+// arch.hpp:111-115 with the reference's argument list: greedy, or Gumbel-max sampling when temperature > 0
+inline void encode_argmax(Enc& e, Buffer logits, int rows, int V, Buffer out_idx, Buffer out_val, const Scratch& s,
+                          float temperature = 0.0f, uint64_t seed = 0) {
+  if (rows > s.max_rows) die("encode_argmax: rows beyond the scratch's max_rows");
+  check(msb_argmax_rows((const float*)logits.ptr(), rows, V, (int*)out_idx.ptr(), out_val.buf ? (float*)out_val.ptr() : nullptr,
+                        temperature, (unsigned long long)seed, s.sample.ptr(), s.sample.size, e.stream), "encode_argmax");
+}
+// arch.hpp:116-119
+inline void encode_topk(Enc& e, Buffer logits, int rows, int V, int k, float temperature, Buffer out_v, Buffer out_i,
+                        Buffer out_lse, const Scratch& s) {
+  if (rows > s.max_rows) die("encode_topk: rows beyond the scratch's max_rows");
+  check(msb_sample_topk((const float*)logits.ptr(), rows, V, k, temperature, (float*)out_v.ptr(), (int*)out_i.ptr(),
+                        (float*)out_lse.ptr(), s.sample.ptr(), s.sample.size, e.stream), "encode_topk");
+}
+// arch.hpp:120-121
+inline void encode_log_softmax(Enc& e, Buffer in, Buffer out, int rows, int V) {
+  check(msb_log_softmax((const float*)in.ptr(), (float*)out.ptr(), rows, V, e.stream), "encode_log_softmax");
+}
+// arch.hpp:122-126 (host function; vals / ids are host copies of encode_topk's output)
+inline uint32_t sample_top_p(const float* vals, const uint32_t* ids, int k, float lse, float temperature, float top_p,
+                             double u) {
+  return (uint32_t)msb_sample_top_p(vals, (const int*)ids, k, lse, temperature, top_p, u);
 }
 }  // namespace arch
 

@@ -123,3 +123,9 @@ lib.msb_hc_scratch_bytes.restype = C.c_size_t
 lib.msb_hc_scratch_bytes.argtypes = [_i]
 lib.msb_hc_step.argtypes = [_vp] * 10 + [_i, _i, _vp, C.c_size_t, _vp]
 lib.msb_compress.argtypes = [_vp] * 7 + [_i] * 6 + [_vp, _i, _vp, _vp]
+lib.msb_sample_scratch_bytes.restype = C.c_size_t
+lib.msb_sample_scratch_bytes.argtypes = [_i]
+lib.msb_argmax_rows.argtypes = [_vp, _i, _i, _vp, _vp, C.c_float, C.c_ulonglong, _vp, C.c_size_t, _vp]
+lib.msb_sample_topk.argtypes = [_vp, _i, _i, _i, C.c_float, _vp, _vp, _vp, _vp, C.c_size_t, _vp]
+lib.msb_log_softmax.argtypes = [_vp, _vp, _i, _i, _vp]
+lib.msb_sample_top_p.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_int), _i, C.c_float, C.c_float, C.c_float, C.c_double]

@@ -97,3 +97,40 @@ def encode_hc_step(e: Enc, h_in, h_out, x_sub, mix_prev, fn, scale, base, mix_ou
     _lib.check(_lib.lib.msb_hc_step(ptr(h_in), ptr(h_out), ptr(x_sub), ptr(mix_prev), ptr(fn), ptr(scale), ptr(base),
                                     ptr(mix_out), ptr(norm_w), ptr(x_out), dim, n, ptr(scratch),
                                     scratch.numel() * scratch.element_size(), e.handle))
+
+
+# ---------------------------------------------------------------------------------------------- sampling head
+SAMPLE_K = 64
+
+
+def sample_scratch(rows=1, device="cuda"):
+    """Zeroed scratch for encode_argmax_rows / encode_sample_topk (one per stream)."""
+    return torch.zeros(_lib.lib.msb_sample_scratch_bytes(rows) // 4 + 4, dtype=torch.int32, device=device)
+
+
+def encode_argmax_rows(e: Enc, logits, rows, V, out_idx, out_val, scratch, temperature=0.0, seed=0):
+    """Per-row argmax, ties -> lowest index; temperature > 0: Gumbel-max sampling keyed by seed (arch.hpp:111-115)."""
+    _lib.check(_lib.lib.msb_argmax_rows(ptr(logits), rows, V, ptr(out_idx), ptr(out_val), float(temperature),
+                                        int(seed) & 0xFFFFFFFFFFFFFFFF, ptr(scratch),
+                                        scratch.numel() * scratch.element_size(), e.handle))
+
+
+def encode_sample_topk(e: Enc, logits, rows, V, k, temperature, out_v, out_i, out_lse, scratch):
+    """Top-k (k <= 64) raw logits + ids per row and the full-row logsumexp(logits / temperature) (arch.hpp:116-119).
+    out_v f32 [rows][64], out_i int32 [rows][64], out_lse f32 [rows]."""
+    _lib.check(_lib.lib.msb_sample_topk(ptr(logits), rows, V, k, float(temperature), ptr(out_v), ptr(out_i), ptr(out_lse),
+                                        ptr(scratch), scratch.numel() * scratch.element_size(), e.handle))
+
+
+def encode_log_softmax(e: Enc, x, out, rows, V):
+    """out = x - logsumexp(x) per row; out may be x (arch.hpp:120-121)."""
+    _lib.check(_lib.lib.msb_log_softmax(ptr(x), ptr(out), rows, V, e.handle))
+
+
+def sample_top_p(vals, ids, k, lse, temperature, top_p, u):
+    """Host-side temperature + top-p pick from encode_sample_topk's output (arch.hpp:122-126): vals / ids are host
+    sequences of at least k entries."""
+    import ctypes as C
+    v = (C.c_float * k)(*[float(x) for x in vals[:k]])
+    i = (C.c_int * k)(*[int(x) for x in ids[:k]])
+    return int(_lib.lib.msb_sample_top_p(v, i, k, float(lse), float(temperature), float(top_p), float(u)))

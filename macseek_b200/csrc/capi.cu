@@ -58,6 +58,13 @@ int device_free(void* p);
 int copy_to_device(void* dst, const void* src, size_t bytes, cudaStream_t st);
 int copy_to_host(void* dst, const void* src, size_t bytes, cudaStream_t st);
 int fill_f32(float* p, float v, size_t n, cudaStream_t st);
+size_t sample_scratch_bytes(int rows);
+int argmax_rows(const float* logits, int rows, int V, int* out_idx, float* out_val, float temperature, uint64_t seed,
+                void* scratch, size_t scratch_bytes, cudaStream_t st);
+int sample_topk(const float* logits, int rows, int V, int k, float temperature, float* out_v, int* out_i, float* out_lse,
+                void* scratch, size_t scratch_bytes, cudaStream_t st);
+int log_softmax(const float* in, float* out, int rows, int V, cudaStream_t st);
+int sample_top_p(const float* vals, const int* ids, int k, float lse, float temperature, float top_p, double u);
 size_t hc_scratch_bytes(int n);
 int hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn, const float* scale,
             const float* base, float* mix_out, const float* norm_w, float* x_out, int D, int n, void* scratch,
@@ -412,6 +419,22 @@ int msb_device_free(void* p) { return device_free(p); }
 int msb_copy_to_device(void* dst, const void* src, size_t bytes, void* stream) { return copy_to_device(dst, src, bytes, (cudaStream_t)stream); }
 int msb_copy_to_host(void* dst, const void* src, size_t bytes, void* stream) { return copy_to_host(dst, src, bytes, (cudaStream_t)stream); }
 int msb_fill_f32(float* p, float value, size_t n, void* stream) { return fill_f32(p, value, n, (cudaStream_t)stream); }
+size_t msb_sample_scratch_bytes(int rows) { return sample_scratch_bytes(rows); }
+int msb_argmax_rows(const float* logits, int rows, int V, int* out_idx, float* out_val, float temperature,
+                    unsigned long long seed, void* scratch, size_t scratch_bytes, void* stream) {
+  return argmax_rows(logits, rows, V, out_idx, out_val, temperature, (uint64_t)seed, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+int msb_sample_topk(const float* logits, int rows, int V, int k, float temperature, float* out_v, int* out_i,
+                    float* out_lse, void* scratch, size_t scratch_bytes, void* stream) {
+  return sample_topk(logits, rows, V, k, temperature, out_v, out_i, out_lse, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+int msb_log_softmax(const float* in, float* out, int rows, int V, void* stream) {
+  return log_softmax(in, out, rows, V, (cudaStream_t)stream);
+}
+int msb_sample_top_p(const float* vals, const int* ids, int k, float lse, float temperature, float top_p, double u) {
+  if (!vals || !ids || k < 1) return -1;
+  return sample_top_p(vals, ids, k, lse, temperature, top_p, u);
+}
 
 size_t msb_hc_scratch_bytes(int n_tokens) { return hc_scratch_bytes(n_tokens); }
 int msb_hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mix_prev, const float* fn,

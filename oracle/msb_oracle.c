@@ -314,6 +314,62 @@ int orc_argmax(const float* x, int n) {
   for (int i = 1; i < n; i++) if (x[i] > x[b]) b = i;
   return b;
 }
+/* top-k descending, ties -> lower index (tests/ref/arch_ref.cpp:199-206: a partial sort under that order; here k
+ * selection passes over the row, the same result) */
+void orc_topk_desc(const float* x, int n, int k, float* v, uint32_t* idx) {
+  unsigned char* used = (unsigned char*)calloc((size_t)n, 1);
+  for (int r = 0; r < k; r++) {
+    int b = -1;
+    for (int i = 0; i < n; i++)
+      if (!used[i] && (b < 0 || x[i] > x[b])) b = i;
+    used[b] = 1; idx[r] = (uint32_t)b; v[r] = x[b];
+  }
+  free(used);
+}
+/* log(sum exp(scale x)) in double, max subtracted (tests/ref/arch_ref.cpp:208-214) */
+double orc_logsumexp(const float* x, int n, double scale) {
+  double m = -INFINITY;
+  for (int i = 0; i < n; i++) if (x[i] * scale > m) m = x[i] * scale;
+  double s = 0;
+  for (int i = 0; i < n; i++) s += exp(x[i] * scale - m);
+  return m + log(s);
+}
+/* y = x - logsumexp(x) (tests/ref/arch_ref.cpp:216-219) */
+void orc_log_softmax(const float* x, float* y, int n) {
+  const double l = orc_logsumexp(x, n, 1.0);
+  for (int i = 0; i < n; i++) y[i] = (float)(x[i] - l);
+}
+/* Gumbel(0,1) noise of element i under the 64-bit seed and the row (src/kernels/arch_sample.metal:15-26,68): two rounds
+ * of a 32-bit mixer, 24 bits -> u in (0,1), -log(-log u).  The reference has this on the GPU only; it is restated here
+ * so that a test can reproduce WHICH element wins, not only the distribution. */
+static uint32_t orc_hash32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+double orc_gumbel(uint32_t i, uint64_t seed, uint32_t row) {
+  const uint32_t s0 = (uint32_t)seed + row * 0x2545F491u, s1 = (uint32_t)(seed >> 32);
+  uint32_t x = orc_hash32(i * 0x9E3779B9u ^ s0);
+  x = orc_hash32(x ^ (s1 * 0x85EBCA6Bu + 0x632BE5ABu));
+  const double u = ((double)(x >> 8) + 0.5) * (1.0 / 16777216.0);
+  return -log(-log(u));
+}
+/* CPU top-p sampler over a top-k list (src/kernels/arch.mm:322-342) */
+uint32_t orc_sample_top_p(const float* vals, const uint32_t* ids, int k, float lse, float temperature, float top_p, double u) {
+  if (temperature <= 0.0f || k <= 1) return ids[0];
+  double pr[64], cum = 0.0, tot = 0.0, acc = 0.0;
+  int keep = k;
+  for (int i = 0; i < k; i++) {
+    pr[i] = exp((double)vals[i] / temperature - (double)lse);
+    cum += pr[i];
+    if (cum >= top_p) { keep = i + 1; break; }
+  }
+  for (int i = 0; i < keep; i++) tot += pr[i];
+  for (int i = 0; i < keep; i++) {
+    acc += pr[i];
+    if (u * tot < acc) return ids[i];
+  }
+  return ids[keep - 1];
+}
 void orc_rmsnorm(const float* x, const float* w, float* y, int dim, double eps) {
   double ss = 0;
   for (int i = 0; i < dim; i++) ss += (double)x[i] * x[i];

@@ -71,6 +71,12 @@ void orc_router(const float* logits, const float* bias, int E, int k, int score_
 void orc_route_lists(const int* ids, const float* w, int n, int k, int E, uint32_t* counts, uint32_t* offsets,
                      uint32_t* entry, uint32_t* tok, float* lw, uint32_t* slot_of);
 int orc_argmax(const float* x, int n);      /* ties -> lowest index, tests/ref/arch_ref.hpp:44 */
+void orc_topk_desc(const float* x, int n, int k, float* v, uint32_t* idx);      /* arch_ref.cpp:199-206 */
+double orc_logsumexp(const float* x, int n, double scale);                      /* arch_ref.cpp:208-214 */
+void orc_log_softmax(const float* x, float* y, int n);                          /* arch_ref.cpp:216-219 */
+double orc_gumbel(uint32_t i, uint64_t seed, uint32_t row);                     /* arch_sample.metal:15-26,68 */
+uint32_t orc_sample_top_p(const float* vals, const uint32_t* ids, int k, float lse, float temperature, float top_p,
+                          double u);                                            /* arch.mm:322-342 */
 /* tests/ref/arch_ref.cpp:77-82 */
 void orc_rmsnorm(const float* x, const float* w, float* y, int dim, double eps);
 

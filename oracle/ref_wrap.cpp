@@ -79,6 +79,10 @@ void msref_route_lists(const int* ids, const float* w, int n, uint32_t* counts, 
 
 // ref_arch::argmax / rmsnorm (tests/ref/arch_ref.cpp)
 int msref_argmax(const float* x, int n) { return ref_arch::argmax(x, n); }
+// ref_arch::topk / logsumexp / log_softmax (tests/ref/arch_ref.cpp:199-219)
+void msref_topk(const float* x, int n, int k, float* v, uint32_t* idx) { ref_arch::topk(x, n, k, v, idx); }
+double msref_logsumexp(const float* x, int n, double scale) { return ref_arch::logsumexp(x, n, scale); }
+void msref_log_softmax(const float* x, float* y, int n) { ref_arch::log_softmax(x, y, n); }
 void msref_rmsnorm(const float* x, const float* w, float* y, int dim, double eps) { ref_arch::rmsnorm(x, w, y, dim, eps); }
 
 // attnref::rope_table (tests/ref/attn_ref.cpp:34): [max_pos][32][2]

@@ -105,6 +105,13 @@ def main():
         for actq in (0, 1):
             ck, ik = ref.compress_tokens(ratio, ckv_in, cg_in if ratio > 1 else None, cn, wk, kn, actq)
             g["cmp_ckv_r%d_q%d" % (ratio, actq)], g["cmp_ikey_r%d_q%d" % (ratio, actq)] = ck, ik
+    # --- sampling head: top-k descending with ties, log-sum-exp at two scales, log-softmax (tests/ref/arch_ref.cpp:199-219)
+    sl = (3.0 * synth.hashed(3000, 12, 1.0)).astype(np.float32)
+    sl[[7, 1207, 2407]] = 20.0                                   # ties -> lower index first
+    g["smp_logits"] = sl
+    g["smp_topk_v"], g["smp_topk_i"] = ref.topk_desc(sl, 64)
+    g["smp_lse"] = np.array([ref.logsumexp(sl, 1.0), ref.logsumexp(sl, 1.0 / 0.7)], dtype=np.float64)
+    g["smp_log_softmax"] = ref.log_softmax(sl)
     out = os.path.join(HERE, "golden_ref.npz")
     np.savez_compressed(out, **g)
     print("wrote", out, os.path.getsize(out), "bytes,", len(g), "arrays")

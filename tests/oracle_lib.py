@@ -71,6 +71,14 @@ class Oracle:
         L.orc_router.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
         L.orc_route_lists.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6
         L.orc_argmax.argtypes = [C.c_void_p, C.c_int]
+        L.orc_topk_desc.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.orc_logsumexp.restype = C.c_double
+        L.orc_logsumexp.argtypes = [C.c_void_p, C.c_int, C.c_double]
+        L.orc_log_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.orc_gumbel.restype = C.c_double
+        L.orc_gumbel.argtypes = [C.c_uint32, C.c_uint64, C.c_uint32]
+        L.orc_sample_top_p.restype = C.c_uint32
+        L.orc_sample_top_p.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float, C.c_double]
         L.orc_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_double]
         L.orc_rope_table.argtypes = [C.c_int, C.c_int, C.c_void_p]
         for n in ("orc_round_e4m3", "orc_round_e2m1"):
@@ -163,6 +171,28 @@ class Oracle:
     def argmax(self, x):
         x = _f32(x)
         return self.lib.orc_argmax(_p(x), x.size)
+
+    def topk_desc(self, x, k):
+        x = _f32(x)
+        v, idx = np.empty(k, np.float32), np.empty(k, np.uint32)
+        self.lib.orc_topk_desc(_p(x), x.size, k, _p(v), _p(idx))
+        return v, idx
+
+    def logsumexp(self, x, scale=1.0):
+        x = _f32(x)
+        return self.lib.orc_logsumexp(_p(x), x.size, float(scale))
+
+    def log_softmax(self, x):
+        x = _f32(x); y = np.empty_like(x)
+        self.lib.orc_log_softmax(_p(x), _p(y), x.size)
+        return y
+
+    def gumbel(self, i, seed, row=0):
+        return self.lib.orc_gumbel(int(i), int(seed), int(row))
+
+    def sample_top_p(self, vals, ids, k, lse, temperature, top_p, u):
+        vals = _f32(vals); ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        return int(self.lib.orc_sample_top_p(_p(vals), _p(ids), k, lse, temperature, top_p, u))
 
     def rmsnorm(self, x, w, eps):
         x = _f32(x); y = np.empty_like(x)
@@ -304,6 +334,10 @@ class Ref:
         L.msref_sparse_attn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.msref_window_row.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.msref_argmax.argtypes = [C.c_void_p, C.c_int]
+        L.msref_topk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.msref_logsumexp.restype = C.c_double
+        L.msref_logsumexp.argtypes = [C.c_void_p, C.c_int, C.c_double]
+        L.msref_log_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.msref_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_double]
         self.threads = L.msref_hardware_threads()
 
@@ -385,6 +419,21 @@ class Ref:
     def argmax(self, x):
         x = _f32(x)
         return self.lib.msref_argmax(_p(x), x.size)
+
+    def topk_desc(self, x, k):
+        x = _f32(x)
+        v, idx = np.empty(k, np.float32), np.empty(k, np.uint32)
+        self.lib.msref_topk(_p(x), x.size, k, _p(v), _p(idx))
+        return v, idx
+
+    def logsumexp(self, x, scale=1.0):
+        x = _f32(x)
+        return self.lib.msref_logsumexp(_p(x), x.size, float(scale))
+
+    def log_softmax(self, x):
+        x = _f32(x); y = np.empty_like(x)
+        self.lib.msref_log_softmax(_p(x), _p(y), x.size)
+        return y
 
     def rmsnorm(self, x, w, eps):
         x = _f32(x); y = np.empty_like(x)

@@ -144,6 +144,34 @@ def test_compressor_golden(orc):
 
 
 # ---------------------------------------------------------------- against the reference code itself (when present)
+def test_sampling_golden(orc):
+    """top-k (ties -> lower index), log-sum-exp, log-softmax against the reference build's outputs; the top-p sampler's
+    structural properties (the reference has no stored vectors for it: tests/test_arch_sample.mm:120-135 checks
+    frequencies)."""
+    sl = G["smp_logits"]
+    v, i = orc.topk_desc(sl, 64)
+    assert np.array_equal(i, G["smp_topk_i"]) and np.array_equal(v.view(np.uint32), G["smp_topk_v"].view(np.uint32))
+    assert list(i[:3]) == [7, 1207, 2407]
+    assert abs(orc.logsumexp(sl, 1.0) - G["smp_lse"][0]) < 1e-12 and abs(orc.logsumexp(sl, 1 / 0.7) - G["smp_lse"][1]) < 1e-12
+    assert np.array_equal(orc.log_softmax(sl).view(np.uint32), G["smp_log_softmax"].view(np.uint32))
+    lse = orc.logsumexp(sl, 1 / 0.7)
+    p = np.exp(v.astype(np.float64) / 0.7 - lse)
+    keep = int(np.searchsorted(np.cumsum(p), 0.3) + 1)
+    N = 20000
+    cnt = np.zeros(64)
+    for it in range(N):
+        tok = orc.sample_top_p(v, i, 64, lse, 0.7, 0.3, (it + 0.5) / N)
+        pos = int(np.where(i == tok)[0][0])
+        assert pos < keep
+        cnt[pos] += 1
+    assert np.all(np.abs(cnt[:keep] / N - p[:keep] / p[:keep].sum()) < 1e-3)
+    assert orc.sample_top_p(v, i, 64, lse, 0.0, 0.3, 0.9) == i[0]           # temperature 0: greedy
+    # Gumbel noise: deterministic per (index, seed, row), different across rows, mean of Gumbel(0,1) = 0.5772
+    a = np.array([orc.gumbel(j, 0x1234567, 0) for j in range(20000)])
+    assert a[5] == orc.gumbel(5, 0x1234567, 0) and a[5] != orc.gumbel(5, 0x1234567, 1)
+    assert abs(a.mean() - 0.5772) < 0.03 and abs(a.var() - np.pi ** 2 / 6) < 0.1
+
+
 @pytest.mark.parametrize("t", ALL_TYPES)
 def test_dequant_vs_reference_1m(orc, ref, t):
     n = 1 << 20                                   # 1M elements per type, as tests/test_quant_ref.mm:97-99
