@@ -371,6 +371,41 @@ def moe_prefill_ep_case(n: int = 4096, check: bool = True, quiet: bool = False):
     return out
 
 
+def hc_cases():
+    """What the reference's real layer runs besides the benchmark step's calls: the hyper-connection step (twice per
+    layer: before the attention side and before the FFN side) and, on KV source layers, the compressor + index key.
+    Timed as graphs of 20 dependent launches at the benchmark's hidden size."""
+    from macseek_b200 import dec_layer as dl
+    D = 4096
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3)
+    rnd = lambda *shape, s=1.0: torch.empty(*shape, device="cuda").normal_(0, s, generator=gen)
+    h, x_sub, x_out = rnd(4 * D), rnd(D), torch.zeros(D, device="cuda")
+    fns = [rnd(24 * 4 * D, s=0.02) for _ in range(8)]                 # 1.5 MB each: rotate so that they come from HBM / L2 in turn
+    scale, base, norm_w = torch.tensor([0.7, 1.3, 0.9], device="cuda"), rnd(24), 1 + rnd(D, s=0.1)
+    mix_prev, mix_out = rnd(24).abs() + 0.05, torch.zeros(24, device="cuda")
+    scratch = arch.hc_scratch(1)
+
+    def hc(i):
+        arch.encode_hc_step(Enc(), h, h, x_sub, mix_prev, fns[i % 8], scale, base, mix_out, norm_w, x_out, D, scratch)
+    r = graph_time(hc)
+    print(f"hc_step dim {D}: median {r[0]:6.2f} us  min {r[1]:6.2f} us per launch", flush=True)
+    cfg = dl.DecConfig(n_layers=1, kv_len=4096)
+    sh = dl.attn_shape(cfg)
+    rope = torch.from_numpy(attn.make_rope_table(4200, True)).cuda()
+    st = attn.DecodeState(sh, 4096, rope, "cuda")
+    c_kv, c_gate, c_norm = rnd(sh.D), rnd(sh.D), 1 + rnd(sh.D, s=0.1)
+    wk = rnd(sh.index_dim * sh.D, s=0.05).to(torch.bfloat16)
+    k_norm = 1 + rnd(sh.index_dim, s=0.1)
+    for ratio in (1, 2):
+        state = torch.zeros(2 * ratio * sh.D, device="cuda")
+
+        def cmp(i, ratio=ratio, state=state):
+            attn.encode_compress(Enc(), st, c_kv, c_gate if ratio > 1 else None, c_norm, wk, k_norm, state, ratio, 100 + i, actq=False)
+        r = graph_time(cmp)
+        print(f"compress ratio {ratio} (row {sh.D}, index key {sh.index_dim}): median {r[0]:6.2f} us  min {r[1]:6.2f} us per launch", flush=True)
+
+
 def layer_stages(n_layers: int = 8, kv_len: int = 200000):
     """The decode layer in context: CUDA graphs of n_layers layers cut after the first k calls of each layer, k = 1 ..;
     the difference between consecutive cuts is what call k adds per layer with all overlaps as in the real step."""
@@ -454,7 +489,7 @@ def sweep():
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "moe_prefill_ep", "layer", "sweep"])
+    ap.add_argument("case", choices=["matvec", "moe", "attn", "gemm", "moe_prefill", "moe_prefill_ep", "layer", "hc", "sweep"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--groups", type=int, default=1)
@@ -478,6 +513,8 @@ def main():
         moe_cases(a.args[0] if a.args else "every", a.eager)
     elif a.case == "layer":
         layer_stages(8, a.kv_len)
+    elif a.case == "hc":
+        hc_cases()
     elif a.case == "moe_prefill":
         moe_prefill_case(a.n if a.n > 1 else 4096, a.eager, a.routing)
     elif a.case == "gemm":

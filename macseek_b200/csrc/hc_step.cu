@@ -3,17 +3,21 @@
 //   h_new[i]  = x_sub ? post[i] * x_sub + sum_j comb[j][i] * h_in[j] : h_in          (4 residual streams of width D)
 //   mix_out   = fn ? split + Sinkhorn( fn . h_new * rsqrt(mean(h_new^2) + 1e-20), scale, base ) : -
 //   x_out     = rmsnorm( sum_j pre[j] * h_new[j] ) * norm_w                          (pre / post / comb from mix_prev)
-// One launch per call, all tokens: grid (blocks over D, tokens).  Every block forms its slice of h_new and of the
-// pre-mixed vector and its partial sums of the 24 fn rows, of |h_new|^2 and of |x|^2; the block that finishes last (a
-// ticket per token) adds the partials in block order, runs the 4 x 4 Sinkhorn on 16 lanes and scales x_out.  HBM-bound
-// by the fn matrix (24 x 4 D floats; 1.6 MB at D = 4096), which is read exactly once.
+// One launch per call, all tokens: grid (blocks over D, tokens).  A block owns 32 consecutive columns d of the four
+// streams; its 8 warps share the 24 rows of fn (3 rows each), so that the 96 fn values a column needs are fetched by 8
+// threads at once instead of one after the other, and D / 32 blocks (128 at D = 4096) spread the 1.6 MB of fn over the
+// machine.  Every thread reads its column of h_in (and x_sub) BEFORE the block's barrier and only warp 0 writes h_out
+// afterwards, so h_out may alias h_in.  Each warp's shuffle sum is the block's partial of its rows; the block that
+// finishes last (a ticket per token) adds the partials in block order, runs the 4 x 4 Sinkhorn on 16 lanes and scales
+// x_out.  Bound by the latency of one pass over fn (24 x 4 D floats, read exactly once), not by its bytes.
 #include <algorithm>
 #include "msb_common.cuh"
 
 namespace msb {
 
 constexpr int kHcThreads = 256;
-constexpr int kHcMaxBlocks = 64;
+constexpr int kHcCols = 32;       // columns per block (one per lane); warp w takes fn rows [3 w, 3 w + 3)
+constexpr int kHcMaxBlocks = 512; // D <= 16384
 constexpr int kHcPart = 26;       // 24 fn rows, sum h_new^2, sum x^2
 
 struct HcParams {
@@ -37,67 +41,73 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-
 
 __global__ void __launch_bounds__(kHcThreads) hc_step_kernel(const HcParams p) {
   pdl_launch_dependents();
-  __shared__ float red[kHcPart][kHcThreads / 32];
   __shared__ float tot[kHcPart];
   __shared__ int is_last;
   const int tok = blockIdx.y, D = p.D, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* hin = p.h_in + (size_t)tok * 4 * D;
   float* hout = p.h_out + (size_t)tok * 4 * D;
   float* xo = p.x_out ? p.x_out + (size_t)tok * D : nullptr;
+  const int d = blockIdx.x * kHcCols + lane;
+  const bool live = d < D;
+  float h[4] = {0.f, 0.f, 0.f, 0.f}, hn[4], xs = 0.f, f[3][4];
+  // fn is a weight: requested before the dependency wait, it arrives while the previous kernel finishes
+  if (live && p.fn) {
+#pragma unroll
+    for (int r = 0; r < 3; r++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) f[r][i] = __ldg(p.fn + ((size_t)(3 * warp + r) * 4 + i) * D + d);
+  }
   pdl_wait();
   float mp[24];
 #pragma unroll
   for (int i = 0; i < 24; i++) mp[i] = p.mix_prev[(size_t)tok * 24 + i];
-  float acc[kHcPart];
-#pragma unroll
-  for (int i = 0; i < kHcPart; i++) acc[i] = 0.f;
-  for (int d = blockIdx.x * kHcThreads + tid; d < D; d += gridDim.x * kHcThreads) {
-    float h[4], hn[4];
+  if (live) {
 #pragma unroll
     for (int j = 0; j < 4; j++) h[j] = hin[(size_t)j * D + d];
-    if (p.x_sub) {
-      const float xs = p.x_sub[(size_t)tok * D + d];
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        float a = mp[4 + i] * xs;
-#pragma unroll
-        for (int j = 0; j < 4; j++) a = fmaf(mp[8 + 4 * j + i], h[j], a);
-        hn[i] = a;
-        hout[(size_t)i * D + d] = a;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; i++) hn[i] = h[i];
-    }
-    if (p.fn) {
-#pragma unroll
-      for (int r = 0; r < 24; r++) {
-        const float* f = p.fn + (size_t)r * 4 * D + d;
-        float a = acc[r];
-#pragma unroll
-        for (int i = 0; i < 4; i++) a = fmaf(__ldg(f + (size_t)i * D), hn[i], a);
-        acc[r] = a;
-      }
-      acc[24] += hn[0] * hn[0] + hn[1] * hn[1] + hn[2] * hn[2] + hn[3] * hn[3];
-    }
-    if (xo) {
-      const float x = mp[0] * hn[0] + mp[1] * hn[1] + mp[2] * hn[2] + mp[3] * hn[3];
-      xo[d] = x;                      // scaled by the finishing block
-      acc[25] += x * x;
-    }
+    if (p.x_sub) xs = p.x_sub[(size_t)tok * D + d];
   }
-  // block partials, fixed order
+  if (p.x_sub) {
 #pragma unroll
-  for (int i = 0; i < kHcPart; i++) {
-    const float v = warp_sum(acc[i]);
-    if (lane == 0) red[i][warp] = v;
+    for (int i = 0; i < 4; i++) {
+      float a = mp[4 + i] * xs;
+#pragma unroll
+      for (int j = 0; j < 4; j++) a = fmaf(mp[8 + 4 * j + i], h[j], a);
+      hn[i] = a;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i++) hn[i] = h[i];
   }
-  __syncthreads();
   float* part = p.part + ((size_t)tok * gridDim.x + blockIdx.x) * kHcPart;
-  if (tid < kHcPart) {
-    float v = 0.f;
-    for (int w = 0; w < kHcThreads / 32; w++) v += red[tid][w];
-    part[tid] = v;
+  if (p.fn) {
+#pragma unroll
+    for (int r = 0; r < 3; r++) {
+      float a = 0.f;
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) a = fmaf(f[r][i], hn[i], a);
+      }
+      a = warp_sum(a);
+      if (lane == 0) part[3 * warp + r] = a;
+    }
+  }
+  __syncthreads();                      // every warp has read its column of h_in: warp 0 may now overwrite it
+  if (warp == 0) {
+    float sq = 0.f, xq = 0.f;
+    if (live) {
+      if (p.x_sub) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) hout[(size_t)i * D + d] = hn[i];
+      }
+      sq = hn[0] * hn[0] + hn[1] * hn[1] + hn[2] * hn[2] + hn[3] * hn[3];
+      if (xo) {
+        const float x = mp[0] * hn[0] + mp[1] * hn[1] + mp[2] * hn[2] + mp[3] * hn[3];
+        xo[d] = x;                      // scaled by the finishing block
+        xq = x * x;
+      }
+    }
+    sq = warp_sum(sq); xq = warp_sum(xq);
+    if (lane == 0) { part[24] = sq; part[25] = xq; }
   }
   __threadfence();
   __syncthreads();
@@ -105,10 +115,14 @@ __global__ void __launch_bounds__(kHcThreads) hc_step_kernel(const HcParams p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  if (tid < kHcPart) {
+  // entry e = warp, warp + 8, ...: its lanes take the blocks' partials 32 at a time (loads in flight together), the
+  // shuffle tree then adds them in a fixed order
+  for (int e = warp; e < kHcPart; e += kHcThreads / 32) {
     double v = 0.0;
-    for (unsigned b = 0; b < gridDim.x; b++) v += (double)__ldcg(p.part + ((size_t)tok * gridDim.x + b) * kHcPart + tid);
-    tot[tid] = (float)v;
+    for (unsigned b = lane; b < gridDim.x; b += 32) v += (double)__ldcg(p.part + ((size_t)tok * gridDim.x + b) * kHcPart + e);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) tot[e] = (float)v;
   }
   if (tid == 0) p.ticket[tok] = 0;
   __syncthreads();
@@ -161,7 +175,8 @@ int hc_step(const float* h_in, float* h_out, const float* x_sub, const float* mi
   p.ticket = reinterpret_cast<unsigned*>(scratch);            // first n words: zero-filled by the caller once
   p.part = reinterpret_cast<float*>(scratch) + ((n + 15) & ~15);
   p.D = D; p.n = n; p.iters = 20; p.hc_eps = 1e-6f;
-  const int blocks = std::max(1, std::min(kHcMaxBlocks - 16, (D + kHcThreads - 1) / kHcThreads));
+  if (D > kHcMaxBlocks * kHcCols) return fail(kErrLimit, "hc_step: D %d beyond %d", D, kHcMaxBlocks * kHcCols);
+  const int blocks = (D + kHcCols - 1) / kHcCols;
   MSB_CUDA(launch_pdl(hc_step_kernel, dim3(blocks, n), dim3(kHcThreads), 0, st, p));
   MSB_LAUNCH_CHECK("hc_step_kernel");
   return kOk;
