@@ -326,6 +326,8 @@ int msb_device_free(void* p);
 int msb_copy_to_device(void* dst, const void* src, size_t bytes, void* stream);
 int msb_copy_to_host(void* dst, const void* src, size_t bytes, void* stream);
 int msb_fill_f32(float* p, float value, size_t n, void* stream);
+/* device -> device copy ordered on the stream (enqueue-only, capturable) */
+int msb_copy_device(void* dst, const void* src, size_t bytes, void* stream);
 
 /* ---------------------------------------------------------------- hyper-connection step and KV compressor
  * One sublayer boundary of the 4-stream residual -- ms::arch::encode_hc_step / HcStep (src/kernels/arch.hpp:44-77);

@@ -73,6 +73,7 @@ struct Options {          // the decode-relevant switches of attn.hpp:26-60
   bool actq = true;
   int max_pos = 262144;
   bool fused_combine = false;
+  int max_chunk = 1;      // tokens per encode_layer call: the state keeps one top-k list (and candidate list) per token of a chunk
 };
 
 struct Shape {
@@ -116,9 +117,9 @@ struct State {
   std::vector<int> slot_of_layer;          // [layers] -> slot (-1)
   // ---- scratch / per-token work buffers
   Buffer dec_scores, dec_bscores, q_prep, w_prep, topk_scratch, sparse_scratch;
-  std::vector<Buffer> topk;                // per index source layer: int [topk] (the current shared top-k)
+  std::vector<Buffer> topk;                // per index source layer: int [max_chunk][topk], row t = token t of the current chunk
   std::vector<int> topk_of_layer;          // [layers] -> index into topk (-1)
-  Buffer cand_list;                        // int [cand_blocks]
+  Buffer cand_list;                        // int [max_chunk][cand_blocks]
   bool is_kv_src(int L) const { return roles.kv_source[L] == L; }
   bool is_index_src(int L) const { return roles.index_source[L] == L; }
   bool uses_candidates(int L) const { return roles.cand_source >= 0 && L > roles.cand_source && is_index_src(L); }
@@ -189,7 +190,7 @@ inline void init(State& s, const Options& o, const Shape& sh, const Roles& roles
     }
     if (s.is_index_src(l)) {
       s.topk_of_layer[l] = (int)s.topk.size();
-      s.topk.push_back(dev.alloc((size_t)sh.topk * 4, "topk"));
+      s.topk.push_back(dev.alloc((size_t)std::max(1, o.max_chunk) * sh.topk * 4, "topk"));
     }
   }
   const int n_max = max_cap + kRowPad;
@@ -199,7 +200,7 @@ inline void init(State& s, const Options& o, const Shape& sh, const Roles& roles
   s.w_prep = dev.alloc((size_t)sh.index_heads * 4, "w_prep");
   s.topk_scratch = dev.alloc(msb_topk_scratch_bytes(n_max), "topk_scratch");
   s.sparse_scratch = dev.alloc(msb_sparse_scratch_bytes(sh.window + sh.topk, sh.heads, sh.D), "sparse_scratch");
-  s.cand_list = dev.alloc((size_t)sh.cand_blocks * 4, "cand_list");
+  s.cand_list = dev.alloc((size_t)std::max(1, o.max_chunk) * sh.cand_blocks * 4, "cand_list");
 }
 inline void init(State& s, const Options& o) { init(s, o, Shape{}, Roles::reference()); }
 
@@ -211,12 +212,12 @@ inline void reset(State& s, void* stream = nullptr) {
     check(msb_fill_f32((float*)s.cst[i].ptr(), 0.f, half, stream), "reset");
     check(msb_fill_f32((float*)s.cst[i].ptr() + half, -INFINITY, half, stream), "reset");
   }
-  std::vector<int> none((size_t)std::max(s.shape.topk, s.shape.cand_blocks), -1);
-  for (auto& t : s.topk) upload(t, none.data(), (size_t)s.shape.topk * 4, stream);
-  upload(s.cand_list, none.data(), (size_t)s.shape.cand_blocks * 4, stream);
+  std::vector<int> none((size_t)std::max(1, s.opt.max_chunk) * std::max(s.shape.topk, s.shape.cand_blocks), -1);
+  for (auto& t : s.topk) upload(t, none.data(), t.size, stream);
+  upload(s.cand_list, none.data(), s.cand_list.size, stream);
 }
 
-struct LayerIO {          // attn.hpp:112-127; all f32, n = 1
+struct LayerIO {          // attn.hpp:112-127; all f32; n tokens: every per-token buffer is [n][...]
   int layer = 0;
   Buffer q, kv, kv_norm, sinks, out;
   Buffer c_kv, c_gate, c_norm, idx_wk, idx_knorm;    // kv source layers
@@ -224,29 +225,41 @@ struct LayerIO {          // attn.hpp:112-127; all f32, n = 1
 };
 using StageHook = std::function<void(int stage)>;
 
-// ---- building blocks, decode (n == 1) ----
+// ---- building blocks.  n == 1 is the decode path.  n > 1 (a prefill chunk at positions start .. start + n - 1) runs
+// the SAME kernels token by token in position order -- causal by construction and bit-identical to n decode calls, the
+// first correct form of the reference's chunked prefill side (attn.mm:292-417,446-516: tiled indexer GEMM, running top-k
+// merge, two-pass sparse attention), which is not built as batched kernels.  Because the window is a ring of `window`
+// rows, a chunk must be processed through encode_layer (window row, compressor, index, attention per token in turn);
+// the single building blocks accept n > 1 only where token order alone keeps them correct.
+inline Buffer tok_row(const Buffer& b, int t, size_t row_floats) { return b.buf ? b.sub((size_t)t * row_floats * 4, row_floats * 4) : b; }
 inline void encode_kv_window(Enc& e, State& s, int layer, const Buffer& kv, const Buffer& norm_w, int start, int n) {
-  if (n != 1) check(MSB_E_ARG, "encode_kv_window: decode only (n == 1)");
-  char* row = (char*)s.win[layer].ptr() + (size_t)(start % s.shape.window) * s.shape.D * s.elem_bytes();
-  check(msb_kv_window((const float*)kv.ptr(), (const float*)norm_w.ptr(), s.rope_row(layer, start), s.opt.actq, s.shape.D,
-                      s.shape.elem_type, row, e.stream), "encode_kv_window");
+  if (n > s.shape.window) check(MSB_E_ARG, "encode_kv_window: more tokens than window rows (use encode_layer for a chunk)");
+  for (int t = 0; t < n; t++) {
+    char* row = (char*)s.win[layer].ptr() + (size_t)((start + t) % s.shape.window) * s.shape.D * s.elem_bytes();
+    check(msb_kv_window((const float*)tok_row(kv, t, s.shape.D).ptr(), (const float*)norm_w.ptr(), s.rope_row(layer, start + t),
+                        s.opt.actq, s.shape.D, s.shape.elem_type, row, e.stream), "encode_kv_window");
+  }
 }
 inline void encode_compress(Enc& e, State& s, int layer, const LayerIO& io, int start, int n, bool /*barrier_after*/ = true) {
-  if (n != 1) check(MSB_E_ARG, "encode_compress: decode only (n == 1)");
   const int slot = s.slot_of_layer[layer];
   if (slot < 0) check(MSB_E_ARG, "encode_compress: not a KV source layer");
   const int r = std::max(1, s.roles.ratio[layer]);
-  check(msb_compress((const float*)io.c_kv.ptr(), (const float*)io.c_gate.ptr(), (const float*)io.c_norm.ptr(),
-                     io.idx_wk.ptr(), (const float*)io.idx_knorm.ptr(), s.rope_row(layer, (start / r) * r),
-                     (float*)s.cst[slot].ptr(), r, start, s.opt.actq, s.shape.D, s.shape.index_dim, s.shape.elem_type,
-                     s.ckv[slot].ptr(), s.shape.key_type, s.ikey[slot].ptr(), e.stream), "encode_compress");
+  for (int t = 0; t < n; t++) {
+    const int pos = start + t;
+    check(msb_compress((const float*)tok_row(io.c_kv, t, s.shape.D).ptr(), (const float*)tok_row(io.c_gate, t, s.shape.D).ptr(),
+                       (const float*)io.c_norm.ptr(), io.idx_wk.ptr(), (const float*)io.idx_knorm.ptr(),
+                       s.rope_row(layer, (pos / r) * r), (float*)s.cst[slot].ptr(), r, pos, s.opt.actq, s.shape.D,
+                       s.shape.index_dim, s.shape.elem_type, s.ckv[slot].ptr(), s.shape.key_type, s.ikey[slot].ptr(), e.stream),
+          "encode_compress");
+  }
 }
 // Index decode of an index source layer: scores of the source's keys below (pos + 1) / ratio, exact top-k into the
 // layer's list; the candidate source also leaves its top candidate blocks in cand_list, and later index sources score
 // only those blocks (attn.mm:222-290).
 inline void encode_index_decode(Enc& e, State& s, int layer, const Buffer& iq, const Buffer& iw, int pos,
-                                const StageHook& hook = {}) {
+                                const StageHook& hook = {}, int row = 0) {
   const Shape& sh = s.shape;
+  if (row < 0 || row >= std::max(1, s.opt.max_chunk)) check(MSB_E_ARG, "encode_index_decode: chunk row beyond Options::max_chunk");
   const int src = s.roles.kv_source[layer], slot = src >= 0 ? s.slot_of_layer[src] : -1, ti = s.topk_of_layer[layer];
   if (slot < 0 || ti < 0) check(MSB_E_ARG, "encode_index_decode: not an index source layer");
   const int r = std::max(1, s.roles.ratio[layer]), len = (pos + 1) / r;
@@ -254,21 +267,22 @@ inline void encode_index_decode(Enc& e, State& s, int layer, const Buffer& iq, c
   if (s.uses_candidates(layer)) {
     const int nb = (len + sh.cand_bs - 1) / sh.cand_bs;
     check(msb_index_decode_list(sh.key_type, s.ikey[slot].ptr(), len, (const float*)iq.ptr(), (const float*)iw.ptr(), cs,
-                                s.opt.actq, sh.index_heads, sh.topk, (const int*)s.cand_list.ptr(), std::min(nb, sh.cand_blocks),
-                                (float*)s.q_prep.ptr(), (float*)s.w_prep.ptr(), (float*)s.dec_scores.ptr(),
-                                (int*)s.topk[ti].ptr(), s.topk_scratch.ptr(), s.topk_scratch.size, e.stream),
+                                s.opt.actq, sh.index_heads, sh.topk, (const int*)s.cand_list.ptr() + (size_t)row * sh.cand_blocks,
+                                std::min(nb, sh.cand_blocks), (float*)s.q_prep.ptr(), (float*)s.w_prep.ptr(),
+                                (float*)s.dec_scores.ptr(), (int*)s.topk[ti].ptr() + (size_t)row * sh.topk, s.topk_scratch.ptr(),
+                                s.topk_scratch.size, e.stream),
           "encode_index_decode (candidates)");
   } else {
     check(msb_index_decode(sh.key_type, s.ikey[slot].ptr(), len, (const float*)iq.ptr(), (const float*)iw.ptr(), cs,
                            s.opt.actq, sh.index_heads, sh.topk, (float*)s.q_prep.ptr(), (float*)s.w_prep.ptr(),
-                           (float*)s.dec_scores.ptr(), (int*)s.topk[ti].ptr(), s.topk_scratch.ptr(), s.topk_scratch.size, 0,
-                           e.stream), "encode_index_decode");
+                           (float*)s.dec_scores.ptr(), (int*)s.topk[ti].ptr() + (size_t)row * sh.topk, s.topk_scratch.ptr(),
+                           s.topk_scratch.size, 0, e.stream), "encode_index_decode");
     if (layer == s.roles.cand_source && len > 0) {
       const int nb = (len + sh.cand_bs - 1) / sh.cand_bs;
       check(msb_block_max((const float*)s.dec_scores.ptr(), len, sh.cand_bs, (float*)s.dec_bscores.ptr(), e.stream),
             "encode_index_decode (block maxima)");
-      check(msb_topk((const float*)s.dec_bscores.ptr(), nb, sh.cand_blocks, (int*)s.cand_list.ptr(), s.topk_scratch.ptr(),
-                     s.topk_scratch.size, 0, e.stream), "encode_index_decode (candidate blocks)");
+      check(msb_topk((const float*)s.dec_bscores.ptr(), nb, sh.cand_blocks, (int*)s.cand_list.ptr() + (size_t)row * sh.cand_blocks,
+                     s.topk_scratch.ptr(), s.topk_scratch.size, 0, e.stream), "encode_index_decode (candidate blocks)");
     }
   }
   if (hook) { hook(0); hook(1); }
@@ -276,27 +290,42 @@ inline void encode_index_decode(Enc& e, State& s, int layer, const Buffer& iq, c
 // Sparse attention of the token at `start` over the layer's window ring and the rows its index source selected
 // (attn.hpp:128-129).  fused_combine is accepted for source compatibility: the result is the same either way.
 inline void encode_sparse(Enc& e, State& s, int layer, const Buffer& q, const Buffer& sinks, const Buffer& out, int start,
-                          int n, bool /*fused_combine*/ = false, const StageHook& hook = {}) {
-  if (n != 1) check(MSB_E_ARG, "encode_sparse: decode only (n == 1)");
+                          int n, bool /*fused_combine*/ = false, const StageHook& hook = {}, int row = 0) {
+  if (n != 1) check(MSB_E_ARG, "encode_sparse: one token per call (a chunk goes through encode_layer: the selected rows are per token)");
+  if (row < 0 || row >= std::max(1, s.opt.max_chunk)) check(MSB_E_ARG, "encode_sparse: chunk row beyond Options::max_chunk");
   const Shape& sh = s.shape;
   const int n_win = start + 1 < sh.window ? start + 1 : sh.window;
   const int src = s.roles.kv_source[layer], slot = src >= 0 ? s.slot_of_layer[src] : -1;
   const int isrc = s.roles.index_source[layer], ti = isrc >= 0 ? s.topk_of_layer[isrc] : -1;
   const bool sel = slot >= 0 && ti >= 0;
   check(msb_sparse_decode((const float*)q.ptr(), s.rope_row(layer, start), (const float*)sinks.ptr(), sh.elem_type,
-                          s.win[layer].ptr(), n_win, sel ? s.ckv[slot].ptr() : nullptr, sel ? (const int*)s.topk[ti].ptr() : nullptr,
+                          s.win[layer].ptr(), n_win, sel ? s.ckv[slot].ptr() : nullptr,
+                          sel ? (const int*)s.topk[ti].ptr() + (size_t)row * sh.topk : nullptr,
                           sel ? sh.topk : 0, sh.heads, sh.D, (float*)out.ptr(), s.sparse_scratch.ptr(), s.sparse_scratch.size,
                           e.stream), "encode_sparse");
   if (hook) { hook(2); hook(3); }
 }
-// The whole attention side of one layer for the token at `start` (attn.hpp:113): window row, compressor on KV source
-// layers, index decode on index source layers, sparse attention.
+// encode_index_prefill (attn.hpp:122): the top-k list of every token of the chunk, row t of the source's list buffer.
+inline void encode_index_prefill(Enc& e, State& s, int layer, const Buffer& iq, const Buffer& iw, int start, int n) {
+  const Shape& sh = s.shape;
+  for (int t = 0; t < n; t++)
+    encode_index_decode(e, s, layer, tok_row(iq, t, (size_t)sh.index_heads * sh.index_dim), tok_row(iw, t, sh.index_heads), start + t, {}, t);
+}
+// The whole attention side of one layer for the tokens at start .. start + n - 1 (attn.hpp:113): per token, in position
+// order, window row, compressor on KV source layers, index decode on index source layers, sparse attention.
 inline void encode_layer(Enc& e, State& s, const LayerIO& io, int start, int n) {
-  if (n != 1) check(MSB_E_ARG, "encode_layer: decode only (n == 1)");
-  encode_kv_window(e, s, io.layer, io.kv, io.kv_norm, start, 1);
-  if (s.is_kv_src(io.layer)) encode_compress(e, s, io.layer, io, start, 1);
-  if (s.is_index_src(io.layer)) encode_index_decode(e, s, io.layer, io.idx_q, io.idx_w, start);
-  encode_sparse(e, s, io.layer, io.q, io.sinks, io.out, start, 1);
+  const Shape& sh = s.shape;
+  if (n > std::max(1, s.opt.max_chunk)) check(MSB_E_ARG, "encode_layer: chunk longer than Options::max_chunk");
+  for (int t = 0; t < n; t++) {
+    LayerIO one = io;
+    one.q = tok_row(io.q, t, (size_t)sh.heads * sh.D); one.kv = tok_row(io.kv, t, sh.D); one.out = tok_row(io.out, t, (size_t)sh.heads * sh.D);
+    one.c_kv = tok_row(io.c_kv, t, sh.D); one.c_gate = tok_row(io.c_gate, t, sh.D);
+    one.idx_q = tok_row(io.idx_q, t, (size_t)sh.index_heads * sh.index_dim); one.idx_w = tok_row(io.idx_w, t, sh.index_heads);
+    encode_kv_window(e, s, io.layer, one.kv, io.kv_norm, start + t, 1);
+    if (s.is_kv_src(io.layer)) encode_compress(e, s, io.layer, one, start + t, 1);
+    if (s.is_index_src(io.layer)) encode_index_decode(e, s, io.layer, one.idx_q, one.idx_w, start + t, {}, t);
+    encode_sparse(e, s, io.layer, one.q, io.sinks, one.out, start + t, 1, false, {}, t);
+  }
 }
 
 }  // namespace attn

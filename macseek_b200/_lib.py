@@ -129,3 +129,4 @@ lib.msb_argmax_rows.argtypes = [_vp, _i, _i, _vp, _vp, C.c_float, C.c_ulonglong,
 lib.msb_sample_topk.argtypes = [_vp, _i, _i, _i, C.c_float, _vp, _vp, _vp, _vp, C.c_size_t, _vp]
 lib.msb_log_softmax.argtypes = [_vp, _vp, _i, _i, _vp]
 lib.msb_sample_top_p.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_int), _i, C.c_float, C.c_float, C.c_float, C.c_double]
+lib.msb_copy_device.argtypes = [_vp, _vp, C.c_size_t, _vp]

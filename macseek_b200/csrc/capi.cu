@@ -58,6 +58,7 @@ int device_free(void* p);
 int copy_to_device(void* dst, const void* src, size_t bytes, cudaStream_t st);
 int copy_to_host(void* dst, const void* src, size_t bytes, cudaStream_t st);
 int fill_f32(float* p, float v, size_t n, cudaStream_t st);
+int copy_device(void* dst, const void* src, size_t bytes, cudaStream_t st);
 size_t sample_scratch_bytes(int rows);
 int argmax_rows(const float* logits, int rows, int V, int* out_idx, float* out_val, float temperature, uint64_t seed,
                 void* scratch, size_t scratch_bytes, cudaStream_t st);
@@ -419,6 +420,7 @@ int msb_device_free(void* p) { return device_free(p); }
 int msb_copy_to_device(void* dst, const void* src, size_t bytes, void* stream) { return copy_to_device(dst, src, bytes, (cudaStream_t)stream); }
 int msb_copy_to_host(void* dst, const void* src, size_t bytes, void* stream) { return copy_to_host(dst, src, bytes, (cudaStream_t)stream); }
 int msb_fill_f32(float* p, float value, size_t n, void* stream) { return fill_f32(p, value, n, (cudaStream_t)stream); }
+int msb_copy_device(void* dst, const void* src, size_t bytes, void* stream) { return copy_device(dst, src, bytes, (cudaStream_t)stream); }
 size_t msb_sample_scratch_bytes(int rows) { return sample_scratch_bytes(rows); }
 int msb_argmax_rows(const float* logits, int rows, int V, int* out_idx, float* out_val, float temperature,
                     unsigned long long seed, void* scratch, size_t scratch_bytes, void* stream) {

@@ -37,6 +37,12 @@ int copy_to_host(void* dst, const void* src, size_t bytes, cudaStream_t st) {
   MSB_CUDA(cudaStreamSynchronize(st));
   return kOk;
 }
+int copy_device(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+  if (bytes == 0) return kOk;
+  if (!dst || !src) return fail(kErrArg, "copy_device: null pointer");
+  MSB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st));
+  return kOk;
+}
 int fill_f32(float* p, float v, size_t n, cudaStream_t st) {
   if (n == 0) return kOk;
   if (!p) return fail(kErrArg, "fill_f32: null pointer");
