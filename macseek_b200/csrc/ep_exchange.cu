@@ -3,10 +3,13 @@
 //
 // The reference model sums the ranks' routed outputs with an all-reduce (reference/inference/model.py:903-904).  Here
 // the MoE down launch of every rank stores its partial row sums straight into slot `rank` of EVERY rank's exchange
-// buffer (peer-mapped memory over NVLink, plain st.global) and then raises flag `rank` there; ep_combine_kernel on each
-// rank waits (bounded) for the `world` flags of the current exchange and adds the slots in rank order, so all ranks
-// compute bit-identical sums.  Slots and flags are double-buffered by the parity of the rank's epoch counter: a rank
-// can run at most one exchange ahead of a peer, because finishing exchange k needs every peer's flag k.
+// buffer (peer-mapped memory over NVLink, plain st.global); each of its blocks then adds 1, with release semantics at
+// system scope, to the arrival counter of the current exchange in every rank's buffer.  ep_combine_kernel on each rank
+// waits (bounded) until world x blocks_per_launch arrivals are in, adds the slots in rank order -- so all ranks compute
+// bit-identical sums -- zeroes the counter and advances the epoch.  Slots and counters are double-buffered by the
+// parity of the rank's epoch counter: a rank can run at most one exchange ahead of a peer, because finishing exchange k
+// needs every peer's arrivals of k, and a peer writes parity p again only after this rank's combine of the previous
+// exchange on p has finished (it needs this rank's contribution to the exchange in between).
 #include <algorithm>
 #include <cstring>
 #include "moe_decode_params.cuh"
@@ -20,12 +23,13 @@ struct EpCombineParams {
   uint8_t* base;       // this rank's exchange buffer
   float* h;            // [dim], h += sum over ranks of their partial
   int world, dim;
+  unsigned expected;   // arrivals of one exchange: world x blocks of a down launch
   int* status;
-  unsigned* ticket;
   long long wait_cycles;
 };
 
-__global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p) {
+// One block: no ticket, no second grid-wide step.  1024 threads x 4 elements cover dim 4096 in one pass.
+__global__ void __launch_bounds__(1024) ep_combine_kernel(const EpCombineParams p) {
   pdl_launch_dependents();
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
@@ -33,18 +37,18 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p
   __syncthreads();
   const unsigned E = *reinterpret_cast<volatile unsigned*>(p.base);
   const int par = (int)(E & 1u);
-  if (threadIdx.x < p.world) {
-    const unsigned* flag = reinterpret_cast<const unsigned*>(p.base + kEpFlagsOff) + par * kMaxEpWorld + threadIdx.x;
+  unsigned* cnt = reinterpret_cast<unsigned*>(p.base + kEpFlagsOff) + par * kMaxEpWorld;
+  if (threadIdx.x == 0) {
     // a device-side failure recorded earlier means a partial may never arrive: do not wait again
     bool ok = *reinterpret_cast<volatile int*>(p.status) == 0;
     if (ok) {
       const long long t0 = clock64();
       for (;;) {
         unsigned v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (v == E + 1u) break;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        if (v == p.expected) break;
         if (clock64() - t0 > p.wait_cycles) { ok = false; atomicCAS(p.status, 0, kDevPeerWait); break; }
-        __nanosleep(64);
+        __nanosleep(32);
       }
     }
     if (!ok) failed = 1;
@@ -52,37 +56,44 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p
   __syncthreads();
   if (!failed) {
     const float* slots = reinterpret_cast<const float*>(p.base + kEpSlotsOff) + (size_t)par * p.world * p.dim;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.dim; i += gridDim.x * blockDim.x) {
-      float v = p.h[i];
-      for (int r = 0; r < p.world; r++) v += __ldcg(slots + (size_t)r * p.dim + i);     // rank order on every rank
-      p.h[i] = v;
+    for (int i = threadIdx.x * 4; i < p.dim; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(p.h + i);
+      float4 s[kMaxEpWorld];
+#pragma unroll
+      for (int r = 0; r < kMaxEpWorld; r++)
+        if (r < p.world) s[r] = __ldcg(reinterpret_cast<const float4*>(slots + (size_t)r * p.dim + i));
+#pragma unroll
+      for (int r = 0; r < kMaxEpWorld; r++)          // rank order on every rank
+        if (r < p.world) { v.x += s[r].x; v.y += s[r].y; v.z += s[r].z; v.w += s[r].w; }
+      *reinterpret_cast<float4*>(p.h + i) = v;
     }
   }
-  // the last block to finish advances the epoch (every block has read E by then); a failed exchange advances it too,
-  // so that the ranks' parities stay aligned if the caller clears the failure and carries on
+  // the counter goes back to zero for the next exchange on this parity and the epoch advances; a failed exchange does
+  // both too, so that the ranks' parities stay aligned if the caller clears the failure and carries on
   __syncthreads();
   if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile unsigned*>(cnt) = 0u;
+    *reinterpret_cast<volatile unsigned*>(p.base) = E + 1u;
     __threadfence();
-    if (atomicAdd(p.ticket, 1u) == gridDim.x - 1) {
-      *p.ticket = 0;
-      *reinterpret_cast<volatile unsigned*>(p.base) = E + 1u;
-      __threadfence();
-    }
   }
 }
 
 int ep_combine(uint8_t* const* base, int world, int rank, float* h, int dim, cudaStream_t st) {
   if (world < 1 || world > kMaxEpWorld || rank < 0 || rank >= world) return fail(kErrArg, "ep_combine: bad world %d / rank %d", world, rank);
-  if (!base || !base[rank] || !h || dim <= 0) return fail(kErrArg, "ep_combine: null pointer or bad dim");
+  if (!base || !base[rank] || !h || dim <= 0 || dim % 4) return fail(kErrArg, "ep_combine: null pointer or bad dim");
+  if (reinterpret_cast<uintptr_t>(h) & 15) return fail(kErrArg, "ep_combine: h must be 16-byte aligned");
   Tables tb;
   int rc = get_tables(&tb);
   if (rc) return rc;
+  int dev = 0, sms = 0;
+  MSB_CUDA(cudaGetDevice(&dev));
+  MSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   EpCombineParams p;
   p.base = base[rank]; p.h = h; p.world = world; p.dim = dim; p.status = tb.status;
-  p.ticket = reinterpret_cast<unsigned*>(tb.status) + 13;
+  // every rank's down launch runs moe_down_blocks(dim) blocks (identical GPUs), each of which arrives once
+  p.expected = (unsigned)world * (unsigned)moe_down_blocks(dim, sms);
   p.wait_cycles = g_peer_wait_cycles;
-  const int blocks = std::max(1, std::min(8, (dim + 1023) / 1024));
-  MSB_CUDA(launch_pdl(ep_combine_kernel, dim3(blocks), dim3(256), 0, st, p));
+  MSB_CUDA(launch_pdl(ep_combine_kernel, dim3(1), dim3(1024), 0, st, p));
   MSB_LAUNCH_CHECK("ep_combine_kernel");
   return kOk;
 }

@@ -411,7 +411,19 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   if (p.ep_world > 0) ep_epoch = *reinterpret_cast<volatile unsigned*>(p.ep_base[p.ep_rank]);
   const int ep_par = (int)(ep_epoch & 1u);
   if (warp == 0) resolve_local(p, hd, p.d_r != 0, true, lane);
-  quantize_x(p.h, xq[0], tid, kMoeNW * 32);
+  if (p.ep_world > 0) {
+    // expert parallel: only the h rows this rank will read (its resident experts' and its slice of the shared expert's)
+    // are quantised -- a fraction of the (n_routed + 1) x inter values, and this runs on every block before its first tile
+    bar_sync_named(1, kMoeNW * 32);
+    const int nl = hd->n_local, nu = nl * Ui + (p.d_s ? Us : 0), nr = p.n_routed;
+    const int* slot = hd->local_slot;
+    quantize_units(p.h, xq[0], tid, kMoeNW * 32, 1.f, nullptr, nu, [=](int v) {
+      const int j = v / Ui;
+      return j < nl ? slot[j] * Ui + (v - j * Ui) : nr * Ui + s_u0 + (v - nl * Ui);
+    });
+  } else {
+    quantize_x(p.h, xq[0], tid, kMoeNW * 32);
+  }
   __syncthreads();
   if (!luts_ok) return;
   const int n_local = hd->n_local;
@@ -485,23 +497,14 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
     tile_count++;
   }
   if (p.ep_world > 0 && warp == 0) {
-    // Every row of this block is stored.  The last block of the launch to get here publishes the partial: after a
-    // system-wide fence it writes E + 1 into flag ep_rank of every rank (release), which the combine kernels poll.
-    __threadfence_system();
+    // Every row of this block is stored (by lanes of this warp).  One release per block: after the warp barrier lane r
+    // adds 1 to the arrival counter of this exchange in rank r's buffer with release semantics at system scope, which
+    // orders the block's partial rows before it; the combine kernels wait for world x gridDim.x arrivals.  No fence
+    // stalls the SM and no block waits for another.
     __syncwarp();
-    unsigned last = 0;
-    if (lane == 0) {
-      unsigned* done = p.sched;
-      last = atomicAdd(done, 1u) == gridDim.x - 1;
-      if (last) *done = 0;
-    }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
-      __threadfence_system();
-      if (lane < p.ep_world) {
-        unsigned* flag = reinterpret_cast<unsigned*>(p.ep_base[lane] + kEpFlagsOff) + ep_par * kMaxEpWorld + p.ep_rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(ep_epoch + 1u) : "memory");
-      }
+    if (lane < p.ep_world) {
+      unsigned* cnt = reinterpret_cast<unsigned*>(p.ep_base[lane] + kEpFlagsOff) + ep_par * kMaxEpWorld;
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(1u) : "memory");
     }
   }
 }
@@ -591,8 +594,8 @@ int launch_down(MoeParams& p, int sms, int dev, cudaStream_t st) {
     static bool done[64] = {};
     int rc = set_smem(kern, dev, done);
     if (rc) return rc;
-    const int tiles = (p.dim + R - 1) / R;
-    MSB_CUDA(launch_pdl(kern, dim3(std::max(1, std::min(sms, tiles))), dim3((kMoeNW + 1) * 32), fixed + (size_t)stages * slot, st, p));
+    static_assert(R == 8, "moe_down_blocks() assumes 8-row tiles");
+    MSB_CUDA(launch_pdl(kern, dim3(moe_down_blocks(p.dim, sms)), dim3((kMoeNW + 1) * 32), fixed + (size_t)stages * slot, st, p));
     MSB_LAUNCH_CHECK("moe_down_kernel");
     return kOk;
   }

@@ -46,7 +46,7 @@ struct MoeParams {
   // takes the r-th slice, so the ranks' partial outputs add up to the whole shared expert.
   int s_lo, s_hi;
   // Expert-parallel exchange (ep_world > 0): the down launch does not touch y; it stores its row sums into slot ep_rank
-  // of every rank's exchange buffer (peer-mapped memory, plain stores) and its last block then raises flag ep_rank there.
+  // of every rank's exchange buffer (peer-mapped memory, plain stores); every block then adds 1 to the exchange's arrival counter there.
   int ep_world, ep_rank;
   uint8_t* ep_base[kMaxEpWorld];
   Tables tb;
@@ -54,9 +54,13 @@ struct MoeParams {
 
 // Exchange buffer of one rank (zero-filled at creation):
 //   +0    u32 epoch E: combines completed on this rank; slot / flag parity of the current exchange = E & 1
-//   +64   u32 flags[2][kMaxEpWorld]: flags[parity][r] == E + 1 once rank r's partial for this exchange is in place
+//   +64   u32 arrivals[2][kMaxEpWorld]: arrivals[parity][0] counts the down-launch blocks (of all ranks) whose partial
+//         rows of this exchange are in place; complete at world x moe_down_blocks(); zeroed again by the combine
 //   +256  f32 slots[2][world][dim]
 constexpr size_t kEpFlagsOff = 64, kEpSlotsOff = 256;
+// blocks of one moe_down_kernel launch (8-row tiles over dim, at most one block per SM): what each rank contributes to
+// an exchange's arrival count
+inline int moe_down_blocks(int dim, int sms) { const int tiles = (dim + 7) / 8; return tiles < sms ? (tiles > 1 ? tiles : 1) : sms; }
 inline size_t ep_exchange_bytes(int dim, int world) { return kEpSlotsOff + sizeof(float) * 2 * (size_t)world * dim; }
 
 size_t moe_decode_scratch_bytes(int inter, int max_routed);

@@ -105,24 +105,28 @@ __device__ __forceinline__ void load_xq(const XqSmem& x, int u, XRegs& r) {
   r.s = m.x; r.sx = m.y; r.sa = __float_as_int(m.z); r.sb = __float_as_int(m.w);
 }
 
-// Quantise x[0 .. 32U) (global or shared fp32, 16-byte aligned) into `q`, optionally scaling every element by
-// `mul` first (fused RMSNorm: mul = rstd, and by gain[i] when gain is given).  Called by all `nthreads` threads of the
-// block (a multiple of 32); 4 threads cooperate on one unit (8 elements each).  Caller synchronises afterwards.
-__device__ __forceinline__ void quantize_x(const float* __restrict__ x, const XqSmem& q, int tid, int nthreads,
-                                           float mul = 1.f, const float* __restrict__ gain = nullptr) {
+// Quantise units of x (global or shared fp32, 16-byte aligned; unit u = elements [32 u, 32 u + 32)) into `q`, optionally
+// scaling every element by `mul` first (fused RMSNorm: mul = rstd, and by gain[i] when gain is given).  Called by all
+// `nthreads` threads of the block (a multiple of 32); 4 threads cooperate on one unit (8 elements each).  The v-th unit
+// handled is unit_of(v), v = 0 .. n_units - 1 (a map lets a caller quantise only the rows it will read).  Caller
+// synchronises afterwards.
+template <class Map>
+__device__ __forceinline__ void quantize_units(const float* __restrict__ x, const XqSmem& q, int tid, int nthreads, float mul,
+                                               const float* __restrict__ gain, int n_units, Map unit_of) {
   const int lane4 = tid & 3;
-  for (int base = 0; base < q.U * 4; base += nthreads) {
+  for (int base = 0; base < n_units * 4; base += nthreads) {
     const int item = base + tid;           // one item = 8 elements
-    const bool live = item < q.U * 4;      // whole quads are live or not
-    const int u = item >> 2;
+    const bool live = item < n_units * 4;  // whole quads are live or not
+    const int u = live ? unit_of(item >> 2) : 0;
+    const int at = 32 * u + 8 * lane4;
     float v[8];
     if (live) {
-      const float4 a = *reinterpret_cast<const float4*>(x + 8 * item);
-      const float4 b = *reinterpret_cast<const float4*>(x + 8 * item + 4);
+      const float4 a = *reinterpret_cast<const float4*>(x + at);
+      const float4 b = *reinterpret_cast<const float4*>(x + at + 4);
       v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
       if (gain) {
-        const float4 ga = *reinterpret_cast<const float4*>(gain + 8 * item);
-        const float4 gb = *reinterpret_cast<const float4*>(gain + 8 * item + 4);
+        const float4 ga = *reinterpret_cast<const float4*>(gain + at);
+        const float4 gb = *reinterpret_cast<const float4*>(gain + at + 4);
         v[0] = v[0] * mul * ga.x; v[1] = v[1] * mul * ga.y; v[2] = v[2] * mul * ga.z; v[3] = v[3] * mul * ga.w;
         v[4] = v[4] * mul * gb.x; v[5] = v[5] * mul * gb.y; v[6] = v[6] * mul * gb.z; v[7] = v[7] * mul * gb.w;
       } else if (mul != 1.f) {
@@ -172,6 +176,10 @@ __device__ __forceinline__ void quantize_x(const float* __restrict__ x, const Xq
       }
     }
   }
+}
+__device__ __forceinline__ void quantize_x(const float* __restrict__ x, const XqSmem& q, int tid, int nthreads,
+                                           float mul = 1.f, const float* __restrict__ gain = nullptr) {
+  quantize_units(x, q, tid, nthreads, mul, gain, q.U, [](int v) { return v; });
 }
 
 __device__ __forceinline__ uint32_t lds_u32_a2(saddr_t p) { return lds_u16(p) | (lds_u16(p + 2) << 16); }
