@@ -154,9 +154,11 @@ int msb_moe_decode_ids_normed(const msb_moe_decode_args* a, const uint64_t* expe
  * msb_moe_decode_ep = msb_moe_decode_ids_normed (norm_in may be NULL) restricted to that shared-expert slice.  With
  * comm == NULL the partial output is accumulated into a.y as usual (combine it yourself, e.g. ncclAllReduce).  With a
  * comm, a.y is ignored: the down launch stores its partial into slot `rank` of every rank's exchange buffer (plain
- * stores to peer-mapped memory) and raises flag `rank` there.  msb_ep_combine then waits -- bounded, about one second of
- * SM clock, after which device status 3 is recorded and h is left unchanged -- for all `world` flags and adds the
- * partials to h in rank order (bit-identical on every rank).  Every rank must issue the same sequence of
+ * stores to peer-mapped memory) and every block of the launch counts itself, with a system-scope release, on this
+ * rank's arrival counter there.  msb_ep_combine then waits -- bounded, about one second of SM clock, after which device
+ * status 3 is recorded and h is left unchanged -- until the blocks of all `world` ranks have arrived (all ranks must be
+ * identical GPUs: a launch's block count is part of the protocol) and adds the partials to h in rank order
+ * (bit-identical on every rank).  Every rank must issue the same sequence of
  * msb_moe_decode_ep / msb_ep_combine pairs; the buffers are double-buffered by a device-side epoch, so the pair can be
  * captured in a CUDA graph and replayed.
  * Exchange buffers: msb_ep_exchange_bytes(dim, world) bytes from msb_ep_alloc (cudaMalloc + zero fill; not for use
@@ -169,7 +171,7 @@ int msb_moe_decode_ep(const msb_moe_decode_args* a, const uint64_t* expert_table
                       int shared_hi, const msb_ep_comm* comm, void* stream);
 size_t msb_ep_exchange_bytes(int dim, int world);
 int msb_ep_combine(const msb_ep_comm* comm, float* h, int dim, void* stream);
-/* Limit of msb_ep_combine's flag wait in SM clock cycles (default 2e9; <= 0 restores it).  Host-side setting, read at
+/* Limit of msb_ep_combine's arrival wait in SM clock cycles (default 2e9; <= 0 restores it).  Host-side setting, read at
  * launch. */
 void msb_set_peer_wait_cycles(long long cycles);
 int msb_ep_alloc(size_t bytes, void** out);

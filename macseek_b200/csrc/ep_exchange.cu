@@ -4,8 +4,8 @@
 // The reference model sums the ranks' routed outputs with an all-reduce (reference/inference/model.py:903-904).  Here
 // the MoE down launch of every rank stores its partial row sums straight into slot `rank` of EVERY rank's exchange
 // buffer (peer-mapped memory over NVLink, plain st.global); each of its blocks then adds 1, with release semantics at
-// system scope, to the arrival counter of the current exchange in every rank's buffer.  ep_combine_kernel on each rank
-// waits (bounded) until world x blocks_per_launch arrivals are in, adds the slots in rank order -- so all ranks compute
+// system scope, to its rank's arrival counter of the current exchange in every rank's buffer (one cache line per source
+// rank).  ep_combine_kernel on each rank waits (bounded) until every source rank's blocks have arrived, adds the slots in rank order -- so all ranks compute
 // bit-identical sums -- zeroes the counter and advances the epoch.  Slots and counters are double-buffered by the
 // parity of the rank's epoch counter: a rank can run at most one exchange ahead of a peer, because finishing exchange k
 // needs every peer's arrivals of k, and a peer writes parity p again only after this rank's combine of the previous
@@ -23,7 +23,7 @@ struct EpCombineParams {
   uint8_t* base;       // this rank's exchange buffer
   float* h;            // [dim], h += sum over ranks of their partial
   int world, dim;
-  unsigned expected;   // arrivals of one exchange: world x blocks of a down launch
+  unsigned expected;   // arrivals per source rank in one exchange: the blocks of a down launch
   int* status;
   long long wait_cycles;
 };
@@ -37,8 +37,8 @@ __global__ void __launch_bounds__(1024) ep_combine_kernel(const EpCombineParams 
   __syncthreads();
   const unsigned E = *reinterpret_cast<volatile unsigned*>(p.base);
   const int par = (int)(E & 1u);
-  unsigned* cnt = reinterpret_cast<unsigned*>(p.base + kEpFlagsOff) + par * kMaxEpWorld;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < p.world) {
+    unsigned* cnt = ep_arrivals(p.base, par, threadIdx.x);        // thread r waits for rank r's blocks
     // a device-side failure recorded earlier means a partial may never arrive: do not wait again
     bool ok = *reinterpret_cast<volatile int*>(p.status) == 0;
     if (ok) {
@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(1024) ep_combine_kernel(const EpCombineParams 
   // the counter goes back to zero for the next exchange on this parity and the epoch advances; a failed exchange does
   // both too, so that the ranks' parities stay aligned if the caller clears the failure and carries on
   __syncthreads();
+  if (threadIdx.x < p.world) *reinterpret_cast<volatile unsigned*>(ep_arrivals(p.base, par, threadIdx.x)) = 0u;
   if (threadIdx.x == 0) {
-    *reinterpret_cast<volatile unsigned*>(cnt) = 0u;
     *reinterpret_cast<volatile unsigned*>(p.base) = E + 1u;
     __threadfence();
   }
@@ -91,7 +91,7 @@ int ep_combine(uint8_t* const* base, int world, int rank, float* h, int dim, cud
   EpCombineParams p;
   p.base = base[rank]; p.h = h; p.world = world; p.dim = dim; p.status = tb.status;
   // every rank's down launch runs moe_down_blocks(dim) blocks (identical GPUs), each of which arrives once
-  p.expected = (unsigned)world * (unsigned)moe_down_blocks(dim, sms);
+  p.expected = (unsigned)moe_down_blocks(dim, sms);
   p.wait_cycles = g_peer_wait_cycles;
   MSB_CUDA(launch_pdl(ep_combine_kernel, dim3(1), dim3(1024), 0, st, p));
   MSB_LAUNCH_CHECK("ep_combine_kernel");

@@ -430,12 +430,12 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   const int row = warp >> 1, half = warp & 1;
   const int grp = lane / LPR, li = lane % LPR;   // LPR < 32: lane groups take alternate sources / unit runs
   uint32_t tile_count = 0;
-  if (p.ep_world > 0 && n_local == 0 && !p.d_s && warp == 0 && lane < R) {
+  if (p.ep_world > 0 && n_local == 0 && !p.d_s && warp == 0 && lane < p.ep_world) {
     // nothing of this token's MoE lives here: the exchange still needs this rank's (zero) partial
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-      const size_t at = ((size_t)(ep_par * p.ep_world + p.ep_rank)) * p.dim + (size_t)t * R + lane;
-      if (t * R + lane < p.dim)
-        for (int r = 0; r < p.ep_world; r++) reinterpret_cast<float*>(p.ep_base[r] + kEpSlotsOff)[at] = 0.f;
+      float* dst = reinterpret_cast<float*>(p.ep_base[lane] + kEpSlotsOff) + ((size_t)(ep_par * p.ep_world + p.ep_rank)) * p.dim + (size_t)t * R;
+      reinterpret_cast<float4*>(dst)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
   for (;;) {
@@ -482,15 +482,25 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->tilebar);
     if (!mbar_wait(&hd->tilebar, tile_count & 1u, ring.abort_flag, ring.status, kDevWaitFull)) return;
-    if (warp == 0 && lane < R && r0 + lane < p.dim) {
-      float s = hd->part[pb][2 * lane][0] + hd->part[pb][2 * lane + 1][0];
-      if (n_local > 0)
-        for (int w = 0; w < kMoeNW; w++) s += hd->rpart[pb][w][lane];
+    if (warp == 0) {
+      float s = 0.f;
+      if (lane < R && r0 + lane < p.dim) {
+        s = hd->part[pb][2 * lane][0] + hd->part[pb][2 * lane + 1][0];
+        if (n_local > 0)
+          for (int w = 0; w < kMoeNW; w++) s += hd->rpart[pb][w][lane];
+      }
       if (p.ep_world > 0) {
-        // this rank's partial sum of the row goes to every rank's exchange buffer (plain peer stores)
-        const size_t at = ((size_t)(ep_par * p.ep_world + p.ep_rank)) * p.dim + r0 + lane;
-        for (int r = 0; r < p.ep_world; r++) reinterpret_cast<float*>(p.ep_base[r] + kEpSlotsOff)[at] = s;
-      } else {
+        // this rank's partial sums of the tile's 8 rows go to every rank's exchange buffer: lane r gathers the eight
+        // values and writes them to rank r as two 16-byte peer stores (dim is a multiple of 256: tiles are whole)
+        float v[R];
+#pragma unroll
+        for (int k = 0; k < R; k++) v[k] = __shfl_sync(0xffffffffu, s, k);
+        if (lane < p.ep_world) {
+          float* dst = reinterpret_cast<float*>(p.ep_base[lane] + kEpSlotsOff) + ((size_t)(ep_par * p.ep_world + p.ep_rank)) * p.dim + r0;
+          reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+          reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
+      } else if (lane < R && r0 + lane < p.dim) {
         p.y[r0 + lane] += s;
       }
     }
@@ -499,11 +509,11 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   if (p.ep_world > 0 && warp == 0) {
     // Every row of this block is stored (by lanes of this warp).  One release per block: after the warp barrier lane r
     // adds 1 to the arrival counter of this exchange in rank r's buffer with release semantics at system scope, which
-    // orders the block's partial rows before it; the combine kernels wait for world x gridDim.x arrivals.  No fence
-    // stalls the SM and no block waits for another.
+    // orders the block's partial rows before it; every rank's counters live on cache lines of their own (one per source
+    // rank), so a counter sees gridDim.x additions however many ranks there are.  No block waits for another.
     __syncwarp();
     if (lane < p.ep_world) {
-      unsigned* cnt = reinterpret_cast<unsigned*>(p.ep_base[lane] + kEpFlagsOff) + ep_par * kMaxEpWorld;
+      unsigned* cnt = ep_arrivals(p.ep_base[lane], ep_par, p.ep_rank);
       asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(1u) : "memory");
     }
   }

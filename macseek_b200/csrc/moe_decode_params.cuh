@@ -54,10 +54,14 @@ struct MoeParams {
 
 // Exchange buffer of one rank (zero-filled at creation):
 //   +0    u32 epoch E: combines completed on this rank; slot / flag parity of the current exchange = E & 1
-//   +64   u32 arrivals[2][kMaxEpWorld]: arrivals[parity][0] counts the down-launch blocks (of all ranks) whose partial
-//         rows of this exchange are in place; complete at world x moe_down_blocks(); zeroed again by the combine
-//   +256  f32 slots[2][world][dim]
-constexpr size_t kEpFlagsOff = 64, kEpSlotsOff = 256;
+//   +128  arrival counters [2][kMaxEpWorld], one 128-byte line each: counter [parity][r] counts the blocks of rank r's
+//         down launch whose partial rows of this exchange are in place; complete at moe_down_blocks(); zeroed again by
+//         the combine
+//   +4096 f32 slots[2][world][dim]
+constexpr size_t kEpFlagsOff = 128, kEpCounterStride = 128, kEpSlotsOff = 4096;
+__host__ __device__ inline unsigned* ep_arrivals(uint8_t* base, int parity, int src_rank) {
+  return reinterpret_cast<unsigned*>(base + kEpFlagsOff + (size_t)(parity * kMaxEpWorld + src_rank) * kEpCounterStride);
+}
 // blocks of one moe_down_kernel launch (8-row tiles over dim, at most one block per SM): what each rank contributes to
 // an exchange's arrival count
 inline int moe_down_blocks(int dim, int sms) { const int tiles = (dim + 7) / 8; return tiles < sms ? (tiles > 1 ? tiles : 1) : sms; }

@@ -125,11 +125,11 @@ def encode_combine(e, comm: EpComm, h: torch.Tensor):
 
 class HostExchange:
     """The exchange protocol of the peer combine, on the host: what `moe_down_kernel`'s epilogue and `ep_combine_kernel`
-    do with peer stores and flags, restated over a torch.distributed key-value store so that the protocol (epochs,
+    do with peer stores and arrival counters, restated over a torch.distributed key-value store so that the protocol (epochs,
     double-buffered slots, rank-ordered sum, BOUNDED wait with a status instead of a hang) can be exercised by CPU ranks.
 
-    publish(partial): this rank's partial of the current epoch becomes visible to every rank (slot write + flag).
-    combine(h, timeout_s): wait -- at most timeout_s -- for every rank's flag of the current epoch, add the partials to h in
+    publish(partial): this rank's partial of the current epoch becomes visible to every rank (slot write + arrival mark).
+    combine(h, timeout_s): wait -- at most timeout_s -- for every rank's arrival in the current epoch, add the partials to h in
     rank order and advance the epoch.  Returns 0, or STATUS_PEER_WAIT (3, the device status word's value for the same
     event) with h untouched when a rank's contribution did not arrive in time; the epoch does not advance then."""
 
