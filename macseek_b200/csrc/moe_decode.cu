@@ -406,7 +406,7 @@ __global__ void __launch_bounds__((kMoeNW + 1) * 32, 1) moe_down_kernel(const Mo
   LaneLuts L;
   const bool luts_ok = load_luts(lut, TR == IQ1_S, TR == IQ2_XXS, false, p.tb, tid, &hd->lutbar, &hd->abort_flag, L, lane);
   pdl_wait();     // h comes from the gate/up kernel
-  // expert-parallel exchange: the epoch (completed combines on this rank) picks the slot / flag parity
+  // expert-parallel exchange: the epoch (completed combines on this rank) picks the slot / counter parity
   unsigned ep_epoch = 0;
   if (p.ep_world > 0) ep_epoch = *reinterpret_cast<volatile unsigned*>(p.ep_base[p.ep_rank]);
   const int ep_par = (int)(ep_epoch & 1u);

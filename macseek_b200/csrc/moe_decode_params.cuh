@@ -53,7 +53,7 @@ struct MoeParams {
 };
 
 // Exchange buffer of one rank (zero-filled at creation):
-//   +0    u32 epoch E: combines completed on this rank; slot / flag parity of the current exchange = E & 1
+//   +0    u32 epoch E: combines completed on this rank; slot / counter parity of the current exchange = E & 1
 //   +128  arrival counters [2][kMaxEpWorld], one 128-byte line each: counter [parity][r] counts the blocks of rank r's
 //         down launch whose partial rows of this exchange are in place; complete at moe_down_blocks(); zeroed again by
 //         the combine
