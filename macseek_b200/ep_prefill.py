@@ -6,8 +6,9 @@ Semantics of the reference model's expert-parallel MoE (reference/inference/mode
 kernels' deterministic per-token reduce (src/kernels/quant_moe_prefill.metal:330-344).
 
 The exchange is a real data movement step of this path, so it uses the collective library (torch.distributed
-all_to_all_single: NCCL over NVLink on GPUs, gloo in the CPU tests); everything else is rank-local.  Rows travel as bf16
-(the prefill's hidden states are bf16), expert outputs come back as f32.
+all_to_all_single: NCCL over NVLink on GPUs, gloo in the CPU tests); everything else is rank-local.  An entry travels
+as one message: its bf16 row (the prefill's hidden states are bf16), its expert id and its routing weight; expert outputs
+come back as f32.
 """
 from __future__ import annotations
 
@@ -62,13 +63,18 @@ def moe_prefill_ep(X: torch.Tensor, ids: torch.Tensor, w: torch.Tensor, n_expert
     n_recv = int(sum(rc))
     dim = X.shape[1]
     dev = X.device
-    send_rows = X[plan.tok].to(torch.bfloat16).contiguous()
-    recv_rows = torch.empty(n_recv, dim, dtype=torch.bfloat16, device=dev)
-    _a2a(recv_rows, send_rows, rc, sc, group)
-    recv_e = torch.empty(n_recv, dtype=torch.int32, device=dev)
-    _a2a(recv_e, plan.expert.contiguous(), rc, sc, group)
-    recv_w = torch.empty(n_recv, dtype=torch.float32, device=dev)
-    _a2a(recv_w, plan.weight.contiguous(), rc, sc, group)
+    # one message per entry: the bf16 row, then the expert id (int32) and the routing weight (f32) -- one all-to-all
+    # instead of three
+    rb = dim * 2
+    send = torch.empty(plan.n * plan.k, rb + 8, dtype=torch.uint8, device=dev)
+    send[:, :rb] = X[plan.tok].to(torch.bfloat16).contiguous().view(torch.uint8).reshape(-1, rb)
+    send[:, rb:rb + 4] = plan.expert.contiguous().view(torch.uint8).reshape(-1, 4)
+    send[:, rb + 4:] = plan.weight.contiguous().view(torch.uint8).reshape(-1, 4)
+    recv = torch.empty(n_recv, rb + 8, dtype=torch.uint8, device=dev)
+    _a2a(recv, send, rc, sc, group)
+    recv_rows = recv[:, :rb].contiguous().view(torch.bfloat16).reshape(n_recv, dim)
+    recv_e = recv[:, rb:rb + 4].contiguous().view(torch.int32).reshape(n_recv)
+    recv_w = recv[:, rb + 4:].contiguous().view(torch.float32).reshape(n_recv)
     if stats is not None:
         stats["rows_sent"], stats["rows_received"] = int(sum(sc)), n_recv
     # local grouped GEMM over the received rows, expert-sorted (stable: ties keep the arrival order)
@@ -89,16 +95,34 @@ def moe_prefill_ep(X: torch.Tensor, ids: torch.Tensor, w: torch.Tensor, n_expert
     return Y
 
 
+class _Buffers:
+    """Work buffers that grow on demand and are reused from call to call (the prefill kernels need their scratch zeroed
+    once, at allocation, not per call)."""
+
+    def __init__(self):
+        self.scratch = None
+        self.out = None
+
+    def get(self, scratch_bytes, m, dim, device):
+        if self.scratch is None or self.scratch.numel() < scratch_bytes:
+            self.scratch = torch.zeros(int(scratch_bytes * 1.25) + 256, dtype=torch.uint8, device=device)
+        if self.out is None or self.out.shape[0] < m or self.out.shape[1] != dim:
+            self.out = torch.empty(int(m * 1.25) + 1, dim, dtype=torch.float32, device=device)
+        out = self.out[:m]
+        out.zero_()
+        return self.scratch, out
+
+
 def cuda_local_experts(lw, e):
     """local_experts callback over macseek_b200's grouped prefill kernels for a MoeLayerWeights holding this rank's
     experts: every received row is its own one-entry token."""
     from . import quant as q
+    bufs = _Buffers()
 
     def run(rows, expert_ids, weights):
         m, dim = rows.shape
-        out = torch.zeros(m, dim, dtype=torch.float32, device=rows.device)
         if m == 0:
-            return out
+            return torch.zeros(0, dim, dtype=torch.float32, device=rows.device)
         used, counts = torch.unique_consecutive(expert_ids, return_counts=True)
         a = q.MoePrefillArgs(lw.dim, lw.inter)
         a.t_gate_up, a.t_down, a.t_shared = lw.t_gate_up, lw.t_down, lw.t_shared
@@ -113,22 +137,20 @@ def cuda_local_experts(lw, e):
         a.tok = torch.arange(m, dtype=torch.int32, device=rows.device)
         a.wt = weights
         a.slot_of = torch.arange(m, dtype=torch.int32, device=rows.device)
+        a.scratch, out = bufs.get(q.moe_prefill_scratch_bytes(m, m, len(a.slots), lw.dim, lw.inter), m, dim, rows.device)
         a.X, a.Y = rows, out
-        a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(m, m, len(a.slots), lw.dim, lw.inter), dtype=torch.uint8,
-                                device=rows.device)
         q.encode_moe_prefill(e, a)
-        e.stream.synchronize()
-        return out
+        return out            # valid until this callback's next call; consumed on the same stream before that
     return run
 
 
 def cuda_shared_expert(lw, e):
     """shared_local callback: the replicated shared expert on the local tokens."""
     from . import quant as q
+    bufs = _Buffers()
 
     def run(rows):
         n, dim = rows.shape
-        out = torch.zeros(n, dim, dtype=torch.float32, device=rows.device)
         a = q.MoePrefillArgs(lw.dim, lw.inter)
         a.t_gate_up, a.t_down, a.t_shared = lw.t_gate_up, lw.t_down, lw.t_shared
         a.n_tokens, a.k_per_token, a.has_shared = n, 1, True
@@ -137,9 +159,8 @@ def cuda_shared_expert(lw, e):
         a.tok = torch.zeros(1, dtype=torch.int32, device=rows.device)
         a.wt = torch.zeros(1, dtype=torch.float32, device=rows.device)
         a.slot_of = torch.full((n,), -1, dtype=torch.int32, device=rows.device)
+        a.scratch, out = bufs.get(q.moe_prefill_scratch_bytes(0, n, 0, lw.dim, lw.inter), n, dim, rows.device)
         a.X, a.Y = rows, out
-        a.scratch = torch.zeros(q.moe_prefill_scratch_bytes(0, n, 0, lw.dim, lw.inter), dtype=torch.uint8, device=rows.device)
         q.encode_moe_prefill(e, a)
-        e.stream.synchronize()
         return out
     return run
