@@ -148,20 +148,17 @@ __device__ __forceinline__ void quantize_units(const float* __restrict__ x, cons
     // |v * inv| <= 32767 (1 + 2^-22) rounds to at most 32767
     constexpr float kMagic = 12582912.f;
     uint32_t f[8];
-    float fsum = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const float r = fmaf(v[i], inv, kMagic);
-      f[i] = __float_as_uint(r);
-      fsum += r - kMagic;                  // exact small integers
-    }
-    const int sum = (int)fsum;
+    for (int i = 0; i < 8; i++) f[i] = __float_as_uint(fmaf(v[i], inv, kMagic));
     uint32_t hw[2], lw[2];
 #pragma unroll
     for (int j = 0; j < 2; j++) {
       hw[j] = __byte_perm(__byte_perm(f[4 * j], f[4 * j + 1], 0x0051), __byte_perm(f[4 * j + 2], f[4 * j + 3], 0x0051), 0x5410);
       lw[j] = __byte_perm(__byte_perm(f[4 * j], f[4 * j + 1], 0x0040), __byte_perm(f[4 * j + 2], f[4 * j + 3], 0x0040), 0x5410);
     }
+    // sum of the 8 fixed-point values = 256 * (sum of the signed high bytes) + (sum of the unsigned low bytes)
+    const int sum = 256 * dp4a_ss(hw[1], 0x01010101u, dp4a_ss(hw[0], 0x01010101u, 0)) +
+                    dp4a_uu(lw[1], 0x01010101u, dp4a_uu(lw[0], 0x01010101u, 0));
     const int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);   // lanes (0,1): elements 0..15, (2,3): 16..31
     const int other = __shfl_xor_sync(0xffffffffu, pair, 2);
     if (live) {
