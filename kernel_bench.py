@@ -4,7 +4,9 @@
     python kernel_bench.py moe {router|gu|down|all}
     python kernel_bench.py attn {index|scores|topk|sparse|all} [--kv-len 200000]
     python kernel_bench.py gemm Q6_K 4096 4096 --n 4096
-    python kernel_bench.py moe_prefill [--n 4096]
+    python kernel_bench.py moe_prefill [--n 4096] [--routing bias|sample]
+    torchrun --nproc-per-node N kernel_bench.py moe_prefill_ep     # the same layer expert-parallel, checked against one GPU
+    python kernel_bench.py hc               # hyper-connection step and KV compressor
     python kernel_bench.py layer            # cost added by each call of the decode layer, in context
     python kernel_bench.py sweep
 
