@@ -27,6 +27,7 @@ namespace msb {
 constexpr int kMpBM = 128, kMpBN = 128, kMpBK = 64;
 constexpr int kMpABytes = kMpBM * kMpBK * 2, kMpBBytes = kMpBN * kMpBK * 2;
 constexpr int kMpStages = 5;
+constexpr int kMpLutBytes = 16384;      // selector tables of the in-kernel decode (IQ1_S 16 KB; IQ2_XXS 2 + 2 KB)
 constexpr int kMpProducerWarps = 8;
 constexpr int kMpThreads = (4 + 1 + 1 + kMpProducerWarps) * 32;
 
@@ -109,8 +110,10 @@ __device__ __forceinline__ MpRaw mp_fetch_unit(const uint8_t* blk, int ib) {
   }
   return r;
 }
+// lut: the selector tables in shared memory (IQ1_S: uint2 [2048]; IQ2_XXS: uint2 [256] then uint4 [128]) -- the raw-byte
+// fetches of 256 rows at a time sweep the L1, so tables left in global memory miss it on most look-ups
 template <int T>
-__device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const Tables& tb, uint4 (&out)[4]) {
+__device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const uint8_t* lut, uint4 (&out)[4]) {
   if (T == IQ1_S) {
     const uint32_t qs = r.a, qh = r.b;
     const float dl = __fmul_rn(r.d, (float)(2 * ((qh >> 12) & 7u) + 1));
@@ -123,7 +126,7 @@ __device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const Tables& tb,
 #pragma unroll
     for (int l = 0; l < 4; l++) {
       const uint32_t idx = ((qs >> (8 * l)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
-      const uint2 sel = __ldg(tb.iq1s_sel + idx);
+      const uint2 sel = reinterpret_cast<const uint2*>(lut)[idx];
       out[l] = make_uint4(__byte_perm(pool_lo, pool_hi, sel.x & 0xFFFFu), __byte_perm(pool_lo, pool_hi, sel.x >> 16),
                           __byte_perm(pool_lo, pool_hi, sel.y & 0xFFFFu), __byte_perm(pool_lo, pool_hi, sel.y >> 16));
     }
@@ -136,8 +139,8 @@ __device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const Tables& tb,
     const uint32_t pool_lo = *reinterpret_cast<const uint32_t*>(&h01), pool_hi = *reinterpret_cast<const uint32_t*>(&h2x);
 #pragma unroll
     for (int l = 0; l < 4; l++) {
-      const uint2 sel = __ldg(tb.iq2_sel + ((q >> (8 * l)) & 0xFFu));
-      const uint4 sg = __ldg(tb.iq2_sign16 + ((a1 >> (7 * l)) & 127u));
+      const uint2 sel = reinterpret_cast<const uint2*>(lut)[(q >> (8 * l)) & 0xFFu];
+      const uint4 sg = reinterpret_cast<const uint4*>(lut + 2048)[(a1 >> (7 * l)) & 127u];
       out[l] = make_uint4(__byte_perm(pool_lo, pool_hi, sel.x & 0xFFFFu) ^ sg.x, __byte_perm(pool_lo, pool_hi, sel.x >> 16) ^ sg.y,
                           __byte_perm(pool_lo, pool_hi, sel.y & 0xFFFFu) ^ sg.z, __byte_perm(pool_lo, pool_hi, sel.y >> 16) ^ sg.w);
     }
@@ -154,8 +157,18 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
   uint8_t* smem = mp_smem_raw + ((1024u - (smem_u32(mp_smem_raw) & 1023u)) & 1023u);
   MpHead* hd = reinterpret_cast<MpHead*>(smem);
   uint8_t* stage0 = smem + 1024;
+  uint8_t* lut = stage0 + (size_t)kMpStages * (kMpABytes + kMpBBytes);      // kMpLutBytes, producers of IQ types only
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr uint32_t kCols = 2 * kMpBN;
+  if constexpr (!DENSE && (T == IQ1_S || T == IQ2_XXS)) {
+    // constant tables: copied before the dependency wait
+    if (T == IQ1_S) {
+      for (int i = tid; i < 2048; i += kMpThreads) reinterpret_cast<uint2*>(lut)[i] = __ldg(p.tb.iq1s_sel + i);
+    } else {
+      for (int i = tid; i < 256; i += kMpThreads) reinterpret_cast<uint2*>(lut)[i] = __ldg(p.tb.iq2_sel + i);
+      for (int i = tid; i < 128; i += kMpThreads) reinterpret_cast<uint4*>(lut + 2048)[i] = __ldg(p.tb.iq2_sign16 + i);
+    }
+  }
 
   if (tid == 0) {
     for (int s = 0; s < kMpStages; s++) { mbar_init(&hd->full[s], DENSE ? 1 : 1 + kMpProducerWarps); mbar_init(&hd->empty[s], 1); }
@@ -272,7 +285,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         if constexpr (T == IQ1_S || T == IQ2_XXS) {
           static_assert(kMpBN * 2 == kMpProducerWarps * 32, "one unit per producer thread");
           uint4 o4[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-          if (ulive) mp_decode_unit<T>(cur, p.tb, o4);
+          if (ulive) mp_decode_unit<T>(cur, lut, o4);
 #pragma unroll
           for (int l = 0; l < 4; l++) *reinterpret_cast<uint4*>(bt + ur * 128 + (((4 * un + l) ^ (ur & 7)) << 4)) = o4[l];
         } else
@@ -456,7 +469,7 @@ int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols, int 
 template <int T, int MODE, bool DENSE>
 int mp_launch(MpGemmParams& p, int sms, int dev, cudaStream_t st) {
   if (p.ntiles <= 0) return kOk;
-  const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes);
+  const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes) + kMpLutBytes;
   auto kern = moep_gemm_kernel<T, MODE, DENSE>;
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
