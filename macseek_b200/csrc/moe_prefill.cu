@@ -29,6 +29,10 @@ constexpr int kMpABytes = kMpBM * kMpBK * 2, kMpBBytes = kMpBN * kMpBK * 2;
 constexpr int kMpStages = 5;
 constexpr int kMpLutBytes = 16384;      // selector tables of the in-kernel decode (IQ1_S 16 KB; IQ2_XXS 2 + 2 KB)
 constexpr int kMpProducerWarps = 8;
+// Raw-block staging of the in-kernel decode: per producer warp 16 tile rows x 8 units x 16 bytes {word a, word b, block
+// scale}, rows 160 bytes apart (so that the four rows a quarter warp touches with one 16-byte access sit 32 bytes apart
+// modulo 128: no bank conflicts on either side)
+constexpr int kMpStgRow = 160, kMpStgWarp = 16 * kMpStgRow, kMpStgBytes = kMpProducerWarps * kMpStgWarp;
 constexpr int kMpThreads = (4 + 1 + 1 + kMpProducerWarps) * 32;
 
 struct MpTile { int slot, row0, rows, n0; };   // expert slot, first entry row, valid rows (<= 128), first weight row
@@ -253,30 +257,67 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       const uint64_t* wp = p.wptr + (size_t)tl.slot * 3;
       const uint8_t* w0 = reinterpret_cast<const uint8_t*>(MODE == 0 ? wp[0] : wp[2]);   // gate | down
       const uint8_t* w1 = reinterpret_cast<const uint8_t*>(wp[1]);                        // up (mode 0)
-      // unit path (IQ1_S / IQ2_XXS): one thread per (tile row, 32-element unit); raw bytes one K block ahead
-      const int ur = pt >> 1, un = pt & 1;
-      const uint8_t* ubase = (MODE == 0 && ur >= 64) ? w1 : w0;
-      const int uwrow = tl.n0 + (MODE == 0 ? (ur & 63) : ur);
-      const bool ulive = uwrow < p.n_out;
-      auto fetch_k = [&](int k) {
-        MpRaw r{0u, 0u, 0.f};
-        if constexpr (T == IQ1_S || T == IQ2_XXS) {
-          const int u = k * 2 + un;
-          if (ulive && k < kb) r = mp_fetch_unit<T>(ubase + (size_t)uwrow * rb + (size_t)(u >> 3) * block_bytes(T), u & 7);
+      // unit path (IQ1_S / IQ2_XXS): thread (ur, un) decodes unit un of tile row ur in every 64-wide K block.  The raw
+      // bytes are FETCHED in another arrangement, one 256-element block (four K blocks) at a time: lane (row 4 q + lane / 8
+      // of the warp's 16, unit lane % 8), q = 0..3, so that one load instruction of the warp touches 4 rows' blocks
+      // instead of 16 (a quarter of the L1 wavefronts, which together with the table look-ups and the tile stores
+      // bound the producers).  The fetched {a, b, d} go through a per-warp staging array in shared memory, written
+      // when the block's turn comes and read back by the decoding thread; the next block's loads are in flight
+      // meanwhile (the rows' bytes come from HBM, every expert weight being read once).
+      const int ur = pt >> 1, un = pt & 1, pw = pt >> 5;
+      const bool ulive = tl.n0 + (MODE == 0 ? (ur & 63) : ur) < p.n_out;
+      const int kg = kb / 4;                                 // K is a multiple of 256
+      const uint8_t* frow[4];                                // the four rows this lane fetches for (null: past n_out)
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const int trow = 16 * pw + 4 * q + (lane >> 3);      // mode 0: tile rows 0..63 = gate rows n0.., 64..127 = up
+        const int wrow = tl.n0 + (MODE == 0 ? (trow & 63) : trow);
+        const uint8_t* base = (MODE == 0 && trow >= 64) ? w1 : w0;
+        frow[q] = wrow < p.n_out ? base + (size_t)wrow * rb : nullptr;
+      }
+      auto fetch_g = [&](int g, MpRaw (&r)[4]) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          r[q] = MpRaw{0u, 0u, 0.f};
+          if constexpr (T == IQ1_S || T == IQ2_XXS) {
+            if (frow[q] && g < kg) r[q] = mp_fetch_unit<T>(frow[q] + (size_t)g * block_bytes(T), lane & 7);
+          }
         }
-        return r;
       };
-      // raw bytes of four K blocks in flight per thread (they come from HBM, a microsecond away); K is a multiple of
-      // 256, so the number of K blocks is a multiple of 4 and the ring index is a compile-time constant
-      MpRaw ring[4] = {fetch_k(0), fetch_k(1), fetch_k(2), fetch_k(3)};
-      for (int k0 = 0; ok && k0 < kb; k0 += 4)
+      // The rows' raw blocks are asked into L2 now, all of them (rb bytes per row, the eight lanes of a row taking
+      // alternate 128-byte lines): the loads above then pay an L2 hit instead of an HBM miss.
+      if constexpr (T == IQ1_S || T == IQ2_XXS) {
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          if (frow[q])
+            for (size_t off = (size_t)(lane & 7) * 128; off < rb; off += 1024) asm volatile("prefetch.global.L2 [%0];" ::"l"(frow[q] + off));
+      }
+      const saddr_t stg = smem_u32(lut + kMpLutBytes) + (uint32_t)(pw * kMpStgWarp);
+      const saddr_t stg_w = stg + (uint32_t)((lane >> 3) * kMpStgRow + (lane & 7) * 16);      // + 4 q rows
+      const saddr_t stg_r = stg + (uint32_t)((lane >> 1) * kMpStgRow + un * 16);               // + 2 kk units
+      MpRaw ring[4];
+      fetch_g(0, ring);
+      for (int k0 = 0; ok && k0 < kb; k0 += 4) {
+      if constexpr (T == IQ1_S || T == IQ2_XXS) {
+        __syncwarp();                                        // the previous block's reads are done
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg_w + (uint32_t)(4 * q * kMpStgRow)), "r"(ring[q].a),
+                       "r"(ring[q].b), "r"(__float_as_uint(ring[q].d)), "r"(0u)
+                       : "memory");
+        __syncwarp();
+        fetch_g(k0 / 4 + 1, ring);
+      }
 #pragma unroll
       for (int kk = 0; kk < 4; kk++) {
         if (!ok) break;
         const int k = k0 + kk;
         const int s = it % kMpStages;
-        const MpRaw cur = ring[kk];
-        ring[kk] = fetch_k(k + 4);
+        MpRaw cur{0u, 0u, 0.f};
+        if constexpr (T == IQ1_S || T == IQ2_XXS) {
+          const uint4 v = lds_u128(stg_r + (uint32_t)(32 * kk));
+          cur.a = v.x; cur.b = v.y; cur.d = __uint_as_float(v.z);
+        }
         if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
           ok = false;
           break;
@@ -316,6 +357,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(&hd->full[s]);
         it++;
+      }
       }
     }
   } else {
@@ -469,7 +511,7 @@ int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols, int 
 template <int T, int MODE, bool DENSE>
 int mp_launch(MpGemmParams& p, int sms, int dev, cudaStream_t st) {
   if (p.ntiles <= 0) return kOk;
-  const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes) + kMpLutBytes;
+  const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes) + kMpLutBytes + kMpStgBytes;
   auto kern = moep_gemm_kernel<T, MODE, DENSE>;
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
