@@ -29,6 +29,7 @@ constexpr int kMpABytes = kMpBM * kMpBK * 2, kMpBBytes = kMpBN * kMpBK * 2;
 constexpr int kMpStages = 5;
 constexpr int kMpLutBytes = 16384;      // selector tables of the in-kernel decode (IQ1_S 16 KB; IQ2_XXS 2 + 2 KB)
 constexpr int kMpProducerWarps = 8;
+constexpr int kMpBatch = 2;            // K blocks a producer thread decodes per hand-over to the MMA (1, 2 or 4)
 // Raw-block staging of the in-kernel decode: per producer warp 16 tile rows x 8 units x 16 bytes {word a, word b, block
 // scale}, rows 160 bytes apart (so that the four rows a quarter warp touches with one 16-byte access sit 32 bytes apart
 // modulo 128: no bank conflicts on either side)
@@ -203,7 +204,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         const MpTile tl = p.tiles[(int)blockIdx.x + i * (int)gridDim.x];
         for (int k = 0; k < kb; k++, it++) {
           const int s = it % kMpStages;
-          if (!mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty)) { ok = false; break; }
+          if (!mbar_wait_sleep(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty, 100)) { ok = false; break; }
           uint8_t* slot = stage0 + (size_t)s * (kMpABytes + kMpBBytes);
           mbar_arrive_expect_tx(&hd->full[s], DENSE ? kMpABytes + kMpBBytes : kMpABytes);
           mp_tma_2d(slot, &p.a_map, k * kMpBK, tl.row0, &hd->full[s]);
@@ -226,10 +227,10 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       bool ok = true;
       for (int i = 0; ok && i < my_tiles; i++) {
         const int buf = i & 1;
-        if (!mbar_wait(&hd->accempty[buf], ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty)) break;
+        if (!mbar_wait_sleep(&hd->accempty[buf], ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty, 100)) break;
         for (int k = 0; k < kb; k++, it++) {
           const int s = it % kMpStages;
-          if (!mbar_wait(&hd->full[s], (it / kMpStages) & 1u, abort_flag, p.status, kDevWaitFull)) { ok = false; break; }
+          if (!mbar_wait_sleep(&hd->full[s], (it / kMpStages) & 1u, abort_flag, p.status, kDevWaitFull, 40)) { ok = false; break; }
           mp_fence_after();
           const uint32_t a_s = smem_u32(stage0 + (size_t)s * (kMpABytes + kMpBBytes)), b_s = a_s + kMpABytes;
 #pragma unroll
@@ -299,6 +300,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       fetch_g(0, ring);
       for (int k0 = 0; ok && k0 < kb; k0 += 4) {
       if constexpr (T == IQ1_S || T == IQ2_XXS) {
+        static_assert(kMpBN * 2 == kMpProducerWarps * 32, "one unit per producer thread");
         __syncwarp();                                        // the previous block's reads are done
 #pragma unroll
         for (int q = 0; q < 4; q++)
@@ -307,29 +309,54 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
                        : "memory");
         __syncwarp();
         fetch_g(k0 / 4 + 1, ring);
-      }
+        // kMpBatch K blocks per hand-over: their units are decoded into registers first (nothing there depends on a free
+        // slot), then the slots are awaited, the tiles stored and ONE proxy fence + warp barrier covers them all
+#pragma unroll
+        for (int kk = 0; kk < 4; kk += kMpBatch) {
+          if (!ok) break;
+          uint4 o4[kMpBatch][4];
+#pragma unroll
+          for (int b = 0; b < kMpBatch; b++) {
+            const uint4 v = lds_u128(stg_r + (uint32_t)(32 * (kk + b)));
+            MpRaw cur;
+            cur.a = v.x; cur.b = v.y; cur.d = __uint_as_float(v.z);
+#pragma unroll
+            for (int l = 0; l < 4; l++) o4[b][l] = make_uint4(0, 0, 0, 0);
+            if (ulive) mp_decode_unit<T>(cur, lut, o4[b]);
+          }
+#pragma unroll
+          for (int b = 0; b < kMpBatch; b++) {
+            const uint32_t itb = it + b;
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(&hd->empty[itb % kMpStages], ((itb / kMpStages) & 1u) ^ 1u, abort_flag,
+                                                         p.status, kDevWaitEmpty)))
+              ok = false;
+          }
+          if (!ok) break;
+#pragma unroll
+          for (int b = 0; b < kMpBatch; b++) {
+            uint8_t* bt = stage0 + (size_t)((it + b) % kMpStages) * (kMpABytes + kMpBBytes) + kMpABytes;
+#pragma unroll
+            for (int l = 0; l < 4; l++) *reinterpret_cast<uint4*>(bt + ur * 128 + (((4 * un + l) ^ (ur & 7)) << 4)) = o4[b][l];
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+#pragma unroll
+            for (int b = 0; b < kMpBatch; b++) mbar_arrive(&hd->full[(it + b) % kMpStages]);
+          }
+          it += kMpBatch;
+        }
+      } else
 #pragma unroll
       for (int kk = 0; kk < 4; kk++) {
         if (!ok) break;
         const int k = k0 + kk;
         const int s = it % kMpStages;
-        MpRaw cur{0u, 0u, 0.f};
-        if constexpr (T == IQ1_S || T == IQ2_XXS) {
-          const uint4 v = lds_u128(stg_r + (uint32_t)(32 * kk));
-          cur.a = v.x; cur.b = v.y; cur.d = __uint_as_float(v.z);
-        }
         if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
           ok = false;
           break;
         }
         uint8_t* bt = stage0 + (size_t)s * (kMpABytes + kMpBBytes) + kMpABytes;
-        if constexpr (T == IQ1_S || T == IQ2_XXS) {
-          static_assert(kMpBN * 2 == kMpProducerWarps * 32, "one unit per producer thread");
-          uint4 o4[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-          if (ulive) mp_decode_unit<T>(cur, lut, o4);
-#pragma unroll
-          for (int l = 0; l < 4; l++) *reinterpret_cast<uint4*>(bt + ur * 128 + (((4 * un + l) ^ (ur & 7)) << 4)) = o4[l];
-        } else
 #pragma unroll
         for (int q = 0; q < kMpBN * 8 / (kMpProducerWarps * 32); q++) {
           const int c = pt + q * kMpProducerWarps * 32, r = c >> 3, j = c & 7;
@@ -365,7 +392,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
     for (int i = 0; i < my_tiles; i++) {
       const int buf = i & 1;
       const MpTile tl = p.tiles[(int)blockIdx.x + i * (int)gridDim.x];
-      if (!__all_sync(0xffffffffu, mbar_wait(&hd->accfull[buf], (i >> 1) & 1u, abort_flag, p.status, kDevWaitFull))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait_sleep(&hd->accfull[buf], (i >> 1) & 1u, abort_flag, p.status, kDevWaitFull, 400))) break;
       mp_fence_after();
       const int lrow = 32 * warp + lane;
       const bool live = lrow < tl.rows;

@@ -105,6 +105,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
 }
+// The same bounded wait for a warp whose wake-up is not urgent (an epilogue warp waiting for a whole tile, a copy thread
+// waiting for a free slot): it sleeps `ns` between polls, so that its polling takes neither issue slots nor
+// shared-memory cycles from the warps that do the work meanwhile.
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                int code, unsigned ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; i++) {
+      if (mbar_try_wait(bar, parity)) return true;
+      __nanosleep(ns);
+    }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > 2000000000LL) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
 // 1-D bulk copy global -> shared through the TMA engine; both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void tma_load_1d(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
