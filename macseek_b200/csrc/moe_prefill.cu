@@ -27,7 +27,12 @@ namespace msb {
 constexpr int kMpBM = 128, kMpBN = 128, kMpBK = 64;
 constexpr int kMpABytes = kMpBM * kMpBK * 2, kMpBBytes = kMpBN * kMpBK * 2;
 constexpr int kMpStages = 5;
-constexpr int kMpLutBytes = 16384;      // selector tables of the in-kernel decode (IQ1_S 16 KB; IQ2_XXS 2 + 2 KB)
+// selector tables of the in-kernel decode.  IQ1_S: 2048 x 8 bytes.  IQ2_XXS: the 256 x 8-byte magnitude selectors in
+// 8 copies (copy = lane % 8; 16 KB) and the 128 sign patterns as one word each in 16 copies (copy = lane % 16; 8 KB),
+// so that the lanes of one shared-memory wavefront mostly read different banks: with single copies of these small
+// tables the look-ups' bank conflicts kept the LSU data pipe 82 % busy.
+constexpr int kMpLutBytes = 24576;
+constexpr int kMpIq2SelCopies = 8, kMpIq2SignCopies = 16, kMpIq2SignOff = 256 * 8 * kMpIq2SelCopies;
 constexpr int kMpProducerWarps = 8;
 constexpr int kMpBatch = 2;            // K blocks a producer thread decodes per hand-over to the MMA (1, 2 or 4)
 // Raw-block staging of the in-kernel decode: per producer warp 16 tile rows x 8 units x 16 bytes {word a, word b, block
@@ -115,10 +120,10 @@ __device__ __forceinline__ MpRaw mp_fetch_unit(const uint8_t* blk, int ib) {
   }
   return r;
 }
-// lut: the selector tables in shared memory (IQ1_S: uint2 [2048]; IQ2_XXS: uint2 [256] then uint4 [128]) -- the raw-byte
+// lut: the selector tables in shared memory (IQ1_S: uint2 [2048]; IQ2_XXS: see kMpLutBytes) -- the raw-byte
 // fetches of 256 rows at a time sweep the L1, so tables left in global memory miss it on most look-ups
 template <int T>
-__device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const uint8_t* lut, uint4 (&out)[4]) {
+__device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const uint8_t* lut, int lane, uint4 (&out)[4]) {
   if (T == IQ1_S) {
     const uint32_t qs = r.a, qh = r.b;
     const float dl = __fmul_rn(r.d, (float)(2 * ((qh >> 12) & 7u) + 1));
@@ -144,10 +149,12 @@ __device__ __forceinline__ void mp_decode_unit(const MpRaw& r, const uint8_t* lu
     const uint32_t pool_lo = *reinterpret_cast<const uint32_t*>(&h01), pool_hi = *reinterpret_cast<const uint32_t*>(&h2x);
 #pragma unroll
     for (int l = 0; l < 4; l++) {
-      const uint2 sel = reinterpret_cast<const uint2*>(lut)[(q >> (8 * l)) & 0xFFu];
-      const uint4 sg = reinterpret_cast<const uint4*>(lut + 2048)[(a1 >> (7 * l)) & 127u];
-      out[l] = make_uint4(__byte_perm(pool_lo, pool_hi, sel.x & 0xFFFFu) ^ sg.x, __byte_perm(pool_lo, pool_hi, sel.x >> 16) ^ sg.y,
-                          __byte_perm(pool_lo, pool_hi, sel.y & 0xFFFFu) ^ sg.z, __byte_perm(pool_lo, pool_hi, sel.y >> 16) ^ sg.w);
+      const uint2 sel = reinterpret_cast<const uint2*>(lut)[((q >> (8 * l)) & 0xFFu) * kMpIq2SelCopies + (lane & (kMpIq2SelCopies - 1))];
+      const uint32_t sg = reinterpret_cast<const uint32_t*>(lut + kMpIq2SignOff)[((a1 >> (7 * l)) & 127u) * kMpIq2SignCopies +
+                                                                                 (lane & (kMpIq2SignCopies - 1))];
+      constexpr uint32_t kS = 0x80008000u;
+      out[l] = make_uint4(__byte_perm(pool_lo, pool_hi, sel.x & 0xFFFFu) ^ (sg & kS), __byte_perm(pool_lo, pool_hi, sel.x >> 16) ^ ((sg << 1) & kS),
+                          __byte_perm(pool_lo, pool_hi, sel.y & 0xFFFFu) ^ ((sg << 2) & kS), __byte_perm(pool_lo, pool_hi, sel.y >> 16) ^ ((sg << 3) & kS));
     }
   }
 }
@@ -170,8 +177,17 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
     if (T == IQ1_S) {
       for (int i = tid; i < 2048; i += kMpThreads) reinterpret_cast<uint2*>(lut)[i] = __ldg(p.tb.iq1s_sel + i);
     } else {
-      for (int i = tid; i < 256; i += kMpThreads) reinterpret_cast<uint2*>(lut)[i] = __ldg(p.tb.iq2_sel + i);
-      for (int i = tid; i < 128; i += kMpThreads) reinterpret_cast<uint4*>(lut + 2048)[i] = __ldg(p.tb.iq2_sign16 + i);
+      for (int i = tid; i < 256 * kMpIq2SelCopies; i += kMpThreads) reinterpret_cast<uint2*>(lut)[i] = __ldg(p.tb.iq2_sel + i / kMpIq2SelCopies);
+      // sign pattern word: bit 15 - j = sign of element 2 j, bit 31 - j = sign of element 2 j + 1 (j = 0..3), so that
+      // (word << j) & 0x80008000 is the XOR mask of the j-th pair of halfs
+      for (int i = tid; i < 128 * kMpIq2SignCopies; i += kMpThreads) {
+        const uint4 sg = __ldg(p.tb.iq2_sign16 + i / kMpIq2SignCopies);
+        const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+        uint32_t e = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) e |= ((w[j] >> 15) & 1u) << (15 - j) | ((w[j] >> 31) & 1u) << (31 - j);
+        reinterpret_cast<uint32_t*>(lut + kMpIq2SignOff)[i] = e;
+      }
     }
   }
 
@@ -322,7 +338,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
             cur.a = v.x; cur.b = v.y; cur.d = __uint_as_float(v.z);
 #pragma unroll
             for (int l = 0; l < 4; l++) o4[b][l] = make_uint4(0, 0, 0, 0);
-            if (ulive) mp_decode_unit<T>(cur, lut, o4[b]);
+            if (ulive) mp_decode_unit<T>(cur, lut, lane, o4[b]);
           }
 #pragma unroll
           for (int b = 0; b < kMpBatch; b++) {
