@@ -119,9 +119,10 @@ def _exchange_main(rank, world, port, out, skip_rank, skip_epoch):
         if st:
             break
     out.put((rank, statuses, h.tolist()))
-    # leave only after every rank has reported: the store's master must outlive the others' last reads
+    # the store's master (rank 0) leaves only after every rank has reported; the others need the store no more once
+    # their own report is in (polling it further would race with the master's exit)
     store.add("done", 1)
-    while int(store.add("done", 0)) < world:
+    while rank == 0 and int(store.add("done", 0)) < world:
         __import__("time").sleep(0.01)
 
 
