@@ -27,6 +27,7 @@ namespace msb {
 constexpr int kMpBM = 128, kMpBN = 128, kMpBK = 64;
 constexpr int kMpABytes = kMpBM * kMpBK * 2, kMpBBytes = kMpBN * kMpBK * 2;
 constexpr int kMpStages = 5;
+constexpr int kMpBNDense = 256, kMpStagesDense = 4;   // the TMA-fed variant's N tile and ring depth (4 x 48 KB)
 // selector tables of the in-kernel decode.  IQ1_S: 2048 x 8 bytes.  IQ2_XXS: the 256 x 8-byte magnitude selectors in
 // 8 copies (copy = lane % 8; 16 KB) and the 128 sign patterns as one word each in 16 copies (copy = lane % 16; 8 KB),
 // so that the lanes of one shared-memory wavefront mostly read different banks: with single copies of these small
@@ -60,7 +61,7 @@ struct MpGemmParams {
 };
 
 struct MpHead {
-  uint64_t full[kMpStages], empty[kMpStages], accfull[2], accempty[2];
+  uint64_t full[kMpStages], empty[kMpStages], accfull[2], accempty[2];   // kMpStages >= kMpStagesDense
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -169,9 +170,13 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
   uint8_t* smem = mp_smem_raw + ((1024u - (smem_u32(mp_smem_raw) & 1023u)) & 1023u);
   MpHead* hd = reinterpret_cast<MpHead*>(smem);
   uint8_t* stage0 = smem + 1024;
-  uint8_t* lut = stage0 + (size_t)kMpStages * (kMpABytes + kMpBBytes);      // kMpLutBytes, producers of IQ types only
+  // The TMA-fed variant works on 128 x 256 tiles: a 128 x 128 x 64 step reads 32 KB of operands from shared memory for
+  // 256 tensor-pipe cycles of work, exactly the shared-memory bandwidth, so any hiccup stalls the MMA; at N = 256 the
+  // step reads 48 KB for 512 cycles.  The producer-fed variant stays at N = 128 (its pace is the producers').
+  constexpr int BN = DENSE ? kMpBNDense : kMpBN, BBytes = BN * kMpBK * 2, STG = DENSE ? kMpStagesDense : kMpStages;
+  uint8_t* lut = stage0 + (size_t)STG * (kMpABytes + BBytes);      // kMpLutBytes, producers of IQ types only
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr uint32_t kCols = 2 * kMpBN;
+  constexpr uint32_t kCols = 2 * BN;
   if constexpr (!DENSE && (T == IQ1_S || T == IQ2_XXS)) {
     // constant tables: copied before the dependency wait
     if (T == IQ1_S) {
@@ -192,7 +197,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
   }
 
   if (tid == 0) {
-    for (int s = 0; s < kMpStages; s++) { mbar_init(&hd->full[s], DENSE ? 1 : 1 + kMpProducerWarps); mbar_init(&hd->empty[s], 1); }
+    for (int s = 0; s < STG; s++) { mbar_init(&hd->full[s], DENSE ? 1 : 1 + kMpProducerWarps); mbar_init(&hd->empty[s], 1); }
     for (int b = 0; b < 2; b++) { mbar_init(&hd->accfull[b], 1); mbar_init(&hd->accempty[b], 4); }
     hd->abort_flag = 0;
     mbar_fence_init();
@@ -219,15 +224,15 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       for (int i = 0; ok && i < my_tiles; i++) {
         const MpTile tl = p.tiles[(int)blockIdx.x + i * (int)gridDim.x];
         for (int k = 0; k < kb; k++, it++) {
-          const int s = it % kMpStages;
-          if (!mbar_wait_sleep(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty, 100)) { ok = false; break; }
-          uint8_t* slot = stage0 + (size_t)s * (kMpABytes + kMpBBytes);
-          mbar_arrive_expect_tx(&hd->full[s], DENSE ? kMpABytes + kMpBBytes : kMpABytes);
+          const int s = it % STG;
+          if (!mbar_wait_sleep(&hd->empty[s], ((it / STG) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty, 100)) { ok = false; break; }
+          uint8_t* slot = stage0 + (size_t)s * (kMpABytes + BBytes);
+          mbar_arrive_expect_tx(&hd->full[s], DENSE ? kMpABytes + BBytes : kMpABytes);
           mp_tma_2d(slot, &p.a_map, k * kMpBK, tl.row0, &hd->full[s]);
           if (DENSE) {
-            if (MODE == 0) {   // 64 gate rows, then the same 64 up rows
+            if (MODE == 0) {   // BN / 2 gate rows, then the same up rows
               mp_tma_2d(slot + kMpABytes, &p.b_map, k * kMpBK, tl.slot * 2 * p.n_out + tl.n0, &hd->full[s]);
-              mp_tma_2d(slot + kMpABytes + kMpBBytes / 2, &p.b_map, k * kMpBK, tl.slot * 2 * p.n_out + p.n_out + tl.n0, &hd->full[s]);
+              mp_tma_2d(slot + kMpABytes + BBytes / 2, &p.b_map, k * kMpBK, tl.slot * 2 * p.n_out + p.n_out + tl.n0, &hd->full[s]);
             } else {
               mp_tma_2d(slot + kMpABytes, &p.b_map, k * kMpBK, tl.slot * p.n_out + tl.n0, &hd->full[s]);
             }
@@ -238,20 +243,20 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kMpBN >> 3) << 17) | ((uint32_t)(kMpBM >> 4) << 24);
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kMpBM >> 4) << 24);
       uint32_t it = 0;
       bool ok = true;
       for (int i = 0; ok && i < my_tiles; i++) {
         const int buf = i & 1;
         if (!mbar_wait_sleep(&hd->accempty[buf], ((i >> 1) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty, 100)) break;
         for (int k = 0; k < kb; k++, it++) {
-          const int s = it % kMpStages;
-          if (!mbar_wait_sleep(&hd->full[s], (it / kMpStages) & 1u, abort_flag, p.status, kDevWaitFull, 40)) { ok = false; break; }
+          const int s = it % STG;
+          if (!mbar_wait_sleep(&hd->full[s], (it / STG) & 1u, abort_flag, p.status, kDevWaitFull, 40)) { ok = false; break; }
           mp_fence_after();
-          const uint32_t a_s = smem_u32(stage0 + (size_t)s * (kMpABytes + kMpBBytes)), b_s = a_s + kMpABytes;
+          const uint32_t a_s = smem_u32(stage0 + (size_t)s * (kMpABytes + BBytes)), b_s = a_s + kMpABytes;
 #pragma unroll
           for (int ks = 0; ks < kMpBK / 16; ks++)
-            mp_mma_f16(tmem + (uint32_t)(buf * kMpBN), mp_desc(a_s + ks * 32), mp_desc(b_s + ks * 32), idesc,
+            mp_mma_f16(tmem + (uint32_t)(buf * BN), mp_desc(a_s + ks * 32), mp_desc(b_s + ks * 32), idesc,
                        (k > 0 || ks > 0) ? 1u : 0u);
           mp_commit(&hd->empty[s]);
         }
@@ -343,14 +348,14 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
 #pragma unroll
           for (int b = 0; b < kMpBatch; b++) {
             const uint32_t itb = it + b;
-            if (ok && !__all_sync(0xffffffffu, mbar_wait(&hd->empty[itb % kMpStages], ((itb / kMpStages) & 1u) ^ 1u, abort_flag,
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(&hd->empty[itb % STG], ((itb / STG) & 1u) ^ 1u, abort_flag,
                                                          p.status, kDevWaitEmpty)))
               ok = false;
           }
           if (!ok) break;
 #pragma unroll
           for (int b = 0; b < kMpBatch; b++) {
-            uint8_t* bt = stage0 + (size_t)((it + b) % kMpStages) * (kMpABytes + kMpBBytes) + kMpABytes;
+            uint8_t* bt = stage0 + (size_t)((it + b) % STG) * (kMpABytes + BBytes) + kMpABytes;
 #pragma unroll
             for (int l = 0; l < 4; l++) *reinterpret_cast<uint4*>(bt + ur * 128 + (((4 * un + l) ^ (ur & 7)) << 4)) = o4[b][l];
           }
@@ -358,7 +363,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
           __syncwarp();
           if (lane == 0) {
 #pragma unroll
-            for (int b = 0; b < kMpBatch; b++) mbar_arrive(&hd->full[(it + b) % kMpStages]);
+            for (int b = 0; b < kMpBatch; b++) mbar_arrive(&hd->full[(it + b) % STG]);
           }
           it += kMpBatch;
         }
@@ -367,12 +372,12 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       for (int kk = 0; kk < 4; kk++) {
         if (!ok) break;
         const int k = k0 + kk;
-        const int s = it % kMpStages;
-        if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / kMpStages) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
+        const int s = it % STG;
+        if (!__all_sync(0xffffffffu, mbar_wait(&hd->empty[s], ((it / STG) & 1u) ^ 1u, abort_flag, p.status, kDevWaitEmpty))) {
           ok = false;
           break;
         }
-        uint8_t* bt = stage0 + (size_t)s * (kMpABytes + kMpBBytes) + kMpABytes;
+        uint8_t* bt = stage0 + (size_t)s * (kMpABytes + BBytes) + kMpABytes;
 #pragma unroll
         for (int q = 0; q < kMpBN * 8 / (kMpProducerWarps * 32); q++) {
           const int c = pt + q * kMpProducerWarps * 32, r = c >> 3, j = c & 7;
@@ -413,14 +418,14 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
       const int lrow = 32 * warp + lane;
       const bool live = lrow < tl.rows;
       const size_t grow = (size_t)tl.row0 + lrow;
-      const uint32_t taddr = tmem + ((uint32_t)(32 * warp) << 16) + (uint32_t)(buf * kMpBN);
+      const uint32_t taddr = tmem + ((uint32_t)(32 * warp) << 16) + (uint32_t)(buf * BN);
       if (MODE == 0) {
         const float wt = live ? p.wt[grow] : 0.f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {      // gate columns [0, BN / 2), the same rows' up columns behind them
           uint32_t g[32], u[32];
           mp_ld32(taddr + c0, g);
-          mp_ld32(taddr + 64 + c0, u);
+          mp_ld32(taddr + BN / 2 + c0, u);
           mp_wait_ld();
           if (live) {
             __half2 hh[16];
@@ -448,7 +453,7 @@ __global__ void __launch_bounds__(kMpThreads, 1) moep_gemm_kernel(const __grid_c
         }
       } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < kMpBN; c0 += 32) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
           mp_ld32(taddr + c0, r);
           mp_wait_ld();
@@ -554,6 +559,8 @@ int mp_make_map(CUtensorMap* map, const void* base, int64_t rows, int cols, int 
 template <int T, int MODE, bool DENSE>
 int mp_launch(MpGemmParams& p, int sms, int dev, cudaStream_t st) {
   if (p.ntiles <= 0) return kOk;
+  static_assert((size_t)kMpStagesDense * (kMpABytes + kMpBNDense * kMpBK * 2) <= (size_t)kMpStages * (kMpABytes + kMpBBytes) + kMpLutBytes + kMpStgBytes,
+                "the TMA-fed variant's ring fits in the same allocation");
   const size_t smem = 1024 + 1024 + (size_t)kMpStages * (kMpABytes + kMpBBytes) + kMpLutBytes + kMpStgBytes;
   auto kern = moep_gemm_kernel<T, MODE, DENSE>;
   static bool configured[64] = {};
@@ -661,8 +668,8 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
     const int m = a.offs[j + 1] - a.offs[j];
     if (m <= 0) continue;
     if (dense_of[j] >= 0) {
-      add_tiles(t1d, dense_of[j], a.offs[j], m, a.inter, 64);
-      add_tiles(t2d, dense_of[j], a.offs[j], m, a.dim, kMpBN);
+      add_tiles(t1d, dense_of[j], a.offs[j], m, a.inter, kMpBNDense / 2);
+      add_tiles(t2d, dense_of[j], a.offs[j], m, a.dim, kMpBNDense);
     } else {
       add_tiles(t1r, j, a.offs[j], m, a.inter, 64);
       add_tiles(t2r, j, a.offs[j], m, a.dim, kMpBN);
@@ -670,8 +677,8 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   }
   if (n_sh) {
     if (dense_of[a.n_exp] >= 0) {
-      add_tiles(t1d, dense_of[a.n_exp], total, n_sh, a.inter, 64);
-      add_tiles(t2d, dense_of[a.n_exp], total, n_sh, a.dim, kMpBN);
+      add_tiles(t1d, dense_of[a.n_exp], total, n_sh, a.inter, kMpBNDense / 2);
+      add_tiles(t2d, dense_of[a.n_exp], total, n_sh, a.dim, kMpBNDense);
     } else {
       add_tiles(t1s, a.n_exp, total, n_sh, a.inter, 64);
       add_tiles(t2s, a.n_exp, total, n_sh, a.dim, kMpBN);
@@ -736,7 +743,7 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   rc = mp_launch_type<0>(a.t_shared, p, sms, dev, st);
   if (rc) return rc;
   if (!t1d.empty()) {
-    rc = mp_make_map(&p.b_map, d_wgu, (int64_t)dense_slots.size() * 2 * a.inter, a.dim, 64);
+    rc = mp_make_map(&p.b_map, d_wgu, (int64_t)dense_slots.size() * 2 * a.inter, a.dim, kMpBNDense / 2);
     if (rc) return rc;
     p.tiles = d_t1 + t1r.size() + t1s.size(); p.ntiles = (int)t1d.size();
     rc = mp_launch<F16, 0, true>(p, sms, dev, st);
@@ -753,7 +760,7 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   rc = mp_launch_type<1>(a.t_shared, p, sms, dev, st);
   if (rc) return rc;
   if (!t2d.empty()) {
-    rc = mp_make_map(&p.b_map, d_wd, (int64_t)dense_slots.size() * a.dim, a.inter, kMpBN);
+    rc = mp_make_map(&p.b_map, d_wd, (int64_t)dense_slots.size() * a.dim, a.inter, kMpBNDense);
     if (rc) return rc;
     p.tiles = d_t2 + t2r.size() + t2s.size(); p.ntiles = (int)t2d.size();
     rc = mp_launch<F16, 1, true>(p, sms, dev, st);
