@@ -16,9 +16,9 @@
 
 namespace msb {
 
-constexpr int kGmBM = 128, kGmBN = 128, kGmBK = 64;          // tile: tokens x weight rows x contraction (halfs)
+constexpr int kGmBM = 128, kGmBN = 256, kGmBK = 64;          // tile: tokens x weight rows x contraction (halfs)
 constexpr int kGmABytes = kGmBM * kGmBK * 2, kGmBBytes = kGmBN * kGmBK * 2;
-constexpr int kGmStages = 6;
+constexpr int kGmStages = 4;
 constexpr int kGmThreads = 6 * 32;
 
 struct GemmParams {
