@@ -585,7 +585,7 @@ int mp_launch_type(int t, MpGemmParams& p, int sms, int dev, cudaStream_t st) {
 size_t al256(size_t b) { return (b + 255) & ~(size_t)255; }
 // Experts with at least kMpDenseMin entries (at most kMpDenseMax routed ones, the largest first, plus the shared expert)
 // are dequantised to half once and read by TMA; the others are dequantised tile by tile inside the kernel.
-constexpr int kMpDenseMin = 256, kMpDenseMax = 12;
+constexpr int kMpDenseMin = 256, kMpDenseMax = 24;
 // upper bounds of the tile counts
 size_t mp_row_tiles(int total, int n_exp, int n_tokens) {
   return (size_t)(total + kMpBM - 1) / kMpBM + (size_t)n_exp + (size_t)(n_tokens + kMpBM - 1) / kMpBM + 1;
