@@ -615,11 +615,13 @@ size_t moe_prefill_scratch_bytes(int total, int n_tokens, int n_exp, int dim, in
   b += al256(rt * ((inter + 63) / 64) * sizeof(MpTile)) + al256(rt * ((dim + 127) / 128) * sizeof(MpTile));
   b += al256((size_t)(n_exp + 1) * 3 * sizeof(uint64_t)) + al256(rows * sizeof(float));
   b += al256(rows * dim * 2) + al256(rows * inter * 2) + al256(rows * dim * 4);
+  b += al256((size_t)(kMpDenseMax + 1) * 3 * sizeof(uint64_t));   // addresses of the dense experts' matrices
   b += 2 * al256((size_t)(kMpDenseMax + 1) * 2 * inter * dim * 2) ;   // half copies of the dense experts: gate|up, down (+ slack)
   return b;
 }
 
 int weights_to_f16(int t, const void* W, int64_t count, __half* out, int part, cudaStream_t st);   // prefill_gemm.cu
+int weights_to_f16_group(int t, const uint64_t* d_srcs, int n_mat, int64_t count, __half* out, cudaStream_t st);
 
 int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   if (a.dim <= 0 || a.inter <= 0 || a.dim % 256 || a.inter % 256) return fail(kErrArg, "moe_prefill: dim/inter must be multiples of 256");
@@ -702,6 +704,7 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   __half* d_xg = reinterpret_cast<__half*>(cur); cur += al256(rows * a.dim * 2);
   __half* d_h = reinterpret_cast<__half*>(cur); cur += al256(rows * a.inter * 2);
   float* d_z = reinterpret_cast<float*>(cur); cur += al256(rows * a.dim * 4);
+  uint64_t* d_dsrc = reinterpret_cast<uint64_t*>(cur); cur += al256((size_t)(kMpDenseMax + 1) * 3 * sizeof(uint64_t));
   __half* d_wgu = reinterpret_cast<__half*>(cur); cur += al256((size_t)(kMpDenseMax + 1) * 2 * a.inter * a.dim * 2);
   __half* d_wd = reinterpret_cast<__half*>(cur);
   // the tables go to the device (pageable source: the runtime stages them before returning)
@@ -718,17 +721,36 @@ int moe_prefill(const MoePrefillArgs& a, cudaStream_t st) {
   if (rows == 0) return kOk;
   MSB_CUDA(launch_pdl(moep_gather_kernel, dim3((unsigned)rows), dim3(256), 0, st, a.X, a.tok, a.wt, d_xg, d_wt, total, n_sh,
                       a.dim));
-  // half copies of the dense experts (gate rows then up rows per expert; down rows per expert)
-  for (size_t q = 0; q < dense_slots.size(); q++) {
-    const int j = dense_slots[q];
-    const int t_gu = j == a.n_exp ? a.t_shared : a.t_gate_up, t_d = j == a.n_exp ? a.t_shared : a.t_down;
+  // half copies of the dense experts (gate rows then up rows per expert; down rows per expert).  The routed ones come
+  // first in dense_slots and share their types: one grouped launch for all their gate / up matrices, one for the down
+  // matrices; the shared expert, when it is dense, has its own type and three launches.
+  {
     const size_t gu = (size_t)a.inter * a.dim;
-    rc = weights_to_f16(t_gu, reinterpret_cast<const void*>(wptr[(size_t)j * 3]), (int64_t)gu, d_wgu + (2 * q) * gu, 0, st);
-    if (rc) return rc;
-    rc = weights_to_f16(t_gu, reinterpret_cast<const void*>(wptr[(size_t)j * 3 + 1]), (int64_t)gu, d_wgu + (2 * q + 1) * gu, 0, st);
-    if (rc) return rc;
-    rc = weights_to_f16(t_d, reinterpret_cast<const void*>(wptr[(size_t)j * 3 + 2]), (int64_t)gu, d_wd + q * gu, 0, st);
-    if (rc) return rc;
+    const size_t nd_r = dense_slots.size() - ((!dense_slots.empty() && dense_slots.back() == a.n_exp) ? 1 : 0);
+    if (nd_r > 0 && !is_dense(a.t_gate_up) && !is_dense(a.t_down)) {
+      std::vector<uint64_t> dsrc(3 * nd_r);
+      for (size_t q = 0; q < nd_r; q++) {
+        dsrc[2 * q] = wptr[(size_t)dense_slots[q] * 3];
+        dsrc[2 * q + 1] = wptr[(size_t)dense_slots[q] * 3 + 1];
+        dsrc[2 * nd_r + q] = wptr[(size_t)dense_slots[q] * 3 + 2];
+      }
+      MSB_CUDA(upload(d_dsrc, dsrc.data(), dsrc.size() * sizeof(uint64_t)));
+      rc = weights_to_f16_group(a.t_gate_up, d_dsrc, (int)(2 * nd_r), (int64_t)gu, d_wgu, st);
+      if (rc) return rc;
+      rc = weights_to_f16_group(a.t_down, d_dsrc + 2 * nd_r, (int)nd_r, (int64_t)gu, d_wd, st);
+      if (rc) return rc;
+    }
+    for (size_t q = 0; q < dense_slots.size(); q++) {
+      const int j = dense_slots[q];
+      if (j != a.n_exp && !is_dense(a.t_gate_up) && !is_dense(a.t_down)) continue;    // done above
+      const int t_gu = j == a.n_exp ? a.t_shared : a.t_gate_up, t_d = j == a.n_exp ? a.t_shared : a.t_down;
+      rc = weights_to_f16(t_gu, reinterpret_cast<const void*>(wptr[(size_t)j * 3]), (int64_t)gu, d_wgu + (2 * q) * gu, 0, st);
+      if (rc) return rc;
+      rc = weights_to_f16(t_gu, reinterpret_cast<const void*>(wptr[(size_t)j * 3 + 1]), (int64_t)gu, d_wgu + (2 * q + 1) * gu, 0, st);
+      if (rc) return rc;
+      rc = weights_to_f16(t_d, reinterpret_cast<const void*>(wptr[(size_t)j * 3 + 2]), (int64_t)gu, d_wd + q * gu, 0, st);
+      if (rc) return rc;
+    }
   }
   MpGemmParams p;
   p.wptr = d_wptr; p.wt = d_wt; p.h = d_h; p.z = d_z; p.status = tb.status; p.limit = a.limit > 0.f ? a.limit : 10.f; p.tb = tb;

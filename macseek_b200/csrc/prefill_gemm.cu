@@ -212,6 +212,24 @@ __global__ void dequant_f16_kernel(const uint8_t* __restrict__ src, __half* __re
   for (int k = 0; k < 4; k++) h[k] = __floats2half2_rn(y[2 * k], y[2 * k + 1]);
   *reinterpret_cast<uint4*>(out + 8 * i) = *reinterpret_cast<uint4*>(h);
 }
+// the same for a group of equally sized matrices in one launch (blockIdx.y = matrix; srcs[g] = its device address, its
+// half copy at out + g * count): a few-microsecond launch per 8 M-weight matrix never reaches the memory system's pace
+template <int T>
+__global__ void dequant_f16_group_kernel(const uint64_t* __restrict__ srcs, __half* __restrict__ out, int64_t n8, Tables tb) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(srcs[blockIdx.y]);
+  constexpr int per_block = block_elems(T) / 8;
+  const uint8_t* blk = src + (i / per_block) * block_bytes(T);
+  float y[8];
+  dequant8<T>(blk, (int)(i % per_block), tb, y);
+  __half2 h[4];
+#pragma unroll
+  for (int k = 0; k < 4; k++) h[k] = __floats2half2_rn(y[2 * k], y[2 * k + 1]);
+  *reinterpret_cast<uint4*>(out + ((int64_t)blockIdx.y * n8 + i) * 8) = *reinterpret_cast<uint4*>(h);
+}
 // dense sources: part 0 = half(w); part 1 (F32 only) = half(w - half(w)), the second term of a two-pass product
 __global__ void dense_f16_kernel(const uint8_t* __restrict__ src, __half* __restrict__ out, int64_t n, int t, int part) {
   pdl_launch_dependents();
@@ -320,6 +338,30 @@ int weights_to_f16(int t, const void* W, int64_t count, __half* out, int part, c
     }
   }
   MSB_LAUNCH_CHECK("weights_to_f16");
+  return kOk;
+}
+
+// n_mat block-quantised matrices of `count` weights each, addresses in the device array d_srcs, to half copies laid
+// back to back at out
+int weights_to_f16_group(int t, const uint64_t* d_srcs, int n_mat, int64_t count, __half* out, cudaStream_t st) {
+  if (n_mat <= 0) return kOk;
+  if (is_dense(t) || n_mat > 65535) return fail(kErrType, "matmul: grouped conversion needs a block-quantised type");
+  Tables tb;
+  int rc = get_tables(&tb);
+  if (rc) return rc;
+  const int threads = 256;
+  const int64_t n8 = count / 8;
+  const dim3 grid((unsigned)((n8 + threads - 1) / threads), (unsigned)n_mat);
+  switch (t) {
+    case Q8_0: MSB_CUDA(launch_pdl(dequant_f16_group_kernel<Q8_0>, grid, dim3(threads), 0, st, d_srcs, out, n8, tb)); break;
+    case Q5_K: MSB_CUDA(launch_pdl(dequant_f16_group_kernel<Q5_K>, grid, dim3(threads), 0, st, d_srcs, out, n8, tb)); break;
+    case Q6_K: MSB_CUDA(launch_pdl(dequant_f16_group_kernel<Q6_K>, grid, dim3(threads), 0, st, d_srcs, out, n8, tb)); break;
+    case IQ2_XXS: MSB_CUDA(launch_pdl(dequant_f16_group_kernel<IQ2_XXS>, grid, dim3(threads), 0, st, d_srcs, out, n8, tb)); break;
+    case IQ1_S: MSB_CUDA(launch_pdl(dequant_f16_group_kernel<IQ1_S>, grid, dim3(threads), 0, st, d_srcs, out, n8, tb)); break;
+    case IQ4_NL: MSB_CUDA(launch_pdl(dequant_f16_group_kernel<IQ4_NL>, grid, dim3(threads), 0, st, d_srcs, out, n8, tb)); break;
+    default: return fail(kErrType, "matmul: unsupported weight type %d", t);
+  }
+  MSB_LAUNCH_CHECK("weights_to_f16_group");
   return kOk;
 }
 
